@@ -1,0 +1,517 @@
+// Grouped / dense bf16 GEMM for sm_100a: TMA -> shared memory -> tcgen05.mma -> TMEM -> epilogue.
+//
+// Computes, for every group g (an expert, or the single group of a dense linear layer),
+//     Y[t, f] = sum_k X[t, k] * W[g][f, k]          t in [offs[g], offs[g+1])
+// with W stored [G, rows, K] K-contiguous ("out, in" like F.linear) and X stored [T, K].
+//
+// Serving is decode heavy: few tokens per expert and large weight matrices, so the kernel is laid out
+// "swap-AB": the WEIGHT tile (128 rows) is the M operand of the UMMA and the TOKEN tile (BN = 32..256 rows)
+// is the N operand. A CTA therefore never pads a handful of tokens up to 128 MMA rows, and the weight
+// stream (the HBM-bound part) is read exactly once. The accumulator lives in TMEM as [128 lanes = features,
+// BN columns = tokens]; the epilogue thread that owns lane i owns output feature i of the tile.
+//
+// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer, warps 2..5 = epilogue.
+// Accumulators are double buffered in TMEM so the epilogue of tile i overlaps the main loop of tile i+1.
+// Persistent grid: CTA b runs tiles b, b + gridDim.x, ...; group sizes are read from device memory, so the
+// host never needs to know the routing result.
+//
+// Epilogues: plain (+ optional residual), SwiGLU (two accumulators: gate rows and up rows of the fused w13
+// weight; out = silu(gate) * up), combine (row scatter through 16-byte token records with a per-row scale
+// and a table of destination base pointers, which may be peer GPUs' buffers), and split-K with a
+// last-arriver reduction through an fp32 workspace.
+//
+// Reference behaviour covered: disagmoe/models/experts.py:81-96 (gmm -> silu*mul -> gmm),
+// disagmoe/models/linear.py:131-136 (F.linear), disagmoe/frontend/engine.py:731-734 (weight scale + un-permute).
+#include "dmoe_kernels.h"
+#include "sm100.cuh"
+
+namespace dmoe {
+
+constexpr int kBM = 128;       // weight rows per tile (UMMA M)
+constexpr int kBK = 64;        // K elements per stage: 64 bf16 = 128 bytes = one swizzle span
+constexpr int kUmmaK = 16;     // K per tcgen05.mma for 16-bit inputs
+constexpr int kThreads = 192;
+constexpr int kEpiThreads = 128;
+constexpr int kSmemBudget = 220 * 1024;
+
+enum { EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_COMBINE = 2 };
+
+struct GemmArgs {
+  const int* offs;   // [G+1] device token offsets, or nullptr for one dense group of T tokens
+  int G, T, F, K;    // F: output features per group
+  int w_rows;        // weight rows per group (F, or 2F for SwiGLU)
+  void* Y;
+  long long ldy;
+  int y_f32;
+  const __nv_bfloat16* R;  // optional residual [T, F]
+  long long ldr;
+  const int4* recs;        // combine: per input row {dst_rank, dst_row, weight (fp32 bits), unused}
+  void* const* bases;      // combine: destination base pointer per rank
+  int splitk;
+  float* ws;
+  int* counters;
+  int* status;
+};
+
+template <int BN, int EPI>
+struct Cfg {
+  static constexpr int kNumA = (EPI == EPI_SWIGLU) ? 2 : 1;
+  static constexpr int kABytes = kBM * kBK * 2;
+  static constexpr int kBBytes = BN * kBK * 2;
+  static constexpr int kStageBytes = kNumA * kABytes + kBBytes;
+  static constexpr int kStagesRaw = (kSmemBudget - 1024) / kStageBytes;
+  static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
+  static constexpr int kAccCols = BN * kNumA;
+  static constexpr int kTmemCols = (2 * kAccCols) < 32 ? 32 : 2 * kAccCols;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 1024 /*barriers, offsets*/;
+  static_assert(kTmemCols <= 512, "accumulators do not fit TMEM");
+  static_assert((kTmemCols & (kTmemCols - 1)) == 0, "TMEM columns must be a power of two");
+  static_assert(kStages >= 3, "pipeline too shallow");
+};
+
+// Walks the persistent tile list. Tiles of group g: for m in [0, MT) for n in [0, ntn_g) for ks in [0, splitk).
+struct TileWalker {
+  const int* offs;  // shared-memory copy, G+1 entries
+  int G, MT, splitk, BN;
+  int g, base;      // tiles of group g start at linear id `base`
+  int tok0, cnt, ntn;
+  __device__ void init(const int* s_offs, int G_, int MT_, int splitk_, int BN_) {
+    offs = s_offs; G = G_; MT = MT_; splitk = splitk_; BN = BN_;
+    g = -1; base = 0; ntn = 0; cnt = 0; tok0 = 0;
+    advance_group();
+  }
+  __device__ void advance_group() {
+    ++g;
+    if (g < G) {
+      tok0 = offs[g];
+      cnt = offs[g + 1] - tok0;
+      if (cnt < 0) cnt = 0;
+      ntn = (cnt + BN - 1) / BN;
+    }
+  }
+  // Positions on linear tile id `tile` (monotonically increasing across calls). False when past the end.
+  __device__ bool seek(int tile, int& m, int& n, int& ks) {
+    while (g < G) {
+      const int ntiles = MT * ntn * splitk;
+      if (tile < base + ntiles) {
+        int r = tile - base;
+        ks = r % splitk; r /= splitk;
+        n = r % ntn;
+        m = r / ntn;
+        return true;
+      }
+      base += ntiles;
+      advance_group();
+    }
+    return false;
+  }
+};
+
+template <int BN, int EPI>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const GemmArgs a) {
+  using C = Cfg<BN, EPI>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* tail = smem + C::kStages * C::kStageBytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(tail);            // [kStages]
+  uint64_t* empty_bar = full_bar + C::kStages;                       // [kStages]
+  uint64_t* tfull_bar = empty_bar + C::kStages;                      // [2]
+  uint64_t* tempty_bar = tfull_bar + 2;                              // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2); // [1]
+  int* abort_word = reinterpret_cast<int*>(tmem_slot + 1);
+  int* last_flag = abort_word + 1;
+  int* s_offs = last_flag + 1;                                       // [G+1] (G <= 128)
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int MT = (a.F + kBM - 1) / kBM;
+  const int kblocks = (a.K + kBK - 1) / kBK;
+  const int kb_per = (kblocks + a.splitk - 1) / a.splitk;
+
+  if (threadIdx.x == 0) {
+    *abort_word = 0;
+    *last_flag = 0;
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&tfull_bar[b]), 1);
+      mbar_init(smem_u32(&tempty_bar[b]), kEpiThreads);
+    }
+    mbar_fence_init();
+    tma_prefetch_desc(&tmW);
+    tma_prefetch_desc(&tmX);
+  }
+  if (a.offs != nullptr) {
+    for (int i = threadIdx.x; i <= a.G; i += blockDim.x) s_offs[i] = a.offs[i];
+  } else if (threadIdx.x == 0) {
+    s_offs[0] = 0;
+    s_offs[1] = a.T;
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      TileWalker tw;
+      tw.init(s_offs, a.G, MT, a.splitk, BN);
+      const uint64_t pol_w = l2_policy_evict_first();
+      const uint64_t pol_x = l2_policy_evict_last();
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok; tile += gridDim.x) {
+        int m, n, ks;
+        if (!tw.seek(tile, m, n, ks)) break;
+        const int wrow = tw.g * a.w_rows + m * kBM;
+        const int xrow = tw.tok0 + n * BN;
+        const int kb0 = ks * kb_per;
+        const int kb1 = min(kblocks, kb0 + kb_per);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_word)) { ok = false; break; }
+          const uint32_t fb = smem_u32(&full_bar[stage]);
+          uint8_t* st = smem + stage * C::kStageBytes;
+          mbar_expect_tx(fb, C::kStageBytes);
+          tma_load_2d(smem_u32(st), &tmW, kb * kBK, wrow, fb, pol_w);
+          if (EPI == EPI_SWIGLU) tma_load_2d(smem_u32(st + C::kABytes), &tmW, kb * kBK, wrow + a.F, fb, pol_w);
+          tma_load_2d(smem_u32(st + C::kNumA * C::kABytes), &tmX, kb * kBK, xrow, fb, pol_x);
+          if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      TileWalker tw;
+      tw.init(s_offs, a.G, MT, a.splitk, BN);
+      constexpr uint32_t idesc = umma_idesc_bf16(kBM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok; tile += gridDim.x, ++it) {
+        int m, n, ks;
+        if (!tw.seek(tile, m, n, ks)) break;
+        const int buf = it & 1;
+        const uint32_t bphase = (it >> 1) & 1;
+        if (!mbar_wait(smem_u32(&tempty_bar[buf]), bphase ^ 1, abort_word)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d0 = tmem_base + buf * C::kAccCols;
+        const int kb0 = ks * kb_per;
+        const int kb1 = min(kblocks, kb0 + kb_per);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(smem_u32(&full_bar[stage]), phase, abort_word)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * C::kStageBytes);
+          const uint64_t da = umma_desc_sw128(sa);
+          const uint64_t db = umma_desc_sw128(sa + C::kNumA * C::kABytes);
+#pragma unroll
+          for (int k = 0; k < kBK / kUmmaK; ++k) {
+            const uint32_t acc = (kb > kb0 || k > 0) ? 1u : 0u;
+            // advancing K by 16 bf16 = 32 bytes inside the 128-byte swizzle span: +2 in the (>>4) address field
+            umma_f16(d0, da + 2 * k, db + 2 * k, idesc, acc);
+            if (EPI == EPI_SWIGLU) {
+              const uint64_t da2 = umma_desc_sw128(sa + C::kABytes);
+              umma_f16(d0 + BN, da2 + 2 * k, db + 2 * k, idesc, acc);
+            }
+          }
+          umma_commit(smem_u32(&empty_bar[stage]));  // frees the smem stage when these MMAs retire
+          if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit(smem_u32(&tfull_bar[buf]));
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;                 // TMEM lane quarter this warp may read
+    const int row = q * 32 + lane;          // accumulator lane = feature within the tile
+    const int et = threadIdx.x - 64;        // 0..127
+    TileWalker tw;
+    tw.init(s_offs, a.G, MT, a.splitk, BN);
+    int it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok; tile += gridDim.x, ++it) {
+      int m, n, ks;
+      if (!tw.seek(tile, m, n, ks)) break;
+      const int buf = it & 1;
+      const uint32_t bphase = (it >> 1) & 1;
+      if (!mbar_wait(smem_u32(&tfull_bar[buf]), bphase, abort_word)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t t0 = tmem_base + buf * C::kAccCols + (static_cast<uint32_t>(q * 32) << 16);
+      const int f = m * kBM + row;
+      const int tok_base = tw.tok0 + n * BN;
+      const int ntok = min(BN, tw.cnt - n * BN);
+      const bool f_ok = f < a.F;
+
+      bool reduce_here = true;       // split-K: only the last arriver runs the real epilogue
+      const int tile_mn = tile / a.splitk;
+      if (a.splitk > 1) {
+        // park this split's partial tile: ws[tile_mn][ks][c4][row][4]
+        float4* wsp = reinterpret_cast<float4*>(a.ws) + (static_cast<size_t>(tile_mn) * a.splitk + ks) * (BN / 4) * kBM;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld32(t0 + c * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            float4 o;
+            o.x = __uint_as_float(v[4 * j]); o.y = __uint_as_float(v[4 * j + 1]);
+            o.z = __uint_as_float(v[4 * j + 2]); o.w = __uint_as_float(v[4 * j + 3]);
+            wsp[(c * 8 + j) * kBM + row] = o;
+          }
+        }
+        tc_fence_before();
+        mbar_arrive(smem_u32(&tempty_bar[buf]));
+        __threadfence();
+        named_bar_sync(1, kEpiThreads);
+        if (et == 0) {
+          const int old = atomicAdd(&a.counters[tile_mn], 1);
+          const int last = (old == a.splitk - 1);
+          if (last) a.counters[tile_mn] = 0;  // self-resetting for the next launch
+          *last_flag = last;
+        }
+        named_bar_sync(1, kEpiThreads);
+        reduce_here = (*last_flag != 0);
+        named_bar_sync(1, kEpiThreads);      // everyone has read last_flag before the next tile rewrites it
+        if (reduce_here) __threadfence();
+      }
+      if (a.splitk > 1 && !reduce_here) continue;
+
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        float acc[32];
+        if (a.splitk > 1) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) acc[j] = 0.f;
+          for (int s = 0; s < a.splitk; ++s) {
+            const float4* wsp = reinterpret_cast<const float4*>(a.ws) +
+                                (static_cast<size_t>(tile_mn) * a.splitk + s) * (BN / 4) * kBM;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float4 o = __ldcg(&wsp[(c * 8 + j) * kBM + row]);
+              acc[4 * j] += o.x; acc[4 * j + 1] += o.y; acc[4 * j + 2] += o.z; acc[4 * j + 3] += o.w;
+            }
+          }
+        } else {
+          uint32_t v[32];
+          tmem_ld32(t0 + c * 32, v);
+          if (EPI == EPI_SWIGLU) {
+            uint32_t u[32];
+            tmem_ld32(t0 + BN + c * 32, u);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float g = __uint_as_float(v[j]);
+              const float up = __uint_as_float(u[j]);
+              acc[j] = (g / (1.f + __expf(-g))) * up;
+            }
+          } else {
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) acc[j] = __uint_as_float(v[j]);
+          }
+          if (c == BN / 32 - 1) {
+            // all of this thread's TMEM reads are done: hand the accumulator buffer back to the MMA warp
+            tc_fence_before();
+            mbar_arrive(smem_u32(&tempty_bar[buf]));
+          }
+        }
+        if (!f_ok) continue;
+        const int jmax = min(32, ntok - c * 32);
+        if (EPI == EPI_COMBINE) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (j >= jmax) break;
+            const int4 rec = __ldg(&a.recs[tok_base + c * 32 + j]);
+            if (rec.y < 0) continue;
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(a.bases[rec.x]) + static_cast<long long>(rec.y) * a.ldy;
+            dst[f] = __float2bfloat16(acc[j] * __int_as_float(rec.z));
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (j >= jmax) break;
+            const long long t = tok_base + c * 32 + j;
+            float v = acc[j];
+            if (a.R != nullptr) v += __bfloat162float(a.R[t * a.ldr + f]);
+            if (a.y_f32) reinterpret_cast<float*>(a.Y)[t * a.ldy + f] = v;
+            else reinterpret_cast<__nv_bfloat16*>(a.Y)[t * a.ldy + f] = __float2bfloat16(v);
+          }
+        }
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------- tear-down
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_word) {
+    if (threadIdx.x == 0 && a.status != nullptr) atomicCAS(a.status, kStatusOk, kStatusBarrierTimeout);
+    // give copies that may still be in flight time to land before shared memory is released
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+  }
+  return fn;
+}
+
+// Tensor map over a row-major [rows, K] bf16 matrix with a [box_rows, 64] box and the 128-byte swizzle.
+static int make_map_2d(CUtensorMap* map, const void* ptr, long long rows, long long K, long long ld_elems,
+                       int box_rows) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (enc == nullptr) return -1;
+  cuuint64_t gdim[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
+  cuuint64_t gstride[1] = {static_cast<cuuint64_t>(ld_elems) * 2};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(kBK), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstride, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -2;
+}
+
+static int g_num_sms = 0;
+static int num_sms() {
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (g_num_sms <= 0) g_num_sms = 148;
+  }
+  return g_num_sms;
+}
+
+template <int BN, int EPI>
+static int launch(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmArgs& a, int max_tiles,
+                  cudaStream_t stream) {
+  using C = Cfg<BN, EPI>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         C::kSmemBytes);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  int grid = num_sms();
+  if (max_tiles < grid) grid = max_tiles;
+  if (grid < 1) grid = 1;
+  gemm_kernel<BN, EPI><<<grid, kThreads, C::kSmemBytes, stream>>>(tmW, tmX, a);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace dmoe
+
+using namespace dmoe;
+
+extern "C" int dmoe_gemm_pick_bn(int tokens_per_group_hint, int epi) {
+  const int cap = (epi == EPI_SWIGLU) ? 128 : 256;
+  int bn = 32;
+  while (bn < tokens_per_group_hint && bn < cap) bn *= 2;
+  return bn;
+}
+
+extern "C" long long dmoe_gemm_workspace_bytes(int T, int F, int bn, int splitk) {
+  if (splitk <= 1) return 0;
+  const long long mt = (F + kBM - 1) / kBM;
+  const long long nt = (T + bn - 1) / bn;
+  return mt * nt * splitk * kBM * bn * 4;
+}
+
+extern "C" int dmoe_gemm(const DmoeGemm* d, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (d->G < 1 || d->G > 128 || d->K % 8 != 0 || d->F < 1 || d->T < 0) return -10;
+  if (d->T == 0) return 0;
+  const int epi = d->epi;
+  int bn = d->bn;
+  if (bn == 0) bn = dmoe_gemm_pick_bn((d->T + d->G - 1) / d->G, epi);
+  if (bn != 32 && bn != 64 && bn != 128 && bn != 256) return -11;
+  if (epi == EPI_SWIGLU && bn > 128) return -11;
+  int splitk = d->splitk < 1 ? 1 : d->splitk;
+  const int kblocks = (d->K + kBK - 1) / kBK;
+  if (splitk > kblocks) splitk = kblocks;
+  if (splitk > 1) {
+    // no split may be empty
+    const int per = (kblocks + splitk - 1) / splitk;
+    splitk = (kblocks + per - 1) / per;
+  }
+  if (splitk > 1 && (epi == EPI_SWIGLU || d->offs != nullptr || d->ws == nullptr || d->counters == nullptr)) return -12;
+  if (splitk > 1 && dmoe_gemm_workspace_bytes(d->T, d->F, bn, splitk) > d->ws_bytes) return -13;
+  if (epi == EPI_COMBINE && (d->recs == nullptr || d->bases == nullptr)) return -14;
+
+  GemmArgs a;
+  a.offs = d->offs;
+  a.G = d->G; a.T = d->T; a.F = d->F; a.K = d->K;
+  a.w_rows = (epi == EPI_SWIGLU) ? 2 * d->F : d->F;
+  a.Y = d->Y; a.ldy = d->ldy; a.y_f32 = d->y_f32;
+  a.R = static_cast<const __nv_bfloat16*>(d->R); a.ldr = d->ldr;
+  a.recs = static_cast<const int4*>(d->recs);
+  a.bases = static_cast<void* const*>(d->bases);
+  a.splitk = splitk; a.ws = static_cast<float*>(d->ws); a.counters = d->counters;
+  a.status = d->status;
+
+  CUtensorMap tmW, tmX;
+  const long long ldx = d->ldx > 0 ? d->ldx : d->K;
+  if (make_map_2d(&tmW, d->W, static_cast<long long>(d->G) * a.w_rows, d->K, d->K, kBM) != 0) return -20;
+  if (make_map_2d(&tmX, d->X, d->T, d->K, ldx, bn) != 0) return -21;
+
+  const long long mt = (d->F + kBM - 1) / kBM;
+  // upper bound of the tile count (group sizes live on the device): every group may add one ragged tile
+  long long max_tiles = mt * ((d->T + bn - 1) / bn + (d->offs ? d->G : 0)) * splitk;
+  if (max_tiles > (1 << 30)) max_tiles = 1 << 30;
+  const int mtiles = static_cast<int>(max_tiles);
+
+#define DMOE_LAUNCH(BN_, EPI_) return launch<BN_, EPI_>(tmW, tmX, a, mtiles, stream)
+  if (epi == EPI_PLAIN) {
+    switch (bn) {
+      case 32: DMOE_LAUNCH(32, EPI_PLAIN);
+      case 64: DMOE_LAUNCH(64, EPI_PLAIN);
+      case 128: DMOE_LAUNCH(128, EPI_PLAIN);
+      default: DMOE_LAUNCH(256, EPI_PLAIN);
+    }
+  } else if (epi == EPI_SWIGLU) {
+    switch (bn) {
+      case 32: DMOE_LAUNCH(32, EPI_SWIGLU);
+      case 64: DMOE_LAUNCH(64, EPI_SWIGLU);
+      default: DMOE_LAUNCH(128, EPI_SWIGLU);
+    }
+  } else if (epi == EPI_COMBINE) {
+    switch (bn) {
+      case 32: DMOE_LAUNCH(32, EPI_COMBINE);
+      case 64: DMOE_LAUNCH(64, EPI_COMBINE);
+      case 128: DMOE_LAUNCH(128, EPI_COMBINE);
+      default: DMOE_LAUNCH(256, EPI_COMBINE);
+    }
+  }
+#undef DMOE_LAUNCH
+  return -15;
+}

@@ -1,0 +1,65 @@
+"""ctypes loader of ``lib/libdmoe_kernels.so`` (the hand-written sm_100a kernels).
+
+The library is built in-tree by :mod:`disagmoe_b200.build`. An op called with CUDA tensors raises if the library
+is missing: there is no silent eager fallback on a GPU box.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+_LIB = None
+_LIB_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "lib", "libdmoe_kernels.so")
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+class DmoeGemm(ctypes.Structure):
+    _fields_ = [
+        ("W", ctypes.c_void_p), ("X", ctypes.c_void_p), ("Y", ctypes.c_void_p), ("R", ctypes.c_void_p),
+        ("offs", ctypes.c_void_p), ("recs", ctypes.c_void_p), ("bases", ctypes.c_void_p), ("ws", ctypes.c_void_p),
+        ("counters", ctypes.c_void_p), ("status", ctypes.c_void_p),
+        ("ldx", ctypes.c_longlong), ("ldy", ctypes.c_longlong), ("ldr", ctypes.c_longlong),
+        ("ws_bytes", ctypes.c_longlong),
+        ("G", ctypes.c_int), ("T", ctypes.c_int), ("F", ctypes.c_int), ("K", ctypes.c_int),
+        ("epi", ctypes.c_int), ("bn", ctypes.c_int), ("splitk", ctypes.c_int), ("y_f32", ctypes.c_int),
+    ]
+
+
+def lib_path() -> str:
+    return _LIB_PATH
+
+
+def available() -> bool:
+    return os.path.exists(_LIB_PATH)
+
+
+def lib():
+    """The loaded kernel library. Raises KernelError if it has not been built."""
+    global _LIB
+    if _LIB is None:
+        if not os.path.exists(_LIB_PATH):
+            raise KernelError(
+                f"{_LIB_PATH} is missing: run `python -m disagmoe_b200.build` (nvcc, sm_100a) before using CUDA ops")
+        _LIB = ctypes.CDLL(_LIB_PATH)
+        _LIB.dmoe_gemm.argtypes = [ctypes.POINTER(DmoeGemm), ctypes.c_void_p]
+        _LIB.dmoe_gemm.restype = ctypes.c_int
+        _LIB.dmoe_gemm_workspace_bytes.restype = ctypes.c_longlong
+    return _LIB
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def check(code: int, what: str):
+    if code != 0:
+        raise KernelError(f"{what} failed with code {code}")
+
+
+def ptr(t):
+    return 0 if t is None else t.data_ptr()

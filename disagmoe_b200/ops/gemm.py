@@ -1,0 +1,211 @@
+"""bf16 GEMMs on the tcgen05 kernel of ``csrc/kernels/gemm.cu``.
+
+``linear``          y = x @ w.T (+ residual)                         -- reference: disagmoe/models/linear.py:131-136
+``grouped_swiglu``  act = silu(x @ w13[g][:I].T) * (x @ w13[g][I:].T)   -- reference: disagmoe/models/experts.py:84-88
+``grouped_linear``  y = x @ w2[g].T per expert group                   -- reference: disagmoe/models/experts.py:89
+``grouped_combine`` the same GEMM whose epilogue scales each row by its router weight and scatters it to the
+                    row (and GPU) it came from                         -- reference: disagmoe/frontend/engine.py:731-734
+
+Weights are K-contiguous ``[groups, out, in]``. CPU tensors take a plain PyTorch path (used by the fp32 CPU
+configuration and as the numerical reference); CUDA tensors always run the sm_100a kernel.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+EPI_PLAIN, EPI_SWIGLU, EPI_COMBINE = 0, 1, 2
+_NUM_SMS = 148
+
+
+class _Scratch:
+    """Per-device split-K workspace, tile counters and status word (allocated once, reused by every call)."""
+
+    def __init__(self, device):
+        self.device = device
+        self.ws = torch.empty(64 << 20, dtype=torch.uint8, device=device)
+        self.counters = torch.zeros(65536, dtype=torch.int32, device=device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def ensure(self, nbytes):
+        if nbytes > self.ws.numel():
+            self.ws = torch.empty(int(nbytes * 1.25), dtype=torch.uint8, device=self.device)
+
+
+_scratch = {}
+
+
+def scratch(device) -> _Scratch:
+    key = torch.device(device).index or 0
+    if key not in _scratch:
+        _scratch[key] = _Scratch(torch.device("cuda", key))
+    return _scratch[key]
+
+
+def check_status(device=None) -> int:
+    """Reads (and clears) the device status word; non-zero means a kernel gave up on a bounded wait."""
+    s = scratch(device if device is not None else torch.cuda.current_device())
+    v = int(s.status.item())
+    if v != 0:
+        s.status.zero_()
+    return v
+
+
+def pick_splitk(T: int, F: int, K: int, bn: int) -> int:
+    tiles = ((F + 127) // 128) * ((T + bn - 1) // bn)
+    kblocks = (K + 63) // 64
+    if tiles >= _NUM_SMS // 2 or kblocks < 8:
+        return 1
+    return max(1, min(_NUM_SMS // tiles, kblocks // 4, 16))
+
+
+def pick_bn(tokens_per_group: int, epi: int) -> int:
+    cap = 128 if epi == EPI_SWIGLU else 256
+    bn = 32
+    while bn < tokens_per_group and bn < cap:
+        bn *= 2
+    return bn
+
+
+def _launch(W, X, Y, R, offs, recs, bases, G, T, F, K, epi, bn, splitk, ldy, y_f32):
+    s = scratch(X.device)
+    d = _lib.DmoeGemm()
+    d.W, d.X, d.Y, d.R = W.data_ptr(), X.data_ptr(), _lib.ptr(Y), _lib.ptr(R)
+    d.offs, d.recs, d.bases = _lib.ptr(offs), _lib.ptr(recs), _lib.ptr(bases)
+    if splitk > 1:
+        need = _lib.lib().dmoe_gemm_workspace_bytes(T, F, bn, splitk)
+        s.ensure(need)
+    d.ws, d.counters, d.status = s.ws.data_ptr(), s.counters.data_ptr(), s.status.data_ptr()
+    d.ws_bytes = s.ws.numel()
+    d.ldx = X.stride(0)
+    d.ldy = ldy
+    d.ldr = R.stride(0) if R is not None else 0
+    d.G, d.T, d.F, d.K = G, T, F, K
+    d.epi, d.bn, d.splitk, d.y_f32 = epi, bn, splitk, int(y_f32)
+    _lib.check(_lib.lib().dmoe_gemm(ctypes.byref(d), _lib.stream_ptr()), "dmoe_gemm")
+
+
+def _check_x(x):
+    assert x.dim() == 2 and x.stride(1) == 1 and x.dtype == torch.bfloat16, "x must be [T, K] bf16, K contiguous"
+    assert x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0, "x rows must be 16-byte aligned"
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor] = None,
+           out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None, bn: int = 0,
+           splitk: int = 0) -> torch.Tensor:
+    """y[T, F] = x[T, K] @ w[F, K].T (+ residual[T, F])."""
+    T, K = x.shape
+    F = w.shape[0]
+    if not x.is_cuda:
+        y = torch.nn.functional.linear(x.float(), w.float())
+        if residual is not None:
+            y = y + residual.float()
+        y = y.to(out_dtype or x.dtype)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    _check_x(x)
+    assert w.is_contiguous() and w.dtype == torch.bfloat16 and w.shape[1] == K
+    odt = out_dtype or torch.bfloat16
+    if out is None:
+        out = torch.empty(T, F, dtype=odt, device=x.device)
+    assert out.stride(1) == 1 and out.dtype in (torch.bfloat16, torch.float32)
+    if T == 0:
+        return out
+    bn = bn or pick_bn(T, EPI_PLAIN)
+    splitk = splitk or pick_splitk(T, F, K, bn)
+    _launch(w, x, out, residual, None, None, None, 1, T, F, K, EPI_PLAIN, bn, splitk, out.stride(0),
+            out.dtype == torch.float32)
+    return out
+
+
+def _grouped_ref(x, w, offs, swiglu):
+    offs = offs.tolist()
+    G = w.shape[0]
+    F = w.shape[1] // 2 if swiglu else w.shape[1]
+    y = torch.zeros(x.shape[0], F, dtype=torch.float32, device=x.device)
+    for g in range(G):
+        a, b = offs[g], offs[g + 1]
+        if b <= a:
+            continue
+        h = x[a:b].float() @ w[g].float().T
+        if swiglu:
+            h = torch.nn.functional.silu(h[:, :F]) * h[:, F:]
+        y[a:b] = h
+    return y
+
+
+def grouped_swiglu(x: torch.Tensor, w13: torch.Tensor, offs: torch.Tensor, out: Optional[torch.Tensor] = None,
+                   bn: int = 0) -> torch.Tensor:
+    """act[T, I] = silu(x @ w13[g, :I].T) * (x @ w13[g, I:].T) for the rows of group g; w13 is [G, 2I, K]."""
+    T, K = x.shape
+    G, F2, _ = w13.shape
+    I = F2 // 2
+    if not x.is_cuda:
+        y = _grouped_ref(x, w13, offs, True).to(x.dtype)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    _check_x(x)
+    assert w13.is_contiguous() and w13.dtype == torch.bfloat16 and offs.dtype == torch.int32 and offs.is_cuda
+    if out is None:
+        out = torch.empty(T, I, dtype=torch.bfloat16, device=x.device)
+    if T == 0:
+        return out
+    bn = bn or pick_bn((T + G - 1) // G, EPI_SWIGLU)
+    _launch(w13, x, out, None, offs, None, None, G, T, I, K, EPI_SWIGLU, bn, 1, out.stride(0), False)
+    return out
+
+
+def grouped_linear(x: torch.Tensor, w: torch.Tensor, offs: torch.Tensor, out: Optional[torch.Tensor] = None,
+                   bn: int = 0) -> torch.Tensor:
+    """y[T, F] = x @ w[g].T for the rows of group g; w is [G, F, K]."""
+    T, K = x.shape
+    G, F, _ = w.shape
+    if not x.is_cuda:
+        y = _grouped_ref(x, w, offs, False).to(x.dtype)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    _check_x(x)
+    assert w.is_contiguous() and w.dtype == torch.bfloat16 and offs.dtype == torch.int32 and offs.is_cuda
+    if out is None:
+        out = torch.empty(T, F, dtype=torch.bfloat16, device=x.device)
+    if T == 0:
+        return out
+    bn = bn or pick_bn((T + G - 1) // G, EPI_PLAIN)
+    _launch(w, x, out, None, offs, None, None, G, T, F, K, EPI_PLAIN, bn, 1, out.stride(0), False)
+    return out
+
+
+def grouped_combine(x: torch.Tensor, w: torch.Tensor, offs: torch.Tensor, recs: torch.Tensor, bases: torch.Tensor,
+                    ld_out: int, bn: int = 0, outs=None) -> None:
+    """GEMM-2 with the combine epilogue: row t of group g becomes ``weight[t] * (x[t] @ w[g].T)`` written to row
+    ``recs[t, 1]`` of the buffer ``bases[recs[t, 0]]`` (row stride ``ld_out`` elements).
+
+    recs: int32 [T, 4] = (dst_rank, dst_row or -1, weight as fp32 bits, 0). bases: int64 [n_ranks] device
+    tensor of raw pointers (peer buffers included). ``outs`` (CPU path only) is the list of destination tensors.
+    """
+    T, K = x.shape
+    G, F, _ = w.shape
+    if not x.is_cuda:
+        y = _grouped_ref(x, w, offs, False)
+        wts = recs[:, 2].contiguous().view(torch.float32)
+        for t in range(T):
+            r, row = int(recs[t, 0]), int(recs[t, 1])
+            if row >= 0:
+                outs[r][row] = (y[t] * wts[t]).to(outs[r].dtype)
+        return
+    _check_x(x)
+    assert recs.dtype == torch.int32 and recs.is_contiguous() and recs.shape[1] == 4 and bases.dtype == torch.int64
+    if T == 0:
+        return
+    bn = bn or pick_bn((T + G - 1) // G, EPI_COMBINE)
+    _launch(w, x, None, None, offs, recs, bases, G, T, F, K, EPI_COMBINE, bn, 1, ld_out, False)
