@@ -35,6 +35,37 @@ int dmoe_gemm(const DmoeGemm* desc, void* stream);
 int dmoe_gemm_pick_bn(int tokens_per_group_hint, int epi);
 long long dmoe_gemm_workspace_bytes(int T, int F, int bn, int splitk);
 
+// ---- row kernels (elementwise.cu) -------------------------------------------------------------------
+// resid_out = resid_in + sum of n_add partial rows; y = rmsnorm(resid_out) * w. resid_in / resid_out / y may be NULL.
+int dmoe_add_rmsnorm(const void* resid_in, const void* add, int n_add, long long add_row_stride,
+                     long long add_part_stride, const void* w, float eps, void* resid_out, void* y, int T, int H,
+                     long long ld_in, long long ld_out, long long ld_y, void* stream);
+// neox RoPE on the q and k heads of qkv rows [q | k | v] in place, then K/V append at slots[t] (slot < 0: no append).
+int dmoe_rope_kv_append(void* qkv, long long ld, const int* positions, const long long* slots, void* kcache,
+                        void* vcache, int T, int n_q, int n_kv, int hd, float theta, void* stream);
+int dmoe_embed(const int* ids, const void* table, void* out, int T, int H, int vocab, long long ld_out, void* stream);
+int dmoe_argmax(const void* logits, int is_f32, long long ld, int T, int V, int* ids, void* stream);
+int dmoe_permute_rows(const void* src, long long ld_src, void* dst, long long ld_dst, const int* map, int n, int H,
+                      int repeat, int gather, void* stream);
+int dmoe_gather_ptrs(const void* ptrs, void* dst, long long ld_dst, int n, int H, void* stream);
+
+// ---- attention (attention.cu) -----------------------------------------------------------------------
+long long dmoe_paged_attention_workspace_floats(int T, int n_q, int hd, int splits);
+int dmoe_paged_attention(const void* q, long long ld_q, const void* kcache, const void* vcache,
+                         const int* block_tables, int max_blocks, const int* bt_row, const int* ctx_len, int block_size,
+                         int T, int n_q, int n_kv, int hd, float scale, int splits, void* out, long long ld_out,
+                         float* workspace, void* stream);
+
+// ---- routing (moe.cu) -------------------------------------------------------------------------------
+// (RMSNorm ->) gate -> softmax -> top-k (-> renormalise); counts[e] += tokens routed to e (may be NULL).
+int dmoe_route(const void* x, long long ld_x, const void* norm_w, float eps, const void* gate_w, int T, int H, int E,
+               int K, int renorm, void* y, long long ld_y, int* topk_ids, float* topk_w, float* logits_out, int* counts,
+               void* stream);
+// Sort-by-expert copy of the routed rows plus their 16-byte records; ws = ints [counts E | cursor E | ticket].
+int dmoe_dispatch_local(const void* y, long long ld_y, const int* topk_ids, const float* topk_w, int T, int K, int H,
+                        int E, int experts_per_rank, int my_rank, int* ws, int* offs, const void* x_bases,
+                        long long ld_dst, const void* rec_bases, int dst_capacity, int* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

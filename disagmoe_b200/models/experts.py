@@ -1,0 +1,90 @@
+"""The expert half of a decoder layer as the expert workers run it: grouped SwiGLU FFN over the local experts.
+
+Counterpart of ``MoEExperts`` / ``MoEExpertsSerial`` (disagmoe/models/experts.py:9-119). Input rows are sorted by
+local expert; ``offs`` [E_local + 1] are the row offsets of the experts (device tensor: the host never needs the
+counts). Weights are held K-contiguous: ``w13 [E_local, 2I, H]`` (gate rows then up rows), ``w2 [E_local, H, I]``.
+GEMM-1 runs with the SiLU-and-mul epilogue fused; GEMM-2 either writes plain rows or runs the combine epilogue
+(router-weight scale + scatter to the token's owner).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..config import ModelConfig
+from ..ops import gemm
+from . import weights as W
+
+
+class MoEExperts(torch.nn.Module):
+    def __init__(self, cfg: ModelConfig, layer_id: int, e_lo: int = 0, e_hi: Optional[int] = None, device="cpu",
+                 dtype: Optional[torch.dtype] = None, max_batch_size: int = 0):
+        super().__init__()
+        self.cfg, self.layer_id = cfg, layer_id
+        self.e_lo, self.e_hi = e_lo, cfg.num_experts if e_hi is None else e_hi
+        self.num_experts = self.e_hi - self.e_lo
+        self.hidden_size, self.intermediate_size = cfg.hidden_size, cfg.intermediate_size
+        self.device, self.dtype = torch.device(device), dtype or cfg.dtype
+        self.cache_up = self.cache_down = None
+        if max_batch_size > 0 and self.device.type == "cuda":
+            # persistent activation buffers (the role of cache_up / cache_down at experts.py:57-58)
+            self.cache_up = torch.empty(max_batch_size, self.intermediate_size, dtype=self.dtype, device=self.device)
+            self.cache_down = torch.empty(max_batch_size, self.hidden_size, dtype=self.dtype, device=self.device)
+
+    def param_names(self):
+        p = f"layers.{self.layer_id}.experts."
+        return [p + "w13_weight", p + "w2_weight"]
+
+    def load_weights(self, sd: W.StateDict) -> None:
+        p = f"layers.{self.layer_id}.experts."
+        w13 = W.shard_experts(sd[p + "w13_weight"], self.e_lo, self.e_hi)
+        w2 = W.shard_experts(sd[p + "w2_weight"], self.e_lo, self.e_hi)
+        w13, w2 = W.to_runtime_expert_layout(w13, w2)
+        self.w13_weight = w13.to(device=self.device, dtype=self.dtype).contiguous()
+        self.w2_weight = w2.to(device=self.device, dtype=self.dtype).contiguous()
+
+    def init_weights(self) -> None:
+        """Seeded random weights drawn directly in the runtime layout on the target device, expert by expert
+        (no checkpoint-layout copy of a multi-GB tensor is ever made)."""
+        cfg, H, I = self.cfg, self.hidden_size, self.intermediate_size
+        E = self.num_experts
+        self.w13_weight = torch.empty(E, 2 * I, H, dtype=self.dtype, device=self.device)
+        self.w2_weight = torch.empty(E, H, I, dtype=self.dtype, device=self.device)
+        for i, e in enumerate(range(self.e_lo, self.e_hi)):
+            n13 = f"layers.{self.layer_id}.experts.w13_weight.{e}"
+            n2 = f"layers.{self.layer_id}.experts.w2_weight.{e}"
+            self.w13_weight[i] = W.init_tensor(cfg, n13, (2 * I, H), self.device, self.dtype)
+            self.w2_weight[i] = W.init_tensor(cfg, n2, (H, I), self.device, self.dtype)
+
+    def forward(self, bs: int, hiddens: torch.Tensor, offs: torch.Tensor, out: Optional[torch.Tensor] = None
+                ) -> torch.Tensor:
+        """hiddens [bs, H] sorted by local expert, offs [E_local + 1] -> [bs, H]."""
+        up_buf = self.cache_up[:bs] if self.cache_up is not None and bs <= self.cache_up.shape[0] else None
+        if out is None and self.cache_down is not None and bs <= self.cache_down.shape[0]:
+            out = self.cache_down[:bs]
+        act = gemm.grouped_swiglu(hiddens, self.w13_weight, offs, out=up_buf)
+        return gemm.grouped_linear(act, self.w2_weight, offs, out=out)
+
+    def forward_combine(self, bs: int, hiddens: torch.Tensor, offs: torch.Tensor, recs: torch.Tensor,
+                        bases: torch.Tensor, ld_out: int, outs=None) -> None:
+        """Same FFN, but GEMM-2 scales every row by its router weight and scatters it to its owner (combine)."""
+        up_buf = self.cache_up[:bs] if self.cache_up is not None and bs <= self.cache_up.shape[0] else None
+        act = gemm.grouped_swiglu(hiddens, self.w13_weight, offs, out=up_buf)
+        gemm.grouped_combine(act, self.w2_weight, offs, recs, bases, ld_out, outs=outs)
+
+
+class MoEExpertsSerial(MoEExperts):
+    """One expert at a time through the dense GEMM entry points (the reference's non-grouped mode)."""
+
+    def forward(self, bs: int, hiddens: torch.Tensor, offs: torch.Tensor, out: Optional[torch.Tensor] = None
+                ) -> torch.Tensor:
+        bounds = offs.tolist()
+        if out is None:
+            out = torch.empty(bs, self.hidden_size, dtype=hiddens.dtype, device=hiddens.device)
+        for e in range(self.num_experts):
+            a, b = bounds[e], bounds[e + 1]
+            if b > a:
+                act = gemm.swiglu_linear(hiddens[a:b], self.w13_weight[e])
+                gemm.linear(act, self.w2_weight[e], out=out[a:b])
+        return out

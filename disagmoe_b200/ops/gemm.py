@@ -209,3 +209,25 @@ def grouped_combine(x: torch.Tensor, w: torch.Tensor, offs: torch.Tensor, recs: 
         return
     bn = bn or pick_bn((T + G - 1) // G, EPI_COMBINE)
     _launch(w, x, None, None, offs, recs, bases, G, T, F, K, EPI_COMBINE, bn, 1, ld_out, False)
+
+
+def swiglu_linear(x: torch.Tensor, w13: torch.Tensor, out: Optional[torch.Tensor] = None, bn: int = 0) -> torch.Tensor:
+    """Dense SwiGLU up-projection: silu(x @ w13[:I].T) * (x @ w13[I:].T); w13 is [2I, K] (a one-group grouped_swiglu)."""
+    T, K = x.shape
+    I = w13.shape[0] // 2
+    if not x.is_cuda:
+        h = x.float() @ w13.float().T
+        y = (torch.nn.functional.silu(h[:, :I]) * h[:, I:]).to(x.dtype)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    _check_x(x)
+    assert w13.is_contiguous() and w13.dtype == torch.bfloat16
+    if out is None:
+        out = torch.empty(T, I, dtype=torch.bfloat16, device=x.device)
+    if T == 0:
+        return out
+    bn = bn or pick_bn(T, EPI_SWIGLU)
+    _launch(w13, x, out, None, None, None, None, 1, T, I, K, EPI_SWIGLU, bn, 1, out.stride(0), False)
+    return out
