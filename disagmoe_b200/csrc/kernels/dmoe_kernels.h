@@ -23,7 +23,15 @@ typedef struct DmoeGemm {
   void* ws;           // split-K workspace (fp32), ws_bytes >= dmoe_gemm_workspace_bytes(...)
   int* counters;      // split-K tile counters, zero-initialised once; the kernel leaves them zero
   int* status;        // optional device status word (0 = ok)
+  // --- multi-GPU fusion (all optional, zero / NULL when unused) ---
+  const int* seg_cnt;   // [S, G] rows that source s delivered for group g; region s = rows [s*seg_cap, (s+1)*seg_cap)
+  const int* wait_flags;  // [n_wait] arrival flags written by peers; the kernel waits for *wait_epoch + 1
+  int* wait_epoch;
+  const void* signal_ptrs;  // device array of n_signal flag-array pointers (peer memory); slot signal_slot is written
+  int* signal_epoch;
+  int* done_ticket;     // one zero-initialised int of scratch (required with wait_flags or signal_ptrs)
   long long ldx, ldy, ldr, ws_bytes;
+  int S, seg_cap, n_wait, n_signal, signal_slot, pad0;
   int G, T, F, K;
   int epi;            // DMOE_EPI_*
   int bn;             // token tile: 32/64/128/256, 0 = pick from T/G
@@ -65,6 +73,19 @@ int dmoe_route(const void* x, long long ld_x, const void* norm_w, float eps, con
 int dmoe_dispatch_local(const void* y, long long ld_y, const int* topk_ids, const float* topk_w, int T, int K, int H,
                         int E, int experts_per_rank, int my_rank, int* ws, int* offs, const void* x_bases,
                         long long ld_dst, const void* rec_bases, int dst_capacity, int* status, void* stream);
+
+// ---- peer-memory dispatch (comm.cu) -----------------------------------------------------------------
+// Stores every routed (token, k) row of this attention rank into its region on the expert GPU that owns the
+// expert, with 16-byte records, per-expert counts and a release flag (*epoch + 1). x_bases / rec_bases / cnt_bases /
+// flag_bases are device arrays of n_dst peer pointers. ws = ints [counts E | cursor E | ticket], counts filled by
+// dmoe_route; cleared for the next launch.
+int dmoe_dispatch_remote(const void* y, long long ld_y, const int* topk_ids, const float* topk_w, int T, int K, int H,
+                         int E, int experts_per_rank, int n_dst, int my_rank, int region_cap, int* ws,
+                         const void* x_bases, long long ld_dst, const void* rec_bases, const void* cnt_bases,
+                         const void* flag_bases, int* epoch, int* status, void* stream);
+// Waits (bounded) until flags[i] >= *epoch + 1 for i < n, then advances *epoch.
+int dmoe_wait_flags(const int* flags, int n, int* epoch, int* status, void* stream);
+int dmoe_enable_peer_access(int peer_device);
 
 #ifdef __cplusplus
 }

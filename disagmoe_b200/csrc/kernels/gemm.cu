@@ -33,6 +33,8 @@ constexpr int kUmmaK = 16;     // K per tcgen05.mma for 16-bit inputs
 constexpr int kThreads = 192;
 constexpr int kEpiThreads = 128;
 constexpr int kSmemBudget = 220 * 1024;
+constexpr int kTailBytes = 10 * 1024;   // barriers + segment table (2 x kMaxSeg ints)
+constexpr int kMaxSeg = 1024;            // groups x sources
 
 enum { EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_COMBINE = 2 };
 
@@ -51,6 +53,21 @@ struct GemmArgs {
   float* ws;
   int* counters;
   int* status;
+  // multi-source input (the expert side of a dispatch): S sources wrote their rows for group g into region s
+  // (rows [s * seg_cap, (s + 1) * seg_cap)), packed group after group; seg_cnt[s * G + g] rows each.
+  const int* seg_cnt;
+  int S;
+  int seg_cap;
+  // arrival gate: wait until wait_flags[i] >= *wait_epoch + 1 for i < n_wait before reading seg_cnt / rows
+  const int* wait_flags;
+  int n_wait;
+  int* wait_epoch;
+  // completion signal: after the last tile, store *signal_epoch + 1 to signal_ptrs[i][signal_slot] for i < n_signal
+  int* const* signal_ptrs;
+  int n_signal;
+  int signal_slot;
+  int* signal_epoch;
+  int* done_ticket;
 };
 
 template <int BN, int EPI>
@@ -59,38 +76,39 @@ struct Cfg {
   static constexpr int kABytes = kBM * kBK * 2;
   static constexpr int kBBytes = BN * kBK * 2;
   static constexpr int kStageBytes = kNumA * kABytes + kBBytes;
-  static constexpr int kStagesRaw = (kSmemBudget - 1024) / kStageBytes;
+  static constexpr int kStagesRaw = (kSmemBudget - 1024 - kTailBytes) / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
   static constexpr int kAccCols = BN * kNumA;
   static constexpr int kTmemCols = (2 * kAccCols) < 32 ? 32 : 2 * kAccCols;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 1024 /*barriers, offsets*/;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + kTailBytes;
   static_assert(kTmemCols <= 512, "accumulators do not fit TMEM");
   static_assert((kTmemCols & (kTmemCols - 1)) == 0, "TMEM columns must be a power of two");
   static_assert(kStages >= 3, "pipeline too shallow");
 };
 
-// Walks the persistent tile list. Tiles of group g: for m in [0, MT) for n in [0, ntn_g) for ks in [0, splitk).
+// Walks the persistent tile list. A group (expert) owns S segments of token rows, one per source; its token
+// tiles enumerate the segments one after the other, so all sources' tokens of an expert meet the same weight tile
+// back to back. Tiles of group g: for m in [0, MT) for n in [0, ntn_g) for ks in [0, splitk).
 struct TileWalker {
-  const int* offs;  // shared-memory copy, G+1 entries
-  int G, MT, splitk, BN;
-  int g, base;      // tiles of group g start at linear id `base`
-  int tok0, cnt, ntn;
-  __device__ void init(const int* s_offs, int G_, int MT_, int splitk_, int BN_) {
-    offs = s_offs; G = G_; MT = MT_; splitk = splitk_; BN = BN_;
-    g = -1; base = 0; ntn = 0; cnt = 0; tok0 = 0;
+  const int* seg_start;  // shared memory, [S * G] absolute first row of segment (s, g)
+  const int* seg_cnt;    // shared memory, [S * G]
+  int G, S, MT, splitk, BN;
+  int g, base;           // tiles of group g start at linear id `base`
+  int ntn;
+  __device__ void init(const int* s_start, const int* s_cnt, int G_, int S_, int MT_, int splitk_, int BN_) {
+    seg_start = s_start; seg_cnt = s_cnt; G = G_; S = S_; MT = MT_; splitk = splitk_; BN = BN_;
+    g = -1; base = 0; ntn = 0;
     advance_group();
   }
   __device__ void advance_group() {
     ++g;
-    if (g < G) {
-      tok0 = offs[g];
-      cnt = offs[g + 1] - tok0;
-      if (cnt < 0) cnt = 0;
-      ntn = (cnt + BN - 1) / BN;
-    }
+    ntn = 0;
+    if (g < G)
+      for (int s = 0; s < S; ++s) ntn += (seg_cnt[s * G + g] + BN - 1) / BN;
   }
   // Positions on linear tile id `tile` (monotonically increasing across calls). False when past the end.
-  __device__ bool seek(int tile, int& m, int& n, int& ks) {
+  // row0 / ntok: first token row and number of valid tokens of the tile.
+  __device__ bool seek(int tile, int& m, int& n, int& ks, int& row0, int& ntok) {
     while (g < G) {
       const int ntiles = MT * ntn * splitk;
       if (tile < base + ntiles) {
@@ -98,7 +116,18 @@ struct TileWalker {
         ks = r % splitk; r /= splitk;
         n = r % ntn;
         m = r / ntn;
-        return true;
+        int nl = n;
+        for (int s = 0; s < S; ++s) {
+          const int c = seg_cnt[s * G + g];
+          const int t = (c + BN - 1) / BN;
+          if (nl < t) {
+            row0 = seg_start[s * G + g] + nl * BN;
+            ntok = min(BN, c - nl * BN);
+            return true;
+          }
+          nl -= t;
+        }
+        return false;  // unreachable
       }
       base += ntiles;
       advance_group();
@@ -106,6 +135,15 @@ struct TileWalker {
     return false;
   }
 };
+
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 
 template <int BN, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -121,7 +159,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2); // [1]
   int* abort_word = reinterpret_cast<int*>(tmem_slot + 1);
   int* last_flag = abort_word + 1;
-  int* s_offs = last_flag + 1;                                       // [G+1] (G <= 128)
+  int* s_start = last_flag + 1;                                      // [S * G]
+  int* s_cnt = s_start + kMaxSeg;                                    // [S * G]
+  const int S = a.S > 0 ? a.S : 1;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -144,11 +184,42 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
     tma_prefetch_desc(&tmW);
     tma_prefetch_desc(&tmX);
   }
-  if (a.offs != nullptr) {
-    for (int i = threadIdx.x; i <= a.G; i += blockDim.x) s_offs[i] = a.offs[i];
+  if (a.n_wait > 0) {
+    // arrival gate: the senders' rows, counts and records are complete once their flag carries this call's epoch
+    if (threadIdx.x < a.n_wait) {
+      const int want = *a.wait_epoch + 1;
+      const bool poisoned = a.status != nullptr && *reinterpret_cast<volatile int*>(a.status) != kStatusOk;
+      const long long t0 = clock64();
+      while (!poisoned && ld_acquire_sys(a.wait_flags + threadIdx.x) < want) {
+        if (clock64() - t0 > 4 * DMOE_WAIT_CYCLES) {
+          if (a.status != nullptr) atomicCAS(a.status, kStatusOk, kStatusFlagTimeout);
+          break;
+        }
+        __nanosleep(100);
+      }
+    }
+    __syncthreads();
+  }
+  if (a.seg_cnt != nullptr) {
+    // (s, g) -> first row: region s starts at s * seg_cap and is packed group after group
+    for (int s = threadIdx.x; s < S; s += blockDim.x) {
+      int run = s * a.seg_cap;
+      for (int g = 0; g < a.G; ++g) {
+        const int c = __ldcg(a.seg_cnt + s * a.G + g);
+        s_start[s * a.G + g] = run;
+        s_cnt[s * a.G + g] = c < 0 ? 0 : min(c, (s + 1) * a.seg_cap - run);
+        run += s_cnt[s * a.G + g];
+      }
+    }
+  } else if (a.offs != nullptr) {
+    for (int i = threadIdx.x; i < a.G; i += blockDim.x) {
+      const int o0 = a.offs[i], o1 = a.offs[i + 1];
+      s_start[i] = o0;
+      s_cnt[i] = o1 > o0 ? o1 - o0 : 0;
+    }
   } else if (threadIdx.x == 0) {
-    s_offs[0] = 0;
-    s_offs[1] = a.T;
+    s_start[0] = 0;
+    s_cnt[0] = a.T;
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), C::kTmemCols);
@@ -163,17 +234,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       TileWalker tw;
-      tw.init(s_offs, a.G, MT, a.splitk, BN);
+      tw.init(s_start, s_cnt, a.G, S, MT, a.splitk, BN);
+      if (a.n_wait > 0) asm volatile("fence.proxy.async;" ::: "memory");  // peers' generic stores -> TMA reads
       const uint64_t pol_w = l2_policy_evict_first();
       const uint64_t pol_x = l2_policy_evict_last();
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok; tile += gridDim.x) {
-        int m, n, ks;
-        if (!tw.seek(tile, m, n, ks)) break;
+        int m, n, ks, xrow, ntok_;
+        if (!tw.seek(tile, m, n, ks, xrow, ntok_)) break;
         const int wrow = tw.g * a.w_rows + m * kBM;
-        const int xrow = tw.tok0 + n * BN;
         const int kb0 = ks * kb_per;
         const int kb1 = min(kblocks, kb0 + kb_per);
         for (int kb = kb0; kb < kb1; ++kb) {
@@ -192,15 +263,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       TileWalker tw;
-      tw.init(s_offs, a.G, MT, a.splitk, BN);
+      tw.init(s_start, s_cnt, a.G, S, MT, a.splitk, BN);
       constexpr uint32_t idesc = umma_idesc_bf16(kBM, BN);
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok; tile += gridDim.x, ++it) {
-        int m, n, ks;
-        if (!tw.seek(tile, m, n, ks)) break;
+        int m, n, ks, row0_, ntok_;
+        if (!tw.seek(tile, m, n, ks, row0_, ntok_)) break;
         const int buf = it & 1;
         const uint32_t bphase = (it >> 1) & 1;
         if (!mbar_wait(smem_u32(&tempty_bar[buf]), bphase ^ 1, abort_word)) { ok = false; break; }
@@ -236,20 +307,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
     const int row = q * 32 + lane;          // accumulator lane = feature within the tile
     const int et = threadIdx.x - 64;        // 0..127
     TileWalker tw;
-    tw.init(s_offs, a.G, MT, a.splitk, BN);
+    tw.init(s_start, s_cnt, a.G, S, MT, a.splitk, BN);
     int it = 0;
     bool ok = true;
     for (int tile = blockIdx.x; ok; tile += gridDim.x, ++it) {
-      int m, n, ks;
-      if (!tw.seek(tile, m, n, ks)) break;
+      int m, n, ks, tok_base, ntok;
+      if (!tw.seek(tile, m, n, ks, tok_base, ntok)) break;
       const int buf = it & 1;
       const uint32_t bphase = (it >> 1) & 1;
       if (!mbar_wait(smem_u32(&tfull_bar[buf]), bphase, abort_word)) { ok = false; break; }
       tc_fence_after();
       const uint32_t t0 = tmem_base + buf * C::kAccCols + (static_cast<uint32_t>(q * 32) << 16);
       const int f = m * kBM + row;
-      const int tok_base = tw.tok0 + n * BN;
-      const int ntok = min(BN, tw.cnt - n * BN);
       const bool f_ok = f < a.F;
 
       bool reduce_here = true;       // split-K: only the last arriver runs the real epilogue
@@ -338,16 +407,50 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
             dst[f] = __float2bfloat16(acc[j] * __int_as_float(rec.z));
           }
         } else {
+          if (a.R != nullptr) {
+            // all residual loads of the chunk are issued before the first store: Y may alias R (in-place update),
+            // so the compiler cannot hoist them itself, and one load -> store round trip per token would serialise
+            float r[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const long long t = tok_base + c * 32 + j;
+              r[j] = (j < jmax) ? __bfloat162float(a.R[t * a.ldr + f]) : 0.f;
+            }
+#pragma unroll
+            for (int j = 0; j < 32; ++j) acc[j] += r[j];
+          }
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             if (j >= jmax) break;
             const long long t = tok_base + c * 32 + j;
-            float v = acc[j];
-            if (a.R != nullptr) v += __bfloat162float(a.R[t * a.ldr + f]);
+            const float v = acc[j];
             if (a.y_f32) reinterpret_cast<float*>(a.Y)[t * a.ldy + f] = v;
             else reinterpret_cast<__nv_bfloat16*>(a.Y)[t * a.ldy + f] = __float2bfloat16(v);
           }
         }
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------- completion: signal peers, advance epochs
+  if (a.done_ticket != nullptr && warp >= 2) {
+    // every epilogue thread makes its (possibly remote) stores visible system-wide, then the CTA takes a ticket.
+    // The last CTA of the grid publishes this call's epoch to every destination and advances the gate's epoch
+    // (by then every CTA has long read it).
+    __threadfence_system();
+    named_bar_sync(1, kEpiThreads);
+    if (threadIdx.x == 64) {
+      const int old = atomicAdd(a.done_ticket, 1);
+      if (old == static_cast<int>(gridDim.x) - 1) {
+        __threadfence_system();
+        if (a.n_signal > 0) {
+          const int epoch = *a.signal_epoch + 1;
+          for (int i = 0; i < a.n_signal; ++i) st_release_sys(a.signal_ptrs[i] + a.signal_slot, epoch);
+          *a.signal_epoch = epoch;
+        }
+        if (a.n_wait > 0) *a.wait_epoch = *a.wait_epoch + 1;
+        *a.done_ticket = 0;
+        __threadfence();
       }
     }
   }
@@ -449,7 +552,7 @@ extern "C" long long dmoe_gemm_workspace_bytes(int T, int F, int bn, int splitk)
 
 extern "C" int dmoe_gemm(const DmoeGemm* d, void* stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  if (d->G < 1 || d->G > 128 || d->K % 8 != 0 || d->F < 1 || d->T < 0) return -10;
+  if (d->G < 1 || d->G > kMaxSeg || d->K % 8 != 0 || d->F < 1 || d->T < 0) return -10;
   if (d->T == 0) return 0;
   const int epi = d->epi;
   int bn = d->bn;
@@ -464,7 +567,7 @@ extern "C" int dmoe_gemm(const DmoeGemm* d, void* stream_) {
     const int per = (kblocks + splitk - 1) / splitk;
     splitk = (kblocks + per - 1) / per;
   }
-  if (splitk > 1 && (epi == EPI_SWIGLU || d->offs != nullptr || d->ws == nullptr || d->counters == nullptr)) return -12;
+  if (splitk > 1 && (epi == EPI_SWIGLU || d->offs != nullptr || d->S > 0 || d->ws == nullptr || d->counters == nullptr)) return -12;
   if (splitk > 1 && dmoe_gemm_workspace_bytes(d->T, d->F, bn, splitk) > d->ws_bytes) return -13;
   if (epi == EPI_COMBINE && (d->recs == nullptr || d->bases == nullptr)) return -14;
 
@@ -478,6 +581,15 @@ extern "C" int dmoe_gemm(const DmoeGemm* d, void* stream_) {
   a.bases = static_cast<void* const*>(d->bases);
   a.splitk = splitk; a.ws = static_cast<float*>(d->ws); a.counters = d->counters;
   a.status = d->status;
+  a.seg_cnt = d->seg_cnt; a.S = d->S; a.seg_cap = d->seg_cap;
+  a.wait_flags = d->wait_flags; a.n_wait = d->n_wait; a.wait_epoch = d->wait_epoch;
+  a.signal_ptrs = reinterpret_cast<int* const*>(d->signal_ptrs); a.n_signal = d->n_signal;
+  a.signal_slot = d->signal_slot; a.signal_epoch = d->signal_epoch; a.done_ticket = d->done_ticket;
+  if (a.S > 0 && (a.seg_cnt == nullptr || a.S * a.G > kMaxSeg || a.S * a.seg_cap > d->T)) return -16;
+  if (a.S == 0 && a.G > kMaxSeg) return -16;
+  if ((a.n_wait > 0 || a.n_signal > 0) && a.done_ticket == nullptr) return -17;
+  if (a.n_wait > kThreads || (a.n_wait > 0 && (a.wait_flags == nullptr || a.wait_epoch == nullptr))) return -17;
+  if (a.n_signal > 0 && (a.signal_ptrs == nullptr || a.signal_epoch == nullptr)) return -17;
 
   CUtensorMap tmW, tmX;
   const long long ldx = d->ldx > 0 ? d->ldx : d->K;
@@ -486,7 +598,7 @@ extern "C" int dmoe_gemm(const DmoeGemm* d, void* stream_) {
 
   const long long mt = (d->F + kBM - 1) / kBM;
   // upper bound of the tile count (group sizes live on the device): every group may add one ragged tile
-  long long max_tiles = mt * ((d->T + bn - 1) / bn + (d->offs ? d->G : 0)) * splitk;
+  long long max_tiles = mt * ((d->T + bn - 1) / bn + ((d->offs || d->S > 0) ? d->G * (d->S > 0 ? d->S : 1) : 0)) * splitk;
   if (max_tiles > (1 << 30)) max_tiles = 1 << 30;
   const int mtiles = static_cast<int>(max_tiles);
 

@@ -293,6 +293,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("row_of", &BlockManager::row_of)
       .def("slot_of", &BlockManager::slot_of)
       .def("update_block_table", &BlockManager::update_block_table)
+      .def("step_decode", &BlockManager::step_decode)
       .def("prepare_block_table", [](BlockManager& b, const AttentionBatchMetadata& meta, const std::vector<int>& lens) {
         int mb = 0;
         auto flat = b.prepare_block_table(meta, lens, &mb);

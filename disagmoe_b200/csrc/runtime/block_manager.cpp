@@ -154,6 +154,27 @@ std::vector<int> BlockManager::prepare_block_table(const AttentionBatchMetadata&
   return flat;
 }
 
+std::vector<int64_t> BlockManager::step_decode(const std::vector<int>& seq_ids, const std::vector<int>& lengths) {
+  const size_t n = seq_ids.size();
+  DMOE_CHECK(lengths.size() == n, "lengths size");
+  std::vector<int64_t> out(2 * n);
+  std::lock_guard<std::mutex> lk(mu_);
+  for (size_t i = 0; i < n; ++i) {
+    auto it = seqs_.find(seq_ids[i]);
+    DMOE_CHECK(it != seqs_.end(), "unknown sequence " << seq_ids[i]);
+    auto& s = it->second;
+    const int pos = lengths[i];
+    const int need = pos / block_size_ + 1;
+    while (static_cast<int>(s.blocks.size()) < need) {
+      s.blocks.push_back(take_block_locked());
+      note_locked(s.row, static_cast<int>(s.blocks.size()) - 1, s.blocks.back());
+    }
+    out[i] = s.row;
+    out[n + i] = static_cast<int64_t>(s.blocks[pos / block_size_]) * block_size_ + pos % block_size_;
+  }
+  return out;
+}
+
 std::vector<BlockTableUpdate> BlockManager::drain_updates() {
   std::lock_guard<std::mutex> lk(mu_);
   std::vector<BlockTableUpdate> out;

@@ -44,6 +44,9 @@ class BlockManager {
   // Flat int32 buffer: n*m block-table entries (row-major, -1 padded) followed by n slot ids of the last token.
   std::vector<int> prepare_block_table(const AttentionBatchMetadata& meta, const std::vector<int>& seq_lens,
                                        int* out_max_blocks = nullptr);
+  // One decode step for many sequences at once: grows sequence i so that position lengths[i] has a slot and
+  // returns its table row and flat slot as [rows..., slots...] (2 * n entries).
+  std::vector<int64_t> step_decode(const std::vector<int>& seq_ids, const std::vector<int>& lengths);
   // Table patches since the previous call.
   std::vector<BlockTableUpdate> drain_updates();
 

@@ -24,6 +24,7 @@ from ..config import CacheConfig, ModelConfig
 from ..models import weights as W
 from ..models.attention import AttnMeta, MoEAttention
 from ..models.experts import MoEExperts
+from ..ops import _lib
 from ..ops import functional as F
 from ..ops import gemm
 from ..utils.utils import get_graph_batch_size, graph_batch_sizes
@@ -90,7 +91,7 @@ class FusedModelExecutor:
                                        a0.q_size, a0.kv_size) if max_prefill_tokens > max_batch_size else self.decode_buf
         self.graphs: Dict[int, torch.cuda.CUDAGraph] = {}
         self.graph_sizes: List[int] = []
-        self.launches_per_step = 0
+        self.graph_launches: Dict[int, int] = {}
 
     # ---- memory -------------------------------------------------------------------------------------------------
     def _profile_num_blocks(self) -> int:
@@ -171,9 +172,11 @@ class FusedModelExecutor:
             torch.cuda.current_stream().wait_stream(side)
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
+            n0 = _lib.LAUNCHES
             with torch.cuda.graph(g):
                 self._forward(buf, b, self.cfg.max_seq_len, False)
             self.graphs[b] = g
+            self.graph_launches[b] = _lib.LAUNCHES - n0
         self.graph_sizes = sorted(self.graphs)
         torch.cuda.synchronize()
 
@@ -193,6 +196,7 @@ class FusedModelExecutor:
                 buf.ctx_len[B:b].fill_(0)
                 buf.ids[B:b].fill_(0)
             self.graphs[b].replay()
+            _lib.add_launches(self.graph_launches[b])
             return buf.next_ids[:B], None
         self._fill(buf, B, ids, positions, slots, ctx_len, bt_row)
         return self._forward(buf, B, int(ctx_len.max()) if not ctx_len.is_cuda else self.cfg.max_seq_len, want_logits)

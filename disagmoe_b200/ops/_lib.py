@@ -23,8 +23,12 @@ class DmoeGemm(ctypes.Structure):
         ("W", ctypes.c_void_p), ("X", ctypes.c_void_p), ("Y", ctypes.c_void_p), ("R", ctypes.c_void_p),
         ("offs", ctypes.c_void_p), ("recs", ctypes.c_void_p), ("bases", ctypes.c_void_p), ("ws", ctypes.c_void_p),
         ("counters", ctypes.c_void_p), ("status", ctypes.c_void_p),
+        ("seg_cnt", ctypes.c_void_p), ("wait_flags", ctypes.c_void_p), ("wait_epoch", ctypes.c_void_p),
+        ("signal_ptrs", ctypes.c_void_p), ("signal_epoch", ctypes.c_void_p), ("done_ticket", ctypes.c_void_p),
         ("ldx", ctypes.c_longlong), ("ldy", ctypes.c_longlong), ("ldr", ctypes.c_longlong),
         ("ws_bytes", ctypes.c_longlong),
+        ("S", ctypes.c_int), ("seg_cap", ctypes.c_int), ("n_wait", ctypes.c_int), ("n_signal", ctypes.c_int),
+        ("signal_slot", ctypes.c_int), ("pad0", ctypes.c_int),
         ("G", ctypes.c_int), ("T", ctypes.c_int), ("F", ctypes.c_int), ("K", ctypes.c_int),
         ("epi", ctypes.c_int), ("bn", ctypes.c_int), ("splitk", ctypes.c_int), ("y_f32", ctypes.c_int),
     ]
@@ -56,9 +60,19 @@ def stream_ptr() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+LAUNCHES = 0   # entry-point calls that launched kernels of this library (a graph replay adds its captured count)
+
+
 def check(code: int, what: str):
+    global LAUNCHES
     if code != 0:
         raise KernelError(f"{what} failed with code {code}")
+    LAUNCHES += 1
+
+
+def add_launches(n: int):
+    global LAUNCHES
+    LAUNCHES += n
 
 
 def ptr(t):

@@ -71,9 +71,40 @@ def pick_bn(tokens_per_group: int, epi: int) -> int:
     return bn
 
 
-def _launch(W, X, Y, R, offs, recs, bases, G, T, F, K, epi, bn, splitk, ldy, y_f32):
+def _group_hint(T: int, G: int) -> int:
+    """Token-tile hint for a grouped GEMM whose group sizes are only known on the device: the mean group size plus
+    head-room for routing imbalance, so that most groups fit one token tile (a second tile re-reads the weights)."""
+    mean = (T + G - 1) // G
+    return mean + mean // 2 + 8 if G > 1 else mean
+
+
+class GemmComm:
+    """Multi-GPU hooks of a grouped GEMM launch (see ``DmoeGemm`` in csrc/kernels/dmoe_kernels.h).
+
+    seg_cnt [S, G] int32 (device): rows source s delivered for group g; region s = rows [s*seg_cap, (s+1)*seg_cap).
+    wait_flags [n_wait] int32 + wait_epoch [1]: arrival gate. signal_ptrs int64 [n_signal] (peer flag arrays) +
+    signal_slot + signal_epoch [1]: completion signal. done_ticket [1]: zero-initialised scratch int.
+    """
+
+    def __init__(self, seg_cnt=None, S=0, seg_cap=0, wait_flags=None, n_wait=0, wait_epoch=None, signal_ptrs=None,
+                 n_signal=0, signal_slot=0, signal_epoch=None, done_ticket=None):
+        self.seg_cnt, self.S, self.seg_cap = seg_cnt, S, seg_cap
+        self.wait_flags, self.n_wait, self.wait_epoch = wait_flags, n_wait, wait_epoch
+        self.signal_ptrs, self.n_signal, self.signal_slot = signal_ptrs, n_signal, signal_slot
+        self.signal_epoch, self.done_ticket = signal_epoch, done_ticket
+
+    def fill(self, d):
+        d.seg_cnt, d.S, d.seg_cap = _lib.ptr(self.seg_cnt), self.S, self.seg_cap
+        d.wait_flags, d.n_wait, d.wait_epoch = _lib.ptr(self.wait_flags), self.n_wait, _lib.ptr(self.wait_epoch)
+        d.signal_ptrs, d.n_signal, d.signal_slot = _lib.ptr(self.signal_ptrs), self.n_signal, self.signal_slot
+        d.signal_epoch, d.done_ticket = _lib.ptr(self.signal_epoch), _lib.ptr(self.done_ticket)
+
+
+def _launch(W, X, Y, R, offs, recs, bases, G, T, F, K, epi, bn, splitk, ldy, y_f32, comm: Optional[GemmComm] = None):
     s = scratch(X.device)
     d = _lib.DmoeGemm()
+    if comm is not None:
+        comm.fill(d)
     d.W, d.X, d.Y, d.R = W.data_ptr(), X.data_ptr(), _lib.ptr(Y), _lib.ptr(R)
     d.offs, d.recs, d.bases = _lib.ptr(offs), _lib.ptr(recs), _lib.ptr(bases)
     if splitk > 1:
@@ -140,8 +171,8 @@ def _grouped_ref(x, w, offs, swiglu):
     return y
 
 
-def grouped_swiglu(x: torch.Tensor, w13: torch.Tensor, offs: torch.Tensor, out: Optional[torch.Tensor] = None,
-                   bn: int = 0) -> torch.Tensor:
+def grouped_swiglu(x: torch.Tensor, w13: torch.Tensor, offs: Optional[torch.Tensor], out: Optional[torch.Tensor] = None,
+                   bn: int = 0, comm: Optional[GemmComm] = None) -> torch.Tensor:
     """act[T, I] = silu(x @ w13[g, :I].T) * (x @ w13[g, I:].T) for the rows of group g; w13 is [G, 2I, K]."""
     T, K = x.shape
     G, F2, _ = w13.shape
@@ -153,13 +184,14 @@ def grouped_swiglu(x: torch.Tensor, w13: torch.Tensor, offs: torch.Tensor, out: 
             return out
         return y
     _check_x(x)
-    assert w13.is_contiguous() and w13.dtype == torch.bfloat16 and offs.dtype == torch.int32 and offs.is_cuda
+    assert w13.is_contiguous() and w13.dtype == torch.bfloat16
+    assert comm is not None or (offs.dtype == torch.int32 and offs.is_cuda)
     if out is None:
         out = torch.empty(T, I, dtype=torch.bfloat16, device=x.device)
     if T == 0:
         return out
-    bn = bn or pick_bn((T + G - 1) // G, EPI_SWIGLU)
-    _launch(w13, x, out, None, offs, None, None, G, T, I, K, EPI_SWIGLU, bn, 1, out.stride(0), False)
+    bn = bn or pick_bn(_group_hint(T, G), EPI_SWIGLU)
+    _launch(w13, x, out, None, offs, None, None, G, T, I, K, EPI_SWIGLU, bn, 1, out.stride(0), False, comm)
     return out
 
 
@@ -180,13 +212,13 @@ def grouped_linear(x: torch.Tensor, w: torch.Tensor, offs: torch.Tensor, out: Op
         out = torch.empty(T, F, dtype=torch.bfloat16, device=x.device)
     if T == 0:
         return out
-    bn = bn or pick_bn((T + G - 1) // G, EPI_PLAIN)
+    bn = bn or pick_bn(_group_hint(T, G), EPI_PLAIN)
     _launch(w, x, out, None, offs, None, None, G, T, F, K, EPI_PLAIN, bn, 1, out.stride(0), False)
     return out
 
 
-def grouped_combine(x: torch.Tensor, w: torch.Tensor, offs: torch.Tensor, recs: torch.Tensor, bases: torch.Tensor,
-                    ld_out: int, bn: int = 0, outs=None) -> None:
+def grouped_combine(x: torch.Tensor, w: torch.Tensor, offs: Optional[torch.Tensor], recs: torch.Tensor,
+                    bases: torch.Tensor, ld_out: int, bn: int = 0, outs=None, comm: Optional[GemmComm] = None) -> None:
     """GEMM-2 with the combine epilogue: row t of group g becomes ``weight[t] * (x[t] @ w[g].T)`` written to row
     ``recs[t, 1]`` of the buffer ``bases[recs[t, 0]]`` (row stride ``ld_out`` elements).
 
@@ -207,8 +239,8 @@ def grouped_combine(x: torch.Tensor, w: torch.Tensor, offs: torch.Tensor, recs: 
     assert recs.dtype == torch.int32 and recs.is_contiguous() and recs.shape[1] == 4 and bases.dtype == torch.int64
     if T == 0:
         return
-    bn = bn or pick_bn((T + G - 1) // G, EPI_COMBINE)
-    _launch(w, x, None, None, offs, recs, bases, G, T, F, K, EPI_COMBINE, bn, 1, ld_out, False)
+    bn = bn or pick_bn(_group_hint(T, G), EPI_COMBINE)
+    _launch(w, x, None, None, offs, recs, bases, G, T, F, K, EPI_COMBINE, bn, 1, ld_out, False, comm)
 
 
 def swiglu_linear(x: torch.Tensor, w13: torch.Tensor, out: Optional[torch.Tensor] = None, bn: int = 0) -> torch.Tensor:

@@ -1,0 +1,71 @@
+"""Fused dispatch / combine pipeline: 2 attention + 2 expert "ranks" emulated on one GPU (arenas that point at each
+other, kernels launched in an order in which no flag wait has to block) against the colocated executor."""
+import pytest
+import torch
+
+from disagmoe_b200.config import CacheConfig, tiny_config
+from disagmoe_b200.executor.fused import FusedModelExecutor
+from disagmoe_b200.models.weights import init_state_dict
+from disagmoe_b200.ops import gemm
+from disagmoe_b200.parallel.disagg import AttentionRank, DisaggShape, ExpertRank, build_layout
+from disagmoe_b200.parallel.peer import PeerArena
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("A,X,n_mb", [(1, 1, 1), (2, 2, 2), (1, 4, 2)])
+def test_emulated_disagg_matches_colocated(A, X, n_mb):
+    cfg = tiny_config.clone(dtype=torch.bfloat16, num_layers=3)
+    sd = {k: v.to(torch.bfloat16) for k, v in init_state_dict(cfg, dtype=torch.float32).items()}
+    B = 3 if n_mb * 3 * 4 <= 60 else 2
+    shape = DisaggShape(A, X, n_mb, B, cfg.top_k, cfg.hidden_size, cfg.num_experts)
+    layout = build_layout(shape)
+    arenas = PeerArena.emulated(A + X, layout.size)
+    attn = [AttentionRank(cfg, shape, arenas[a], layout, a, num_blocks=64, state_dict=sd) for a in range(A)]
+    exps = [ExpertRank(cfg, shape, arenas[A + x], layout, x, state_dict=sd) for x in range(X)]
+    ref = FusedModelExecutor(cfg, CacheConfig(block_size=16), device="cuda", max_batch_size=B, max_prefill_tokens=B,
+                             state_dict=sd, num_blocks=64, enable_cuda_graph=False)
+    g = torch.Generator().manual_seed(0)
+    kv = torch.randn(ref.kv_cache.shape, generator=g).to(torch.bfloat16).cuda() * 0.5
+    for step in range(2):   # two iterations: epochs and cleared histograms must carry over
+        inputs = {}
+        for a in range(A):
+            if step == 0:
+                attn[a].kv_cache.copy_(kv)
+            perm = torch.randperm(60, generator=g)   # disjoint KV blocks for every sequence of the rank
+            for m in range(n_mb):
+                ids = torch.randint(0, cfg.vocab_size, (B,), generator=g).int()
+                ctx = torch.randint(3, 40, (B,), generator=g).int()
+                rows = torch.arange(B, dtype=torch.int32) + m * B
+                bt = perm[m * B * 4:(m + 1) * B * 4].view(B, 4).int()
+                attn[a].block_tables[m * B:(m + 1) * B, :4] = bt.cuda()
+                slots = torch.tensor([int(bt[i, int(ctx[i]) // 16]) * 16 + int(ctx[i]) % 16 for i in range(B)])
+                d = attn[a].mb[m]
+                d["ids"].copy_(ids); d["positions"].copy_(ctx); d["ctx_len"].copy_(ctx + 1)
+                d["bt_row"].copy_(rows); d["slots"].copy_(slots)
+                inputs[(a, m)] = (ids, ctx, slots, bt)
+        for a in range(A):
+            attn[a].kv_cache_before = attn[a].kv_cache.clone()
+            for m in range(n_mb):
+                attn[a].embed(m)
+        for l in range(cfg.num_layers):
+            for m in range(n_mb):
+                for a in range(A):
+                    attn[a].layer(l, m)
+                for x in range(X):
+                    exps[x].layer(l, m)
+        for a in range(A):
+            for m in range(n_mb):
+                attn[a].head(m)
+        torch.cuda.synchronize()
+        assert gemm.check_status() == 0
+        for (a, m), (ids, ctx, slots, bt) in inputs.items():
+            if step == 0:
+                ref.kv_cache.copy_(kv)
+            else:
+                ref.kv_cache.copy_(attn[a].kv_cache_before)
+            ref.block_tables[:B, :4] = bt.cuda()
+            _, lg = ref.decode(ids, ctx, slots, ctx + 1, torch.arange(B, dtype=torch.int32), want_logits=True)
+            got = attn[a].mb[m]["logits"]
+            err = (got - lg).abs().max().item() / lg.abs().max().item()
+            assert err < 0.03, f"rank {a} mb {m} step {step}: rel err {err}"
