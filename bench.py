@@ -174,14 +174,16 @@ def main():
     launches = (runner.launch_count() - launches0) if hasattr(runner, "launch_count") else 0
 
     tokens_local = runner.tokens_per_step() if hasattr(runner, "tokens_per_step") else B
-    t = torch.tensor([dev_ms, e2e_ms, float(tokens_local), float(launches), float(h2d), float(d2h)], device="cuda",
-                     dtype=torch.float64)
+    from disagmoe_b200.ops import gemm as _gemm
+    kstatus = _gemm.check_status(torch.device("cuda", local_rank))   # non-zero: a bounded device wait gave up
+    t = torch.tensor([dev_ms, e2e_ms, float(tokens_local), float(launches), float(h2d), float(d2h), float(kstatus)],
+                     device="cuda", dtype=torch.float64)
     if world > 1:
         mx = t.clone()
         dist.all_reduce(mx, op=dist.ReduceOp.MAX)
         sm = t.clone()
         dist.all_reduce(sm, op=dist.ReduceOp.SUM)
-        dev_ms, e2e_ms = float(mx[0]), float(mx[1])
+        dev_ms, e2e_ms, kstatus = float(mx[0]), float(mx[1]), int(mx[6])
         tokens_step, launches, h2d, d2h = float(sm[2]), int(sm[3]), float(sm[4]), float(sm[5])
     else:
         tokens_step = float(tokens_local)
@@ -201,7 +203,10 @@ def main():
             "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms / K, 3),
                     "h2d_bytes_per_step": int(h2d / K), "d2h_bytes_per_step": int(d2h / K)},
             "gpu_launches": int(launches),
+            "kernel_status": int(kstatus),
         }
+        if kstatus != 0:
+            out["invalid"] = "a device-side wait timed out (kernel status %d): results are not valid" % kstatus
         print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()

@@ -13,6 +13,8 @@
 // Replaces, on the device: disagmoe/frontend/engine.py:667-677 (tolist + counting sort + permute),
 // csrc/muhelper/muhelper.cpp:189-228 (per-EP-rank ZMQ metadata message + ncclSend) and the receive side
 // csrc/muhelper/muhelper.cpp:485-515 (ZMQ recv + ncclRecv + stream sync).
+#include <string.h>
+
 #include "dmoe_kernels.h"
 #include "sm100.cuh"
 
@@ -184,3 +186,34 @@ extern "C" int dmoe_enable_peer_access(int peer_device) {
   }
   return static_cast<int>(e);
 }
+
+// ---- peer arenas: allocation and CUDA IPC mapping ----------------------------------------------------------
+// The arena is a plain cudaMalloc block (so its IPC handle names exactly this block); a peer's handle is opened
+// with THIS process's device current, which maps the block for loads / stores issued by kernels of this device.
+extern "C" int dmoe_peer_alloc(long long nbytes, void** ptr, void* handle64) {
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, static_cast<size_t>(nbytes));
+  if (e != cudaSuccess) return static_cast<int>(e);
+  e = cudaMemset(p, 0, static_cast<size_t>(nbytes));
+  if (e != cudaSuccess) return static_cast<int>(e);
+  cudaIpcMemHandle_t h;
+  e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  static_assert(sizeof(h) == 64, "IPC handle size");
+  memcpy(handle64, &h, sizeof(h));
+  *ptr = p;
+  return static_cast<int>(cudaDeviceSynchronize());
+}
+
+extern "C" int dmoe_peer_open(const void* handle64, void** ptr) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  void* p = nullptr;
+  cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  *ptr = p;
+  return 0;
+}
+
+extern "C" int dmoe_peer_close(void* ptr) { return static_cast<int>(cudaIpcCloseMemHandle(ptr)); }
+extern "C" int dmoe_peer_free(void* ptr) { return static_cast<int>(cudaFree(ptr)); }

@@ -86,6 +86,12 @@ int dmoe_dispatch_remote(const void* y, long long ld_y, const int* topk_ids, con
 // Waits (bounded) until flags[i] >= *epoch + 1 for i < n, then advances *epoch.
 int dmoe_wait_flags(const int* flags, int n, int* epoch, int* status, void* stream);
 int dmoe_enable_peer_access(int peer_device);
+// Peer arena: a zeroed cudaMalloc block + its 64-byte CUDA IPC handle; dmoe_peer_open maps a peer's block into
+// this process for kernels of the CURRENT device (peer access is enabled lazily by the driver).
+int dmoe_peer_alloc(long long nbytes, void** ptr, void* handle64);
+int dmoe_peer_open(const void* handle64, void** ptr);
+int dmoe_peer_close(void* ptr);
+int dmoe_peer_free(void* ptr);
 
 #ifdef __cplusplus
 }

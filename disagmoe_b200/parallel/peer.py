@@ -22,6 +22,20 @@ def _align(x: int, a: int = 256) -> int:
     return (x + a - 1) // a * a
 
 
+class _RawCudaBuffer:
+    """Exposes a raw device address through ``__cuda_array_interface__`` so that torch can view it as a tensor."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3,
+                                         "strides": None}
+
+
+def _wrap_device_memory(ptr: int, nbytes: int, device: torch.device) -> torch.Tensor:
+    """uint8 tensor over ``nbytes`` at device address ``ptr`` (memory owned by the kernel library, never freed by
+    torch). The tensor is labelled with ``device``: for a mapped peer block that is the device whose kernels use it."""
+    return torch.as_tensor(_RawCudaBuffer(ptr, nbytes), device=device)
+
+
 class ArenaLayout:
     """Names -> (offset, nbytes) with 256-byte alignment; identical on every rank."""
 
@@ -47,28 +61,34 @@ class PeerArena:
     # ---- construction --------------------------------------------------------------------------------------
     @staticmethod
     def create(nbytes: int, group=None, device: Optional[torch.device] = None) -> "PeerArena":
-        """Collective over ``group`` (NCCL): allocates the local arena, exchanges IPC handles, maps every peer."""
+        """Collective over ``group``: allocates the local arena, exchanges CUDA IPC handles, maps every peer.
+
+        The arena is allocated and mapped by the kernel library itself: a peer's block has to be opened with this
+        process's own device current so that kernels running on it may load from and store to the block."""
         import torch.distributed as dist
         device = device or torch.device("cuda", torch.cuda.current_device())
+        assert torch.cuda.current_device() == device.index, "make the arena's device current first"
         rank, world = dist.get_rank(group), dist.get_world_size(group)
-        # a dedicated cudaMalloc block (not a slice of a cached segment shared with other tensors)
-        local = torch.zeros(_align(nbytes, 2 << 20), dtype=torch.uint8, device=device)
-        handle = local.untyped_storage()._share_cuda_()
+        nbytes = _align(nbytes, 2 << 20)
+        lib = _lib.lib()
+        p = ctypes.c_void_p()
+        handle = ctypes.create_string_buffer(64)
+        _lib.check(lib.dmoe_peer_alloc(ctypes.c_longlong(nbytes), ctypes.byref(p), handle), "dmoe_peer_alloc")
+        _lib.LAUNCHES -= 1
         gathered = [None] * world
-        dist.all_gather_object(gathered, (handle, device.index, local.numel()), group=group)
-        peers, keep = [], []
-        for r, (h, dev_idx, n) in enumerate(gathered):
+        dist.all_gather_object(gathered, (handle.raw, nbytes), group=group)
+        ptrs = []
+        for r, (h, n) in enumerate(gathered):
             if r == rank:
-                peers.append(local)
+                ptrs.append(p.value)
                 continue
-            _lib.check(_lib.lib().dmoe_enable_peer_access(ctypes.c_int(dev_idx)), "dmoe_enable_peer_access")
+            q = ctypes.c_void_p()
+            _lib.check(lib.dmoe_peer_open(ctypes.c_char_p(h), ctypes.byref(q)), "dmoe_peer_open")
             _lib.LAUNCHES -= 1
-            st = torch.UntypedStorage._new_shared_cuda(*h)
-            t = torch.empty(0, dtype=torch.uint8, device=torch.device("cuda", dev_idx)).set_(st, 0, (n,), (1,))
-            keep.append(st)
-            peers.append(t)
+            ptrs.append(q.value)
+        peers = [_wrap_device_memory(ptrs[r], nbytes, device) for r in range(world)]
         dist.barrier(group=group)
-        return PeerArena(rank, world, local, peers, keep)
+        return PeerArena(rank, world, peers[rank], peers, keep=ptrs)
 
     @staticmethod
     def emulated(world: int, nbytes: int, device="cuda") -> List["PeerArena"]:
