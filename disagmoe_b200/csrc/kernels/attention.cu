@@ -8,8 +8,8 @@
 // The work of one CTA is (token, kv head, kv split): the GQ query heads that share the kv head are processed
 // together, so every K/V byte is read once per group. It is a bandwidth problem (256 B of K and of V per
 // cached token and kv head), so the kernel is built around wide loads kept in flight rather than around
-// tensor cores: K/V rows stream through a 4-deep cp.async ring in shared memory (16 cached tokens per stage),
-// a warp covers 4 cached tokens at a time, 8 lanes per token, 16-byte reads; scores are reduced with 3 shuffles; softmax is online (base 2); the 16 (warp, lane-group) partial states are merged through
+// CUDA-core FLOPs: K/V rows stream through per-warp cp.async rings in shared memory and the GQ x 16-token score and
+// output tiles run on the tensor cores (mma.sync m16n8k16: the group is far too small for a tcgen05 tile); softmax is online (base 2); the 16 (warp, lane-group) partial states are merged through
 // shared memory. With splits > 1 ("flash decoding") partial outputs + log-sum-exp go to a workspace and a
 // second kernel merges them.
 //
@@ -37,18 +37,44 @@ __device__ __forceinline__ void cvt8(const bf16x8a& p, float* f) {
   }
 }
 
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+  // src-size 0 zero-fills the 16 destination bytes (rows past the end of the context)
+  const int sz = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(sz) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+// D (16x8 fp32) += A (16x16 bf16, row) * B (16x8 bf16, col)
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
 
-constexpr int kAttnStages = 4;     // cp.async ring depth
-constexpr int kAttnStageTok = 16;  // cached tokens per stage (block_size must be a multiple of it)
+constexpr int kAttnStages = 3;     // cp.async ring depth, per warp
+constexpr int kAttnStageTok = 16;  // cached tokens per stage and warp (block_size must be a multiple of it)
+constexpr int kAttnWarps = kAttnThreads / 32;
 
+// Tensor-core formulation: the GQ query heads of one kv head are the (zero padded) 16 rows of an m16n8k16 tile.
+// Each warp owns every 4th chunk of 16 cached tokens and streams them through its private cp.async ring
+// (swizzled so that ldmatrix is bank-conflict free): S = Q K^T (2 n-tiles), online softmax on the accumulator
+// fragments, P re-used in place as the A operand of O += P V (V read with ldmatrix.trans).
 template <int HD, int GQ>
 __global__ void __launch_bounds__(kAttnThreads)
 paged_attn_kernel(const __nv_bfloat16* __restrict__ q, long long ld_q, const __nv_bfloat16* __restrict__ kcache,
@@ -56,139 +82,159 @@ paged_attn_kernel(const __nv_bfloat16* __restrict__ q, long long ld_q, const __n
                   const int* __restrict__ bt_row, const int* __restrict__ ctx_len, int block_size, int n_kv,
                   float scale_log2, int splits, __nv_bfloat16* __restrict__ out, long long ld_out,
                   float* __restrict__ part_o, float* __restrict__ part_lse) {
-  constexpr int CH = HD / 64;     // 16-byte chunks per lane (8 lanes cover one row)
-  constexpr int EL = CH * 8;      // elements per lane
-  constexpr int ROWB = HD * 2;    // bytes of one cached row of one kv head
-  constexpr int STAGEB = 2 * kAttnStageTok * ROWB;  // K rows then V rows
-  constexpr int CPT = (kAttnStageTok * (HD / 8)) / kAttnThreads;  // 16-byte copies per thread per stage, K or V
-  __shared__ float s_m[kAttnParts][GQ];
-  __shared__ float s_l[kAttnParts][GQ];
-  extern __shared__ __align__(16) uint8_t s_dyn[];  // cp.async ring; reused as [kAttnParts][GQ][HD] floats at the end
-  float* s_acc = reinterpret_cast<float*>(s_dyn);
+  static_assert(GQ <= 8, "the query group must fit the first 8 rows of the MMA tile");
+  constexpr int ROWB = HD * 2;                       // bytes of one cached row of one kv head
+  constexpr int NCH = HD / 8;                        // 16-byte chunks per row
+  constexpr int TILEB = kAttnStageTok * ROWB;        // K (or V) tile of one stage
+  constexpr int STAGEB = 2 * TILEB;
+  constexpr int WARPB = kAttnStages * STAGEB;
+  constexpr int CPL = kAttnStageTok * NCH / 32;      // 16-byte copies per lane per tile
+  constexpr int KS = HD / 16;                        // k-steps of Q K^T
+  constexpr int NT = HD / 8;                         // n-tiles of the output
+  __shared__ float s_m[kAttnWarps][8];
+  __shared__ float s_l[kAttnWarps][8];
+  extern __shared__ __align__(128) uint8_t s_dyn[];  // per-warp rings; reused as [warps][GQ][HD] floats at the end
 
   const int t = blockIdx.x, hkv = blockIdx.y, split = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int grp = lane >> 3, sub = lane & 7;
-  const int part = warp * 4 + grp;
+  const int g = lane >> 2, tq = lane & 3;            // accumulator row / column-pair of this lane
   const int n_q = n_kv * GQ;
 
   const int len = ctx_len[t];
   const int row = bt_row != nullptr ? bt_row[t] : t;
   const int* bt = block_tables + static_cast<long long>(row) * max_blocks;
-  // split the context in block-aligned chunks
   const int nblk = (len + block_size - 1) / block_size;
   const int blk_per = (nblk + splits - 1) / splits;
   const int c0 = min(len, split * blk_per * block_size);
   const int c1 = min(len, (split + 1) * blk_per * block_size);
-  const int nst = (c1 - c0 + kAttnStageTok - 1) / kAttnStageTok;
+  const int nchunk = (c1 - c0 + kAttnStageTok - 1) / kAttnStageTok;
+  const int my_chunks = nchunk > warp ? (nchunk - warp + kAttnWarps - 1) / kAttnWarps : 0;
   const long long tok_stride = static_cast<long long>(n_kv) * HD;
-  const uint32_t ring = smem_u32(s_dyn);
+  const uint32_t ring = smem_u32(s_dyn) + warp * WARPB;
 
-  // stage s holds cached tokens [c0 + 16 s, c0 + 16 s + 16) of this kv head: K rows, then V rows
-  auto issue = [&](int s) {
-    if (s < nst) {
-      const int tok0 = c0 + s * kAttnStageTok;
+  auto issue = [&](int j) {
+    if (j < my_chunks) {
+      const int tok0 = c0 + (warp + j * kAttnWarps) * kAttnStageTok;
       const long long blk = bt[tok0 / block_size];
       const long long slot0 = blk * block_size + tok0 % block_size;
-      const uint32_t dst0 = ring + (s % kAttnStages) * STAGEB;
+      const uint32_t dst0 = ring + (j % kAttnStages) * STAGEB;
 #pragma unroll
-      for (int i = 0; i < CPT; ++i) {
-        const int id = threadIdx.x + i * kAttnThreads;
-        const int r = id / (HD / 8), c = id % (HD / 8);
-        if (tok0 + r < c1) {
-          const long long off = (slot0 + r) * tok_stride + hkv * HD + c * 8;
-          cp_async16(dst0 + r * ROWB + c * 16, kcache + off);
-          cp_async16(dst0 + kAttnStageTok * ROWB + r * ROWB + c * 16, vcache + off);
-        }
+      for (int i = 0; i < CPL; ++i) {
+        const int id = lane + i * 32;
+        const int r = id / NCH, c = id % NCH;
+        const bool valid = tok0 + r < c1;
+        const long long off = valid ? (slot0 + r) * tok_stride + hkv * HD + c * 8 : 0;
+        const uint32_t d = dst0 + r * ROWB + ((c ^ (r & 7)) << 4);
+        cp_async16(d, kcache + off, valid);
+        cp_async16(d + TILEB, vcache + off, valid);
       }
     }
     cp_async_commit();
   };
 #pragma unroll
-  for (int s = 0; s < kAttnStages - 1; ++s) issue(s);
+  for (int j = 0; j < kAttnStages - 1; ++j) issue(j);
 
-  float qr[GQ][EL];
-#pragma unroll
-  for (int g = 0; g < GQ; ++g) {
+  // Q fragments (rows >= GQ are zero)
+  uint32_t qa[KS][4];
+  {
     const __nv_bfloat16* qp = q + static_cast<long long>(t) * ld_q + (hkv * GQ + g) * HD;
 #pragma unroll
-    for (int c = 0; c < CH; ++c) {
-      cvt8(*reinterpret_cast<const bf16x8a*>(qp + (c * 8 + sub) * 8), &qr[g][c * 8]);
+    for (int ks = 0; ks < KS; ++ks) {
+      qa[ks][0] = g < GQ ? *reinterpret_cast<const uint32_t*>(qp + ks * 16 + 2 * tq) : 0u;
+      qa[ks][2] = g < GQ ? *reinterpret_cast<const uint32_t*>(qp + ks * 16 + 8 + 2 * tq) : 0u;
+      qa[ks][1] = 0u;
+      qa[ks][3] = 0u;
     }
-#pragma unroll
-    for (int i = 0; i < EL; ++i) qr[g][i] *= scale_log2;
   }
-
-  float m[GQ], l[GQ], acc[GQ][EL];
+  float o[NT][4];
 #pragma unroll
-  for (int g = 0; g < GQ; ++g) {
-    m[g] = -INFINITY;
-    l[g] = 0.f;
-#pragma unroll
-    for (int i = 0; i < EL; ++i) acc[g][i] = 0.f;
-  }
+  for (int i = 0; i < NT; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+  float m = -INFINITY, l = 0.f;
 
-  const unsigned gmask = 0xFFu << (grp * 8);  // the 8 lanes that share one cached token
-  for (int s = 0; s < nst; ++s) {
-    issue(s + kAttnStages - 1);
+  // ldmatrix lane roles
+  const int lm_mi = lane >> 3, lm_r = lane & 7;
+  for (int j = 0; j < my_chunks; ++j) {
+    issue(j + kAttnStages - 1);
     cp_async_wait<kAttnStages - 1>();
-    __syncthreads();
-    if (c0 + s * kAttnStageTok + part < c1) {   // uniform across the 8 lanes of a group
-      const uint8_t* kb = s_dyn + (s % kAttnStages) * STAGEB + part * ROWB;
-      const uint8_t* vb = kb + kAttnStageTok * ROWB;
-      float kf[EL], vf[EL];
+    __syncwarp();
+    const uint32_t kb = ring + (j % kAttnStages) * STAGEB;
+    const uint32_t vb = kb + TILEB;
+    const int tok0 = c0 + (warp + j * kAttnWarps) * kAttnStageTok;
+    float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+    {
+      const int r = (lm_mi >> 1) * 8 + lm_r;          // token row this lane addresses
 #pragma unroll
-      for (int c = 0; c < CH; ++c) cvt8(*reinterpret_cast<const bf16x8a*>(kb + (c * 8 + sub) * 16), &kf[c * 8]);
-#pragma unroll
-      for (int c = 0; c < CH; ++c) cvt8(*reinterpret_cast<const bf16x8a*>(vb + (c * 8 + sub) * 16), &vf[c * 8]);
-#pragma unroll
-      for (int g = 0; g < GQ; ++g) {
-        float sc = 0.f;
-#pragma unroll
-        for (int i = 0; i < EL; ++i) sc += qr[g][i] * kf[i];
-        sc += __shfl_xor_sync(gmask, sc, 1);
-        sc += __shfl_xor_sync(gmask, sc, 2);
-        sc += __shfl_xor_sync(gmask, sc, 4);
-        const float mn = fmaxf(m[g], sc);
-        const float corr = exp2f(m[g] - mn);
-        const float p = exp2f(sc - mn);
-        m[g] = mn;
-        l[g] = l[g] * corr + p;
-#pragma unroll
-        for (int i = 0; i < EL; ++i) acc[g][i] = acc[g][i] * corr + p * vf[i];
+      for (int ks = 0; ks < KS; ++ks) {
+        const int c = 2 * ks + (lm_mi & 1);
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4(kb + r * ROWB + ((c ^ (r & 7)) << 4), b0, b1, b2, b3);
+        mma_bf16_16816(s0, qa[ks], b0, b1);
+        mma_bf16_16816(s1, qa[ks], b2, b3);
       }
     }
-    __syncthreads();  // the ring slot is free for the copy issued at the top of the next iteration
+    // row g: tokens tok0 + 2 tq + {0, 1} (s0) and tok0 + 8 + 2 tq + {0, 1} (s1)
+    const int tk = tok0 + 2 * tq;
+    float p00 = tk < c1 ? s0[0] * scale_log2 : -INFINITY;
+    float p01 = tk + 1 < c1 ? s0[1] * scale_log2 : -INFINITY;
+    float p10 = tk + 8 < c1 ? s1[0] * scale_log2 : -INFINITY;
+    float p11 = tk + 9 < c1 ? s1[1] * scale_log2 : -INFINITY;
+    float mx = fmaxf(fmaxf(p00, p01), fmaxf(p10, p11));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float mn = fmaxf(m, mx);                     // finite: token tok0 itself is always valid
+    const float corr = exp2f(m - mn);
+    p00 = exp2f(p00 - mn); p01 = exp2f(p01 - mn); p10 = exp2f(p10 - mn); p11 = exp2f(p11 - mn);
+    float ls = p00 + p01 + p10 + p11;
+    ls += __shfl_xor_sync(0xffffffffu, ls, 1);
+    ls += __shfl_xor_sync(0xffffffffu, ls, 2);
+    l = l * corr + ls;
+    m = mn;
+#pragma unroll
+    for (int i = 0; i < NT; ++i) { o[i][0] *= corr; o[i][1] *= corr; }
+    uint32_t pa[4] = {pack_bf16(p00, p01), 0u, pack_bf16(p10, p11), 0u};
+    {
+      const int r = (lm_mi & 1) * 8 + lm_r;
+#pragma unroll
+      for (int dp = 0; dp < NT / 2; ++dp) {
+        const int c = 2 * dp + (lm_mi >> 1);
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4_trans(vb + r * ROWB + ((c ^ (r & 7)) << 4), b0, b1, b2, b3);
+        mma_bf16_16816(o[2 * dp], pa, b0, b1);
+        mma_bf16_16816(o[2 * dp + 1], pa, b2, b3);
+      }
+    }
+    __syncwarp();   // every lane is done with this ring slot before it is refilled
   }
   cp_async_wait<0>();
   __syncthreads();
 
+  // merge the warps' partial states
+  float* s_acc = reinterpret_cast<float*>(s_dyn);   // [warps][GQ][HD]
+  if (g < GQ) {
+    if (tq == 0) { s_m[warp][g] = m; s_l[warp][g] = l; }
 #pragma unroll
-  for (int g = 0; g < GQ; ++g) {
-    if (sub == 0) { s_m[part][g] = m[g]; s_l[part][g] = l[g]; }
-#pragma unroll
-    for (int c = 0; c < CH; ++c)
-#pragma unroll
-      for (int i = 0; i < 8; ++i) s_acc[(part * GQ + g) * HD + (c * 8 + sub) * 8 + i] = acc[g][c * 8 + i];
+    for (int i = 0; i < NT; ++i) {
+      s_acc[(warp * GQ + g) * HD + i * 8 + 2 * tq] = o[i][0];
+      s_acc[(warp * GQ + g) * HD + i * 8 + 2 * tq + 1] = o[i][1];
+    }
   }
   __syncthreads();
-
-  for (int o = threadIdx.x; o < GQ * HD; o += kAttnThreads) {
-    const int g = o / HD, d = o % HD;
+  for (int idx = threadIdx.x; idx < GQ * HD; idx += kAttnThreads) {
+    const int gg = idx / HD, d = idx % HD;
     float M = -INFINITY;
 #pragma unroll
-    for (int p = 0; p < kAttnParts; ++p) M = fmaxf(M, s_m[p][g]);
+    for (int w = 0; w < kAttnWarps; ++w) M = fmaxf(M, s_m[w][gg]);
     float L = 0.f, O = 0.f;
     if (M > -INFINITY) {
 #pragma unroll
-      for (int p = 0; p < kAttnParts; ++p) {
-        const float w = exp2f(s_m[p][g] - M);
-        L += s_l[p][g] * w;
-        O += s_acc[(p * GQ + g) * HD + d] * w;
+      for (int w = 0; w < kAttnWarps; ++w) {
+        const float wgt = exp2f(s_m[w][gg] - M);
+        L += s_l[w][gg] * wgt;
+        O += s_acc[(w * GQ + gg) * HD + d] * wgt;
       }
     }
     const float val = L > 0.f ? O / L : 0.f;
-    const int head = hkv * GQ + g;
+    const int head = hkv * GQ + gg;
     if (splits == 1) {
       out[static_cast<long long>(t) * ld_out + head * HD + d] = __float2bfloat16(val);
     } else {
@@ -222,8 +268,8 @@ template <int HD, int GQ>
 static int launch_attn(const void* q, long long ld_q, const void* kc, const void* vc, const int* bt, int max_blocks,
                        const int* bt_row, const int* ctx_len, int block_size, int T, int n_kv, float scale, int splits,
                        void* out, long long ld_out, float* part_o, float* part_lse, cudaStream_t stream) {
-  const size_t merge_b = static_cast<size_t>(kAttnParts) * GQ * HD * sizeof(float);
-  const size_t ring_b = static_cast<size_t>(kAttnStages) * 2 * kAttnStageTok * HD * 2;
+  const size_t merge_b = static_cast<size_t>(kAttnWarps) * GQ * HD * sizeof(float);
+  const size_t ring_b = static_cast<size_t>(kAttnWarps) * kAttnStages * 2 * kAttnStageTok * HD * 2;
   const size_t smem = merge_b > ring_b ? merge_b : ring_b;
   static bool configured = false;
   if (!configured) {
