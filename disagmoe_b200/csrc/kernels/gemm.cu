@@ -22,6 +22,8 @@
 //
 // Reference behaviour covered: disagmoe/models/experts.py:81-96 (gmm -> silu*mul -> gmm),
 // disagmoe/models/linear.py:131-136 (F.linear), disagmoe/frontend/engine.py:731-734 (weight scale + un-permute).
+#include <string.h>
+
 #include "dmoe_kernels.h"
 #include "sm100.cuh"
 
@@ -626,4 +628,108 @@ extern "C" int dmoe_gemm(const DmoeGemm* d, void* stream_) {
   }
 #undef DMOE_LAUNCH
   return -15;
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// Allocation-free entry point (see dmoe_noalloc.h): the split-K scratch is a file-scope device array.
+#include <stdio.h>
+
+#include "dmoe_noalloc.h"
+
+constexpr long long kNoallocCounterBytes = DMOE_NOALLOC_MAX_TILES * 4ll;
+constexpr long long kNoallocBytes = DMOE_NOALLOC_WS_BYTES + kNoallocCounterBytes + 256;
+// layout: [partial tiles | tile counters | status word]
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoallocBytes];
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+unsigned char* g_noalloc_ptr[kMaxDevices] = {nullptr};   // device address of the array, per device
+char g_noalloc_error[256] = "";
+
+// In host code `g_noalloc_scratch` is only a handle of the symbol, not a device address: the address a kernel may
+// use has to be asked for, once per device, with that device current.
+int noalloc_setup(int dev, unsigned char** out) {
+  if (dev < 0 || dev >= kMaxDevices) return DMOE_NOALLOC_E_SETUP;
+  if (g_noalloc_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      snprintf(g_noalloc_error, sizeof(g_noalloc_error), "cudaGetSymbolAddress failed on device %d: %s", dev,
+               cudaGetErrorString(e));
+      return DMOE_NOALLOC_E_SETUP;
+    }
+    g_noalloc_ptr[dev] = static_cast<unsigned char*>(p);
+  }
+  *out = g_noalloc_ptr[dev];
+  return 0;
+}
+}  // namespace
+
+extern "C" const char* dmoe_noalloc_last_error(void) { return g_noalloc_error; }
+
+extern "C" int dmoe_linear_noalloc(const void* W, const void* X, void* Y, int T, int F, int K, long long ldx,
+                                   long long ldy, int bn, int splitk, void* stream_) {
+  g_noalloc_error[0] = 0;
+  if (W == nullptr || X == nullptr || Y == nullptr || T < 0 || F < 1 || K < 8 || K % 8 != 0) {
+    snprintf(g_noalloc_error, sizeof(g_noalloc_error), "bad argument (T=%d F=%d K=%d; K must be a multiple of 8)", T, F, K);
+    return DMOE_NOALLOC_E_BAD_ARG;
+  }
+  if (T == 0) return 0;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return DMOE_NOALLOC_E_SETUP;
+  unsigned char* base = nullptr;
+  const int rc = noalloc_setup(dev, &base);
+  if (rc != 0) return rc;
+  if (bn == 0) bn = dmoe_gemm_pick_bn(T, DMOE_EPI_PLAIN);
+  if (bn != 32 && bn != 64 && bn != 128 && bn != 256) {
+    snprintf(g_noalloc_error, sizeof(g_noalloc_error), "token tile %d is not one of 32/64/128/256", bn);
+    return DMOE_NOALLOC_E_BAD_ARG;
+  }
+  const int kblocks = (K + 63) / 64;
+  const long long tiles = static_cast<long long>((F + 127) / 128) * ((T + bn - 1) / bn);
+  if (splitk == 0) {
+    splitk = 1;
+    if (tiles < 74 && kblocks >= 8) {
+      splitk = static_cast<int>(148 / tiles);
+      if (splitk > kblocks / 4) splitk = kblocks / 4;
+      if (splitk > 16) splitk = 16;
+      if (splitk < 1) splitk = 1;
+    }
+  }
+  if (splitk > kblocks) splitk = kblocks;
+  const long long need = dmoe_gemm_workspace_bytes(T, F, bn, splitk);
+  if (need > DMOE_NOALLOC_WS_BYTES || (splitk > 1 && tiles > DMOE_NOALLOC_MAX_TILES)) {
+    snprintf(g_noalloc_error, sizeof(g_noalloc_error),
+             "problem too large for the built-in scratch: T=%d F=%d tile=%d splitk=%d needs %lld bytes of partial tiles "
+             "and %lld counters; the limits are %lld bytes and %d counters",
+             T, F, bn, splitk, need, tiles, static_cast<long long>(DMOE_NOALLOC_WS_BYTES), DMOE_NOALLOC_MAX_TILES);
+    return DMOE_NOALLOC_E_TOO_LARGE;
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  unsigned char* counters = base + DMOE_NOALLOC_WS_BYTES;
+  // the counters and the status word must start at zero; the array keeps whatever the previous call left behind
+  cudaError_t e = cudaMemsetAsync(counters, 0, static_cast<size_t>(kNoallocCounterBytes + 256), stream);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  DmoeGemm d;
+  memset(&d, 0, sizeof(d));
+  d.W = W; d.X = X; d.Y = Y;
+  d.ws = base; d.ws_bytes = DMOE_NOALLOC_WS_BYTES;
+  d.counters = reinterpret_cast<int*>(counters);
+  d.status = reinterpret_cast<int*>(counters + kNoallocCounterBytes);
+  d.ldx = ldx > 0 ? ldx : K;
+  d.ldy = ldy > 0 ? ldy : F;
+  d.G = 1; d.T = T; d.F = F; d.K = K;
+  d.epi = DMOE_EPI_PLAIN; d.bn = bn; d.splitk = splitk; d.y_f32 = 0;
+  return dmoe_gemm(&d, stream_);
+}
+
+extern "C" int dmoe_noalloc_last_status(int* status_out) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || status_out == nullptr) return DMOE_NOALLOC_E_SETUP;
+  unsigned char* base = nullptr;
+  const int rc = noalloc_setup(dev, &base);
+  if (rc != 0) return rc;
+  return static_cast<int>(cudaMemcpy(status_out, base + DMOE_NOALLOC_WS_BYTES + kNoallocCounterBytes, sizeof(int),
+                                     cudaMemcpyDeviceToHost));
 }
