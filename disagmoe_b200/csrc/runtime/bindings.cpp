@@ -399,6 +399,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("tokens_in_layer", &MuPool::tokens_in_layer);
   py::class_<MuAttentionPool, MuPool, std::shared_ptr<MuAttentionPool>>(m, "MuAttentionPool")
       .def("num_pending_tokens", &MuAttentionPool::num_pending_tokens)
+      .def("release_seqs", &MuAttentionPool::release_seqs)
+      .def("set_unordered_layer", &MuAttentionPool::set_unordered_layer)
       .def("fetch_attention_batch", &MuAttentionPool::fetch_attention_batch);
 
   py::class_<Scheduler, std::shared_ptr<Scheduler>>(m, "Scheduler")

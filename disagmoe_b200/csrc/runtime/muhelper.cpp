@@ -345,6 +345,13 @@ MuAttentionPool::MuAttentionPool(std::vector<int> layer_ids, int device_id, std:
       parts_needed_(std::move(parts_needed)) {
   partial_.resize(layer_ids_.size());
   ready_.resize(layer_ids_.size());
+  next_pos_.resize(layer_ids_.size());
+}
+
+void MuAttentionPool::release_seqs(const std::vector<int>& seq_ids) {
+  std::lock_guard<std::mutex> lk(batch_mu_);
+  for (auto& m : next_pos_)
+    for (int s : seq_ids) m.erase(s);
 }
 
 void MuAttentionPool::process_batch(torch::Tensor tensor, metadata_t meta, int kind) {
@@ -441,16 +448,32 @@ AttentionBatch MuAttentionPool::fetch_attention_batch() {
     local = layer_scheduler_->schedule();
     if (local < 0) return AttentionBatch{};
     auto& q = ready_[local];
-    // a batch holds either token-id rows (to be embedded) or hidden rows, never both
-    const bool ids_first = !q.empty() && q.front().token_id >= 0;
-    std::deque<TokenTopKInfo> rest;
-    while (!q.empty()) {
-      auto t = std::move(q.front());
-      q.pop_front();
-      if ((t.token_id >= 0) == ids_first && static_cast<int>(toks.size()) < max_batch_size_) toks.push_back(std::move(t));
-      else rest.push_back(std::move(t));
+    // a batch holds either token-id rows (to be embedded) or hidden rows, never both; prompt tokens are taken in
+    // position order per sequence, a token whose predecessors have not run at this layer yet stays queued
+    std::vector<TokenTopKInfo> all(std::make_move_iterator(q.begin()), std::make_move_iterator(q.end()));
+    q.clear();
+    std::stable_sort(all.begin(), all.end(), [](const TokenTopKInfo& a, const TokenTopKInfo& b) {
+      return std::make_pair(a.seq_id, a.position) < std::make_pair(b.seq_id, b.position);
+    });
+    bool have_kind = false, ids_kind = false;
+    auto& next = next_pos_[local];
+    for (auto& t : all) {
+      const bool is_ids = t.token_id >= 0;
+      bool ok = static_cast<int>(toks.size()) < max_batch_size_ && (!have_kind || is_ids == ids_kind);
+      if (ok && t.init_prefill_len >= 0 && !unordered_.count(local)) {
+        auto it = next.find(t.seq_id);
+        const int expect = it == next.end() ? 0 : it->second;
+        ok = t.position == expect;
+        if (ok) next[t.seq_id] = expect + 1;
+      }
+      if (ok) {
+        have_kind = true;
+        ids_kind = is_ids;
+        toks.push_back(std::move(t));
+      } else {
+        q.push_back(std::move(t));
+      }
     }
-    q = std::move(rest);
     if (!q.empty()) layer_scheduler_->add_tokens_to_layer(local, static_cast<int>(q.size()));
   }
   if (toks.empty()) return AttentionBatch{};

@@ -189,9 +189,17 @@ class MuAttentionPool : public MuPool {
   // The TP worker side: takes exactly the tokens (seq id, position) the driver scheduled for `layer_id`.
   AttentionBatch fetch_batch_from(int layer_id, const std::vector<std::pair<int, int>>& tokens, int timeout_ms = 30000);
   int num_pending_tokens();
+  // Forgets the per-sequence prefill progress of finished sequences.
+  void release_seqs(const std::vector<int>& seq_ids);
+  // A layer whose step has no dependency between the tokens of a prompt (the LM-head step) takes tokens in any order.
+  void set_unordered_layer(int layer_id) { unordered_.insert(local_layer(layer_id)); }
 
  private:
   AttentionBatch pack(int local_layer, std::vector<TokenTopKInfo>& toks);
+  // Causal order inside a prompt: prompt token i of a sequence may run at a layer only after tokens 0..i-1 ran there
+  // (their K/V must be in the cache). next_pos_[layer][seq] is the next prompt position that may be scheduled.
+  std::vector<std::map<int, int>> next_pos_;
+  std::set<int> unordered_;
   std::map<int, int> parts_needed_;
   // per local layer: incomplete tokens keyed by (seq, position); complete tokens in arrival order
   std::vector<std::map<std::pair<int, int>, TokenTopKInfo>> partial_;

@@ -1,0 +1,435 @@
+"""Cluster controller: spawns one worker process per device, wires them up from a ``ModelPlacement`` and drives
+requests through the tokenizer / sampler pair.
+
+Counterpart of disagmoe/frontend/controller.py:46-432 and ray_helper.py. Ray is replaced by plain processes
+(``multiprocessing`` spawn) with a pipe-based RPC: ``worker.call("method", *args)``. The tokenizer and the sampler are
+native objects living in the controller process. NCCL unique ids are minted per edge only when the workers are CUDA
+devices; CPU workers use the socket transport (the tensor bytes ride in the control message).
+"""
+from __future__ import annotations
+
+import asyncio
+import multiprocessing as mp
+import os
+import random
+import threading
+import time
+import traceback
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Tuple
+
+from .. import disagmoe_c as C
+from ..config import CacheConfig, ModelConfig, SamplingConfig
+from ..scheduler.dpscheduler import get_dp_scheduler
+from ..utils.constants import SAMPLER_DEV_ID, TOKENIZER_DEV_ID
+from ..utils.logger import get_logger
+from ..utils.placement import ModelPlacement
+from .datatypes import SloStat
+from .engine import Engine, InitCoreArgs, SamplerEngine, TokenizerEngine
+
+
+def _worker_main(conn, device_id: int, device: str, env: Dict[str, str]) -> None:
+    os.environ.update(env)
+    eng = Engine(device_id, device)
+    while True:
+        try:
+            msg = conn.recv()
+        except EOFError:
+            break
+        if msg is None:
+            break
+        method, args, kwargs = msg
+        try:
+            res = getattr(eng, method)(*args, **kwargs)
+            conn.send(("ok", res))
+        except Exception:
+            conn.send(("err", traceback.format_exc()))
+    try:
+        eng.terminate()
+    except Exception:
+        pass
+
+
+class WorkerHandle:
+    """RPC stub of one worker process."""
+
+    def __init__(self, device_id: int, device: str, env: Optional[Dict[str, str]] = None):
+        ctx = mp.get_context("spawn")
+        self.device_id = device_id
+        self.conn, child = ctx.Pipe()
+        self.proc = ctx.Process(target=_worker_main, args=(child, device_id, device, env or {}), daemon=True)
+        self.proc.start()
+        self.lock = threading.Lock()
+
+    def call_async(self, method: str, *args, **kwargs) -> None:
+        self.lock.acquire()
+        self.conn.send((method, args, kwargs))
+
+    def wait(self, timeout: float = 300.0):
+        try:
+            if not self.conn.poll(timeout):
+                raise TimeoutError(f"worker {self.device_id} did not answer within {timeout} s")
+            status, res = self.conn.recv()
+        finally:
+            self.lock.release()
+        if status != "ok":
+            raise RuntimeError(f"worker {self.device_id} failed:\n{res}")
+        return res
+
+    def call(self, method: str, *args, timeout: float = 300.0, **kwargs):
+        self.call_async(method, *args, **kwargs)
+        return self.wait(timeout)
+
+    def alive(self) -> bool:
+        return self.proc.is_alive()
+
+    def stop(self) -> None:
+        try:
+            with self.lock:
+                self.conn.send(None)
+        except Exception:
+            pass
+        self.proc.join(timeout=10)
+        if self.proc.is_alive():
+            self.proc.terminate()
+
+
+class LocalWorker:
+    """Same interface as ``WorkerHandle`` for an engine living in the controller process (single-process runs)."""
+
+    def __init__(self, device_id: int, device: str):
+        self.device_id = device_id
+        self.engine = Engine(device_id, device)
+        self._res = None
+
+    def call_async(self, method, *args, **kwargs):
+        self._res = getattr(self.engine, method)(*args, **kwargs)
+
+    def wait(self, timeout: float = 300.0):
+        return self._res
+
+    def call(self, method, *args, timeout: float = 300.0, **kwargs):
+        return getattr(self.engine, method)(*args, **kwargs)
+
+    def alive(self) -> bool:
+        return True
+
+    def stop(self) -> None:
+        self.engine.terminate()
+
+
+@dataclass
+class AsyncResult:
+    req_id: int
+    event: threading.Event
+    slo: Optional[SloStat] = None
+    tokens: Optional[List[int]] = None
+
+    def get(self, timeout: Optional[float] = None) -> SloStat:
+        if not self.event.wait(timeout):
+            raise TimeoutError(f"request {self.req_id} did not finish")
+        return self.slo
+
+
+class Controller:
+    def __init__(self, n_node: int, n_gpu_per_node: int, device: str = "cuda", in_process: bool = False,
+                 heartbeat_timeout_s: float = 30.0):
+        self.n_node, self.n_gpu_per_node = n_node, n_gpu_per_node
+        self.device_kind = device
+        self.in_process = in_process
+        self.workers: Dict[int, object] = {}
+        self.tokenizer: Optional[TokenizerEngine] = None
+        self.sampler: Optional[SamplerEngine] = None
+        self.placement: Optional[ModelPlacement] = None
+        self.model_config: Optional[ModelConfig] = None
+        self.req_counter = 0
+        self.results: Dict[int, AsyncResult] = {}
+        self.dp_scheduler = None
+        self.port_shift = random.randint(0, 400) * 16 * 4 % 6000
+        self.heartbeat_timeout_s = heartbeat_timeout_s
+        self.suspect_workers: List[int] = []
+        self._poll_thread: Optional[threading.Thread] = None
+        self._end = False
+        self._logger = get_logger("controller")
+        self._free_blocks: Dict[int, int] = {}
+        self._req_rank: Dict[int, int] = {}
+        self._lock = threading.Lock()
+
+    # ---- workers --------------------------------------------------------------------------------------------
+    def _device_of(self, device_id: int) -> str:
+        if self.device_kind == "cpu":
+            return "cpu"
+        return f"cuda:{device_id % self.n_gpu_per_node}"
+
+    def _create_engines(self, placement: ModelPlacement) -> None:
+        for d in placement.device_ids():
+            if self.in_process:
+                self.workers[d] = LocalWorker(d, self._device_of(d))
+            else:
+                self.workers[d] = WorkerHandle(d, self._device_of(d))
+
+    def _all(self, method: str, *args, **kwargs) -> Dict[int, object]:
+        for w in self.workers.values():
+            w.call_async(method, *args, **kwargs)
+        return {d: w.wait() for d, w in self.workers.items()}
+
+    def _get_nccl_ids(self, placement: ModelPlacement) -> Dict[Tuple[int, int], bytes]:
+        ids = {}
+        if self.device_kind != "cuda":
+            return ids
+        for src, outs in placement.out_device_ids.items():
+            for dst in outs:
+                if C.is_embedding_node(src) or C.is_embedding_node(dst) or src == dst:
+                    continue
+                ids[(src, dst)] = C.get_nccl_unique_id()
+        return ids
+
+    # ---- init -----------------------------------------------------------------------------------------------
+    def init_engine(self, placement: ModelPlacement, model_config: ModelConfig, cache_config: Optional[CacheConfig] = None,
+                    sampling_config: Optional[SamplingConfig] = None, state_dict_path: Optional[str] = None,
+                    keep_logits: bool = False, dtype=None, ignore_eos: bool = True) -> None:
+        self.placement, self.model_config = placement, model_config
+        cache_config = cache_config or CacheConfig()
+        sampling_config = sampling_config or SamplingConfig(1, 2)
+        L = model_config.num_layers
+        C.set_port_base(self.port_shift)
+        C.set_inproc_transport(self.in_process)
+        self._create_engines(placement)
+        nccl = self._get_nccl_ids(placement)
+        # who runs attention layer l for dp rank r (layer L = the LM-head step, hosted where layer 0 runs)
+        attn_peer: Dict[int, Dict[int, int]] = {}
+        for l in range(L):
+            for d in placement.attn_devices_of_layer(l):
+                if placement.is_worker_device(d):
+                    continue
+                attn_peer.setdefault(l, {})[placement.attn_dp_rank_at(d)] = d
+        attn_peer[L] = dict(attn_peer[0])
+        expert_ranks = [(l, e, r) for (l, e), r in placement.expert_ranks.items()]
+        hosts = {d: "127.0.0.1" for d in list(self.workers) + [TOKENIZER_DEV_ID, SAMPLER_DEV_ID]}
+        self._all("setup_engine", model_config, cache_config, dtype, self.in_process)
+        for d, w in self.workers.items():
+            outs = list(placement.out_device_ids.get(d, []))
+            ins = list(placement.in_device_ids.get(d, []))
+            if placement.has_attn(d):
+                # the residual stream goes to the attention worker of the next layer; the head step reports to the sampler
+                dp = placement.attn_dp_rank_at(d)
+                for l in placement.attn_layer_ids_at(d):
+                    nxt = attn_peer[l + 1].get(dp, next(iter(attn_peer[l + 1].values())))
+                    if nxt not in outs:
+                        outs.append(nxt)
+                if attn_peer[L].get(dp) == d and SAMPLER_DEV_ID not in outs:
+                    outs.append(SAMPLER_DEV_ID)
+            if placement.has_expert(d):
+                # experts of the last layer return to the LM-head step instead of the sampler
+                outs = [o for o in outs if o != SAMPLER_DEV_ID or placement.has_attn(d)]
+                for r, dev in attn_peer[L].items():
+                    if any(l == L - 1 for l, _ in placement.expert_ids_at(d)) and dev not in outs:
+                        outs.append(dev)
+            infos = []
+            for o in outs:
+                infos.append((list(placement.expert.get(o, [])), list(placement.attn.get(o, [])),
+                              placement.attn_dp_rank_at(o) if o in placement.attn else 0))
+            # every device that may send to d
+            senders = set(ins)
+            for s in self.workers:
+                if s == d:
+                    continue
+            args = InitCoreArgs(
+                layer_ids=placement.layer_ids_at(d), in_device_ids=[], out_device_ids=outs, out_channel_infos=infos,
+                in_nccl_ids={}, out_nccl_ids={o: nccl[(d, o)] for o in outs if (d, o) in nccl},
+                attn_peer=attn_peer, expert_ranks=expert_ranks,
+                local_attn_dp_rank=placement.attn_dp_rank_at(d) if d in placement.attn else 0,
+                expert_ids=list(placement.expert_ids_at(d)), hosts=hosts, port_shift=self.port_shift,
+                state_dict_path=state_dict_path, keep_logits=keep_logits)
+            self._pending_args = getattr(self, "_pending_args", {})
+            self._pending_args[d] = args
+        # in-edges are the transpose of the (extended) out-edges
+        for d, a in self._pending_args.items():
+            for o in a.out_device_ids:
+                if o in self._pending_args and d not in self._pending_args[o].in_device_ids:
+                    self._pending_args[o].in_device_ids.append(d)
+                    if (d, o) in nccl:
+                        self._pending_args[o].in_nccl_ids[d] = nccl[(d, o)]
+        # mailboxes are bound in init_core, NCCL communicators need both ends at once: run it on all workers together
+        for d, w in self.workers.items():
+            w.call_async("init_core", self._pending_args[d], placement)
+        for w in self.workers.values():
+            w.wait()
+        layer0 = attn_peer[0]
+        self.tokenizer = TokenizerEngine(TOKENIZER_DEV_ID, list(layer0.values()), layer0)
+        self.sampler = SamplerEngine(SAMPLER_DEV_ID, list(layer0.values()), layer0, sampling_config.min_output_len,
+                                     sampling_config.max_output_len, model_config.top_k, ignore_eos)
+        self.sampling_config = sampling_config
+        self.cache_config = cache_config
+        self.dp_size = len(layer0)
+        self._free_blocks = {r: self.workers[dev].call("num_free_blocks") for r, dev in layer0.items()}
+        self.attn_peer = attn_peer
+
+    def start_engine(self) -> None:
+        self._all("start")
+        self.tokenizer.start()
+        self.sampler.start()
+        self._end = False
+        self._poll_thread = threading.Thread(target=self._poll_loop, daemon=True, name="controller-poll")
+        self._poll_thread.start()
+
+    # ---- requests -------------------------------------------------------------------------------------------
+    def get_new_req_id(self) -> int:
+        self.req_counter += 1
+        return self.req_counter
+
+    def _pick_dp_rank(self, need_blocks: int) -> int:
+        # admission by free KV blocks (the "max" policy of the DP scheduler); waits while no replica has room
+        while True:
+            with self._lock:
+                r = max(self._free_blocks, key=lambda k: (self._free_blocks[k], -k))
+                if self._free_blocks[r] >= need_blocks:
+                    self._free_blocks[r] -= need_blocks
+                    return r
+            time.sleep(0.005)
+
+    def put_single_request(self, prompt, output_len: Optional[int] = None, req_id: Optional[int] = None) -> AsyncResult:
+        """``prompt`` is a list of token ids or an int (a prompt of that many pseudo-random ids)."""
+        cfg = self.model_config
+        if isinstance(prompt, int):
+            rnd = random.Random(self.req_counter + 1)
+            prompt = [rnd.randrange(3, cfg.vocab_size) for _ in range(prompt)]
+        rid = req_id if req_id is not None else self.get_new_req_id()
+        max_out = output_len if output_len is not None else self.sampling_config.max_output_len
+        need = (len(prompt) + max_out + self.cache_config.block_size - 1) // self.cache_config.block_size
+        rank = self._pick_dp_rank(need)
+        res = AsyncResult(rid, threading.Event())
+        with self._lock:
+            self.results[rid] = res
+            self._req_rank[rid] = (rank, need)
+        if output_len is not None:
+            self.sampler.set_request_output_len(rid, output_len)
+        self.tokenizer.put_single_request(rid, prompt, rank)
+        return res
+
+    def put_requests(self, prompts: List, output_lens: Optional[List[int]] = None) -> List[AsyncResult]:
+        return [self.put_single_request(p, None if output_lens is None else output_lens[i])
+                for i, p in enumerate(prompts)]
+
+    def _poll_loop(self) -> None:
+        last_beat = time.time()
+        while not self._end:
+            try:
+                self.process_finished_results(self.sampler.fetch_finished_results())
+            except Exception:
+                self._logger.error(traceback.format_exc())
+            if time.time() - last_beat > max(1.0, self.heartbeat_timeout_s / 3):
+                last_beat = time.time()
+                self.check_workers()
+            time.sleep(0.002)
+
+    def process_finished_results(self, stats) -> None:
+        if not stats:
+            return
+        done = [s.req_id for s in stats]
+        self.release_kv_cache(done)
+        for s in stats:
+            with self._lock:
+                res = self.results.get(s.req_id)
+                rank_need = self._req_rank.pop(s.req_id, None)
+                if rank_need is not None:
+                    self._free_blocks[rank_need[0]] += rank_need[1]
+            if res is not None:
+                res.slo = SloStat.from_c(s)
+                res.tokens = self.sampler.get_output_tokens(s.req_id)
+                res.event.set()
+
+    def release_kv_cache(self, req_ids: List[int]) -> None:
+        for d, w in self.workers.items():
+            if self.placement.has_attn(d):
+                w.call("release_seqs", req_ids)
+
+    def wait_for_requests(self, n_request: int, timeout: float = 600.0) -> Dict[int, SloStat]:
+        t0 = time.time()
+        while time.time() - t0 < timeout:
+            with self._lock:
+                done = {r: a.slo for r, a in self.results.items() if a.event.is_set()}
+            if len(done) >= n_request:
+                return done
+            err = self.first_worker_error()
+            if err:
+                raise RuntimeError(err)
+            time.sleep(0.01)
+        raise TimeoutError(f"{n_request} requests did not finish within {timeout} s")
+
+    # ---- failure detection ----------------------------------------------------------------------------------
+    def check_workers(self) -> List[int]:
+        """Marks workers whose process died (or whose RPC no longer answers) as suspect; returns their ids."""
+        bad = []
+        for d, w in self.workers.items():
+            if not w.alive():
+                bad.append(d)
+        for d in bad:
+            if d not in self.suspect_workers:
+                self.suspect_workers.append(d)
+                self._logger.error(f"worker {d} is not alive")
+        return bad
+
+    def first_worker_error(self) -> Optional[str]:
+        for d, w in self.workers.items():
+            if d in self.suspect_workers:
+                return f"worker {d} died"
+            if isinstance(w, LocalWorker):
+                e = w.engine.check_error()
+                if e:
+                    return e
+        return None
+
+    # ---- stats / control ------------------------------------------------------------------------------------
+    def fetch_step_stats(self):
+        return self._all("fetch_step_stats")
+
+    def fetch_logits(self) -> Dict[Tuple[int, int], object]:
+        out = {}
+        for d, w in self.workers.items():
+            if self.placement.has_attn(d):
+                out.update(w.call("fetch_logits"))
+        return out
+
+    def fetch_sampler_step_infos(self):
+        return self.sampler.fetch_sampler_step_infos()
+
+    def worker_errors(self) -> Dict[int, Optional[str]]:
+        return self._all("check_error")
+
+    def set_schedule_policy(self, policy: str) -> None:
+        self._all("set_schedule_policy", policy)
+
+    def set_schedule_block(self, step: int) -> None:
+        self._all("set_schedule_block", step)
+
+    def start_profile(self, profile_dir: Optional[str] = None) -> None:
+        self._all("start_profile", profile_dir)
+
+    def stop_profile(self) -> None:
+        self._all("stop_profile")
+
+    def reset(self) -> None:
+        self._all("reset")
+        self.sampler.reset()
+        with self._lock:
+            self.results.clear()
+
+    def stop_workers(self) -> None:
+        self._end = True
+        if self._poll_thread is not None:
+            self._poll_thread.join(timeout=5)
+        if self.tokenizer is not None:
+            self.tokenizer.terminate()
+        if self.sampler is not None:
+            self.sampler.terminate()
+        for w in self.workers.values():
+            try:
+                w.call("terminate", timeout=20)
+            except Exception:
+                pass
+            w.stop()
+
+
+def init_controller(n_node: int, n_gpu_per_node: int, device: str = "cuda", in_process: bool = False) -> Controller:
+    return Controller(n_node, n_gpu_per_node, device=device, in_process=in_process)

@@ -1,0 +1,480 @@
+"""Per-device worker: the host-scheduled, layer-by-layer engine of the disaggregated deployment.
+
+Every worker owns the native runtime of its role(s) -- receive pool, layer scheduler, dispatcher
+(:mod:`disagmoe_b200.disagmoe_c`) -- and a Python loop that asks the scheduler for the next layer's batch, runs the
+layer's module and hands the result to the dispatcher. Tokens flow asynchronously: there is no global step.
+
+    attention worker   batch = complete tokens of one layer (their partial rows: top-k expert outputs + the residual
+                       part). Sum + RMSNorm, attention, o_proj, router; the k routed copies go to the expert workers
+                       (sorted by expert), the residual stream goes to the attention worker of the next layer.
+                       Layer ``num_layers`` is the LM-head step: final norm, logits, greedy token -> sampler.
+    expert worker      batch = rows of one layer sorted by local expert; grouped SwiGLU FFN, router-weight scale,
+                       rows returned to the attention replica (dp rank) that owns each sequence.
+
+Counterpart of disagmoe/frontend/engine.py:47-1089 (Engine, SamplerEngine, TokenizerEngine). What is different on
+purpose: real model semantics (embedding, positions, prefill over all prompt tokens, residual stream, LM head), no
+busy-spinning on the scheduler (the loop blocks in a GIL-free native wait), clean shutdown, any device (CPU fp32 for
+the correctness configuration, CUDA bf16 with the sm_100a kernels).
+"""
+from __future__ import annotations
+
+import os
+import threading
+import time
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from .. import disagmoe_c as C
+from ..config import CacheConfig, ModelConfig
+from ..models import weights as W
+from ..models.attention import AttnMeta, MoEAttention
+from ..models.experts import MoEExperts
+from ..ops import functional as F
+from ..ops import gemm
+from ..utils.logger import get_logger
+from ..utils.metrics import Metric
+from ..utils.placement import ModelPlacement
+from ..utils.utils import StepInfo, Timer, nvtx_range, time_ms
+
+
+@dataclass
+class InitCoreArgs:
+    """Everything a worker needs to build its native runtime (the role of the argument list of
+    ``Engine.init_core`` at disagmoe/frontend/engine.py:180-269)."""
+    layer_ids: List[int]
+    in_device_ids: List[int]
+    out_device_ids: List[int]
+    out_channel_infos: List[Tuple[List[Tuple[int, int]], List[int], int]]
+    in_nccl_ids: Dict[int, bytes] = field(default_factory=dict)
+    out_nccl_ids: Dict[int, bytes] = field(default_factory=dict)
+    attn_peer: Dict[int, Dict[int, int]] = field(default_factory=dict)     # layer -> dp rank -> device
+    expert_ranks: List[Tuple[int, int, int]] = field(default_factory=list)
+    local_attn_dp_rank: int = 0
+    expert_ids: List[Tuple[int, int]] = field(default_factory=list)       # (layer, expert) run here
+    hosts: Dict[int, str] = field(default_factory=dict)
+    port_shift: int = 0
+    state_dict_path: Optional[str] = None
+    keep_logits: bool = False
+
+
+class Engine:
+    def __init__(self, device_id: int = 0, device: str = "cpu"):
+        self.device_id = device_id
+        self.device = torch.device(device)
+        self.model_config: Optional[ModelConfig] = None
+        self.cache_config: Optional[CacheConfig] = None
+        self.handles = None
+        self.attn_layers: Dict[int, MoEAttention] = {}
+        self.expert_layers: Dict[int, MoEExperts] = {}
+        self.block_mgr = None
+        self.kv_cache = None
+        self.loop_thread: Optional[threading.Thread] = None
+        self.end_flag = False
+        self.metric = Metric()
+        self.step_infos: List[StepInfo] = []
+        self.timer = Timer()
+        self.logits_log: Dict[Tuple[int, int], torch.Tensor] = {}
+        self._logger = get_logger(f"engine{device_id}")
+        self.error: Optional[str] = None
+        self._max_rows = 1024
+
+    # ---- set-up ---------------------------------------------------------------------------------------------
+    def set_hosts(self, pid_tag: int, hosts: Dict[int, str]) -> None:
+        C.set_hosts(pid_tag, hosts)
+
+    def setup_engine(self, model_config: ModelConfig, cache_config: CacheConfig, dtype: Optional[torch.dtype] = None,
+                     inproc: bool = False) -> None:
+        self.model_config, self.cache_config = model_config, cache_config
+        self.dtype = dtype or model_config.dtype
+        if self.device.type == "cuda":
+            torch.cuda.set_device(self.device)
+        C.set_inproc_transport(inproc)
+
+    def init_core(self, args: InitCoreArgs, placement: ModelPlacement) -> None:
+        cfg = self.model_config
+        L = cfg.num_layers
+        C.set_port_base(args.port_shift)
+        if args.hosts:
+            C.set_hosts(os.getpid(), args.hosts)
+        self.args = args
+        self.has_attn = placement.has_attn(self.device_id)
+        self.has_expert = placement.has_expert(self.device_id)
+        self.dp_rank = args.local_attn_dp_rank
+        ea = C.EngineArgs()
+        ea.local_id, ea.top_k = self.device_id, cfg.top_k
+        ea.has_attn, ea.has_expert = self.has_attn, self.has_expert
+        pc = C.ParallelConfig()
+        pc.tp, pc.ep, pc.dp, pc.n_exp_per_rank = cfg.tp_size, cfg.ep_size, cfg.dp_size, cfg.num_experts_per_rank
+        pc.expert_ranks = [tuple(t) for t in args.expert_ranks]
+        ea.cfg = pc
+        attn_layers = sorted(placement.attn_layer_ids_at(self.device_id)) if self.has_attn else []
+        self.hosts_head = self.has_attn and args.attn_peer.get(L, {}).get(self.dp_rank) == self.device_id
+        ea.attn_layer_ids = attn_layers + ([L] if self.hosts_head else [])
+        self.local_experts: Dict[int, List[int]] = {}
+        for l, e in args.expert_ids:
+            self.local_experts.setdefault(l, []).append(e)
+        ea.expert_layer_ids = sorted(self.local_experts)
+        ea.in_device_ids, ea.out_device_ids = args.in_device_ids, args.out_device_ids
+        ea.out_channel_infos = [C.ChannelInfo([tuple(x) for x in e], a, d) for e, a, d in args.out_channel_infos]
+        ea.in_nccl_ids, ea.out_nccl_ids = args.in_nccl_ids, args.out_nccl_ids
+        ea.attn_peer = args.attn_peer
+        parts = {}
+        for l in ea.attn_layer_ids:
+            if l == 0:
+                parts[l] = 0
+            else:
+                parts[l] = 1 if cfg.is_dense_layer(l - 1) else cfg.top_k + 1
+        ea.parts_needed = parts
+        ea.num_dp_groups = max(1, cfg.dp_size)
+        ea.device = str(self.device)
+        self.handles = C.init_engine_colocate(ea) if (self.has_attn and self.has_expert) else C.init_engine(ea)
+        if self.hosts_head:
+            self.handles.attn_pool.set_unordered_layer(L)
+        if self.has_attn:
+            self.handles.attn_scheduler.set_max_batch_size(cfg.max_batch_size_attn)
+        if self.has_expert:
+            self.handles.scheduler.set_max_batch_size(cfg.max_batch_size_expert)
+        self._build_executor(attn_layers)
+
+    def _build_executor(self, attn_layers: List[int]) -> None:
+        cfg, dev, dt = self.model_config, self.device, self.dtype
+        sd = None
+        if self.args.state_dict_path:
+            sd = W.load_state_dict(self.args.state_dict_path)
+        for l in attn_layers:
+            m = MoEAttention(cfg, l, device=dev, dtype=dt)
+            m.load_weights(sd) if sd is not None else m.init_weights()
+            self.attn_layers[l] = m
+        for l, experts in self.local_experts.items():
+            experts.sort()
+            assert experts == list(range(experts[0], experts[-1] + 1)), "a worker holds a contiguous expert range"
+            e = MoEExperts(cfg, l, experts[0], experts[-1] + 1, device=dev, dtype=dt,
+                           max_batch_size=cfg.max_batch_size_expert if dev.type == "cuda" else 0)
+            e.load_weights(sd) if sd is not None else e.init_weights()
+            self.expert_layers[l] = e
+        if self.has_attn:
+            names = ["embed_tokens.weight", "norm.weight", "lm_head.weight"]
+            g = sd if sd is not None else W.init_state_dict(cfg, dev, dt, names)
+            self.embed_w = g["embed_tokens.weight"].to(device=dev, dtype=dt).contiguous()
+            self.norm_w = g["norm.weight"].to(device=dev, dtype=dt)
+            self.lm_head_w = g["lm_head.weight"].to(device=dev, dtype=dt).contiguous()
+            cc = self.cache_config
+            nb = cc.num_gpu_blocks or 1024
+            self.block_size = cc.block_size
+            kvh = next(iter(self.attn_layers.values())).num_kv_heads if self.attn_layers else cfg.num_kv_heads
+            self.kv_cache = {l: torch.zeros(2, nb, cc.block_size, kvh, cfg.head_dim, dtype=dt, device=dev)
+                             for l in attn_layers}
+            self.block_mgr = C.BlockManager(cc.block_size, nb - cc.num_reserved_blocks, cc.num_reserved_blocks, 0)
+            self.max_blocks = (cfg.max_seq_len + cc.block_size - 1) // cc.block_size
+
+    # ---- loop -----------------------------------------------------------------------------------------------
+    def start(self) -> None:
+        C.start_engine(self.handles)
+        self.end_flag = False
+        self.loop_thread = threading.Thread(target=self._loop, daemon=True, name=f"engine-loop-{self.device_id}")
+        self.loop_thread.start()
+
+    def _loop(self) -> None:
+        C.recorder_create(f"engine@{self.device_id}")
+        try:
+            while not self.end_flag:
+                did = False
+                if self.has_attn:
+                    self.timer.start("schedule")
+                    b = self.handles.attn_scheduler.schedule()
+                    if b.metadata is not None:
+                        t_sched = self.timer.stop("schedule")
+                        self._timed_step(lambda: self.process_batch_attn(b), b.metadata.layer_id,
+                                         b.metadata.num_tokens(), t_sched, self.handles.attn_scheduler)
+                        did = True
+                if self.has_expert:
+                    self.timer.start("schedule")
+                    tb = self.handles.scheduler.schedule()
+                    if tb.metadata is not None:
+                        t_sched = self.timer.stop("schedule")
+                        self._timed_step(lambda: self.process_batch_expert(tb), tb.metadata.layer_id,
+                                         tb.metadata.num_tokens(), t_sched, self.handles.scheduler)
+                        did = True
+                if not did:
+                    # blocks without the GIL until tokens are queued (or 20 ms pass)
+                    if self.has_attn:
+                        self.handles.attn_scheduler.wait_for_new_requests(5 if self.has_expert else 20)
+                    if self.has_expert:
+                        self.handles.scheduler.wait_for_new_requests(5 if self.has_attn else 20)
+        except Exception as e:   # surfaced through check_error(); the worker stays up for diagnosis
+            import traceback
+            self.error = traceback.format_exc()
+            self._logger.error(self.error)
+
+    def _timed_step(self, fn, layer_id, n_tokens, t_sched, sched) -> None:
+        t0 = time_ms()
+        self.timer.start("step")
+        with nvtx_range("engine.step"):
+            fn()
+        t_step = self.timer.stop("step")
+        self.metric.step()
+        self.metric.update("t_schedule", t_sched)
+        self.metric.update("t_step", t_step)
+        self.metric.update("effective_tokens", n_tokens)
+        for name in ("preprocess", "execute", "postprocess"):
+            v = self.timer.get(name)
+            if v is not None:
+                self.metric.update("t_" + name, v)
+        if self.model_config.enable_trace:
+            snap = sched.get_pool_snapshot()
+            self.metric.update("queueing_tokens", float(sum(snap)))
+            self.step_infos.append(StepInfo(t0, time_ms(), n_tokens, layer_id, layer_id,
+                                            {i: v for i, v in enumerate(snap)}, threading.get_ident(), os.getpid()))
+
+    # ---- attention role -------------------------------------------------------------------------------------
+    def _attn_meta(self, m) -> AttnMeta:
+        """Block-table bookkeeping for the batch (every row grows its sequence so that its position has a slot) and
+        the device-side attention metadata."""
+        bm = self.block_mgr
+        seqs, pos = m.seq_ids, m.positions
+        rows_of: Dict[int, int] = {}
+        slots, bt_row = [], []
+        for s, p, plen in zip(seqs, pos, m.init_prefill_lens):
+            if not bm.has_seq_block_list(s):
+                bm.allocate(s, max(plen, p + 1))
+            bm.append_tokens(s, p, 1)
+        for s, p in zip(seqs, pos):
+            slots.append(bm.slot_of(s, p))
+            bt_row.append(rows_of.setdefault(s, len(rows_of)))
+        width = max(len(bm.get_seq_block_list(s)) for s in rows_of)
+        table = torch.zeros(len(rows_of), width, dtype=torch.int32)
+        for s, r in rows_of.items():
+            bl = bm.get_seq_block_list(s)
+            table[r, :len(bl)] = torch.tensor(bl, dtype=torch.int32)
+        dev = self.device
+        t = lambda x, dt=torch.int32: torch.tensor(x, dtype=dt).to(dev)
+        return AttnMeta(t(pos), t(slots, torch.int64), table.to(dev), t(bt_row), t([p + 1 for p in pos]),
+                        num_prefill_tokens=m.num_prefill_tokens, num_decode_tokens=m.num_decode_tokens,
+                        max_ctx=max(pos) + 1)
+
+    def process_batch_attn(self, batch) -> None:
+        cfg = self.model_config
+        m = batch.metadata
+        L = cfg.num_layers
+        layer = m.layer_id
+        n = m.num_tokens()
+        self.timer.start("preprocess")
+        if batch.data is None:
+            ids = torch.tensor(m.token_ids, dtype=torch.int32).to(self.device)
+            resid, parts = F.embed(ids, self.embed_w), None
+        else:
+            resid, parts = None, batch.data
+        if layer == L:
+            self.timer.stop("preprocess")
+            return self._head_step(m, parts)
+        meta = self._attn_meta(m)
+        self.timer.stop("preprocess")
+        self.timer.start("execute")
+        if resid is None:
+            # the first partial row doubles as the residual buffer that the layer updates in place
+            resid = parts[:, 0].contiguous()
+            parts = parts[:, 1:] if parts.shape[1] > 1 else None
+        out = self.attn_layers[layer].forward(resid, parts, (self.kv_cache[layer][0], self.kv_cache[layer][1]), meta)
+        self.timer.stop("execute")
+        self.timer.start("postprocess")
+        keep = list(range(n))
+        if layer == L - 1:
+            # only rows whose logits are needed go on: decode rows and the last token of every prompt
+            keep = [i for i in range(n) if m.init_prefill_lens[i] < 0 or m.positions[i] == m.init_prefill_lens[i] - 1]
+        base = m.to_metadata()
+        sel = base if len(keep) == n else base.at(keep)
+        idx = None if len(keep) == n else torch.tensor(keep, dtype=torch.long, device=self.device)
+        resid_rows = out.residual if idx is None else out.residual.index_select(0, idx)
+        k = cfg.top_k
+        dispatcher = self.handles.attn_dispatcher
+        if out.expert_input is not None and len(keep) > 0:
+            y = out.expert_input if idx is None else out.expert_input.index_select(0, idx)
+            ids_l = (out.topk_ids if idx is None else out.topk_ids.index_select(0, idx)).reshape(-1).tolist()
+            w_l = (out.topk_weights if idx is None else out.topk_weights.index_select(0, idx)).reshape(-1).tolist()
+            em = C.Metadata.deserialize(sel.serialize())
+            em.duplicate_topk(k)                      # token-major: row i*k + j is slot j of token i
+            em.exp_ids, em.topk_weights = ids_l, w_l
+            order = sorted(range(len(ids_l)), key=lambda i: ids_l[i])     # stable sort by expert id
+            em = em.at(order)
+            em.layer_id = layer
+            rows = y.index_select(0, torch.tensor([i // k for i in order], dtype=torch.long, device=self.device))
+            em.shape = [rows.shape[0], rows.shape[1]]
+            em.dtype = "fp32" if rows.dtype == torch.float32 else "bf16"
+            dispatcher.put(C.TensorBatch(rows.contiguous(), em), 0)
+        if len(keep) > 0:
+            rm = C.Metadata.deserialize(sel.serialize())
+            rm.layer_id = layer + 1
+            rm.exp_ids = [-1] * len(keep)
+            rm.topk_slots = [0 if out.expert_input is None else k] * len(keep)
+            rm.shape = [resid_rows.shape[0], resid_rows.shape[1]]
+            rm.dtype = "fp32" if resid_rows.dtype == torch.float32 else "bf16"
+            dispatcher.put(C.TensorBatch(resid_rows.contiguous(), rm), 1)
+        self.timer.stop("postprocess")
+
+    def _head_step(self, m, parts) -> None:
+        cfg = self.model_config
+        resid = parts[:, 0].contiguous()
+        rest = parts[:, 1:] if parts.shape[1] > 1 else None
+        _, h = F.add_rmsnorm(resid, rest, self.norm_w, cfg.rms_norm_eps, resid_out=resid)
+        logits = gemm.linear(h, self.lm_head_w, out_dtype=torch.float32)
+        ids = F.argmax(logits).tolist()
+        if self.args.keep_logits:
+            lc = logits.float().cpu()
+            for i, (s, p) in enumerate(zip(m.seq_ids, m.positions)):
+                self.logits_log[(s, p)] = lc[i]
+        sm = m.to_metadata()
+        sm.token_ids = ids
+        sm.shape = [len(ids), 0]
+        self.handles.attn_dispatcher.put(_id_batch(sm), 2)
+
+    # ---- expert role ----------------------------------------------------------------------------------------
+    def process_batch_expert(self, batch) -> None:
+        cfg = self.model_config
+        meta = batch.metadata
+        layer = meta.layer_id
+        self.timer.start("preprocess")
+        experts = self.local_experts[layer]
+        offs = torch.tensor(meta.get_expert_offsets(cfg.num_experts, experts), dtype=torch.int32).to(self.device)
+        n = meta.num_tokens()
+        self.timer.stop("preprocess")
+        self.timer.start("execute")
+        out = self.expert_layers[layer].forward(n, batch.data, offs)
+        w = torch.tensor(meta.topk_weights, dtype=torch.float32).to(self.device)
+        out = (out.float() * w[:, None]).to(out.dtype)
+        self.timer.stop("execute")
+        self.timer.start("postprocess")
+        mapping = meta.sort_by_prefill_order()      # rows grouped by the attention replica that owns them
+        inv = [0] * n
+        for old, new in enumerate(mapping):
+            inv[new] = old
+        out = out.index_select(0, torch.tensor(inv, dtype=torch.long, device=self.device))
+        meta.step_layer()
+        self.handles.expert_dispatcher.put(C.TensorBatch(out.contiguous(), meta), 0)
+        self.timer.stop("postprocess")
+
+    # ---- control --------------------------------------------------------------------------------------------
+    def release_seqs(self, seq_ids: List[int]) -> None:
+        if self.block_mgr is not None:
+            held = [s for s in seq_ids if self.block_mgr.has_seq_block_list(s)]
+            self.block_mgr.batch_release(held)
+            self.handles.attn_pool.release_seqs(seq_ids)
+
+    def num_free_blocks(self) -> int:
+        return self.block_mgr.num_free_blocks() if self.block_mgr is not None else 0
+
+    def fetch_step_stats(self):
+        infos, self.step_infos = self.step_infos, []
+        traces = {k: [(t.msg, t.t_start, t.t_dur, t.track_id) for t in v] for k, v in C.recorder_output().items()}
+        return infos, traces, self.metric
+
+    def fetch_logits(self) -> Dict[Tuple[int, int], torch.Tensor]:
+        out, self.logits_log = self.logits_log, {}
+        return out
+
+    def set_schedule_policy(self, policy: str) -> None:
+        if self.has_attn:
+            self.handles.attn_scheduler.set_schedule_policy(policy)
+        if self.has_expert:
+            self.handles.scheduler.set_schedule_policy(policy)
+
+    def set_schedule_block(self, step: int) -> None:
+        if self.has_attn:
+            self.handles.attn_scheduler.set_schedule_block(step)
+        if self.has_expert:
+            self.handles.scheduler.set_schedule_block(step)
+
+    def check_error(self) -> Optional[str]:
+        return self.error
+
+    def heartbeat(self) -> float:
+        return time.time()
+
+    def start_profile(self, profile_dir: Optional[str] = None) -> None:
+        C.recorder_enable(True)
+        self._torch_prof = None
+        if profile_dir:
+            acts = [torch.profiler.ProfilerActivity.CPU]
+            if self.device.type == "cuda":
+                acts.append(torch.profiler.ProfilerActivity.CUDA)
+            self._torch_prof = torch.profiler.profile(
+                activities=acts, on_trace_ready=torch.profiler.tensorboard_trace_handler(profile_dir))
+            self._torch_prof.start()
+
+    def stop_profile(self) -> None:
+        if getattr(self, "_torch_prof", None) is not None:
+            self._torch_prof.stop()
+            self._torch_prof = None
+
+    def reset(self) -> None:
+        self.metric = Metric()
+        self.step_infos = []
+
+    def terminate(self) -> None:
+        self.end_flag = True
+        if self.loop_thread is not None:
+            self.loop_thread.join(timeout=10)
+        if self.handles is not None:
+            C.stop_engine(self.handles)
+
+
+def _id_batch(meta):
+    b = C.TensorBatch()
+    b.metadata = meta
+    return b
+
+
+class TokenizerEngine:
+    """Front door: turns a request into one row per prompt token and hands it to the native ``Tokenizer``."""
+
+    def __init__(self, device_id: int, out_device_ids: List[int], attn_peer: Dict[int, int]):
+        self.tokenizer = C.init_tokenizer(device_id, out_device_ids, attn_peer)
+        self.t_submitted: Dict[int, float] = {}
+
+    def start(self) -> None:
+        self.tokenizer.start()
+
+    def put_single_request(self, req_id: int, prompt_ids: List[int], dp_rank: int) -> None:
+        self.t_submitted[req_id] = time.time()
+        self.tokenizer.put_request(req_id, list(prompt_ids), dp_rank)
+
+    def put_request(self, req_ids: List[int], prompts: List[List[int]], dp_ranks: List[int]) -> None:
+        for r, p, d in zip(req_ids, prompts, dp_ranks):
+            self.put_single_request(r, p, d)
+
+    def terminate(self) -> None:
+        self.tokenizer.terminate()
+
+
+class SamplerEngine:
+    """Bookkeeping end of the loop (output lengths, finish rule, SLO timestamps) around the native ``Sampler``."""
+
+    def __init__(self, device_id: int, out_device_ids: List[int], attn_peer: Dict[int, int], min_output_len: int,
+                 max_output_len: int, top_k: int = 1, ignore_eos: bool = True):
+        self.sampler = C.init_sampler(device_id, min_output_len, max_output_len, top_k, out_device_ids, attn_peer,
+                                      ignore_eos, False)
+
+    def start(self) -> None:
+        self.sampler.start_all()
+
+    def set_request_output_len(self, req_id: int, n: int) -> None:
+        self.sampler.set_request_output_len(req_id, n)
+
+    def fetch_finished_results(self):
+        return self.sampler.fetch_finished_slo_stats()
+
+    def fetch_sampler_step_infos(self):
+        return self.sampler.fetch_step_infos()
+
+    def get_output_tokens(self, req_id: int) -> List[int]:
+        return self.sampler.get_output_tokens(req_id)
+
+    def num_finished(self) -> int:
+        return self.sampler.num_finished()
+
+    def reset(self) -> None:
+        self.sampler.reset()
+
+    def terminate(self) -> None:
+        self.sampler.stop_all()
