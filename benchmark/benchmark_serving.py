@@ -1,0 +1,238 @@
+"""Open-loop serving benchmark (reference: benchmark/benchmark_serving.py).
+
+    python -m benchmark.benchmark_serving -r 8 -n 200 -i 1024 --min-input-len 128 -o 512 --min-output-len 64 -K 2 \
+        --backend colocated --model mixtral
+    python -m benchmark.benchmark_serving --device cpu --model tiny -g 2 --ep-size 1 --step-attn 1 -n 16 -r 50 ...
+
+Requests arrive by the chosen generator; every request is a prompt of random token ids and a fixed output length.
+Reported: duration, request and output-token throughput, request latency and inter-token latency (TPOT) mean /
+median / p99, time to first token; optional CSV row, sampler-throughput and TTFT CSVs, and a Chrome trace of the
+engine steps with the per-layer queue snapshot.
+"""
+from __future__ import annotations
+
+import gzip
+import json
+import os
+import pickle
+import sys
+import time
+from dataclasses import dataclass, asdict
+from typing import Dict, List, Optional
+
+import numpy as np
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from benchmark.utils import get_parser_base
+from benchmark.workload import Workload, get_generator
+from disagmoe_b200.config import CacheConfig, SamplingConfig, get_preset
+from disagmoe_b200.frontend.datatypes import SloStat
+from disagmoe_b200.utils.placement import ClusterConfig, get_model_placement
+
+
+@dataclass
+class BenchmarkMetrics:
+    e2e_duration: float = -1
+    req_throughput: float = -1
+    token_throughput: float = -1
+    req_latency_mean_ms: float = -1
+    req_latency_median_ms: float = -1
+    req_latency_p99_ms: float = -1
+    itl_latency_mean_ms: float = -1
+    itl_latency_median_ms: float = -1
+    itl_latency_p99_ms: float = -1
+    ttft_mean_ms: float = -1
+    ttft_p99_ms: float = -1
+
+    def __repr__(self):
+        return "Metrics:\n" + "\n".join(f"  {k}: {v:.2f}" for k, v in asdict(self).items())
+
+    def write_to_file(self, args) -> None:
+        import pandas as pd
+        row = {"num_requests": args.num_requests, "rate": args.rate, "DP_size": args.dp_size, "EP_size": args.ep_size,
+               "num_experts": args.num_experts, **{k: round(v, 3) for k, v in asdict(self).items()}}
+        os.makedirs(os.path.dirname(os.path.abspath(args.file)) or ".", exist_ok=True)
+        df = pd.read_csv(args.file) if os.path.exists(args.file) else pd.DataFrame(columns=list(row))
+        df.loc[len(df)] = row
+        df.to_csv(args.file, index=False)
+
+
+def analyze_results(results: List[SloStat], arrivals: Dict[int, float], duration: float) -> BenchmarkMetrics:
+    """``results`` carry absolute timestamps (seconds); ``arrivals`` maps request id -> submission time."""
+    lat, itl, ttft, total = [], [], [], 0
+    for r in results:
+        total += len(r.t_tokens)
+        t0 = arrivals.get(r.req_id, r.t_prefill)
+        lat.append(r.t_decode - t0)
+        ttft.append(r.t_prefill - t0)
+        itl.extend(np.diff(r.t_tokens).tolist())
+    if not itl:
+        itl = [0.0]
+    ms = 1000.0
+    return BenchmarkMetrics(
+        e2e_duration=duration, req_throughput=len(results) / duration, token_throughput=total / duration,
+        req_latency_mean_ms=float(np.mean(lat)) * ms, req_latency_median_ms=float(np.median(lat)) * ms,
+        req_latency_p99_ms=float(np.percentile(lat, 99)) * ms,
+        itl_latency_mean_ms=float(np.mean(itl)) * ms, itl_latency_median_ms=float(np.median(itl)) * ms,
+        itl_latency_p99_ms=float(np.percentile(itl, 99)) * ms,
+        ttft_mean_ms=float(np.mean(ttft)) * ms, ttft_p99_ms=float(np.percentile(ttft, 99)) * ms)
+
+
+def model_config_from_args(args):
+    cfg = get_preset(args.model)
+    if args.model in ("mixtral", "duo"):
+        cfg = cfg.clone(num_layers=args.num_layers, num_experts=args.num_experts, top_k=args.topk)
+    return cfg.clone(ep_size=args.ep_size, tp_size=args.tp_size, dp_size=args.dp_size,
+                     enable_cuda_graph_attn=args.cuda_graph_attn, enable_grouped_gemm=not args.serial_gemm,
+                     graph_stride=args.graph_stride, max_batch_size_attn=args.max_batch_size_attn,
+                     max_batch_size_expert=args.max_batch_size_expert, enable_trace=args.trace)
+
+
+def make_workload(args) -> Workload:
+    Gen = get_generator(args.generator_type if args.rate > 0 else "offline")
+    gen = Gen(max(args.rate, 1e-9), 1.0, args.min_input_len, args.max_input_len, args.seed, args.min_output_len,
+              args.max_output_len)
+    return gen.generate_duration(args.duration) if args.duration > 0 else gen.generate_num(args.num_requests)
+
+
+def launch(args):
+    """Builds the placement and the controller, starts every worker (reference: benchmark_serving.py:88-131)."""
+    from disagmoe_b200.frontend.controller import init_controller
+    cfg = model_config_from_args(args)
+    cluster = ClusterConfig(n_node=args.num_nodes, n_gpu=args.num_gpus)
+    if args.placement == "pipeline":
+        place = get_model_placement(cfg, cluster, "pipeline", args.step_attn, args.step_expert, args.zigzag_attn)
+    else:
+        place = get_model_placement(cfg, cluster, args.placement)
+    master = init_controller(args.num_nodes, args.num_gpus, device=args.device)
+    master.init_engine(place, cfg, CacheConfig(block_size=args.block_size, gpu_memory_utilization=args.gpu_usage,
+                                               num_gpu_blocks=args.num_blocks or 4096),
+                       SamplingConfig(args.min_output_len, args.max_output_len))
+    master.start_engine()
+    if args.layer_scheduler_type != "mbfs":
+        master.set_schedule_policy(args.layer_scheduler_type)
+    if args.layer_scheduler_step > 1:
+        master.set_schedule_block(args.layer_scheduler_step)
+    return master, cfg
+
+
+def run_benchmark_controller(master, cfg, wl: Workload, args):
+    rng = np.random.default_rng(args.seed)
+    t0 = time.time()
+    results, arrivals = [], {}
+    for i, (arrival, in_len) in enumerate(wl):
+        now = time.time() - t0
+        if arrival > now:
+            time.sleep(arrival - now)
+        prompt = rng.integers(3, cfg.vocab_size, in_len).tolist()
+        out_len = wl.output_lens[i] if wl.output_lens else args.max_output_len
+        res = master.put_single_request(prompt, output_len=out_len)
+        arrivals[res.req_id] = time.time()
+        results.append(res)
+    stats = [r.get(timeout=3600) for r in results]
+    return stats, arrivals, time.time() - t0
+
+
+def run_benchmark_colocated(cfg, wl: Workload, args):
+    """One GPU, fused executor: the driver loop admits arrived requests and steps the engine."""
+    import torch
+    from disagmoe_b200.frontend.colocated import ColocatedEngine
+    eng = ColocatedEngine(cfg, CacheConfig(block_size=args.block_size, gpu_memory_utilization=args.gpu_usage,
+                                           num_gpu_blocks=args.num_blocks), device=args.device,
+                          max_batch_size=args.max_batch_size_attn,
+                          max_prefill_tokens=max(args.max_input_len, args.max_batch_size_attn, 2048),
+                          enable_cuda_graph=args.cuda_graph_attn,
+                          dtype=torch.float32 if args.device == "cpu" else None)
+    if args.cuda_graph_attn:
+        eng.executor.capture()
+    rng = np.random.default_rng(args.seed)
+    t0 = time.time()
+    nxt, arrivals = 0, {}
+    while nxt < len(wl) or eng.has_unfinished():
+        now = time.time() - t0
+        while nxt < len(wl) and wl.arrivals[nxt] <= now:
+            out_len = wl.output_lens[nxt] if wl.output_lens else args.max_output_len
+            eng.add_request(nxt, rng.integers(3, cfg.vocab_size, wl.input_lens[nxt]).tolist(), out_len)
+            arrivals[nxt] = time.time()
+            nxt += 1
+        if eng.has_unfinished():
+            eng.step()
+        elif nxt < len(wl):
+            time.sleep(max(0.0, min(0.001, wl.arrivals[nxt] - now)))
+    stats = [SloStat(r, s.t_tokens[0], s.t_arrival, s.t_tokens[-1], s.t_tokens) for r, s in eng.finished.items()]
+    return stats, arrivals, time.time() - t0
+
+
+def generate_step_trace(step_stats, path_prefix: str) -> None:
+    """Chrome trace (one pid per worker; each engine step is an event carrying the per-layer queue snapshot), the
+    running metrics, and the queue-length history (reference: benchmark_serving.py:187-259)."""
+    events, metrics, queues = [], {}, {}
+    for pid, (infos, traces, metric) in step_stats.items():
+        metrics[pid] = asdict(metric) if hasattr(metric, "__dataclass_fields__") else metric
+        queues[pid] = [(s.start_timestamp_ms, s.pool_snapshot) for s in infos]
+        for s in infos:
+            events.append({"name": f"layer {s.layer_id}, batch {s.batch_size}", "cat": "step", "ph": "X",
+                           "ts": s.start_timestamp_ms * 1e3, "dur": (s.end_timestamp_ms - s.start_timestamp_ms) * 1e3,
+                           "pid": pid, "tid": 0, "args": {"pool": s.pool_snapshot}})
+        for tname, ranges in traces.items():
+            for msg, t_start, t_dur, track in ranges:
+                events.append({"name": msg, "cat": "native", "ph": "X", "ts": t_start * 1e3, "dur": t_dur * 1e3,
+                               "pid": pid, "tid": f"{tname}/{track}"})
+    os.makedirs(os.path.dirname(os.path.abspath(path_prefix)) or ".", exist_ok=True)
+    with gzip.open(path_prefix + "trace.json.gz", "wt") as f:
+        json.dump(events, f)
+    with open(path_prefix + "trace_metrics.json", "w") as f:
+        json.dump(metrics, f, indent=1)
+    with open(path_prefix + "queue_length.pkl", "wb") as f:
+        pickle.dump(queues, f)
+
+
+def write_ttft_and_throughput(stats: List[SloStat], arrivals, sampler_steps, prefix: str) -> None:
+    import pandas as pd
+    os.makedirs(os.path.dirname(os.path.abspath(prefix)) or ".", exist_ok=True)
+    pd.DataFrame({"req_id": [s.req_id for s in stats],
+                  "ttft_ms": [(s.t_prefill - arrivals.get(s.req_id, s.t_prefill)) * 1e3 for s in stats]}
+                 ).to_csv(prefix + "ttft.csv", index=False)
+    if sampler_steps:
+        pd.DataFrame({"time_stamp": [s.time_stamp for s in sampler_steps],
+                      "num_tokens": [s.num_tokens for s in sampler_steps]}).to_csv(prefix + "sampler_step.csv", index=False)
+
+
+def main(argv=None):
+    args = get_parser_base().parse_args(argv)
+    np.random.seed(args.seed)
+    wl = make_workload(args)
+    prefix = os.path.join(os.path.dirname(os.path.abspath(args.file)), "")
+    try:
+        if args.backend == "colocated":
+            cfg = model_config_from_args(args)
+            stats, arrivals, dur = run_benchmark_colocated(cfg, wl, args)
+            sampler_steps = []
+        else:
+            master, cfg = launch(args)
+            try:
+                if args.profile_dir or args.trace:
+                    master.start_profile(args.profile_dir)
+                stats, arrivals, dur = run_benchmark_controller(master, cfg, wl, args)
+                from disagmoe_b200.frontend.datatypes import SamplerStepInfo
+                sampler_steps = [SamplerStepInfo.from_c(s) for s in master.fetch_sampler_step_infos()]
+                if args.trace:
+                    generate_step_trace(master.fetch_step_stats(), prefix)
+                if args.profile_dir:
+                    master.stop_profile()
+            finally:
+                master.stop_workers()
+        metrics = analyze_results(stats, arrivals, dur)
+        if args.analyze_throughput:
+            write_ttft_and_throughput(stats, arrivals, sampler_steps, prefix)
+    except Exception as e:   # a failed run still leaves a row, as the reference does
+        print("benchmark failed:", repr(e))
+        metrics = BenchmarkMetrics()
+    print(metrics)
+    metrics.write_to_file(args)
+    return metrics
+
+
+if __name__ == "__main__":
+    main()

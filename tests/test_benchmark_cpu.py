@@ -1,0 +1,43 @@
+"""Benchmark harness on CPU: workload generators, metric analysis, an end-to-end tiny serving run with trace output."""
+import os
+
+import numpy as np
+
+from benchmark.benchmark_serving import analyze_results, main
+from benchmark.workload import get_generator
+from disagmoe_b200.frontend.datatypes import SloStat
+
+
+def test_generators():
+    for name in ("uniform", "poisson", "offline", "incremental_poisson"):
+        g = get_generator(name)(10.0, 1.0, 5, 9, seed=1, min_output_len=2, max_output_len=4)
+        wl = g.generate_num(50)
+        assert len(wl) == 50 and all(5 <= l < 9 for l in wl.input_lens) and all(2 <= o < 4 for o in wl.output_lens)
+        assert all(b >= a for a, b in zip(wl.arrivals, wl.arrivals[1:]))
+    p = get_generator("poisson")(20.0, 1.0, 1, 2, seed=0).generate_num(4000)
+    assert abs(np.mean(np.diff(p.arrivals)) - 0.05) < 0.005
+    assert get_generator("uniform")(4.0, 1.0, 1, 2).generate_duration(10).arrivals[-1] == 39 / 4.0
+
+
+def test_analyze_results():
+    stats = [SloStat(0, 1.0, 0.5, 2.0, [1.0, 1.5, 2.0]), SloStat(1, 1.2, 0.6, 1.6, [1.2, 1.4, 1.6])]
+    m = analyze_results(stats, {0: 0.5, 1: 0.6}, duration=2.0)
+    assert m.req_throughput == 1.0 and m.token_throughput == 3.0
+    assert abs(m.req_latency_mean_ms - 1250) < 1e-6 and abs(m.itl_latency_median_ms - 350) < 1e-6
+    assert abs(m.ttft_mean_ms - 550) < 1e-6
+
+
+def test_end_to_end_tiny_cpu(tmp_path):
+    out = tmp_path / "bench.csv"
+    m = main(["--device", "cpu", "--model", "tiny", "-g", "2", "--ep-size", "1", "--step-attn", "1", "--step-expert", "1",
+              "-n", "6", "-r", "200", "--min-input-len", "4", "-i", "9", "--min-output-len", "3", "-o", "5", "-K", "2",
+              "--trace", "--analyze-throughput", "-f", str(out), "--num-blocks", "128"])
+    assert m.token_throughput > 0 and m.itl_latency_p99_ms >= 0
+    assert out.exists() and (tmp_path / "trace.json.gz").exists() and (tmp_path / "ttft.csv").exists()
+
+
+def test_colocated_backend_cpu(tmp_path):
+    m = main(["--device", "cpu", "--model", "tiny", "--backend", "colocated", "-n", "5", "-r", "0", "--min-input-len", "4",
+              "-i", "8", "--min-output-len", "2", "-o", "4", "-f", str(tmp_path / "b.csv"), "--num-blocks", "64",
+              "--max-batch-size-attn", "4"])
+    assert m.req_throughput > 0
