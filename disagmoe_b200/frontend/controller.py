@@ -159,14 +159,19 @@ class Controller:
     def _device_of(self, device_id: int) -> str:
         if self.device_kind == "cpu":
             return "cpu"
-        return f"cuda:{device_id % self.n_gpu_per_node}"
+        # a worker process sees exactly one GPU (CUDA_VISIBLE_DEVICES), so every native helper thread is on the right
+        # device without a cudaSetDevice of its own -- the arrangement the reference gets from Ray
+        return f"cuda:{device_id % self.n_gpu_per_node}" if self.in_process else "cuda:0"
 
     def _create_engines(self, placement: ModelPlacement) -> None:
         for d in placement.device_ids():
             if self.in_process:
                 self.workers[d] = LocalWorker(d, self._device_of(d))
             else:
-                self.workers[d] = WorkerHandle(d, self._device_of(d))
+                env = {}
+                if self.device_kind == "cuda":
+                    env["CUDA_VISIBLE_DEVICES"] = str(d % self.n_gpu_per_node)
+                self.workers[d] = WorkerHandle(d, self._device_of(d), env)
 
     def _all(self, method: str, *args, **kwargs) -> Dict[int, object]:
         for w in self.workers.values():

@@ -1,0 +1,43 @@
+"""Reference-style data path on real GPUs: host-scheduled workers in separate processes, NCCL p2p per edge
+(native NcclChannel), bf16 kernels. Needs 2 GPUs; skipped otherwise."""
+import os
+import tempfile
+
+import pytest
+import torch
+
+from disagmoe_b200.config import CacheConfig, SamplingConfig, tiny_config
+from disagmoe_b200.models.oracle import OracleModel
+from disagmoe_b200.models.weights import init_state_dict, save_state_dict
+from disagmoe_b200.utils.placement import ClusterConfig, get_model_placement
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_two_gpu_workers_over_nccl_channels():
+    from disagmoe_b200.frontend.controller import init_controller
+    cfg = tiny_config.clone(ep_size=1, dtype=torch.bfloat16)
+    sd = {k: v.to(torch.bfloat16) for k, v in init_state_dict(cfg, dtype=torch.float32).items()}
+    path = os.path.join(tempfile.mkdtemp(), "tiny_bf16.pt")
+    save_state_dict(sd, path)
+    place = get_model_placement(cfg, ClusterConfig(1, 2), "pipeline", 1, 1)
+    ctl = init_controller(1, 2, device="cuda")
+    try:
+        ctl.init_engine(place, cfg, CacheConfig(block_size=16, num_gpu_blocks=256), SamplingConfig(4, 5),
+                        state_dict_path=path, keep_logits=True)
+        ctl.start_engine()
+        g = torch.Generator().manual_seed(0)
+        prompts = [torch.randint(0, cfg.vocab_size, (12,), generator=g).tolist() for _ in range(4)]
+        res = [ctl.put_single_request(p, output_len=4) for p in prompts]
+        ctl.wait_for_requests(4, timeout=120)
+        logits = ctl.fetch_logits()
+        oracle = OracleModel(cfg, {k: v.float() for k, v in sd.items()})
+        for r, p in zip(res, prompts):
+            ref = oracle.forward(r.req_id, p)[-1]
+            got = logits[(r.req_id, 11)]
+            assert (got - ref).abs().max() / ref.abs().max() < 0.06
+            assert len(r.tokens) == 4
+        assert not [e for e in ctl.worker_errors().values() if e]
+    finally:
+        ctl.stop_workers()
