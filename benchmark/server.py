@@ -1,0 +1,84 @@
+"""HTTP front end for interactive experiments (reference: benchmark/server.py:21-91, Flask there, FastAPI here).
+
+    python -m benchmark.server --device cpu --model tiny -g 2 --ep-size 1 --step-attn 1 --port 6699
+
+POST /run_once     {"rate": 10, "time": 10, "distribution": "poisson"}  runs one open-loop workload, returns its metrics
+POST /set_schedule {"policy": "mbflfs", "step": 8}                     switches the layer-scheduling policy / block size
+                                                                       of every worker at run time
+GET  /health       worker liveness
+"""
+from __future__ import annotations
+
+import copy
+import os
+import sys
+from dataclasses import asdict
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from benchmark.benchmark_serving import analyze_results, launch, make_workload, run_benchmark_controller
+from benchmark.utils import get_parser_base
+
+POLICIES = ("mbfs", "flfs", "mbflfs", "mbtfs", "bin")
+
+
+def create_app(args):
+    from fastapi import FastAPI, HTTPException
+    app = FastAPI(title="disagmoe_b200 benchmark server")
+    state = {"master": None, "cfg": None, "args": args}
+
+    @app.on_event("startup")
+    def _startup():
+        state["master"], state["cfg"] = launch(args)
+
+    @app.on_event("shutdown")
+    def _shutdown():
+        if state["master"] is not None:
+            state["master"].stop_workers()
+
+    @app.post("/run_once")
+    def run_once(body: dict):
+        try:
+            rate, secs = float(body.get("rate", 10)), float(body.get("time", 10))
+            dist_name = str(body.get("distribution", "poisson"))
+        except (TypeError, ValueError):
+            raise HTTPException(400, "rate and time must be numbers")
+        a = copy.copy(state["args"])
+        a.rate, a.num_requests, a.generator_type, a.duration = rate, int(rate * secs), dist_name, 0
+        wl = make_workload(a)
+        stats, arrivals, dur = run_benchmark_controller(state["master"], state["cfg"], wl, a)
+        return asdict(analyze_results(stats, arrivals, dur))
+
+    @app.post("/set_schedule")
+    def set_schedule(body: dict):
+        policy, step = body.get("policy"), body.get("step")
+        if policy is None and step is None:
+            raise HTTPException(400, "missing parameter: policy or step")
+        if policy is not None:
+            if policy not in POLICIES:
+                raise HTTPException(400, f"invalid policy {policy!r}; one of {POLICIES}")
+            state["master"].set_schedule_policy(policy)
+            state["args"].layer_scheduler_type = policy
+        if step is not None:
+            state["master"].set_schedule_block(int(step))
+            state["args"].layer_scheduler_step = int(step)
+        return {"ok": True}
+
+    @app.get("/health")
+    def health():
+        m = state["master"]
+        return {"suspect_workers": m.check_workers() if m else [], "workers": len(m.workers) if m else 0}
+
+    return app
+
+
+def main():
+    p = get_parser_base()
+    p.add_argument("--port", type=int, default=6699)
+    args = p.parse_args()
+    import uvicorn
+    uvicorn.run(create_app(args), host="127.0.0.1", port=args.port, log_level="warning")
+
+
+if __name__ == "__main__":
+    main()
