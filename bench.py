@@ -101,6 +101,7 @@ def main():
     ap.add_argument("--ctx-max", type=int, default=1536)
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (the result is then marked invalid)")
     ap.add_argument("--model", default="mixtral")
+    ap.add_argument("--attn-tp", type=int, default=1, help="tensor-parallel degree of the attention GPUs (N >= 4)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -127,7 +128,7 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
         from disagmoe_b200.parallel.disagg import DisaggDecodeBench
-        runner = DisaggDecodeBench(cfg, world, rank, local_rank, B, args.ctx_min, args.ctx_max, K + W, g)
+        runner = DisaggDecodeBench(cfg, world, rank, local_rank, B, args.ctx_min, args.ctx_max, K + W, g, tp=args.attn_tp)
         parallelism = runner.parallelism
     else:
         from disagmoe_b200.frontend.colocated import ColocatedEngine

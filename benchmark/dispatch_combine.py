@@ -78,7 +78,8 @@ class FusedAttnSide:
             _vp(y), c_ll(y.stride(0)), _vp(ids), _vp(w), c_int(S.batch), c_int(cfg.top_k), c_int(cfg.hidden_size),
             c_int(cfg.num_experts), c_int(S.experts_per_rank), c_int(S.n_expert), c_int(self.a), c_int(S.region_cap),
             _vp(self.ws), _vp(self.tables[0]), c_ll(cfg.hidden_size), _vp(self.tables[1]), _vp(self.tables[2]),
-            _vp(self.tables[3]), _vp(self.disp_epoch), _vp(self.status), c_vp(_lib.stream_ptr())), "dispatch_remote")
+            _vp(self.tables[3]), _vp(self.disp_epoch), _vp(self.status), c_int(0), c_int(S.batch), c_vp(_lib.stream_ptr())),
+            "dispatch_remote")
         _lib.check(_lib.lib().dmoe_wait_flags(_vp(self.comb_flag), c_int(S.n_expert), _vp(self.wait_epoch),
                                               _vp(self.status), c_vp(_lib.stream_ptr())), "wait_flags")
         F.add_rmsnorm(self.x, self.parts, self.norm_w, 1e-5, resid_out=self.out, y=self.y)

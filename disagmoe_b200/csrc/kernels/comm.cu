@@ -42,6 +42,7 @@ struct DispatchRemoteArgs {
   const int* topk_ids;          // [T, K]
   const float* topk_w;          // [T, K]
   int T, K, H, E, experts_per_rank, n_dst, my_rank, region_cap;
+  int tok_lo, tok_hi;           // this rank dispatches tokens [tok_lo, tok_hi) (a TP rank sends its slice only)
   int* ws;                      // [counts E | cursor E | ticket]
   void* const* x_bases;         // [n_dst] receive-row buffers on the destinations ([n_src * region_cap, H] bf16)
   long long ld_dst;
@@ -68,8 +69,8 @@ __global__ void __launch_bounds__(256) dispatch_remote_kernel(const DispatchRemo
   __syncthreads();
   const int nvec = a.H / 8;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-  const int npairs = a.T * a.K;
-  for (int p = blockIdx.x * nw + warp; p < npairs; p += gridDim.x * nw) {
+  const int npairs = a.tok_hi * a.K;
+  for (int p = a.tok_lo * a.K + blockIdx.x * nw + warp; p < npairs; p += gridDim.x * nw) {
     const int e = a.topk_ids[p];
     if (e < 0 || e >= a.E) {
       if (lane == 0 && a.status != nullptr) atomicCAS(a.status, kStatusOk, kStatusBadIndex);
@@ -146,7 +147,7 @@ extern "C" int dmoe_dispatch_remote(const void* y, long long ld_y, const int* to
                                     int K, int H, int E, int experts_per_rank, int n_dst, int my_rank, int region_cap,
                                     int* ws, const void* x_bases, long long ld_dst, const void* rec_bases,
                                     const void* cnt_bases, const void* flag_bases, int* epoch, int* status,
-                                    void* stream) {
+                                    int tok_lo, int tok_hi, void* stream) {
   if (H % 8 != 0 || E > kMaxExpertsComm || experts_per_rank < 1 || n_dst < 1 || n_dst > kMaxRanksComm ||
       n_dst * experts_per_rank != E || epoch == nullptr)
     return -10;
@@ -156,7 +157,10 @@ extern "C" int dmoe_dispatch_remote(const void* y, long long ld_y, const int* to
   a.region_cap = region_cap; a.ws = ws; a.x_bases = static_cast<void* const*>(x_bases); a.ld_dst = ld_dst;
   a.rec_bases = static_cast<void* const*>(rec_bases); a.cnt_bases = static_cast<int* const*>(cnt_bases);
   a.flag_bases = static_cast<int* const*>(flag_bases); a.epoch = epoch; a.status = status;
-  const int npairs = T * K;
+  if (tok_hi <= 0 || tok_hi > T) tok_hi = T;
+  if (tok_lo < 0 || tok_lo > tok_hi) tok_lo = 0;
+  a.tok_lo = tok_lo; a.tok_hi = tok_hi;
+  const int npairs = (tok_hi - tok_lo) * K;
   int grid = (npairs + 7) / 8;
   if (grid > 148 * 2) grid = 148 * 2;
   if (grid < 1) grid = 1;   // an empty batch still publishes zero counts and its flag

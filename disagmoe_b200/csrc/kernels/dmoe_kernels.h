@@ -31,7 +31,8 @@ typedef struct DmoeGemm {
   int* signal_epoch;
   int* done_ticket;     // one zero-initialised int of scratch (required with wait_flags or signal_ptrs)
   long long ldx, ldy, ldr, ws_bytes;
-  int S, seg_cap, n_wait, n_signal, signal_slot, pad0;
+  int S, seg_cap, n_wait, n_signal, signal_slot;
+  int fanout;           // combine: every row is stored to the `fanout` consecutive ranks of the sender's TP group (0/1 = one)
   int G, T, F, K;
   int epi;            // DMOE_EPI_*
   int bn;             // token tile: 32/64/128/256, 0 = pick from T/G
@@ -69,6 +70,10 @@ int dmoe_paged_attention(const void* q, long long ld_q, const void* kcache, cons
 int dmoe_route(const void* x, long long ld_x, const void* norm_w, float eps, const void* gate_w, int T, int H, int E,
                int K, int renorm, void* y, long long ld_y, int* topk_ids, float* topk_w, float* logits_out, int* counts,
                void* stream);
+int dmoe_route_ex(const void* x, long long ld_x, const void* norm_w, float eps, const void* gate_w, int T, int H, int E,
+                  int K, int renorm, void* y, long long ld_y, int* topk_ids, float* topk_w, int* counts,
+                  const void* add_ptrs, int n_add, long long ld_add, void* resid_out, long long ld_resid, int count_lo,
+                  int count_hi, void* stream);
 // Sort-by-expert copy of the routed rows plus their 16-byte records; ws = ints [counts E | cursor E | ticket].
 int dmoe_dispatch_local(const void* y, long long ld_y, const int* topk_ids, const float* topk_w, int T, int K, int H,
                         int E, int experts_per_rank, int my_rank, int* ws, int* offs, const void* x_bases,
@@ -82,7 +87,7 @@ int dmoe_dispatch_local(const void* y, long long ld_y, const int* topk_ids, cons
 int dmoe_dispatch_remote(const void* y, long long ld_y, const int* topk_ids, const float* topk_w, int T, int K, int H,
                          int E, int experts_per_rank, int n_dst, int my_rank, int region_cap, int* ws,
                          const void* x_bases, long long ld_dst, const void* rec_bases, const void* cnt_bases,
-                         const void* flag_bases, int* epoch, int* status, void* stream);
+                         const void* flag_bases, int* epoch, int* status, int tok_lo, int tok_hi, void* stream);
 // Waits (bounded) until flags[i] >= *epoch + 1 for i < n, then advances *epoch.
 int dmoe_wait_flags(const int* flags, int n, int* epoch, int* status, void* stream);
 int dmoe_enable_peer_access(int peer_device);

@@ -70,6 +70,7 @@ struct GemmArgs {
   int signal_slot;
   int* signal_epoch;
   int* done_ticket;
+  int fanout;   // combine: destinations per row (TP group size of the senders)
 };
 
 template <int BN, int EPI>
@@ -405,8 +406,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
             if (j >= jmax) break;
             const int4 rec = __ldg(&a.recs[tok_base + c * 32 + j]);
             if (rec.y < 0) continue;
-            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(a.bases[rec.x]) + static_cast<long long>(rec.y) * a.ldy;
-            dst[f] = __float2bfloat16(acc[j] * __int_as_float(rec.z));
+            const __nv_bfloat16 val = __float2bfloat16(acc[j] * __int_as_float(rec.z));
+            if (a.fanout <= 1) {
+              (reinterpret_cast<__nv_bfloat16*>(a.bases[rec.x]) + static_cast<long long>(rec.y) * a.ldy)[f] = val;
+            } else {
+              // tensor-parallel senders: every member of the sender's TP group keeps the full residual stream
+              const int g0 = rec.x / a.fanout * a.fanout;
+              for (int i = 0; i < a.fanout; ++i)
+                (reinterpret_cast<__nv_bfloat16*>(a.bases[g0 + i]) + static_cast<long long>(rec.y) * a.ldy)[f] = val;
+            }
           }
         } else {
           if (a.R != nullptr) {
@@ -587,6 +595,7 @@ extern "C" int dmoe_gemm(const DmoeGemm* d, void* stream_) {
   a.wait_flags = d->wait_flags; a.n_wait = d->n_wait; a.wait_epoch = d->wait_epoch;
   a.signal_ptrs = reinterpret_cast<int* const*>(d->signal_ptrs); a.n_signal = d->n_signal;
   a.signal_slot = d->signal_slot; a.signal_epoch = d->signal_epoch; a.done_ticket = d->done_ticket;
+  a.fanout = d->fanout;
   if (a.S > 0 && (a.seg_cnt == nullptr || a.S * a.G > kMaxSeg || a.S * a.seg_cap > d->T)) return -16;
   if (a.S == 0 && a.G > kMaxSeg) return -16;
   if ((a.n_wait > 0 || a.n_signal > 0) && a.done_ticket == nullptr) return -17;

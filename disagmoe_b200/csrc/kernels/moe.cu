@@ -35,7 +35,8 @@ __global__ void __launch_bounds__(kRouteThreads)
 route_kernel(const __nv_bfloat16* __restrict__ x, long long ld_x, const __nv_bfloat16* __restrict__ norm_w, float eps,
              const __nv_bfloat16* __restrict__ gate_w, int H, int E, int K, int renorm,
              __nv_bfloat16* __restrict__ y, long long ld_y, int* __restrict__ topk_ids, float* __restrict__ topk_w,
-             float* __restrict__ logits_out, int* __restrict__ counts) {
+             float* __restrict__ logits_out, int* __restrict__ counts, const void* const* __restrict__ add_ptrs, int n_add,
+             long long ld_add, __nv_bfloat16* __restrict__ resid_out, long long ld_resid, int count_lo, int count_hi) {
   extern __shared__ float srow[];            // [H] normalised row (fp32, as rounded to bf16)
   __shared__ float red[32];
   __shared__ float slog[kMaxExperts];
@@ -55,8 +56,31 @@ route_kernel(const __nv_bfloat16* __restrict__ x, long long ld_x, const __nv_bfl
         const float2 f = __bfloat1622float2(p.v[j]);
         xr[i][2 * j] = f.x;
         xr[i][2 * j + 1] = f.y;
-        ss += f.x * f.x + f.y * f.y;
       }
+      // tensor-parallel attention: the o_proj partial sums of all TP ranks (peer memory) are reduced here, so the
+      // all-reduce costs no kernel of its own
+      for (int a = 0; a < n_add; ++a) {
+        const bf16x8m q = *reinterpret_cast<const bf16x8m*>(static_cast<const __nv_bfloat16*>(add_ptrs[a]) + t * ld_add + v * 8);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(q.v[j]);
+          xr[i][2 * j] += f.x;
+          xr[i][2 * j + 1] += f.y;
+        }
+      }
+      if (n_add > 0) {
+        bf16x8m r;   // the residual stream is stored in bf16: round once, and normalise what is stored
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          r.v[j] = __floats2bfloat162_rn(xr[i][2 * j], xr[i][2 * j + 1]);
+          const float2 f = __bfloat1622float2(r.v[j]);
+          xr[i][2 * j] = f.x;
+          xr[i][2 * j + 1] = f.y;
+        }
+        if (resid_out != nullptr) *reinterpret_cast<bf16x8m*>(resid_out + t * ld_resid + v * 8) = r;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += xr[i][j] * xr[i][j];
     }
   }
   float inv = 1.f;
@@ -150,7 +174,7 @@ route_kernel(const __nv_bfloat16* __restrict__ x, long long ld_x, const __nv_bfl
       for (int k = 0; k < K; ++k) {
         topk_ids[t * K + k] = isel[k];
         topk_w[t * K + k] = renorm ? wsel[k] / wtot : wsel[k];
-        if (counts != nullptr) atomicAdd(&counts[isel[k]], 1);
+        if (counts != nullptr && t >= count_lo && t < count_hi) atomicAdd(&counts[isel[k]], 1);
       }
     }
   }
@@ -250,7 +274,25 @@ extern "C" int dmoe_route(const void* x, long long ld_x, const void* norm_w, flo
   route_kernel<<<T, kRouteThreads, H * sizeof(float), static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), ld_x, static_cast<const __nv_bfloat16*>(norm_w), eps,
       static_cast<const __nv_bfloat16*>(gate_w), H, E, K, renorm, static_cast<__nv_bfloat16*>(y), ld_y, topk_ids, topk_w,
-      logits_out, counts);
+      logits_out, counts, nullptr, 0, 0, nullptr, 0, 0, T);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Same router with the tensor-parallel reduction folded in: x + sum of n_add partial rows (device array of pointers,
+// typically the TP peers' o_proj outputs) is written to resid_out and normalised; only tokens in [count_lo, count_hi)
+// enter the expert histogram (the slice this rank dispatches).
+extern "C" int dmoe_route_ex(const void* x, long long ld_x, const void* norm_w, float eps, const void* gate_w, int T,
+                             int H, int E, int K, int renorm, void* y, long long ld_y, int* topk_ids, float* topk_w,
+                             int* counts, const void* add_ptrs, int n_add, long long ld_add, void* resid_out,
+                             long long ld_resid, int count_lo, int count_hi, void* stream) {
+  if (H % 8 != 0 || H > kRouteThreads * kRouteMaxVec * 8 || E > kMaxExperts || K > kMaxTopK || K > E) return -10;
+  if (T == 0) return 0;
+  cudaFuncSetAttribute(route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 8192 * 4);
+  route_kernel<<<T, kRouteThreads, H * sizeof(float), static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), ld_x, static_cast<const __nv_bfloat16*>(norm_w), eps,
+      static_cast<const __nv_bfloat16*>(gate_w), H, E, K, renorm, static_cast<__nv_bfloat16*>(y), ld_y, topk_ids, topk_w,
+      nullptr, counts, static_cast<const void* const*>(add_ptrs), n_add, ld_add, static_cast<__nv_bfloat16*>(resid_out),
+      ld_resid, count_lo, count_hi);
   return static_cast<int>(cudaGetLastError());
 }
 

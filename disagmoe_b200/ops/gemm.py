@@ -87,17 +87,19 @@ class GemmComm:
     """
 
     def __init__(self, seg_cnt=None, S=0, seg_cap=0, wait_flags=None, n_wait=0, wait_epoch=None, signal_ptrs=None,
-                 n_signal=0, signal_slot=0, signal_epoch=None, done_ticket=None):
+                 n_signal=0, signal_slot=0, signal_epoch=None, done_ticket=None, fanout=0):
         self.seg_cnt, self.S, self.seg_cap = seg_cnt, S, seg_cap
         self.wait_flags, self.n_wait, self.wait_epoch = wait_flags, n_wait, wait_epoch
         self.signal_ptrs, self.n_signal, self.signal_slot = signal_ptrs, n_signal, signal_slot
         self.signal_epoch, self.done_ticket = signal_epoch, done_ticket
+        self.fanout = fanout
 
     def fill(self, d):
         d.seg_cnt, d.S, d.seg_cap = _lib.ptr(self.seg_cnt), self.S, self.seg_cap
         d.wait_flags, d.n_wait, d.wait_epoch = _lib.ptr(self.wait_flags), self.n_wait, _lib.ptr(self.wait_epoch)
         d.signal_ptrs, d.n_signal, d.signal_slot = _lib.ptr(self.signal_ptrs), self.n_signal, self.signal_slot
         d.signal_epoch, d.done_ticket = _lib.ptr(self.signal_epoch), _lib.ptr(self.done_ticket)
+        d.fanout = self.fanout
 
 
 def _launch(W, X, Y, R, offs, recs, bases, G, T, F, K, epi, bn, splitk, ldy, y_f32, comm: Optional[GemmComm] = None):
@@ -127,7 +129,7 @@ def _check_x(x):
 
 def linear(x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor] = None,
            out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None, bn: int = 0,
-           splitk: int = 0) -> torch.Tensor:
+           splitk: int = 0, comm: Optional["GemmComm"] = None) -> torch.Tensor:
     """y[T, F] = x[T, K] @ w[F, K].T (+ residual[T, F])."""
     T, K = x.shape
     F = w.shape[0]
@@ -151,7 +153,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor] = 
     bn = bn or pick_bn(T, EPI_PLAIN)
     splitk = splitk or pick_splitk(T, F, K, bn)
     _launch(w, x, out, residual, None, None, None, 1, T, F, K, EPI_PLAIN, bn, splitk, out.stride(0),
-            out.dtype == torch.float32)
+            out.dtype == torch.float32, comm)
     return out
 
 

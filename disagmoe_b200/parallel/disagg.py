@@ -53,6 +53,7 @@ class DisaggShape:
     top_k: int
     hidden: int
     num_experts: int
+    tp: int = 1         # attention tensor-parallel degree: consecutive groups of `tp` attention ranks share sequences
 
     @property
     def experts_per_rank(self) -> int:
@@ -60,7 +61,7 @@ class DisaggShape:
 
     @property
     def region_cap(self) -> int:   # rows one attention rank can send to one expert rank in one launch
-        return self.batch * self.top_k
+        return (self.batch // self.tp) * self.top_k
 
 
 def build_layout(s: DisaggShape) -> ArenaLayout:
@@ -73,6 +74,9 @@ def build_layout(s: DisaggShape) -> ArenaLayout:
         L.add(f"disp_flag{m}", s.n_attn * 4)
         L.add(f"parts{m}", s.batch * s.top_k * s.hidden * 2)
         L.add(f"comb_flag{m}", s.n_expert * 4)
+        if s.tp > 1:
+            L.add(f"opart{m}", s.batch * s.hidden * 2)     # this rank's o_proj partial sums, read by its TP peers
+            L.add(f"oflag{m}", s.tp * 4)
     return L
 
 
@@ -85,9 +89,13 @@ class AttentionRank:
         dev = device or arena.local.device
         self.device = dev
         dt = torch.bfloat16
+        self.tp = shape.tp
+        self.tp_rank = attn_rank % shape.tp
+        self.group0 = attn_rank // shape.tp * shape.tp      # first attention rank of this TP group
+        assert shape.batch % shape.tp == 0
         self.layers: List[MoEAttention] = []
         for l in range(cfg.num_layers):
-            m = MoEAttention(cfg, l, device=dev, dtype=dt)
+            m = MoEAttention(cfg, l, tp_size=self.tp, tp_rank=self.tp_rank, device=dev, dtype=dt)
             m.load_weights(state_dict) if state_dict is not None else m.init_weights()
             self.layers.append(m)
         names = ["embed_tokens.weight", "norm.weight", "lm_head.weight"]
@@ -117,6 +125,16 @@ class AttentionRank:
                 cnt_bases=arena.ptr_table(expert_ranks, layout.offset(f"recv_cnt{m}")),
                 flag_bases=arena.ptr_table(expert_ranks, layout.offset(f"disp_flag{m}")),
             )
+            if self.tp > 1:
+                group = [self.group0 + i for i in range(self.tp)]
+                d.update(
+                    opart=arena.view(layout.offset(f"opart{m}"), (B, H), dt),
+                    oflag=arena.view(layout.offset(f"oflag{m}"), (self.tp,), torch.int32),
+                    opart_ptrs=arena.ptr_table(group, layout.offset(f"opart{m}")),
+                    oflag_ptrs=arena.ptr_table(group, layout.offset(f"oflag{m}")),
+                    o_signal_epoch=z(1), o_wait_epoch=z(1), o_ticket=z(1),
+                    y=torch.zeros(B, H, dtype=dt, device=dev), topk_ids=z(B, k),
+                    topk_w=torch.zeros(B, k, dtype=torch.float32, device=dev))
             self.mb.append(d)
         self.status = gemm.scratch(dev).status
 
@@ -131,6 +149,12 @@ class AttentionRank:
 
     def layer(self, l: int, m: int) -> None:
         """Attention half of layer l for micro-batch m, ending with the peer-memory dispatch."""
+        self.layer_attn(l, m)
+        self.layer_route_dispatch(l, m)
+
+    def layer_attn(self, l: int, m: int) -> None:
+        """[wait for the experts' combine] add + RMSNorm, QKV, RoPE / KV append, paged attention, o_proj. With tensor
+        parallelism the o_proj partial sum goes to this rank's peer-visible buffer and the GEMM signals the TP peers."""
         d, S, cfg = self.mb[m], self.shape, self.cfg
         parts = None
         if l > 0:
@@ -138,15 +162,50 @@ class AttentionRank:
                                                   _vp(self.status), c_vp(_lib.stream_ptr())), "dmoe_wait_flags")
             parts = d["parts"]
         a = self.layers[l]
-        a.counts = d["ws"][:S.num_experts]
-        resid2 = a.attention(d["resid"], parts, (self.kv_cache[l, 0], self.kv_cache[l, 1]), self._meta(m))
-        y, ids, w, _ = a.route(resid2)
+        kv = (self.kv_cache[l, 0], self.kv_cache[l, 1])
+        if self.tp == 1:
+            d["resid2"] = a.attention(d["resid"], parts, kv, self._meta(m))
+            return
+        meta = self._meta(m)
+        resid, h = F.add_rmsnorm(d["resid"], parts, a.pre_ln, cfg.rms_norm_eps, resid_out=d["resid"])
+        qkv = gemm.linear(h, a.qkv_w)
+        F.rope_kv_append(qkv, meta.positions, meta.slots, kv[0], kv[1], a.num_heads, a.num_kv_heads, a.head_dim,
+                         cfg.rope_theta)
+        attn = F.paged_attention(qkv[:, :a.q_size], kv[0], kv[1], meta.block_tables, meta.bt_row, meta.ctx_len,
+                                 a.num_heads, a.num_kv_heads, a.head_dim,
+                                 splits=F.pick_attn_splits(S.batch, a.num_kv_heads, cfg.max_seq_len, self.block_size))
+        sig = gemm.GemmComm(signal_ptrs=d["oflag_ptrs"], n_signal=self.tp, signal_slot=self.tp_rank,
+                            signal_epoch=d["o_signal_epoch"], done_ticket=d["o_ticket"])
+        gemm.linear(attn, a.o_w, out=d["opart"], comm=sig)
+
+    def layer_route_dispatch(self, l: int, m: int) -> None:
+        """Post-attention RMSNorm + router + dispatch. With tensor parallelism the router kernel first sums the TP
+        ranks' o_proj partials straight out of their memory (the all-reduce), and this rank dispatches only its
+        slice of the tokens."""
+        d, S, cfg = self.mb[m], self.shape, self.cfg
+        a = self.layers[l]
+        lo, hi = 0, S.batch
+        if self.tp == 1:
+            a.counts = d["ws"][:S.num_experts]
+            y, ids, w, _ = a.route(d["resid2"])
+        else:
+            _lib.check(_lib.lib().dmoe_wait_flags(_vp(d["oflag"]), c_int(self.tp), _vp(d["o_wait_epoch"]),
+                                                  _vp(self.status), c_vp(_lib.stream_ptr())), "dmoe_wait_flags")
+            per = S.batch // self.tp
+            lo, hi = self.tp_rank * per, (self.tp_rank + 1) * per
+            y, ids, w = d["y"], d["topk_ids"], d["topk_w"]
+            _lib.check(_lib.lib().dmoe_route_ex(
+                _vp(d["resid"]), c_ll(S.hidden), _vp(a.post_ln), ctypes.c_float(cfg.rms_norm_eps), _vp(a.gate_w),
+                c_int(S.batch), c_int(S.hidden), c_int(S.num_experts), c_int(S.top_k), c_int(int(cfg.norm_topk_prob)),
+                _vp(y), c_ll(S.hidden), _vp(ids), _vp(w), _vp(d["ws"]), _vp(d["opart_ptrs"]), c_int(self.tp),
+                c_ll(S.hidden), _vp(d["resid"]), c_ll(S.hidden), c_int(lo), c_int(hi), c_vp(_lib.stream_ptr())),
+                "dmoe_route_ex")
         _lib.check(_lib.lib().dmoe_dispatch_remote(
             _vp(y), c_ll(y.stride(0)), _vp(ids), _vp(w), c_int(S.batch), c_int(S.top_k), c_int(S.hidden),
             c_int(S.num_experts), c_int(S.experts_per_rank), c_int(S.n_expert), c_int(self.a), c_int(S.region_cap),
             _vp(d["ws"]), _vp(d["x_bases"]), c_ll(S.hidden), _vp(d["rec_bases"]), _vp(d["cnt_bases"]),
-            _vp(d["flag_bases"]), _vp(d["disp_epoch"]), _vp(self.status), c_vp(_lib.stream_ptr())),
-            "dmoe_dispatch_remote")
+            _vp(d["flag_bases"]), _vp(d["disp_epoch"]), _vp(self.status), c_int(lo), c_int(hi),
+            c_vp(_lib.stream_ptr())), "dmoe_dispatch_remote")
 
     def head(self, m: int) -> None:
         d, S, cfg = self.mb[m], self.shape, self.cfg
@@ -208,7 +267,7 @@ class ExpertRank:
         gemm.grouped_swiglu(d["rows"], e.w13_weight, None, out=self.act, bn=self.bn, comm=gate)
         sig = gemm.GemmComm(seg_cnt=d["cnt"], S=S.n_attn, seg_cap=S.region_cap, signal_ptrs=d["signal_ptrs"],
                             n_signal=S.n_attn, signal_slot=self.x, signal_epoch=d["signal_epoch"],
-                            done_ticket=self.ticket)
+                            done_ticket=self.ticket, fanout=S.tp)
         gemm.grouped_combine(self.act, e.w2_weight, None, d["recs"], d["parts_bases"], S.hidden, bn=self.bn, comm=sig)
 
     def iteration(self) -> None:
@@ -221,19 +280,24 @@ class DisaggDecodeBench:
     """Decode-throughput runner used by ``bench.py`` for N >= 2 GPUs (one process per GPU, NCCL only for bootstrap)."""
 
     def __init__(self, cfg: ModelConfig, world: int, rank: int, local_rank: int, batch: int, ctx_min: int, ctx_max: int,
-                 total_steps: int, gen: torch.Generator, n_mb: int = 2):
+                 total_steps: int, gen: torch.Generator, n_mb: int = 2, tp: int = 1):
         import torch.distributed as dist
         assert world % 2 == 0, "needs an even number of GPUs: half attention, half experts"
         A = X = world // 2
-        assert cfg.num_experts % X == 0
+        assert cfg.num_experts % X == 0 and A % tp == 0
         self.cfg, self.world, self.rank = cfg, world, rank
-        self.shape = DisaggShape(A, X, n_mb, batch, cfg.top_k, cfg.hidden_size, cfg.num_experts)
+        # a TP group of `tp` attention GPUs serves tp x batch sequences per micro-batch (per-GPU load stays `batch`)
+        batch = batch * tp
+        self.shape = DisaggShape(A, X, n_mb, batch, cfg.top_k, cfg.hidden_size, cfg.num_experts, tp)
+        self.tp = tp
+        if tp > 1 and rank < A:
+            gen = torch.Generator().manual_seed(4321 + rank // tp)    # every member of a TP group sees the same requests
         self.layout = build_layout(self.shape)
         self.device = torch.device("cuda", local_rank)
         self.arena = PeerArena.create(self.layout.size, device=self.device)
         self.is_attn = rank < A
-        self.parallelism = f"attn dp{A} x {n_mb} micro-batches + expert ep{X} ({cfg.num_experts // X} experts/GPU), " \
-                           f"fused peer-memory dispatch/combine"
+        self.parallelism = f"attn dp{A // tp}" + (f" x tp{tp}" if tp > 1 else "") + \
+            f" x {n_mb} micro-batches + expert ep{X} ({cfg.num_experts // X} experts/GPU), fused peer-memory dispatch/combine"
         self.h2d_bytes_last = self.d2h_bytes_last = 0
         self.profile_events = False
         self.event_pairs = []
@@ -336,7 +400,10 @@ class DisaggDecodeBench:
             self.event_pairs.append(ev)
 
     def tokens_per_step(self) -> int:
-        return self.shape.n_mb * self.shape.batch if self.is_attn else 0
+        # a sequence served by a TP group is counted once (by the group's first rank)
+        if not self.is_attn or self.rank % self.tp != 0:
+            return 0
+        return self.shape.n_mb * self.shape.batch
 
     def launch_count(self) -> int:
         return _lib.LAUNCHES

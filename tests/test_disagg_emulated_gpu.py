@@ -69,3 +69,62 @@ def test_emulated_disagg_matches_colocated(A, X, n_mb):
             got = attn[a].mb[m]["logits"]
             err = (got - lg).abs().max().item() / lg.abs().max().item()
             assert err < 0.03, f"rank {a} mb {m} step {step}: rel err {err}"
+
+
+@pytest.mark.parametrize("A,X,tp,n_mb", [(2, 1, 2, 1), (4, 2, 2, 2)])
+def test_emulated_tensor_parallel_attention(A, X, tp, n_mb):
+    """Attention TP: head-sharded QKV / attention / o_proj per rank, o_proj partials reduced inside the router kernel
+    from the peers' buffers, every rank dispatches its token slice, experts fan the combine out to the whole group."""
+    cfg = tiny_config.clone(dtype=torch.bfloat16, num_layers=2)
+    sd = {k: v.to(torch.bfloat16) for k, v in init_state_dict(cfg, dtype=torch.float32).items()}
+    B = 4
+    shape = DisaggShape(A, X, n_mb, B, cfg.top_k, cfg.hidden_size, cfg.num_experts, tp)
+    layout = build_layout(shape)
+    arenas = PeerArena.emulated(A + X, layout.size)
+    attn = [AttentionRank(cfg, shape, arenas[a], layout, a, num_blocks=64, state_dict=sd) for a in range(A)]
+    exps = [ExpertRank(cfg, shape, arenas[A + x], layout, x, state_dict=sd) for x in range(X)]
+    ref = FusedModelExecutor(cfg, CacheConfig(block_size=16), device="cuda", max_batch_size=B, max_prefill_tokens=B,
+                             state_dict=sd, num_blocks=64, enable_cuda_graph=False)
+    g = torch.Generator().manual_seed(0)
+    kv = torch.randn(ref.kv_cache.shape, generator=g).to(torch.bfloat16).cuda() * 0.5     # [L, 2, nb, bs, kvh, hd]
+    kvh = cfg.num_kv_heads // tp
+    inputs = {}
+    for grp in range(A // tp):
+        perm = torch.randperm(60, generator=g)
+        for m in range(n_mb):
+            ids = torch.randint(0, cfg.vocab_size, (B,), generator=g).int()
+            ctx = torch.randint(3, 40, (B,), generator=g).int()
+            bt = perm[m * B * 4:(m + 1) * B * 4].view(B, 4).int()
+            slots = torch.tensor([int(bt[i, int(ctx[i]) // 16]) * 16 + int(ctx[i]) % 16 for i in range(B)])
+            inputs[(grp, m)] = (ids, ctx, slots, bt)
+            for r in range(tp):
+                a = attn[grp * tp + r]
+                a.kv_cache.copy_(kv[..., r * kvh:(r + 1) * kvh, :])
+                a.block_tables[m * B:(m + 1) * B, :4] = bt.cuda()
+                d = a.mb[m]
+                d["ids"].copy_(ids); d["positions"].copy_(ctx); d["ctx_len"].copy_(ctx + 1)
+                d["bt_row"].copy_(torch.arange(B, dtype=torch.int32) + m * B); d["slots"].copy_(slots)
+    for a in attn:
+        for m in range(n_mb):
+            a.embed(m)
+    for l in range(cfg.num_layers):
+        for m in range(n_mb):
+            for a in attn:
+                a.layer_attn(l, m)
+            for a in attn:
+                a.layer_route_dispatch(l, m)
+            for e in exps:
+                e.layer(l, m)
+    for a in attn:
+        for m in range(n_mb):
+            a.head(m)
+    torch.cuda.synchronize()
+    assert gemm.check_status() == 0
+    for (grp, m), (ids, ctx, slots, bt) in inputs.items():
+        ref.kv_cache.copy_(kv)
+        ref.block_tables[:B, :4] = bt.cuda()
+        _, lg = ref.decode(ids, ctx, slots, ctx + 1, torch.arange(B, dtype=torch.int32), want_logits=True)
+        for r in range(tp):
+            got = attn[grp * tp + r].mb[m]["logits"]
+            err = (got - lg).abs().max().item() / lg.abs().max().item()
+            assert err < 0.03, f"group {grp} tp rank {r} mb {m}: rel err {err}"
