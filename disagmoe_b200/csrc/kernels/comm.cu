@@ -122,13 +122,13 @@ __global__ void __launch_bounds__(256) dispatch_remote_kernel(const DispatchRemo
 }
 
 // Thread i waits until flags[i] >= *epoch + 1; then *epoch is advanced.
-__global__ void wait_flags_kernel(const int* flags, int n, int* epoch, int* status) {
+__global__ void wait_flags_kernel(const int* flags, int n, int* epoch, int* status, long long max_cycles) {
   const int want = *epoch + 1;
   if (threadIdx.x < n) {
     const bool poisoned = status != nullptr && *reinterpret_cast<volatile int*>(status) != kStatusOk;
     const long long t0 = clock64();
     while (!poisoned && ld_acquire_sys_i32(flags + threadIdx.x) < want) {
-      if (clock64() - t0 > 4 * DMOE_WAIT_CYCLES) {
+      if (clock64() - t0 > max_cycles) {
         if (status != nullptr) atomicCAS(status, kStatusOk, kStatusFlagTimeout);
         break;
       }
@@ -168,9 +168,16 @@ extern "C" int dmoe_dispatch_remote(const void* y, long long ld_y, const int* to
   return static_cast<int>(cudaGetLastError());
 }
 
+static long long g_flag_wait_cycles = 4 * DMOE_WAIT_CYCLES;
+
+// Cycle budget of every later flag wait launched through dmoe_wait_flags (<= 0 restores the default of ~4 s).
+extern "C" void dmoe_set_flag_wait_cycles(long long cycles) {
+  g_flag_wait_cycles = cycles > 0 ? cycles : 4 * DMOE_WAIT_CYCLES;
+}
+
 extern "C" int dmoe_wait_flags(const int* flags, int n, int* epoch, int* status, void* stream) {
   if (n < 0 || n > 256 || epoch == nullptr) return -10;
-  wait_flags_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(flags, n, epoch, status);
+  wait_flags_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(flags, n, epoch, status, g_flag_wait_cycles);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -90,6 +90,7 @@ int dmoe_dispatch_remote(const void* y, long long ld_y, const int* topk_ids, con
                          const void* flag_bases, int* epoch, int* status, int tok_lo, int tok_hi, void* stream);
 // Waits (bounded) until flags[i] >= *epoch + 1 for i < n, then advances *epoch.
 int dmoe_wait_flags(const int* flags, int n, int* epoch, int* status, void* stream);
+void dmoe_set_flag_wait_cycles(long long cycles);
 int dmoe_enable_peer_access(int peer_device);
 // Peer arena: a zeroed cudaMalloc block + its 64-byte CUDA IPC handle; dmoe_peer_open maps a peer's block into
 // this process for kernels of the CURRENT device (peer access is enabled lazily by the driver).

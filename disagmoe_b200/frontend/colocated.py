@@ -191,6 +191,40 @@ class ColocatedEngine:
                 return out
         return self._decode()
 
+    # ---- serving-state snapshot ----------------------------------------------------------------------------------
+    def save_state(self, path: str) -> None:
+        """Writes the request table and the KV pages of every live sequence (between two steps). A new engine with the
+        same weights continues from it with :meth:`load_state` and produces the same tokens."""
+        seqs = []
+        for s in self.running.values():
+            blocks = self.block_mgr.get_seq_block_list(s.req_id)
+            pages = self.executor.kv_cache[:, :, torch.tensor(blocks, device=self.device)].cpu()
+            seqs.append(dict(req_id=s.req_id, prompt=s.prompt, max_new_tokens=s.max_new_tokens, length=s.length,
+                             last_token=s.last_token, outputs=list(s.outputs), pages=pages))
+        waiting = [dict(req_id=s.req_id, prompt=s.prompt, max_new_tokens=s.max_new_tokens) for s in self.waiting]
+        finished = {r: list(s.outputs) for r, s in self.finished.items()}
+        tmp = path + ".tmp"
+        torch.save(dict(running=seqs, waiting=waiting, finished=finished, block_size=self.block_size), tmp)
+        import os
+        os.replace(tmp, path)
+
+    def load_state(self, path: str) -> None:
+        st = torch.load(path, map_location="cpu", weights_only=False)
+        assert st["block_size"] == self.block_size and not self.running and not self.waiting
+        for d in st["running"]:
+            s = _Seq(d["req_id"], d["prompt"], d["max_new_tokens"], length=d["length"], last_token=d["last_token"],
+                     outputs=list(d["outputs"]), t_arrival=time.time())
+            self.block_mgr.allocate(s.req_id, s.length + 1)
+            blocks = self.block_mgr.get_seq_block_list(s.req_id)
+            n = d["pages"].shape[2]
+            self.executor.kv_cache[:, :, torch.tensor(blocks[:n], device=self.device)] = d["pages"].to(self.device)
+            self.running[s.req_id] = s
+        for d in st["waiting"]:
+            self.add_request(d["req_id"], d["prompt"], d["max_new_tokens"])
+        for r, outs in st["finished"].items():
+            self.finished[r] = _Seq(r, [], len(outs), outputs=list(outs))
+        self._apply_block_table_patches()
+
     def launch_count(self) -> int:
         from ..ops import _lib
         return _lib.LAUNCHES

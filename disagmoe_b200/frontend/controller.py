@@ -63,13 +63,20 @@ class WorkerHandle:
 
     def call_async(self, method: str, *args, **kwargs) -> None:
         self.lock.acquire()
-        self.conn.send((method, args, kwargs))
+        try:
+            self.conn.send((method, args, kwargs))
+        except (OSError, ValueError) as e:
+            self.lock.release()
+            raise RuntimeError(f"worker {self.device_id} is gone: {e}")
 
     def wait(self, timeout: float = 300.0):
         try:
             if not self.conn.poll(timeout):
                 raise TimeoutError(f"worker {self.device_id} did not answer within {timeout} s")
-            status, res = self.conn.recv()
+            try:
+                status, res = self.conn.recv()
+            except (EOFError, OSError) as e:
+                raise RuntimeError(f"worker {self.device_id} is gone: {e}")
         finally:
             self.lock.release()
         if status != "ok":
@@ -85,8 +92,11 @@ class WorkerHandle:
 
     def stop(self) -> None:
         try:
-            with self.lock:
-                self.conn.send(None)
+            if self.lock.acquire(timeout=5):
+                try:
+                    self.conn.send(None)
+                finally:
+                    self.lock.release()
         except Exception:
             pass
         self.proc.join(timeout=10)
@@ -346,7 +356,7 @@ class Controller:
 
     def release_kv_cache(self, req_ids: List[int]) -> None:
         for d, w in self.workers.items():
-            if self.placement.has_attn(d):
+            if self.placement.has_attn(d) and d not in self.suspect_workers and w.alive():
                 w.call("release_seqs", req_ids)
 
     def wait_for_requests(self, n_request: int, timeout: float = 600.0) -> Dict[int, SloStat]:
@@ -430,7 +440,8 @@ class Controller:
             self.sampler.terminate()
         for w in self.workers.values():
             try:
-                w.call("terminate", timeout=20)
+                if w.alive():
+                    w.call("terminate", timeout=20)
             except Exception:
                 pass
             w.stop()

@@ -1,0 +1,99 @@
+"""Failure detection, checkpoint layout / sharding, and serving-state resume -- all on CPU, no device is ever faulted:
+a failure is a worker process that exits between steps, seen by the controller through process liveness."""
+import os
+import tempfile
+import time
+
+import pytest
+import torch
+
+from disagmoe_b200.config import CacheConfig, SamplingConfig, mixtral_config, tiny_config
+from disagmoe_b200.frontend.colocated import ColocatedEngine
+from disagmoe_b200.frontend.controller import init_controller
+from disagmoe_b200.models import weights as W
+from disagmoe_b200.models.linear import QKVParallelLinear, RowParallelLinear
+from disagmoe_b200.utils.placement import ClusterConfig, get_model_placement
+
+
+def test_dead_worker_is_detected_and_requests_fail_fast():
+    cfg = tiny_config.clone(ep_size=1)
+    place = get_model_placement(cfg, ClusterConfig(1, 2), "pipeline", 1, 1)
+    ctl = init_controller(1, 2, device="cpu")
+    try:
+        ctl.init_engine(place, cfg, CacheConfig(block_size=16, num_gpu_blocks=64), SamplingConfig(2, 3),
+                        dtype=torch.float32)
+        ctl.start_engine()
+        r = ctl.put_single_request([5, 6, 7], output_len=2)
+        r.get(timeout=60)                       # the system works
+        assert ctl.check_workers() == []
+        # the expert worker leaves between steps (nothing in flight); the controller learns it on the host
+        ctl.workers[1].proc.terminate()
+        ctl.workers[1].proc.join(timeout=10)
+        assert ctl.check_workers() == [1] and ctl.suspect_workers == [1]
+        ctl.put_single_request([8, 9, 10], output_len=2)
+        t0 = time.time()
+        with pytest.raises(RuntimeError, match="worker 1 died"):
+            ctl.wait_for_requests(2, timeout=30)
+        assert time.time() - t0 < 5, "a dead peer must surface quickly, not after the request timeout"
+    finally:
+        ctl.stop_workers()
+
+
+def test_state_dict_save_load_and_sharding_rules():
+    cfg = tiny_config.clone(num_kv_heads=2)
+    sd = W.init_state_dict(cfg)
+    assert W.check_state_dict(cfg, sd) == []
+    path = os.path.join(tempfile.mkdtemp(), "ckpt.pt")
+    W.save_state_dict(sd, path)
+    back = W.load_state_dict(path)
+    assert all(torch.equal(sd[k], back[k]) for k in sd)
+    # seeded init is independent of which tensors a process materialises
+    one = W.init_state_dict(cfg, names=["layers.1.gate.weight"])
+    assert torch.equal(one["layers.1.gate.weight"], sd["layers.1.gate.weight"])
+    # TP shards: the functional rule and the layer's weight_loader agree (kv heads replicated when tp > kv heads)
+    full = sd["layers.0.qkv_proj.weight"]
+    for tp in (2, 4):
+        for r in range(tp):
+            lin = QKVParallelLinear(cfg.hidden_size, cfg.head_dim, cfg.num_heads, cfg.num_kv_heads, tp_size=tp, tp_rank=r,
+                                    params_dtype=torch.float32)
+            lin.weight_loader(lin.weight, full)
+            assert torch.equal(lin.weight.data, W.shard_qkv(full, cfg, tp, r))
+            o = RowParallelLinear(cfg.num_heads * cfg.head_dim, cfg.hidden_size, tp_size=tp, tp_rank=r,
+                                  params_dtype=torch.float32)
+            o.weight_loader(o.weight, sd["layers.0.o_proj.weight"])
+            assert torch.equal(o.weight.data, W.shard_o_proj(sd["layers.0.o_proj.weight"], cfg, tp, r))
+    # expert slices and the runtime (K-contiguous) layout round trip
+    w13, w2 = sd["layers.0.experts.w13_weight"], sd["layers.0.experts.w2_weight"]
+    r13, r2 = W.to_runtime_expert_layout(W.shard_experts(w13, 2, 4), W.shard_experts(w2, 2, 4))
+    assert r13.shape == (2, 2 * cfg.intermediate_size, cfg.hidden_size) and r2.shape == (2, cfg.hidden_size, cfg.intermediate_size)
+    c13, c2 = W.to_checkpoint_expert_layout(r13, r2)
+    assert torch.equal(c13, w13[2:4]) and torch.equal(c2, w2[2:4])
+    shapes = W.param_shapes(mixtral_config)
+    assert shapes["layers.0.qkv_proj.weight"] == (6144, 4096) and shapes["layers.31.experts.w13_weight"] == (8, 4096, 28672)
+
+
+def test_serving_state_snapshot_resumes_with_identical_tokens():
+    cfg = tiny_config
+    sd = W.init_state_dict(cfg)
+    mk = lambda: ColocatedEngine(cfg, CacheConfig(block_size=16), device="cpu", max_batch_size=4, max_prefill_tokens=64,
+                                 state_dict=sd, num_blocks=64, enable_cuda_graph=False, dtype=torch.float32)
+    g = torch.Generator().manual_seed(3)
+    prompts = {i: torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for i, n in enumerate((14, 30, 9))}
+    ref = mk()
+    for i, p in prompts.items():
+        ref.add_request(i, p, 12)
+    want = ref.run_until_done(100)
+    a = mk()
+    for i, p in prompts.items():
+        a.add_request(i, p, 12)
+    for _ in range(5):
+        a.step()
+    path = os.path.join(tempfile.mkdtemp(), "serving_state.pt")
+    a.save_state(path)
+    del a
+    b = mk()
+    # occupy some blocks first so that the restored sequences land on different physical pages
+    b.block_mgr.allocate(999, 40); b.block_mgr.drain_updates()
+    b.load_state(path)
+    got = b.run_until_done(100)
+    assert got == want

@@ -130,3 +130,39 @@ def test_embed_argmax_permute_gather():
     ptrs = torch.tensor([src[i].data_ptr() for i in g.tolist()], dtype=torch.int64, device=DEV)
     o2 = torch.empty(77, H, dtype=torch.bfloat16, device=DEV)
     assert torch.equal(F.gather_ptrs(ptrs, 77, H, o2), src[g.long()])
+
+
+def test_flag_wait_gives_up_with_status_and_context_survives():
+    """A wait on a flag that nothing sets runs out after its cycle budget, records kStatusFlagTimeout in the status
+    word and returns; the context stays usable and later waits of the poisoned run return at once."""
+    import ctypes
+    import time
+    from disagmoe_b200.ops import _lib
+    lib = _lib.lib()
+    lib.dmoe_set_flag_wait_cycles.argtypes = [ctypes.c_longlong]
+    lib.dmoe_set_flag_wait_cycles(ctypes.c_longlong(200_000_000))       # ~0.1 s
+    try:
+        s = gemm.scratch("cuda")
+        s.status.zero_()
+        flags = torch.zeros(4, dtype=torch.int32, device=DEV)
+        epoch = torch.zeros(1, dtype=torch.int32, device=DEV)
+        vp = lambda t: ctypes.c_void_p(t.data_ptr())
+        call = lambda: lib.dmoe_wait_flags(vp(flags), ctypes.c_int(4), vp(epoch), vp(s.status),
+                                           ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+        t0 = time.time()
+        assert call() == 0
+        torch.cuda.synchronize()
+        assert time.time() - t0 < 3.0
+        assert int(s.status.item()) == 2 and int(epoch.item()) == 1
+        t0 = time.time()
+        assert call() == 0                  # poisoned: no second wait
+        torch.cuda.synchronize()
+        assert time.time() - t0 < 0.05
+        assert gemm.check_status() == 2     # read and cleared
+        flags.fill_(3)
+        assert call() == 0                  # flags already carry the epoch: passes without waiting
+        torch.cuda.synchronize()
+        assert gemm.check_status() == 0 and int(epoch.item()) == 3
+        assert torch.allclose(torch.ones(4, device=DEV) * 2, torch.full((4,), 2.0, device=DEV))   # context still fine
+    finally:
+        lib.dmoe_set_flag_wait_cycles(ctypes.c_longlong(0))
