@@ -63,7 +63,7 @@ class FusedAttnSide:
         dev = x.device
         z = lambda *s: torch.zeros(*s, dtype=torch.int32, device=dev)
         ex = [shape.n_attn + i for i in range(shape.n_expert)]
-        self.ws, self.disp_epoch, self.wait_epoch = z(2 * cfg.num_experts + 8), z(1), z(1)
+        self.ws, self.disp_epoch, self.wait_epoch = z(3 * cfg.num_experts + 8), z(1), z(1)
         self.parts = arena.view(layout.offset("parts0"), (shape.batch, cfg.top_k, cfg.hidden_size), torch.bfloat16)
         self.comb_flag = arena.view(layout.offset("comb_flag0"), (shape.n_expert,), torch.int32)
         self.tables = [arena.ptr_table(ex, layout.offset(n)) for n in ("recv_rows0", "recv_recs0", "recv_cnt0", "disp_flag0")]
@@ -195,18 +195,18 @@ def main():
             er = ExpertRank.__new__(ExpertRank)
             er.cfg, er.shape, er.arena, er.layout, er.x, er.device = cfg, shape, arena, layout, rank - A, dev
             er.layers = [experts_mod]
-            rows = A * shape.region_cap
+            rows = (E // X) * shape.region_cap
             z = lambda *s: torch.zeros(*s, dtype=torch.int32, device=dev)
             er.act = torch.zeros(rows, I, dtype=torch.bfloat16, device=dev)
             er.ticket = z(1)
             er.mb = [dict(rows=arena.view(layout.offset("recv_rows0"), (rows, H), torch.bfloat16),
                           recs=arena.view(layout.offset("recv_recs0"), (rows, 4), torch.int32),
-                          cnt=arena.view(layout.offset("recv_cnt0"), (A, E // X), torch.int32),
+                          cnt=arena.view(layout.offset("recv_cnt0"), (E // X,), torch.int32),
                           flag=arena.view(layout.offset("disp_flag0"), (A,), torch.int32),
                           wait_epoch=z(1), signal_epoch=z(1),
                           parts_bases=arena.ptr_table(list(range(A)), layout.offset("parts0")),
                           signal_ptrs=arena.ptr_table(list(range(A)), layout.offset("comb_flag0")))]
-            er.bn = gemm.pick_bn(gemm._group_hint(A * shape.region_cap, E), gemm.EPI_SWIGLU)
+            er.bn = gemm.pick_bn(gemm._group_hint(A * T * k, E), gemm.EPI_SWIGLU)
             fused = er
         nccl = NcclPath(cfg, A, X, rank, T, x, gate_w, norm_w, experts_mod)
 

@@ -1,0 +1,96 @@
+"""Stand-alone device time of each side of the fused disaggregated pipeline on ONE GPU (no peer has to exist):
+
+  attention side   one iteration of an attention rank (2 micro-batches x all layers) with every flag pre-satisfied, so no
+                   wait blocks and the dispatch stores land in a local arena
+  expert side      one iteration of an expert rank holding `--experts-per-rank` experts per layer, fed with a fixed
+                   number of rows per expert, arrival flags pre-satisfied
+
+    python benchmark/profile_disagg_sides.py --n-attn 4 --n-expert 4
+
+The two numbers bound the pipelined step time from below (the slower side) and from above (their sum).
+"""
+import argparse
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import torch
+
+from disagmoe_b200.config import get_preset
+from disagmoe_b200.ops import gemm
+from disagmoe_b200.parallel.disagg import AttentionRank, DisaggShape, ExpertRank, build_layout
+from disagmoe_b200.parallel.peer import PeerArena
+
+
+def timed(fn, iters=5):
+    for _ in range(2):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record(); fn(); e.record()
+        torch.cuda.synchronize()
+        ts.append(s.elapsed_time(e))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", default="mixtral")
+    ap.add_argument("--layers", type=int, default=32)
+    ap.add_argument("--batch", type=int, default=256)
+    ap.add_argument("--n-attn", type=int, default=4)
+    ap.add_argument("--n-expert", type=int, default=4)
+    ap.add_argument("--ctx", type=int, default=864)
+    ap.add_argument("--side", default="both")
+    a = ap.parse_args()
+    cfg = get_preset(a.model).clone(num_layers=a.layers)
+    S = DisaggShape(a.n_attn, a.n_expert, 2, a.batch, cfg.top_k, cfg.hidden_size, cfg.num_experts)
+    layout = build_layout(S)
+    big = 2 ** 30
+    if a.side in ("both", "attn"):
+        arenas = PeerArena.emulated(a.n_attn + a.n_expert, layout.size)
+        B = a.batch
+        blocks = 2 * B * ((a.ctx + 32) // 16 + 1) + 8
+        r = AttentionRank(cfg, S, arenas[0], layout, 0, blocks)
+        r.kv_cache.normal_(0, 0.5)
+        per = (a.ctx + 32) // 16 + 1
+        for m, d in enumerate(r.mb):
+            d["comb_flag"].fill_(big)
+            d["ids"].random_(0, cfg.vocab_size)
+            d["positions"].fill_(a.ctx); d["ctx_len"].fill_(a.ctx + 1)
+            rows = torch.arange(B, dtype=torch.int32, device="cuda") + m * B
+            d["bt_row"].copy_(rows)
+            bt = (rows.long()[:, None] * per + torch.arange(per, device="cuda")[None]).int()
+            r.block_tables[m * B:(m + 1) * B, :per] = bt
+            d["slots"].copy_(bt[:, a.ctx // 16].long() * 16 + a.ctx % 16)
+        ms = timed(r.iteration)
+        print(f"attention side: {ms:.2f} ms per iteration ({ms / a.layers / 2 * 1e3:.0f} us per layer and micro-batch), "
+              f"status {gemm.check_status()}")
+        del r, arenas
+        torch.cuda.empty_cache()
+    if a.side in ("both", "expert"):
+        arenas = PeerArena.emulated(a.n_attn + a.n_expert, layout.size)
+        x = ExpertRank(cfg, S, arenas[a.n_attn], layout, 0)
+        pairs = a.n_attn * a.batch * cfg.top_k // cfg.num_experts      # rows per expert per launch
+        for d in x.mb:
+            d["flag"].fill_(big)
+            d["cnt"].fill_(pairs)
+            d["rows"].normal_(0, 1)
+            d["recs"].zero_()
+            d["recs"][:, 1] = torch.arange(d["recs"].shape[0], device="cuda").int() % (a.batch * cfg.top_k)
+        def it():
+            for l in range(cfg.num_layers):
+                for m in range(2):
+                    x.layer(l, m)
+                    x.mb[m]["cnt"].fill_(pairs)      # the combine cleared the cursors; refill for the next launch
+        ms = timed(it)
+        print(f"expert side ({S.experts_per_rank} experts/GPU, {pairs} rows per expert, tile {x.bn}): {ms:.2f} ms per "
+              f"iteration ({ms / a.layers / 2 * 1e3:.0f} us per layer and micro-batch), status {gemm.check_status()}")
+
+
+if __name__ == "__main__":
+    main()

@@ -1,11 +1,12 @@
 // Attention -> expert token dispatch over peer memory (NVLink / NVSwitch), issued from the kernel.
 //
 // dispatch_remote_kernel: every routed (token, k) pair of this attention rank is stored straight into the receive
-// region this rank owns on the GPU that holds its expert: row copy (16-byte stores), a 16-byte token record
-// {source rank, row in the source's partial-output buffer, router weight, expert} next to it, and, once every row
-// of the launch is out, the per-expert row counts and a release flag carrying the launch's epoch. No host round
-// trip, no NCCL, no TCP message: sizes travel with the data. Rows of one destination are packed expert after expert
-// (the sender knows its own per-expert histogram), so the consumer's grouped GEMM can address them as segments.
+// region of its expert on the GPU that holds the expert: row copy (16-byte stores), a 16-byte token record {source
+// rank, row in the source's partial-output buffer, router weight, expert} next to it, and, once every row of the
+// launch is out, a release flag carrying the launch's epoch. Each sender first reserves a block of rows per expert
+// with one system-scope atomic add on the expert's cursor (reserve_kernel), so the rows of an expert arrive contiguous
+// from all senders and the cursor is the row count the consumer's grouped GEMM reads. No host round trip, no NCCL, no
+// TCP message: sizes travel with the data.
 //
 // wait_flags_kernel: bounded wait on peers' flags (used before an op that reads rows peers combine into this GPU).
 // A wait that runs out records kStatusFlagTimeout and returns; later waits of a poisoned run return at once.
@@ -47,7 +48,8 @@ struct DispatchRemoteArgs {
   void* const* x_bases;         // [n_dst] receive-row buffers on the destinations ([n_src * region_cap, H] bf16)
   long long ld_dst;
   void* const* rec_bases;       // [n_dst] record buffers ([n_src * region_cap] int4)
-  int* const* cnt_bases;        // [n_dst] count tables ([n_src, experts_per_rank] int)
+  int* const* cnt_bases;        // [n_dst] per-expert row cursors on the destinations ([experts_per_rank] int)
+  const int* row_base;          // [E] first row (inside the expert's region) reserved for this rank by reserve_kernel
   int* const* flag_bases;       // [n_dst] arrival flags ([n_src] int)
   int* epoch;                   // launch counter of this dispatcher (device resident)
   int* status;
@@ -58,14 +60,8 @@ __global__ void __launch_bounds__(256) dispatch_remote_kernel(const DispatchRemo
   int* counts = a.ws;
   int* cursor = a.ws + a.E;
   int* ticket = a.ws + 2 * a.E;
-  if (threadIdx.x == 0) {
-    int run = 0;
-    for (int e = 0; e < a.E; ++e) {
-      if (e % a.experts_per_rank == 0) run = 0;   // every destination's region is packed from its first row
-      s_base[e] = run;
-      run += counts[e];
-    }
-  }
+  // every expert owns one region of region_cap rows on its GPU; this rank's rows start at the offset it reserved
+  for (int e = threadIdx.x; e < a.E; e += blockDim.x) s_base[e] = a.row_base[e];
   __syncthreads();
   const int nvec = a.H / 8;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
@@ -85,7 +81,7 @@ __global__ void __launch_bounds__(256) dispatch_remote_kernel(const DispatchRemo
       if (lane == 0 && a.status != nullptr) atomicCAS(a.status, kStatusOk, kStatusCapacity);
       continue;
     }
-    const long long row = static_cast<long long>(a.my_rank) * a.region_cap + row_in_region;
+    const long long row = static_cast<long long>(e % a.experts_per_rank) * a.region_cap + row_in_region;
     const int t = p / a.K;
     const bf16x8c* sp = reinterpret_cast<const bf16x8c*>(a.y + static_cast<long long>(t) * a.ld_y);
     bf16x8c* dp = reinterpret_cast<bf16x8c*>(static_cast<__nv_bfloat16*>(a.x_bases[dst]) + row * a.ld_dst);
@@ -107,11 +103,6 @@ __global__ void __launch_bounds__(256) dispatch_remote_kernel(const DispatchRemo
     if (old == static_cast<int>(gridDim.x) - 1) {
       __threadfence_system();
       const int epoch = *a.epoch + 1;
-      for (int d = 0; d < a.n_dst; ++d) {
-        int* cnt = a.cnt_bases[d] + a.my_rank * a.experts_per_rank;
-        for (int i = 0; i < a.experts_per_rank; ++i) cnt[i] = counts[d * a.experts_per_rank + i];
-      }
-      __threadfence_system();
       for (int d = 0; d < a.n_dst; ++d) st_release_sys_i32(a.flag_bases[d] + a.my_rank, epoch);
       *a.epoch = epoch;
       for (int e = 0; e < a.E; ++e) { counts[e] = 0; cursor[e] = 0; }
@@ -119,6 +110,16 @@ __global__ void __launch_bounds__(256) dispatch_remote_kernel(const DispatchRemo
       __threadfence();
     }
   }
+}
+
+// Row reservation of one dispatch launch: for every expert e this rank adds its row count to the expert's cursor on
+// the owning GPU (one system-scope atomic over NVLink) and keeps the old value as the first row of its block. Rows of
+// an expert therefore arrive contiguous from all senders, so the consumer's GEMM sees one segment per expert.
+__global__ void reserve_kernel(const int* counts, int E, int experts_per_rank, int* const* cnt_bases, int* row_base) {
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= E) return;
+  const int c = counts[e];
+  row_base[e] = c > 0 ? atomicAdd_system(cnt_bases[e / experts_per_rank] + e % experts_per_rank, c) : 0;
 }
 
 // Thread i waits until flags[i] >= *epoch + 1; then *epoch is advanced.
@@ -157,13 +158,16 @@ extern "C" int dmoe_dispatch_remote(const void* y, long long ld_y, const int* to
   a.region_cap = region_cap; a.ws = ws; a.x_bases = static_cast<void* const*>(x_bases); a.ld_dst = ld_dst;
   a.rec_bases = static_cast<void* const*>(rec_bases); a.cnt_bases = static_cast<int* const*>(cnt_bases);
   a.flag_bases = static_cast<int* const*>(flag_bases); a.epoch = epoch; a.status = status;
+  a.row_base = ws + 2 * E + 8;
   if (tok_hi <= 0 || tok_hi > T) tok_hi = T;
   if (tok_lo < 0 || tok_lo > tok_hi) tok_lo = 0;
   a.tok_lo = tok_lo; a.tok_hi = tok_hi;
   const int npairs = (tok_hi - tok_lo) * K;
   int grid = (npairs + 7) / 8;
   if (grid > 148 * 2) grid = 148 * 2;
-  if (grid < 1) grid = 1;   // an empty batch still publishes zero counts and its flag
+  if (grid < 1) grid = 1;   // an empty batch still publishes its flag
+  reserve_kernel<<<(E + 63) / 64, 64, 0, static_cast<cudaStream_t>(stream)>>>(ws, E, experts_per_rank, a.cnt_bases,
+                                                                               ws + 2 * E + 8);
   dispatch_remote_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
   return static_cast<int>(cudaGetLastError());
 }

@@ -32,6 +32,9 @@ typedef struct DmoeGemm {
   int* done_ticket;     // one zero-initialised int of scratch (required with wait_flags or signal_ptrs)
   long long ldx, ldy, ldr, ws_bytes;
   int S, seg_cap, n_wait, n_signal, signal_slot;
+  int group_regions;    // 1: group g owns rows [g*seg_cap, (g+1)*seg_cap) and seg_cnt[g] is its row count (S unused)
+  int clear_n;          // the last CTA zeroes clear_ptr[0..clear_n) before it signals (the dispatch cursors)
+  int* clear_ptr;
   int fanout;           // combine: every row is stored to the `fanout` consecutive ranks of the sender's TP group (0/1 = one)
   int G, T, F, K;
   int epi;            // DMOE_EPI_*
@@ -81,9 +84,10 @@ int dmoe_dispatch_local(const void* y, long long ld_y, const int* topk_ids, cons
 
 // ---- peer-memory dispatch (comm.cu) -----------------------------------------------------------------
 // Stores every routed (token, k) row of this attention rank into its region on the expert GPU that owns the
-// expert, with 16-byte records, per-expert counts and a release flag (*epoch + 1). x_bases / rec_bases / cnt_bases /
-// flag_bases are device arrays of n_dst peer pointers. ws = ints [counts E | cursor E | ticket], counts filled by
-// dmoe_route; cleared for the next launch.
+// expert ([experts_per_rank, region_cap] rows per destination), with 16-byte records and a release flag (*epoch + 1);
+// row blocks are reserved on the destinations' per-expert cursors (cnt_bases) with system-scope atomics. x_bases /
+// rec_bases / cnt_bases / flag_bases are device arrays of n_dst peer pointers. ws = ints [counts E | cursor E |
+// ticket, 7 pad | row_base E], counts filled by dmoe_route; cleared for the next launch.
 int dmoe_dispatch_remote(const void* y, long long ld_y, const int* topk_ids, const float* topk_w, int T, int K, int H,
                          int E, int experts_per_rank, int n_dst, int my_rank, int region_cap, int* ws,
                          const void* x_bases, long long ld_dst, const void* rec_bases, const void* cnt_bases,

@@ -71,6 +71,9 @@ struct GemmArgs {
   int* signal_epoch;
   int* done_ticket;
   int fanout;   // combine: destinations per row (TP group size of the senders)
+  int group_regions;
+  int clear_n;
+  int* clear_ptr;
 };
 
 template <int BN, int EPI>
@@ -164,7 +167,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
   int* last_flag = abort_word + 1;
   int* s_start = last_flag + 1;                                      // [S * G]
   int* s_cnt = s_start + kMaxSeg;                                    // [S * G]
-  const int S = a.S > 0 ? a.S : 1;
+  const int S = (a.S > 0 && !a.group_regions) ? a.S : 1;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -203,7 +206,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
     }
     __syncthreads();
   }
-  if (a.seg_cnt != nullptr) {
+  if (a.seg_cnt != nullptr && a.group_regions) {
+    // every group owns a fixed region; its row count is the cursor the senders advanced
+    for (int g = threadIdx.x; g < a.G; g += blockDim.x) {
+      const int c = __ldcg(a.seg_cnt + g);
+      s_start[g] = g * a.seg_cap;
+      s_cnt[g] = c < 0 ? 0 : min(c, a.seg_cap);
+    }
+  } else if (a.seg_cnt != nullptr) {
     // (s, g) -> first row: region s starts at s * seg_cap and is packed group after group
     for (int s = threadIdx.x; s < S; s += blockDim.x) {
       int run = s * a.seg_cap;
@@ -452,6 +462,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
     if (threadIdx.x == 64) {
       const int old = atomicAdd(a.done_ticket, 1);
       if (old == static_cast<int>(gridDim.x) - 1) {
+        for (int i = 0; i < a.clear_n; ++i) a.clear_ptr[i] = 0;
         __threadfence_system();
         if (a.n_signal > 0) {
           const int epoch = *a.signal_epoch + 1;
@@ -577,7 +588,7 @@ extern "C" int dmoe_gemm(const DmoeGemm* d, void* stream_) {
     const int per = (kblocks + splitk - 1) / splitk;
     splitk = (kblocks + per - 1) / per;
   }
-  if (splitk > 1 && (epi == EPI_SWIGLU || d->offs != nullptr || d->S > 0 || d->ws == nullptr || d->counters == nullptr)) return -12;
+  if (splitk > 1 && (epi == EPI_SWIGLU || d->offs != nullptr || d->S > 0 || d->group_regions || d->ws == nullptr || d->counters == nullptr)) return -12;
   if (splitk > 1 && dmoe_gemm_workspace_bytes(d->T, d->F, bn, splitk) > d->ws_bytes) return -13;
   if (epi == EPI_COMBINE && (d->recs == nullptr || d->bases == nullptr)) return -14;
 
@@ -595,8 +606,9 @@ extern "C" int dmoe_gemm(const DmoeGemm* d, void* stream_) {
   a.wait_flags = d->wait_flags; a.n_wait = d->n_wait; a.wait_epoch = d->wait_epoch;
   a.signal_ptrs = reinterpret_cast<int* const*>(d->signal_ptrs); a.n_signal = d->n_signal;
   a.signal_slot = d->signal_slot; a.signal_epoch = d->signal_epoch; a.done_ticket = d->done_ticket;
-  a.fanout = d->fanout;
-  if (a.S > 0 && (a.seg_cnt == nullptr || a.S * a.G > kMaxSeg || a.S * a.seg_cap > d->T)) return -16;
+  a.fanout = d->fanout; a.group_regions = d->group_regions; a.clear_n = d->clear_n; a.clear_ptr = d->clear_ptr;
+  if (a.group_regions && (a.seg_cnt == nullptr || static_cast<long long>(a.G) * a.seg_cap > d->T)) return -16;
+  if (!a.group_regions && a.S > 0 && (a.seg_cnt == nullptr || a.S * a.G > kMaxSeg || a.S * a.seg_cap > d->T)) return -16;
   if (a.S == 0 && a.G > kMaxSeg) return -16;
   if ((a.n_wait > 0 || a.n_signal > 0) && a.done_ticket == nullptr) return -17;
   if (a.n_wait > kThreads || (a.n_wait > 0 && (a.wait_flags == nullptr || a.wait_epoch == nullptr))) return -17;
@@ -609,7 +621,7 @@ extern "C" int dmoe_gemm(const DmoeGemm* d, void* stream_) {
 
   const long long mt = (d->F + kBM - 1) / kBM;
   // upper bound of the tile count (group sizes live on the device): every group may add one ragged tile
-  long long max_tiles = mt * ((d->T + bn - 1) / bn + ((d->offs || d->S > 0) ? d->G * (d->S > 0 ? d->S : 1) : 0)) * splitk;
+  long long max_tiles = mt * ((d->T + bn - 1) / bn + ((d->offs || d->S > 0 || d->group_regions) ? d->G * (d->S > 0 ? d->S : 1) : 0)) * splitk;
   if (max_tiles > (1 << 30)) max_tiles = 1 << 30;
   const int mtiles = static_cast<int>(max_tiles);
 

@@ -28,7 +28,8 @@ class DmoeGemm(ctypes.Structure):
         ("ldx", ctypes.c_longlong), ("ldy", ctypes.c_longlong), ("ldr", ctypes.c_longlong),
         ("ws_bytes", ctypes.c_longlong),
         ("S", ctypes.c_int), ("seg_cap", ctypes.c_int), ("n_wait", ctypes.c_int), ("n_signal", ctypes.c_int),
-        ("signal_slot", ctypes.c_int), ("fanout", ctypes.c_int),
+        ("signal_slot", ctypes.c_int), ("group_regions", ctypes.c_int), ("clear_n", ctypes.c_int),
+        ("clear_ptr", ctypes.c_void_p), ("fanout", ctypes.c_int),
         ("G", ctypes.c_int), ("T", ctypes.c_int), ("F", ctypes.c_int), ("K", ctypes.c_int),
         ("epi", ctypes.c_int), ("bn", ctypes.c_int), ("splitk", ctypes.c_int), ("y_f32", ctypes.c_int),
     ]

@@ -87,12 +87,13 @@ class GemmComm:
     """
 
     def __init__(self, seg_cnt=None, S=0, seg_cap=0, wait_flags=None, n_wait=0, wait_epoch=None, signal_ptrs=None,
-                 n_signal=0, signal_slot=0, signal_epoch=None, done_ticket=None, fanout=0):
+                 n_signal=0, signal_slot=0, signal_epoch=None, done_ticket=None, fanout=0, group_regions=False,
+                 clear=None):
         self.seg_cnt, self.S, self.seg_cap = seg_cnt, S, seg_cap
         self.wait_flags, self.n_wait, self.wait_epoch = wait_flags, n_wait, wait_epoch
         self.signal_ptrs, self.n_signal, self.signal_slot = signal_ptrs, n_signal, signal_slot
         self.signal_epoch, self.done_ticket = signal_epoch, done_ticket
-        self.fanout = fanout
+        self.fanout, self.group_regions, self.clear = fanout, group_regions, clear
 
     def fill(self, d):
         d.seg_cnt, d.S, d.seg_cap = _lib.ptr(self.seg_cnt), self.S, self.seg_cap
@@ -100,6 +101,8 @@ class GemmComm:
         d.signal_ptrs, d.n_signal, d.signal_slot = _lib.ptr(self.signal_ptrs), self.n_signal, self.signal_slot
         d.signal_epoch, d.done_ticket = _lib.ptr(self.signal_epoch), _lib.ptr(self.done_ticket)
         d.fanout = self.fanout
+        d.group_regions = int(self.group_regions)
+        d.clear_ptr, d.clear_n = _lib.ptr(self.clear), (0 if self.clear is None else self.clear.numel())
 
 
 def _launch(W, X, Y, R, offs, recs, bases, G, T, F, K, epi, bn, splitk, ldy, y_f32, comm: Optional[GemmComm] = None):

@@ -5,8 +5,8 @@ the routed experts (expert parallel, ``num_experts / X`` experts each). One deco
 per layer:
 
     attention rank   [wait combine flags]  add+RMSNorm -> QKV -> RoPE/KV append -> paged attention -> o_proj+residual
-                     -> RMSNorm+gate+top-k -> dispatch kernel: rows, records, counts and a release flag are stored
-                     straight into the owning expert GPU's receive region
+                     -> RMSNorm+gate+top-k -> dispatch: a block of rows per expert is reserved on the owning expert GPU
+                     (one system-scope atomic per expert), then rows, records and a release flag are stored there
     expert rank      grouped GEMM-1 (+SwiGLU), gated on the arrival flags, reads the rows where they landed
                      -> grouped GEMM-2 whose epilogue scales by the router weight and stores every row into the
                      source attention GPU's partial-output buffer, then signals that GPU
@@ -60,17 +60,17 @@ class DisaggShape:
         return self.num_experts // self.n_expert
 
     @property
-    def region_cap(self) -> int:   # rows one attention rank can send to one expert rank in one launch
-        return (self.batch // self.tp) * self.top_k
+    def region_cap(self) -> int:   # rows of one expert's receive region: every sender could route all its pairs to it
+        return self.n_attn * (self.batch // self.tp) * self.top_k
 
 
 def build_layout(s: DisaggShape) -> ArenaLayout:
     L = ArenaLayout()
-    rows = s.n_attn * s.region_cap
+    rows = s.experts_per_rank * s.region_cap
     for m in range(s.n_mb):
         L.add(f"recv_rows{m}", rows * s.hidden * 2)
         L.add(f"recv_recs{m}", rows * 16)
-        L.add(f"recv_cnt{m}", s.n_attn * s.experts_per_rank * 4)
+        L.add(f"recv_cnt{m}", s.experts_per_rank * 4)      # per-expert row cursors, advanced by the senders
         L.add(f"disp_flag{m}", s.n_attn * 4)
         L.add(f"parts{m}", s.batch * s.top_k * s.hidden * 2)
         L.add(f"comb_flag{m}", s.n_expert * 4)
@@ -116,7 +116,7 @@ class AttentionRank:
         for m in range(S.n_mb):
             d = dict(
                 ids=z(B), positions=z(B), slots=z(B, dt_=torch.int64), ctx_len=z(B), bt_row=z(B),
-                resid=torch.zeros(B, H, dtype=dt, device=dev), ws=z(2 * E + 8), disp_epoch=z(1), wait_epoch=z(1),
+                resid=torch.zeros(B, H, dtype=dt, device=dev), ws=z(3 * E + 8), disp_epoch=z(1), wait_epoch=z(1),
                 next_ids=z(B), logits=torch.zeros(B, cfg.vocab_size, dtype=torch.float32, device=dev),
                 parts=arena.view(layout.offset(f"parts{m}"), (B, k, H), dt),
                 comb_flag=arena.view(layout.offset(f"comb_flag{m}"), (S.n_expert,), torch.int32),
@@ -241,7 +241,7 @@ class ExpertRank:
             e = MoEExperts(cfg, l, expert_rank * epr, (expert_rank + 1) * epr, device=dev, dtype=torch.bfloat16)
             e.load_weights(state_dict) if state_dict is not None else e.init_weights()
             self.layers.append(e)
-        rows = S.n_attn * S.region_cap
+        rows = epr * S.region_cap
         z = lambda *s: torch.zeros(*s, dtype=torch.int32, device=dev)
         self.act = torch.zeros(rows, cfg.intermediate_size, dtype=torch.bfloat16, device=dev)
         self.ticket = z(1)
@@ -251,23 +251,25 @@ class ExpertRank:
             self.mb.append(dict(
                 rows=arena.view(layout.offset(f"recv_rows{m}"), (rows, S.hidden), torch.bfloat16),
                 recs=arena.view(layout.offset(f"recv_recs{m}"), (rows, 4), torch.int32),
-                cnt=arena.view(layout.offset(f"recv_cnt{m}"), (S.n_attn, epr), torch.int32),
+                cnt=arena.view(layout.offset(f"recv_cnt{m}"), (epr,), torch.int32),
                 flag=arena.view(layout.offset(f"disp_flag{m}"), (S.n_attn,), torch.int32),
                 wait_epoch=z(1), signal_epoch=z(1),
                 parts_bases=arena.ptr_table(attn_ranks, layout.offset(f"parts{m}")),
                 signal_ptrs=arena.ptr_table(attn_ranks, layout.offset(f"comb_flag{m}")),
             ))
-        self.bn = gemm.pick_bn(gemm._group_hint(S.region_cap, S.num_experts), gemm.EPI_SWIGLU)
+        pairs = S.n_attn * (S.batch // S.tp) * S.top_k       # (token, k) pairs arriving per launch, all experts
+        self.bn = gemm.pick_bn(gemm._group_hint(pairs, S.num_experts), gemm.EPI_SWIGLU)
 
     def layer(self, l: int, m: int) -> None:
         d, S = self.mb[m], self.shape
         e = self.layers[l]
-        gate = gemm.GemmComm(seg_cnt=d["cnt"], S=S.n_attn, seg_cap=S.region_cap, wait_flags=d["flag"], n_wait=S.n_attn,
-                             wait_epoch=d["wait_epoch"], done_ticket=self.ticket)
+        gate = gemm.GemmComm(seg_cnt=d["cnt"], seg_cap=S.region_cap, group_regions=True, wait_flags=d["flag"],
+                             n_wait=S.n_attn, wait_epoch=d["wait_epoch"], done_ticket=self.ticket)
         gemm.grouped_swiglu(d["rows"], e.w13_weight, None, out=self.act, bn=self.bn, comm=gate)
-        sig = gemm.GemmComm(seg_cnt=d["cnt"], S=S.n_attn, seg_cap=S.region_cap, signal_ptrs=d["signal_ptrs"],
+        # the last CTA clears the row cursors before it signals: the senders reserve again only after that signal
+        sig = gemm.GemmComm(seg_cnt=d["cnt"], seg_cap=S.region_cap, group_regions=True, signal_ptrs=d["signal_ptrs"],
                             n_signal=S.n_attn, signal_slot=self.x, signal_epoch=d["signal_epoch"],
-                            done_ticket=self.ticket, fanout=S.tp)
+                            done_ticket=self.ticket, fanout=S.tp, clear=d["cnt"])
         gemm.grouped_combine(self.act, e.w2_weight, None, d["recs"], d["parts_bases"], S.hidden, bn=self.bn, comm=sig)
 
     def iteration(self) -> None:
