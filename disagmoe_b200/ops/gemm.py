@@ -56,11 +56,13 @@ def check_status(device=None) -> int:
 
 
 def pick_splitk(T: int, F: int, K: int, bn: int) -> int:
+    """Split-K factor of a dense GEMM: enough (tile, split) work items to occupy most of the 148 SMs when the output
+    has few tiles (decode-size token counts), never more than one split per 4 K-blocks."""
     tiles = ((F + 127) // 128) * ((T + bn - 1) // bn)
     kblocks = (K + 63) // 64
-    if tiles >= _NUM_SMS // 2 or kblocks < 8:
+    if tiles >= 80 or kblocks < 8:
         return 1
-    return max(1, min(_NUM_SMS // tiles, kblocks // 4, 16))
+    return max(1, min((128 + tiles // 2) // tiles, kblocks // 4, 16))
 
 
 def pick_bn(tokens_per_group: int, epi: int) -> int:
@@ -153,7 +155,10 @@ def linear(x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor] = 
     assert out.stride(1) == 1 and out.dtype in (torch.bfloat16, torch.float32)
     if T == 0:
         return out
-    bn = bn or pick_bn(T, EPI_PLAIN)
+    if not bn:
+        bn = pick_bn(T, EPI_PLAIN)
+        if bn == 256 and ((F + 127) // 128) * ((T + 255) // 256) < 74:
+            bn = 128     # too few 256-wide tiles to fill the GPU: halve the tile instead of splitting K further
     splitk = splitk or pick_splitk(T, F, K, bn)
     _launch(w, x, out, residual, None, None, None, 1, T, F, K, EPI_PLAIN, bn, splitk, out.stride(0),
             out.dtype == torch.float32, comm)
