@@ -60,6 +60,7 @@ class ColocatedEngine:
         self.h2d_bytes_last = 0
         self.d2h_bytes_last = 0
         self.steps = 0
+        self._last_was_prefill = False
         self.profile_events = False     # when set, every decode step appends a (start, end) CUDA event pair
         self.event_pairs = []
 
@@ -185,10 +186,15 @@ class ColocatedEngine:
         sequence. Returns (req_id, token) pairs produced by this step."""
         self.h2d_bytes_last = self.d2h_bytes_last = 0
         self.steps += 1
-        if self.waiting and len(self.running) < self.max_batch_size:
+        # prefill and decode steps alternate while both have work, so a burst of arrivals cannot stall the running
+        # sequences for more than one prefill step (bounds the inter-token latency tail)
+        want_prefill = self.waiting and len(self.running) < self.max_batch_size
+        if want_prefill and not (self._last_was_prefill and self.running):
             out = self._prefill()
             if out:
+                self._last_was_prefill = True
                 return out
+        self._last_was_prefill = False
         return self._decode()
 
     # ---- serving-state snapshot ----------------------------------------------------------------------------------
