@@ -470,6 +470,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("init_engine", &init_engine, py::call_guard<py::gil_scoped_release>());
   m.def("init_engine_colocate", &init_engine_colocate, py::call_guard<py::gil_scoped_release>());
   m.def("start_engine", &start_engine);
+  m.def("helper_error", &helper_error);
   m.def("stop_engine", &stop_engine, py::call_guard<py::gil_scoped_release>());
   m.def("init_sampler", &init_sampler, py::arg("device_id"), py::arg("min_output_len"), py::arg("max_output_len"),
         py::arg("top_k"), py::arg("out_device_ids"), py::arg("attn_peer"), py::arg("ignore_eos") = true,

@@ -117,6 +117,7 @@ GpuApi::GpuApi() {
   LOAD(hn, ncclBroadcast) LOAD(hn, ncclAllReduce) LOAD(hn, ncclGetErrorString)
   LOAD(hr, cudaStreamCreateWithFlags) LOAD(hr, cudaStreamSynchronize) LOAD(hr, cudaStreamDestroy)
   LOAD(hr, cudaMemcpyAsync) LOAD(hr, cudaSetDevice)
+  LOAD(hr, cudaEventCreateWithFlags) LOAD(hr, cudaEventRecord) LOAD(hr, cudaStreamWaitEvent) LOAD(hr, cudaEventDestroy)
 #undef LOAD
   ok_ = true;
 }
@@ -177,18 +178,33 @@ NcclChannel::~NcclChannel() {
   auto& a = GpuApi::get();
   if (comm_ != nullptr && a.available()) a.ncclCommDestroy(comm_);
   if (stream_ != nullptr && a.available()) a.cudaStreamDestroy(stream_);
+  if (fence_ != nullptr && a.available()) a.cudaEventDestroy(fence_);
 }
 
 void NcclChannel::instantiate() {
   auto& a = gpu_or_throw();
   CUDA_OK(a.cudaStreamCreateWithFlags(&stream_, 1 /*cudaStreamNonBlocking*/));
+  CUDA_OK(a.cudaEventCreateWithFlags(&fence_, 2 /*cudaEventDisableTiming*/));
   NCCL_OK(a.ncclCommInitRank(&comm_, 2, uid_, rank()));
+}
+
+// The rows of a batch are produced by kernels on the default stream of the engine thread, and a freshly allocated
+// receive buffer may be a cached block that kernels still queued there read. The channel's own stream is
+// non-blocking, so both directions order themselves behind the default stream explicitly.
+void NcclChannel::wait_for_compute() {
+  auto& a = gpu_or_throw();
+  CUDA_OK(a.cudaEventRecord(fence_, nullptr));
+  CUDA_OK(a.cudaStreamWaitEvent(stream_, fence_, 0));
 }
 
 void NcclChannel::send(const torch::Tensor& t, const Metadata&) {
   auto& a = gpu_or_throw();
   DMOE_CHECK(t.is_cuda() && t.is_contiguous(), "NCCL send needs a contiguous CUDA tensor");
+  wait_for_compute();
   NCCL_OK(a.ncclSend(t.data_ptr(), t.numel(), nccl_dtype_of(t), 1 - rank(), comm_, stream_));
+  // the caller may drop its reference as soon as this returns, and the caching allocator would hand the block to the
+  // next compute-stream allocation: the send has to be complete first
+  CUDA_OK(a.cudaStreamSynchronize(stream_));
 }
 
 void NcclChannel::recv(torch::Tensor& t, const Metadata& meta) {
@@ -196,6 +212,7 @@ void NcclChannel::recv(torch::Tensor& t, const Metadata& meta) {
   if (!t.defined()) {
     t = torch::empty(meta.shape, torch::TensorOptions().dtype(dtype_from_string(meta.dtype)).device(torch::kCUDA));
   }
+  wait_for_compute();
   NCCL_OK(a.ncclRecv(t.data_ptr(), t.numel(), nccl_dtype_of(t), 1 - rank(), comm_, stream_));
 }
 

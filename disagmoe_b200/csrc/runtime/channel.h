@@ -110,6 +110,10 @@ struct GpuApi {
   int (*cudaStreamDestroy)(void*) = nullptr;
   int (*cudaMemcpyAsync)(void*, const void*, size_t, int, void*) = nullptr;
   int (*cudaSetDevice)(int) = nullptr;
+  int (*cudaEventCreateWithFlags)(void**, unsigned) = nullptr;
+  int (*cudaEventRecord)(void*, void*) = nullptr;
+  int (*cudaStreamWaitEvent)(void*, void*, unsigned) = nullptr;
+  int (*cudaEventDestroy)(void*) = nullptr;
   static void set_library_paths(const std::string& nccl, const std::string& cudart);
 
  private:
@@ -130,9 +134,11 @@ class NcclChannel : public Channel {
 
  private:
   int rank() const { return local_ < other_ ? 0 : 1; }
+  void wait_for_compute();   // orders stream_ after everything enqueued so far on the default (compute) stream
   NcclId uid_;
   void* comm_ = nullptr;
   void* stream_ = nullptr;
+  void* fence_ = nullptr;    // CUDA event reused by wait_for_compute
 };
 
 class NcclGroupChannel : public Channel {

@@ -43,6 +43,21 @@ TensorBatch TensorBatch::concat(const std::vector<TensorBatch>& batches) {
 }
 
 // ------------------------------------------------------------------------------------------------ MuHelper
+namespace {
+std::mutex g_err_mu;
+std::string g_helper_error;
+}  // namespace
+
+void set_helper_error(const std::string& what) {
+  std::lock_guard<std::mutex> lk(g_err_mu);
+  if (g_helper_error.empty()) g_helper_error = what;
+}
+
+std::string helper_error() {
+  std::lock_guard<std::mutex> lk(g_err_mu);
+  return g_helper_error;
+}
+
 void MuHelper::start() {
   if (thread_.joinable()) return;
   end_flag_.store(false);
@@ -52,6 +67,7 @@ void MuHelper::start() {
       run();
     } catch (const std::exception& e) {
       DMOE_LOG(ERROR) << name() << "@" << device_id_ << " stopped: " << e.what();
+      set_helper_error(std::string(name()) + "@" + std::to_string(device_id_) + " stopped: " + e.what());
     }
   });
 }

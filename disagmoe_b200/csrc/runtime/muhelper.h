@@ -49,6 +49,10 @@ struct AttentionBatch {
   int num_parts = 0;
 };
 
+// First exception that ended a helper thread of this process (empty while all of them run).
+void set_helper_error(const std::string& what);
+std::string helper_error();
+
 class MuHelper {
  public:
   MuHelper(std::vector<int> layer_ids, int device_id) : layer_ids_(std::move(layer_ids)), device_id_(device_id) {}

@@ -393,6 +393,18 @@ class Controller:
                 e = w.engine.check_error()
                 if e:
                     return e
+        # worker processes are asked over RPC, at most once a second
+        now = time.time()
+        if now - getattr(self, "_last_remote_check", 0.0) >= 1.0:
+            self._last_remote_check = now
+            for d, w in self.workers.items():
+                if not isinstance(w, LocalWorker) and d not in self.suspect_workers:
+                    try:
+                        e = w.call("check_error")
+                    except Exception as ex:     # the RPC itself failed: the worker is gone
+                        return f"worker {d}: {ex}"
+                    if e:
+                        return f"worker {d}: {e}"
         return None
 
     # ---- stats / control ------------------------------------------------------------------------------------

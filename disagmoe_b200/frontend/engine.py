@@ -386,7 +386,8 @@ class Engine:
             self.handles.scheduler.set_schedule_block(step)
 
     def check_error(self) -> Optional[str]:
-        return self.error
+        """The engine loop's exception, or the one that ended a native helper thread (pool / dispatcher) of this worker."""
+        return self.error or (C.helper_error() or None)
 
     def heartbeat(self) -> float:
         return time.time()
