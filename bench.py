@@ -102,6 +102,9 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (the result is then marked invalid)")
     ap.add_argument("--model", default="mixtral")
     ap.add_argument("--attn-tp", type=int, default=1, help="tensor-parallel degree of the attention GPUs (N >= 4)")
+    ap.add_argument("--n-attn", type=int, default=0, help="attention GPUs out of N (default N/2); the rest hold experts")
+    ap.add_argument("--route-skew", type=float, default=0.0,
+                    help="Zipf exponent of a synthetic expert-popularity skew added to the router logits (0 = none)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -121,14 +124,15 @@ def main():
     cfg = get_preset(args.model)
     if args.layers:
         cfg = cfg.clone(num_layers=args.layers)
-    cfg.max_seq_len = 4096
+    cfg.max_seq_len = max(4096, (args.ctx_max + K + W + 2 + 15) // 16 * 16)
     g = torch.Generator().manual_seed(1234 + rank)
     B = args.batch
 
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
         from disagmoe_b200.parallel.disagg import DisaggDecodeBench
-        runner = DisaggDecodeBench(cfg, world, rank, local_rank, B, args.ctx_min, args.ctx_max, K + W, g, tp=args.attn_tp)
+        runner = DisaggDecodeBench(cfg, world, rank, local_rank, B, args.ctx_min, args.ctx_max, K + W, g, tp=args.attn_tp,
+                                   n_attn=args.n_attn, route_skew=args.route_skew)
         parallelism = runner.parallelism
     else:
         from disagmoe_b200.frontend.colocated import ColocatedEngine
@@ -137,13 +141,16 @@ def main():
         blocks = sum((c + K + W + 2 + 15) // 16 for c in ctx) + 64
         eng = ColocatedEngine(cfg, CacheConfig(block_size=16), device="cuda", max_batch_size=B, max_prefill_tokens=B,
                               num_blocks=blocks, enable_cuda_graph=True)
+        for layer in eng.executor.attn.values():
+            layer.set_route_skew(args.route_skew)
         eng.executor.kv_cache.normal_(0, 0.5)      # synthetic KV history (the reference fills its cache with randn too)
         eng.executor.capture([B])
         first = torch.randint(0, cfg.vocab_size, (B,), generator=g).tolist()
         for i in range(B):
             eng.add_synthetic_request(i, ctx[i], first[i], K + W + 1)
         runner = eng
-        parallelism = "colocated1 (attention + 8 experts on one GPU)"
+        parallelism = f"colocated1 (attention + {cfg.num_experts} experts on one GPU)" + \
+            (f", Zipf({args.route_skew}) expert popularity" if args.route_skew > 0 else "")
 
     def sync_all():
         torch.cuda.synchronize()

@@ -26,6 +26,7 @@ def main():
     ap.add_argument("--ctx-min", type=int, default=192)
     ap.add_argument("--ctx-max", type=int, default=1536)
     ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--graph", action="store_true", help="replay the captured CUDA graph instead of eager launches")
     args = ap.parse_args()
     cfg = get_preset(args.model).clone(num_layers=args.layers)
     g = torch.Generator().manual_seed(0)
@@ -33,8 +34,10 @@ def main():
     ctx = torch.randint(args.ctx_min, args.ctx_max + 1, (B,), generator=g).tolist()
     blocks = sum((c + args.steps + 18) // 16 for c in ctx) + 64
     eng = ColocatedEngine(cfg, CacheConfig(block_size=16), device="cuda", max_batch_size=B, max_prefill_tokens=B,
-                          num_blocks=blocks, enable_cuda_graph=False)
+                          num_blocks=blocks, enable_cuda_graph=args.graph)
     eng.executor.kv_cache.normal_(0, 0.5)
+    if args.graph:
+        eng.executor.capture([B])
     first = torch.randint(0, cfg.vocab_size, (B,), generator=g).tolist()
     for i in range(B):
         eng.add_synthetic_request(i, ctx[i], first[i], args.steps + 1)
@@ -43,7 +46,8 @@ def main():
         eng.step()
     torch.cuda.synchronize()
     ms = [a.elapsed_time(b) for a, b in eng.event_pairs]
-    print(f"layers={args.layers} batch={B} steps={args.steps} ms/step={ms} launches/step={9 * args.layers + 4}")
+    ms = [round(x, 2) for x in ms]
+    print(f"layers={args.layers} batch={B} steps={args.steps} graph={args.graph} ms/step={ms} launches/step={9 * args.layers + 4}")
 
 
 if __name__ == "__main__":

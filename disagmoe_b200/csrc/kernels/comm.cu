@@ -150,7 +150,7 @@ extern "C" int dmoe_dispatch_remote(const void* y, long long ld_y, const int* to
                                     const void* cnt_bases, const void* flag_bases, int* epoch, int* status,
                                     int tok_lo, int tok_hi, void* stream) {
   if (H % 8 != 0 || E > kMaxExpertsComm || experts_per_rank < 1 || n_dst < 1 || n_dst > kMaxRanksComm ||
-      n_dst * experts_per_rank != E || epoch == nullptr)
+      n_dst * experts_per_rank < E || (n_dst - 1) * experts_per_rank >= E || epoch == nullptr)
     return -10;
   DispatchRemoteArgs a;
   a.y = static_cast<const __nv_bfloat16*>(y); a.ld_y = ld_y; a.topk_ids = topk_ids; a.topk_w = topk_w;

@@ -72,11 +72,11 @@ int dmoe_paged_attention(const void* q, long long ld_q, const void* kcache, cons
 // (RMSNorm ->) gate -> softmax -> top-k (-> renormalise); counts[e] += tokens routed to e (may be NULL).
 int dmoe_route(const void* x, long long ld_x, const void* norm_w, float eps, const void* gate_w, int T, int H, int E,
                int K, int renorm, void* y, long long ld_y, int* topk_ids, float* topk_w, float* logits_out, int* counts,
-               void* stream);
+               const float* logit_bias, void* stream);
 int dmoe_route_ex(const void* x, long long ld_x, const void* norm_w, float eps, const void* gate_w, int T, int H, int E,
                   int K, int renorm, void* y, long long ld_y, int* topk_ids, float* topk_w, int* counts,
                   const void* add_ptrs, int n_add, long long ld_add, void* resid_out, long long ld_resid, int count_lo,
-                  int count_hi, void* stream);
+                  int count_hi, const float* logit_bias, void* stream);
 // Sort-by-expert copy of the routed rows plus their 16-byte records; ws = ints [counts E | cursor E | ticket].
 int dmoe_dispatch_local(const void* y, long long ld_y, const int* topk_ids, const float* topk_w, int T, int K, int H,
                         int E, int experts_per_rank, int my_rank, int* ws, int* offs, const void* x_bases,

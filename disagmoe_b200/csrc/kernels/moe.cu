@@ -36,7 +36,8 @@ route_kernel(const __nv_bfloat16* __restrict__ x, long long ld_x, const __nv_bfl
              const __nv_bfloat16* __restrict__ gate_w, int H, int E, int K, int renorm,
              __nv_bfloat16* __restrict__ y, long long ld_y, int* __restrict__ topk_ids, float* __restrict__ topk_w,
              float* __restrict__ logits_out, int* __restrict__ counts, const void* const* __restrict__ add_ptrs, int n_add,
-             long long ld_add, __nv_bfloat16* __restrict__ resid_out, long long ld_resid, int count_lo, int count_hi) {
+             long long ld_add, __nv_bfloat16* __restrict__ resid_out, long long ld_resid, int count_lo, int count_hi,
+             const float* __restrict__ logit_bias) {
   extern __shared__ float srow[];            // [H] normalised row (fp32, as rounded to bf16)
   __shared__ float red[32];
   __shared__ float slog[kMaxExperts];
@@ -118,6 +119,7 @@ route_kernel(const __nv_bfloat16* __restrict__ x, long long ld_x, const __nv_bfl
     }
   }
   __syncthreads();
+  if (gate_w == nullptr) return;   // reduction + normalisation only (a dense-FFN layer has no router)
 
   // gate logits: warp w takes experts w, w + nw, ...
   for (int e = warp; e < E; e += nw) {
@@ -132,7 +134,8 @@ route_kernel(const __nv_bfloat16* __restrict__ x, long long ld_x, const __nv_bfl
       }
     }
     acc = warp_sum(acc);
-    if (lane == 0) slog[e] = acc;
+    // the optional bias skews expert popularity (synthetic load-imbalance experiments); it enters the softmax too
+    if (lane == 0) slog[e] = acc + (logit_bias != nullptr ? logit_bias[e] : 0.f);
   }
   __syncthreads();
 
@@ -163,7 +166,19 @@ route_kernel(const __nv_bfloat16* __restrict__ x, long long ld_x, const __nv_bfl
         const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
         if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
       }
-      wsel[k] = __expf(best - mx) / sum;
+      if (bi >= E) {
+        // no finite logit left (NaN activations): fall back to the lowest expert not chosen yet with weight 0, so
+        // that the ids stay valid and the damage stays visible in the output instead of corrupting the dispatch
+        bi = 0;
+        for (bool again = true; again;) {
+          again = false;
+          for (int j = 0; j < k; ++j)
+            if (isel[j] == bi) { ++bi; again = true; }
+        }
+        wsel[k] = 0.f;
+      } else {
+        wsel[k] = __expf(best - mx) / sum;
+      }
       isel[k] = bi;
       wtot += wsel[k];
       __syncwarp();
@@ -173,7 +188,7 @@ route_kernel(const __nv_bfloat16* __restrict__ x, long long ld_x, const __nv_bfl
     if (lane == 0) {
       for (int k = 0; k < K; ++k) {
         topk_ids[t * K + k] = isel[k];
-        topk_w[t * K + k] = renorm ? wsel[k] / wtot : wsel[k];
+        topk_w[t * K + k] = (renorm && wtot > 0.f) ? wsel[k] / wtot : wsel[k];
         if (counts != nullptr && t >= count_lo && t < count_hi) atomicAdd(&counts[isel[k]], 1);
       }
     }
@@ -263,7 +278,7 @@ using namespace dmoe;
 
 extern "C" int dmoe_route(const void* x, long long ld_x, const void* norm_w, float eps, const void* gate_w, int T, int H,
                           int E, int K, int renorm, void* y, long long ld_y, int* topk_ids, float* topk_w,
-                          float* logits_out, int* counts, void* stream) {
+                          float* logits_out, int* counts, const float* logit_bias, void* stream) {
   if (H % 8 != 0 || H > kRouteThreads * kRouteMaxVec * 8 || E > kMaxExperts || K > kMaxTopK || K > E) return -10;
   if (T == 0) return 0;
   static bool configured = false;
@@ -274,25 +289,27 @@ extern "C" int dmoe_route(const void* x, long long ld_x, const void* norm_w, flo
   route_kernel<<<T, kRouteThreads, H * sizeof(float), static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), ld_x, static_cast<const __nv_bfloat16*>(norm_w), eps,
       static_cast<const __nv_bfloat16*>(gate_w), H, E, K, renorm, static_cast<__nv_bfloat16*>(y), ld_y, topk_ids, topk_w,
-      logits_out, counts, nullptr, 0, 0, nullptr, 0, 0, T);
+      logits_out, counts, nullptr, 0, 0, nullptr, 0, 0, T, logit_bias);
   return static_cast<int>(cudaGetLastError());
 }
 
 // Same router with the tensor-parallel reduction folded in: x + sum of n_add partial rows (device array of pointers,
 // typically the TP peers' o_proj outputs) is written to resid_out and normalised; only tokens in [count_lo, count_hi)
-// enter the expert histogram (the slice this rank dispatches).
+// enter the expert histogram (the slice this rank dispatches). gate_w == nullptr stops after the normalised rows
+// (layers with a dense FFN). logit_bias (fp32 [E], optional) is added to the gate logits.
 extern "C" int dmoe_route_ex(const void* x, long long ld_x, const void* norm_w, float eps, const void* gate_w, int T,
                              int H, int E, int K, int renorm, void* y, long long ld_y, int* topk_ids, float* topk_w,
                              int* counts, const void* add_ptrs, int n_add, long long ld_add, void* resid_out,
-                             long long ld_resid, int count_lo, int count_hi, void* stream) {
-  if (H % 8 != 0 || H > kRouteThreads * kRouteMaxVec * 8 || E > kMaxExperts || K > kMaxTopK || K > E) return -10;
+                             long long ld_resid, int count_lo, int count_hi, const float* logit_bias, void* stream) {
+  if (H % 8 != 0 || H > kRouteThreads * kRouteMaxVec * 8) return -10;
+  if (gate_w != nullptr && (E > kMaxExperts || K > kMaxTopK || K > E)) return -10;
   if (T == 0) return 0;
   cudaFuncSetAttribute(route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 8192 * 4);
   route_kernel<<<T, kRouteThreads, H * sizeof(float), static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), ld_x, static_cast<const __nv_bfloat16*>(norm_w), eps,
       static_cast<const __nv_bfloat16*>(gate_w), H, E, K, renorm, static_cast<__nv_bfloat16*>(y), ld_y, topk_ids, topk_w,
       nullptr, counts, static_cast<const void* const*>(add_ptrs), n_add, ld_add, static_cast<__nv_bfloat16*>(resid_out),
-      ld_resid, count_lo, count_hi);
+      ld_resid, count_lo, count_hi, logit_bias);
   return static_cast<int>(cudaGetLastError());
 }
 

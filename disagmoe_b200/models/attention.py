@@ -62,6 +62,7 @@ class MoEAttention(torch.nn.Module):
         self.weighted_router: Optional[torch.Tensor] = None   # expert popularity for trace-weighted routing
         self._gen: Optional[torch.Generator] = None
         self.counts: Optional[torch.Tensor] = None            # device histogram fed to the dispatch kernel
+        self.route_bias: Optional[torch.Tensor] = None        # fp32 [E] added to the gate logits (popularity skew)
 
     # ---- weights ------------------------------------------------------------------------------------------
     def param_names(self):
@@ -140,10 +141,42 @@ class MoEAttention(torch.nn.Module):
     def route(self, resid2: torch.Tensor, want_logits: bool = False):
         cfg = self.cfg
         y, ids, w, logits = F.route(resid2, self.post_ln, cfg.rms_norm_eps, self.gate_w, cfg.top_k, cfg.norm_topk_prob,
-                                    counts=self.counts if resid2.is_cuda else None, want_logits=want_logits)
+                                    counts=self.counts if resid2.is_cuda else None, want_logits=want_logits,
+                                    logit_bias=self.route_bias)
         if self.weighted_router is not None:
             ids, w = self._random_routing_with_weights(resid2.shape[0], resid2.device)
         return y, ids, w, logits
+
+    def set_route_skew(self, zipf_alpha: float) -> None:
+        """Skews expert popularity towards a Zipf(alpha) distribution over expert ids (expert 0 the most popular) by
+        adding log-popularity to the gate logits; alpha = 0 removes the skew. Stays on the device (graph-capturable),
+        unlike the trace-weighted sampling below."""
+        if self.is_dense:
+            return
+        if zipf_alpha <= 0:
+            self.route_bias = None
+            return
+        E = self.cfg.num_experts
+        pop = 1.0 / torch.arange(1, E + 1, dtype=torch.float64) ** zipf_alpha
+        self.route_bias = torch.log(pop / pop.sum()).float().to(self.device)
+
+    def shared_experts(self, y: torch.Tensor, resid: torch.Tensor) -> torch.Tensor:
+        """resid += shared_expert(y) (times sigmoid(y . g) for a gated shared expert), in place."""
+        if self.shared_w13 is None:
+            return resid
+        if self.shared_gate is None:
+            return self._ffn(y, self.shared_w13, self.shared_w2, resid)
+        sh = self._ffn(y, self.shared_w13, self.shared_w2, None)
+        g = torch.sigmoid(y.float() @ self.shared_gate.float().T)
+        resid.copy_((resid.float() + sh.float() * g).to(resid.dtype))
+        return resid
+
+    def dense_ffn(self, resid: torch.Tensor, h: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """resid += mlp(rmsnorm(resid)) for a layer with a dense FFN, in place (h: the normalised rows if the
+        caller already has them)."""
+        if h is None:
+            h = F.rmsnorm(resid, self.post_ln, self.cfg.rms_norm_eps)
+        return self._ffn(h, self.mlp_w13, self.mlp_w2, resid)
 
     def _random_routing_with_weights(self, T: int, device) -> Tuple[torch.Tensor, torch.Tensor]:
         """Trace-weighted routing: expert ids sampled without replacement from a popularity vector
@@ -163,16 +196,9 @@ class MoEAttention(torch.nn.Module):
         cfg = self.cfg
         resid2 = self.attention(resid, parts, kv_cache, meta)
         if self.is_dense:
-            h2 = F.rmsnorm(resid2, self.post_ln, cfg.rms_norm_eps)
-            return AttnOutput(None, self._ffn(h2, self.mlp_w13, self.mlp_w2, resid2), None, None)
+            return AttnOutput(None, self.dense_ffn(resid2), None, None)
         y, ids, w, logits = self.route(resid2, want_logits)
-        if self.shared_w13 is not None:
-            if self.shared_gate is None:
-                resid2 = self._ffn(y, self.shared_w13, self.shared_w2, resid2)
-            else:
-                sh = self._ffn(y, self.shared_w13, self.shared_w2, None)
-                g = torch.sigmoid(y.float() @ self.shared_gate.float().T)
-                resid2.copy_((resid2.float() + sh.float() * g).to(resid2.dtype))
+        resid2 = self.shared_experts(y, resid2)
         out = AttnOutput(y, resid2, w, ids)
         out.router_logits = logits
         return out

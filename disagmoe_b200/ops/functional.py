@@ -187,11 +187,12 @@ def gather_ptrs(ptrs: torch.Tensor, n: int, H: int, out: torch.Tensor) -> torch.
 
 def route(x: torch.Tensor, norm_w: Optional[torch.Tensor], eps: float, gate_w: torch.Tensor, top_k: int,
           renormalize: bool = True, y: Optional[torch.Tensor] = None, counts: Optional[torch.Tensor] = None,
-          want_logits: bool = False):
+          want_logits: bool = False, logit_bias: Optional[torch.Tensor] = None):
     """(RMSNorm ->) gate -> softmax -> top-k. Returns (y, topk_ids int32 [T,k], topk_w fp32 [T,k], logits or None).
-    ``counts`` (int32 [E], device) is incremented per routed (token, k) pair."""
+    ``counts`` (int32 [E], device) is incremented per routed (token, k) pair. ``logit_bias`` (fp32 [E]) is added to
+    the gate logits (synthetic popularity skew)."""
     if not x.is_cuda:
-        yy, ids, w, logits = reference.route(x, norm_w, eps, gate_w, top_k, renormalize)
+        yy, ids, w, logits = reference.route(x, norm_w, eps, gate_w, top_k, renormalize, logit_bias)
         if counts is not None:
             counts += torch.bincount(ids.reshape(-1).long(), minlength=gate_w.shape[0]).int()
         if y is not None:
@@ -206,10 +207,11 @@ def route(x: torch.Tensor, norm_w: Optional[torch.Tensor], eps: float, gate_w: t
     w = torch.empty(T, top_k, dtype=torch.float32, device=x.device)
     logits = torch.empty(T, E, dtype=torch.float32, device=x.device) if want_logits else None
     assert gate_w.is_contiguous() and gate_w.dtype == torch.bfloat16 and x.stride(1) == 1
+    assert logit_bias is None or (logit_bias.dtype == torch.float32 and logit_bias.is_cuda and logit_bias.numel() == E)
     _lib.check(_lib.lib().dmoe_route(
         _vp(x), c_ll(x.stride(0)), _vp(norm_w), c_float(eps), _vp(gate_w), c_int(T), c_int(H), c_int(E), c_int(top_k),
-        c_int(int(renormalize)), _vp(y), c_ll(y.stride(0)), _vp(ids), _vp(w), _vp(logits), _vp(counts), _st()),
-        "dmoe_route")
+        c_int(int(renormalize)), _vp(y), c_ll(y.stride(0)), _vp(ids), _vp(w), _vp(logits), _vp(counts),
+        _vp(logit_bias), _st()), "dmoe_route")
     return y, ids, w, logits
 
 

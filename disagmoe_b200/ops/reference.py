@@ -83,10 +83,13 @@ def paged_attention(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
 
 
 def route(x: torch.Tensor, norm_w: Optional[torch.Tensor], eps: float, gate_w: torch.Tensor, top_k: int,
-          renormalize: bool) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+          renormalize: bool, logit_bias: Optional[torch.Tensor] = None
+          ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
     """(y, topk_ids int32 [T,k], topk_w fp32 [T,k], logits fp32): y = rmsnorm(x) (or x), softmax -> top-k."""
     y = rmsnorm(x, norm_w, eps) if norm_w is not None else x
     logits = y.float() @ gate_w.float().T
+    if logit_bias is not None:
+        logits = logits + logit_bias.float().to(logits.device)
     probs = torch.softmax(logits, dim=-1)
     w, ids = torch.topk(probs, top_k, dim=-1)
     if renormalize:

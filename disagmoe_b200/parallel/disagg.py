@@ -57,7 +57,8 @@ class DisaggShape:
 
     @property
     def experts_per_rank(self) -> int:
-        return self.num_experts // self.n_expert
+        # experts are dealt out in contiguous blocks of ceil(E / X); the last expert rank may hold fewer
+        return (self.num_experts + self.n_expert - 1) // self.n_expert
 
     @property
     def region_cap(self) -> int:   # rows of one expert's receive region: every sender could route all its pairs to it
@@ -75,7 +76,12 @@ def build_layout(s: DisaggShape) -> ArenaLayout:
         L.add(f"parts{m}", s.batch * s.top_k * s.hidden * 2)
         L.add(f"comb_flag{m}", s.n_expert * 4)
         if s.tp > 1:
-            L.add(f"opart{m}", s.batch * s.hidden * 2)     # this rank's o_proj partial sums, read by its TP peers
+            # this rank's o_proj partial sums, read by its TP peers. Two buffers used by layer parity: a peer may
+            # still read layer l's partials while this rank already writes layer l + 1's (nothing else orders the two
+            # when layer l has a dense FFN and so no round trip through the expert GPUs); by layer l + 2 the peer's
+            # own layer l + 1 signal proves it is done with layer l
+            L.add(f"opart{m}_0", s.batch * s.hidden * 2)
+            L.add(f"opart{m}_1", s.batch * s.hidden * 2)
             L.add(f"oflag{m}", s.tp * 4)
     return L
 
@@ -128,9 +134,9 @@ class AttentionRank:
             if self.tp > 1:
                 group = [self.group0 + i for i in range(self.tp)]
                 d.update(
-                    opart=arena.view(layout.offset(f"opart{m}"), (B, H), dt),
+                    opart=[arena.view(layout.offset(f"opart{m}_{p}"), (B, H), dt) for p in range(2)],
                     oflag=arena.view(layout.offset(f"oflag{m}"), (self.tp,), torch.int32),
-                    opart_ptrs=arena.ptr_table(group, layout.offset(f"opart{m}")),
+                    opart_ptrs=[arena.ptr_table(group, layout.offset(f"opart{m}_{p}")) for p in range(2)],
                     oflag_ptrs=arena.ptr_table(group, layout.offset(f"oflag{m}")),
                     o_signal_epoch=z(1), o_wait_epoch=z(1), o_ticket=z(1),
                     y=torch.zeros(B, H, dtype=dt, device=dev), topk_ids=z(B, k),
@@ -157,7 +163,7 @@ class AttentionRank:
         parallelism the o_proj partial sum goes to this rank's peer-visible buffer and the GEMM signals the TP peers."""
         d, S, cfg = self.mb[m], self.shape, self.cfg
         parts = None
-        if l > 0:
+        if l > 0 and not cfg.is_dense_layer(l - 1):     # a dense-FFN layer sends nothing to the expert GPUs
             _lib.check(_lib.lib().dmoe_wait_flags(_vp(d["comb_flag"]), c_int(S.n_expert), _vp(d["wait_epoch"]),
                                                   _vp(self.status), c_vp(_lib.stream_ptr())), "dmoe_wait_flags")
             parts = d["parts"]
@@ -176,7 +182,7 @@ class AttentionRank:
                                  splits=F.pick_attn_splits(S.batch, a.num_kv_heads, cfg.max_seq_len, self.block_size))
         sig = gemm.GemmComm(signal_ptrs=d["oflag_ptrs"], n_signal=self.tp, signal_slot=self.tp_rank,
                             signal_epoch=d["o_signal_epoch"], done_ticket=d["o_ticket"])
-        gemm.linear(attn, a.o_w, out=d["opart"], comm=sig)
+        gemm.linear(attn, a.o_w, out=d["opart"][l % 2], comm=sig)
 
     def layer_route_dispatch(self, l: int, m: int) -> None:
         """Post-attention RMSNorm + router + dispatch. With tensor parallelism the router kernel first sums the TP
@@ -185,6 +191,9 @@ class AttentionRank:
         d, S, cfg = self.mb[m], self.shape, self.cfg
         a = self.layers[l]
         lo, hi = 0, S.batch
+        if a.is_dense and self.tp == 1:
+            a.dense_ffn(d["resid"])
+            return
         if self.tp == 1:
             a.counts = d["ws"][:S.num_experts]
             y, ids, w, _ = a.route(d["resid2"])
@@ -197,15 +206,23 @@ class AttentionRank:
             _lib.check(_lib.lib().dmoe_route_ex(
                 _vp(d["resid"]), c_ll(S.hidden), _vp(a.post_ln), ctypes.c_float(cfg.rms_norm_eps), _vp(a.gate_w),
                 c_int(S.batch), c_int(S.hidden), c_int(S.num_experts), c_int(S.top_k), c_int(int(cfg.norm_topk_prob)),
-                _vp(y), c_ll(S.hidden), _vp(ids), _vp(w), _vp(d["ws"]), _vp(d["opart_ptrs"]), c_int(self.tp),
-                c_ll(S.hidden), _vp(d["resid"]), c_ll(S.hidden), c_int(lo), c_int(hi), c_vp(_lib.stream_ptr())),
-                "dmoe_route_ex")
+                _vp(y), c_ll(S.hidden), _vp(ids), _vp(w), _vp(d["ws"]), _vp(d["opart_ptrs"][l % 2]), c_int(self.tp),
+                c_ll(S.hidden), _vp(d["resid"]), c_ll(S.hidden), c_int(lo), c_int(hi), _vp(a.route_bias),
+                c_vp(_lib.stream_ptr())), "dmoe_route_ex")
+            if a.is_dense:
+                # the router kernel ran without a gate: it summed the TP partials into the residual stream and
+                # normalised it; every TP rank then applies the (replicated) dense FFN to all rows
+                a.dense_ffn(d["resid"], h=y)
+                return
         _lib.check(_lib.lib().dmoe_dispatch_remote(
             _vp(y), c_ll(y.stride(0)), _vp(ids), _vp(w), c_int(S.batch), c_int(S.top_k), c_int(S.hidden),
             c_int(S.num_experts), c_int(S.experts_per_rank), c_int(S.n_expert), c_int(self.a), c_int(S.region_cap),
             _vp(d["ws"]), _vp(d["x_bases"]), c_ll(S.hidden), _vp(d["rec_bases"]), _vp(d["cnt_bases"]),
             _vp(d["flag_bases"]), _vp(d["disp_epoch"]), _vp(self.status), c_int(lo), c_int(hi),
             c_vp(_lib.stream_ptr())), "dmoe_dispatch_remote")
+        # shared experts stay on the attention GPU and run while the expert GPUs work on the rows just sent
+        # (replicated over the ranks of a TP group)
+        a.shared_experts(y, d["resid"])
 
     def head(self, m: int) -> None:
         d, S, cfg = self.mb[m], self.shape, self.cfg
@@ -238,7 +255,11 @@ class ExpertRank:
         epr = S.experts_per_rank
         self.layers: List[MoEExperts] = []
         for l in range(cfg.num_layers):
-            e = MoEExperts(cfg, l, expert_rank * epr, (expert_rank + 1) * epr, device=dev, dtype=torch.bfloat16)
+            if cfg.is_dense_layer(l):
+                self.layers.append(None)
+                continue
+            e = MoEExperts(cfg, l, expert_rank * epr, min((expert_rank + 1) * epr, cfg.num_experts), device=dev,
+                           dtype=torch.bfloat16)
             e.load_weights(state_dict) if state_dict is not None else e.init_weights()
             self.layers.append(e)
         rows = epr * S.region_cap
@@ -263,6 +284,8 @@ class ExpertRank:
     def layer(self, l: int, m: int) -> None:
         d, S = self.mb[m], self.shape
         e = self.layers[l]
+        if e is None:
+            return
         gate = gemm.GemmComm(seg_cnt=d["cnt"], seg_cap=S.region_cap, group_regions=True, wait_flags=d["flag"],
                              n_wait=S.n_attn, wait_epoch=d["wait_epoch"], done_ticket=self.ticket)
         gemm.grouped_swiglu(d["rows"], e.w13_weight, None, out=self.act, bn=self.bn, comm=gate)
@@ -282,11 +305,13 @@ class DisaggDecodeBench:
     """Decode-throughput runner used by ``bench.py`` for N >= 2 GPUs (one process per GPU, NCCL only for bootstrap)."""
 
     def __init__(self, cfg: ModelConfig, world: int, rank: int, local_rank: int, batch: int, ctx_min: int, ctx_max: int,
-                 total_steps: int, gen: torch.Generator, n_mb: int = 2, tp: int = 1):
+                 total_steps: int, gen: torch.Generator, n_mb: int = 2, tp: int = 1, n_attn: int = 0,
+                 route_skew: float = 0.0):
         import torch.distributed as dist
-        assert world % 2 == 0, "needs an even number of GPUs: half attention, half experts"
-        A = X = world // 2
-        assert cfg.num_experts % X == 0 and A % tp == 0
+        A = n_attn or world // 2
+        X = world - A
+        assert 1 <= A < world and A % tp == 0, "ranks [0, A) are attention GPUs, the rest hold experts"
+        assert (X - 1) * ((cfg.num_experts + X - 1) // X) < cfg.num_experts, "an expert GPU would hold no expert"
         self.cfg, self.world, self.rank = cfg, world, rank
         # a TP group of `tp` attention GPUs serves tp x batch sequences per micro-batch (per-GPU load stays `batch`)
         batch = batch * tp
@@ -299,7 +324,8 @@ class DisaggDecodeBench:
         self.arena = PeerArena.create(self.layout.size, device=self.device)
         self.is_attn = rank < A
         self.parallelism = f"attn dp{A // tp}" + (f" x tp{tp}" if tp > 1 else "") + \
-            f" x {n_mb} micro-batches + expert ep{X} ({cfg.num_experts // X} experts/GPU), fused peer-memory dispatch/combine"
+            f" x {n_mb} micro-batches + expert ep{X} (up to {self.shape.experts_per_rank} experts/GPU), " \
+            "fused peer-memory dispatch/combine" + (f", Zipf({route_skew}) expert popularity" if route_skew > 0 else "")
         self.h2d_bytes_last = self.d2h_bytes_last = 0
         self.profile_events = False
         self.event_pairs = []
@@ -309,6 +335,8 @@ class DisaggDecodeBench:
             ctx = torch.randint(ctx_min, ctx_max + 1, (n_mb * B,), generator=gen).tolist()
             blocks = sum((c + total_steps + 2 + 15) // 16 for c in ctx) + 64
             self.runner = AttentionRank(cfg, self.shape, self.arena, self.layout, rank, blocks)
+            for layer in self.runner.layers:
+                layer.set_route_skew(route_skew)
             self.runner.kv_cache.normal_(0, 0.5)
             self.block_mgr = C.BlockManager(16, blocks, 0, n_mb * B)
             self.lens = ctx

@@ -13,10 +13,23 @@ from disagmoe_b200.parallel.peer import PeerArena
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("A,X,n_mb", [(1, 1, 1), (2, 2, 2), (1, 4, 2)])
-def test_emulated_disagg_matches_colocated(A, X, n_mb):
-    cfg = tiny_config.clone(dtype=torch.bfloat16, num_layers=3)
+def _model(variant, num_layers):
+    """'mixtral': routed experts only. 'shared_dense': first layer with a dense FFN, a sigmoid-gated shared expert next to
+    the routed ones and a Zipf(1.2) popularity skew on the router (the Qwen-MoE / DeepSeek-V2-Lite layer types)."""
+    cfg = tiny_config.clone(dtype=torch.bfloat16, num_layers=num_layers)
+    skew = 0.0
+    if variant == "shared_dense":
+        cfg = cfg.clone(first_k_dense=1, dense_intermediate_size=768, num_shared_experts=1, shared_intermediate_size=512,
+                        shared_expert_gate=True, norm_topk_prob=False)
+        skew = 1.2
     sd = {k: v.to(torch.bfloat16) for k, v in init_state_dict(cfg, dtype=torch.float32).items()}
+    return cfg, sd, skew
+
+
+@pytest.mark.parametrize("A,X,n_mb,variant", [(1, 1, 1, "mixtral"), (2, 2, 2, "mixtral"), (1, 4, 2, "mixtral"),
+                                              (2, 3, 2, "shared_dense"), (1, 3, 1, "mixtral")])
+def test_emulated_disagg_matches_colocated(A, X, n_mb, variant):
+    cfg, sd, skew = _model(variant, 3)
     B = 3 if n_mb * 3 * 4 <= 60 else 2
     shape = DisaggShape(A, X, n_mb, B, cfg.top_k, cfg.hidden_size, cfg.num_experts)
     layout = build_layout(shape)
@@ -25,6 +38,8 @@ def test_emulated_disagg_matches_colocated(A, X, n_mb):
     exps = [ExpertRank(cfg, shape, arenas[A + x], layout, x, state_dict=sd) for x in range(X)]
     ref = FusedModelExecutor(cfg, CacheConfig(block_size=16), device="cuda", max_batch_size=B, max_prefill_tokens=B,
                              state_dict=sd, num_blocks=64, enable_cuda_graph=False)
+    for layer in [x for a in attn for x in a.layers] + list(ref.attn.values()):
+        layer.set_route_skew(skew)
     g = torch.Generator().manual_seed(0)
     kv = torch.randn(ref.kv_cache.shape, generator=g).to(torch.bfloat16).cuda() * 0.5
     for step in range(2):   # two iterations: epochs and cleared histograms must carry over
@@ -71,12 +86,12 @@ def test_emulated_disagg_matches_colocated(A, X, n_mb):
             assert err < 0.03, f"rank {a} mb {m} step {step}: rel err {err}"
 
 
-@pytest.mark.parametrize("A,X,tp,n_mb", [(2, 1, 2, 1), (4, 2, 2, 2)])
-def test_emulated_tensor_parallel_attention(A, X, tp, n_mb):
+@pytest.mark.parametrize("A,X,tp,n_mb,variant", [(2, 1, 2, 1, "mixtral"), (4, 2, 2, 2, "mixtral"),
+                                                 (2, 3, 2, 2, "shared_dense")])
+def test_emulated_tensor_parallel_attention(A, X, tp, n_mb, variant):
     """Attention TP: head-sharded QKV / attention / o_proj per rank, o_proj partials reduced inside the router kernel
     from the peers' buffers, every rank dispatches its token slice, experts fan the combine out to the whole group."""
-    cfg = tiny_config.clone(dtype=torch.bfloat16, num_layers=2)
-    sd = {k: v.to(torch.bfloat16) for k, v in init_state_dict(cfg, dtype=torch.float32).items()}
+    cfg, sd, skew = _model(variant, 3 if variant == "shared_dense" else 2)
     B = 4
     shape = DisaggShape(A, X, n_mb, B, cfg.top_k, cfg.hidden_size, cfg.num_experts, tp)
     layout = build_layout(shape)
@@ -85,6 +100,8 @@ def test_emulated_tensor_parallel_attention(A, X, tp, n_mb):
     exps = [ExpertRank(cfg, shape, arenas[A + x], layout, x, state_dict=sd) for x in range(X)]
     ref = FusedModelExecutor(cfg, CacheConfig(block_size=16), device="cuda", max_batch_size=B, max_prefill_tokens=B,
                              state_dict=sd, num_blocks=64, enable_cuda_graph=False)
+    for layer in [x for a in attn for x in a.layers] + list(ref.attn.values()):
+        layer.set_route_skew(skew)
     g = torch.Generator().manual_seed(0)
     kv = torch.randn(ref.kv_cache.shape, generator=g).to(torch.bfloat16).cuda() * 0.5     # [L, 2, nb, bs, kvh, hd]
     kvh = cfg.num_kv_heads // tp
