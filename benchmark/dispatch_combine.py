@@ -93,7 +93,7 @@ class NcclPath:
         self.cfg, self.A, self.X, self.rank, self.T = cfg, A, X, rank, T
         self.x, self.gate_w, self.norm_w, self.experts = x, gate_w, norm_w, experts
         self.is_attn = rank < A
-        self.epr = cfg.num_experts // X
+        self.epr = (cfg.num_experts + X - 1) // X          # contiguous blocks; the last expert GPU may hold fewer
         self.dev = torch.device("cuda", torch.cuda.current_device())
 
     def run(self):
@@ -110,7 +110,7 @@ class NcclPath:
             order = torch.argsort(flat, stable=True)
             rows = h.index_select(0, order // k)                      # permute + duplicate
             per_expert = torch.bincount(flat, minlength=cfg.num_experts)
-            send_counts[A:] = per_expert.view(X, self.epr)
+            send_counts[A:] = torch.nn.functional.pad(per_expert, (0, X * self.epr - cfg.num_experts)).view(X, self.epr)
             meta = torch.stack([order.float(), wts.reshape(-1)[order]], 1)   # per-row metadata travelling with the rows
         else:
             rows = torch.empty(0, H, dtype=torch.bfloat16, device=dev)
@@ -129,8 +129,8 @@ class NcclPath:
             eid = torch.cat([torch.repeat_interleave(torch.arange(self.epr, device=dev), cnt[a]) for a in range(A)])
             perm = torch.argsort(eid, stable=True)
             xs = got.index_select(0, perm)
-            offs = cnt.sum(0).cumsum(0).int()
             e = self.experts
+            offs = cnt.sum(0).cumsum(0).int()[:e.num_experts]
             up = torch._grouped_mm(xs, e.w13_weight.transpose(1, 2), offs=offs)
             I = up.shape[1] // 2
             act = torch.nn.functional.silu(up[:, :I]) * up[:, I:]
@@ -164,7 +164,8 @@ def main():
     A = args.attn or world // 2
     X = world - A
     cfg = mixtral_config.clone(num_layers=1)
-    assert cfg.num_experts % X == 0
+    EPR = (cfg.num_experts + X - 1) // X
+    assert (X - 1) * EPR < cfg.num_experts, "an expert GPU would hold no expert"
     peak_tf, hbm_gbs, src = load_peaks()
     is_attn = rank < A
     H, I, E, k = cfg.hidden_size, cfg.intermediate_size, cfg.num_experts, cfg.top_k
@@ -177,8 +178,7 @@ def main():
     arena = PeerArena.create(layout_bytes, device=dev)
     experts_mod = None
     if not is_attn:
-        epr = E // X
-        experts_mod = MoEExperts(cfg, 0, (rank - A) * epr, (rank - A + 1) * epr, device=dev, dtype=torch.bfloat16)
+        experts_mod = MoEExperts(cfg, 0, (rank - A) * EPR, min((rank - A + 1) * EPR, E), device=dev, dtype=torch.bfloat16)
         experts_mod.init_weights()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     for T in sizes:
@@ -195,13 +195,13 @@ def main():
             er = ExpertRank.__new__(ExpertRank)
             er.cfg, er.shape, er.arena, er.layout, er.x, er.device = cfg, shape, arena, layout, rank - A, dev
             er.layers = [experts_mod]
-            rows = (E // X) * shape.region_cap
+            rows = EPR * shape.region_cap
             z = lambda *s: torch.zeros(*s, dtype=torch.int32, device=dev)
             er.act = torch.zeros(rows, I, dtype=torch.bfloat16, device=dev)
             er.ticket = z(1)
             er.mb = [dict(rows=arena.view(layout.offset("recv_rows0"), (rows, H), torch.bfloat16),
                           recs=arena.view(layout.offset("recv_recs0"), (rows, 4), torch.int32),
-                          cnt=arena.view(layout.offset("recv_cnt0"), (E // X,), torch.int32),
+                          cnt=arena.view(layout.offset("recv_cnt0"), (EPR,), torch.int32),
                           flag=arena.view(layout.offset("disp_flag0"), (A,), torch.int32),
                           wait_epoch=z(1), signal_epoch=z(1),
                           parts_bases=arena.ptr_table(list(range(A)), layout.offset("parts0")),
@@ -257,10 +257,10 @@ def main():
         if rank == 0:
             pairs = A * T * k
             flops = 2.0 * pairs * 3 * H * I                        # whole job
-            t_compute = flops / X / (peak_tf * 1e12)               # per expert GPU, even routing
-            nv_bytes = max(T * k * H * 2.0, pairs * H * 2.0 / X)   # per direction: what one attention GPU sends / one expert GPU receives
+            t_compute = flops * EPR / E / (peak_tf * 1e12)         # the fullest expert GPU (EPR of E experts), even routing
+            nv_bytes = max(T * k * H * 2.0, pairs * H * 2.0 * EPR / E)   # per direction: what one attention GPU sends / one expert GPU receives
             t_link = nv_bytes / (NVLINK_GBS * 1e9)
-            t_hbm = (E // X) * 3 * H * I * 2.0 / (hbm_gbs * 1e9)
+            t_hbm = EPR * 3 * H * I * 2.0 / (hbm_gbs * 1e9)
             roof = max(t_compute, t_link)
             roof_hbm = max(roof, t_hbm)
             line = {"tokens_per_attn_gpu": T, "split": f"{A}+{X}", "peaks": src, "kernel_status": int(st),
