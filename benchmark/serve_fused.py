@@ -1,0 +1,120 @@
+"""Open-loop serving benchmark on the fused disaggregated data plane (one process per GPU):
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29600 \
+        benchmark/serve_fused.py --model mixtral --n-attn 4 --attn-tp 4 -r 16 -n 256 \
+        --min-input-len 128 -i 1024 --min-output-len 64 -o 512
+
+Every rank builds the same synthetic workload from the seed (Poisson arrivals, uniform prompt / output lengths,
+uniform random token ids); request i belongs to attention group i mod (number of groups), so no request ever travels
+between processes. Rank 0 gathers the per-request timestamps and prints the same metrics as
+``benchmark.benchmark_serving`` (request / token throughput, request latency, inter-token latency and time to first
+token: mean / median / p99), the share of iterations that replayed a CUDA graph, and the device status word.
+``--check`` replays the same requests through the single-GPU colocated engine on rank 0 afterwards and reports the
+fraction of generated tokens that agree (greedy decoding; bf16 reduction orders differ, so near-ties may flip).
+"""
+import argparse
+import json
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from benchmark.benchmark_serving import analyze_results
+from benchmark.workload import get_generator
+from disagmoe_b200.config import CacheConfig, get_preset
+from disagmoe_b200.parallel.serving import FusedServingRank
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", default="mixtral")
+    ap.add_argument("-L", "--num-layers", type=int, default=0)
+    ap.add_argument("--n-attn", type=int, default=0)
+    ap.add_argument("--attn-tp", type=int, default=1)
+    ap.add_argument("-r", "--rate", type=float, default=8.0, help="requests per second over the whole job; 0 = all at once")
+    ap.add_argument("-n", "--num-requests", type=int, default=64)
+    ap.add_argument("--min-input-len", type=int, default=128)
+    ap.add_argument("-i", "--max-input-len", type=int, default=1024)
+    ap.add_argument("--min-output-len", type=int, default=64)
+    ap.add_argument("-o", "--max-output-len", type=int, default=512)
+    ap.add_argument("--generator-type", default="poisson")
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--max-seqs-per-mb", type=int, default=128)
+    ap.add_argument("--max-tokens-per-mb", type=int, default=2048)
+    ap.add_argument("--max-prefill-tokens-per-mb", type=int, default=0)
+    ap.add_argument("--num-blocks", type=int, default=16384)
+    ap.add_argument("--route-skew", type=float, default=0.0)
+    ap.add_argument("--time-limit", type=float, default=600.0)
+    ap.add_argument("--check", action="store_true")
+    ap.add_argument("-f", "--file", default="", help="append the metrics as one JSON line")
+    args = ap.parse_args()
+
+    rank, world, lr = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(lr)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", lr))
+    cfg = get_preset(args.model)
+    if args.num_layers:
+        cfg = cfg.clone(num_layers=args.num_layers)
+    cfg = cfg.clone(dtype=torch.bfloat16)
+    A = args.n_attn or world // 2
+    tp = args.attn_tp
+    groups = A // tp
+
+    Gen = get_generator(args.generator_type if args.rate > 0 else "offline")
+    gen = Gen(max(args.rate, 1e-9), 1.0, args.min_input_len, args.max_input_len, args.seed, args.min_output_len,
+              args.max_output_len)
+    wl = gen.generate_num(args.num_requests)
+    rng = np.random.default_rng(args.seed + 1)
+    reqs = []
+    for i in range(len(wl)):
+        at, n_in = wl[i]
+        n_out = int(wl.output_lens[i]) if len(wl.output_lens) else args.max_output_len
+        reqs.append((i, rng.integers(0, cfg.vocab_size, int(n_in)).tolist(), n_out, float(at)))
+
+    srv = FusedServingRank(cfg, world, rank, lr, A, tp, max_seqs_per_mb=args.max_seqs_per_mb,
+                           max_tokens_per_mb=args.max_tokens_per_mb, num_blocks=args.num_blocks,
+                           route_skew=args.route_skew,
+                           max_prefill_tokens_per_mb=args.max_prefill_tokens_per_mb or None)
+    mine = [r for r in reqs if srv.is_leader and r[0] % groups == rank // tp]
+    res = srv.serve(mine, time_limit=args.time_limit)
+    gathered = [None] * world if rank == 0 else None
+    dist.gather_object(res, gathered, dst=0, group=srv.ctl)
+    if rank == 0:
+        slo = [s for g in gathered for s in g["slo"]]
+        arrivals = {k: v for g in gathered for k, v in g["arrivals"].items()}
+        duration = max(g["duration"] for g in gathered)
+        m = analyze_results(slo, arrivals, duration)
+        print(m)
+        its = gathered[0]["iterations"]
+        extra = {"iterations": its, "graph_iterations": gathered[0]["graph_iterations"],
+                 "kernel_status": max(g["kernel_status"] for g in gathered), "requests_finished": len(slo),
+                 "layout": f"{groups} attention group(s) x tp{tp} + {world - A} expert GPUs"}
+        print(json.dumps(extra))
+        if args.check:
+            from disagmoe_b200.frontend.colocated import ColocatedEngine
+            outs = {k: v for g in gathered for k, v in g.get("outputs", {}).items()}
+            del srv
+            torch.cuda.empty_cache()
+            eng = ColocatedEngine(cfg, CacheConfig(block_size=16), device="cuda", max_batch_size=64,
+                                  max_prefill_tokens=2048, num_blocks=4096, enable_cuda_graph=False)
+            for r in reqs:
+                eng.add_request(r[0], r[1], r[2])
+            ref = eng.run_until_done()
+            same = sum(int(a == b) for k in ref for a, b in zip(ref[k], outs.get(k, [])))
+            first = sum(int(ref[k][0] == outs[k][0]) for k in ref if outs.get(k))
+            total = sum(len(v) for v in ref.values())
+            print(json.dumps({"check_tokens_agree": round(same / max(total, 1), 4),
+                              "check_first_tokens_agree": round(first / max(len(ref), 1), 4)}))
+        if args.file:
+            from dataclasses import asdict
+            with open(args.file, "a") as f:
+                f.write(json.dumps({"args": vars(args), **asdict(m), **extra}) + "\n")
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -143,14 +143,41 @@ class AttentionRank:
                     topk_w=torch.zeros(B, k, dtype=torch.float32, device=dev))
             self.mb.append(d)
         self.status = gemm.scratch(dev).status
+        self.active = [B] * S.n_mb      # rows of every micro-batch that the next launches process (<= B)
+        self._views: Dict[tuple, dict] = {}
+
+    _ROW_KEYS = ("ids", "positions", "slots", "ctx_len", "bt_row", "resid", "next_ids", "logits", "parts", "y",
+                 "topk_ids", "topk_w")
+
+    def set_active(self, m: int, T: int) -> None:
+        """The next launches of micro-batch m process its first T rows (1 <= T <= batch): a serving step fills the
+        buffers with however many decode and prompt tokens it scheduled."""
+        assert 1 <= T <= self.shape.batch
+        self.active[m] = T
+
+    def _d(self, m: int) -> dict:
+        T = self.active[m]
+        full = self.mb[m]
+        if T == self.shape.batch:
+            return full
+        v = self._views.get((m, T))
+        if v is None:
+            v = dict(full)
+            for k in self._ROW_KEYS:
+                if k in full:
+                    v[k] = full[k][:T]
+            if "opart" in full:
+                v["opart"] = [t[:T] for t in full["opart"]]
+            self._views[(m, T)] = v
+        return v
 
     def _meta(self, m: int) -> AttnMeta:
-        d = self.mb[m]
+        d = self._d(m)
         return AttnMeta(d["positions"], d["slots"], self.block_tables, d["bt_row"], d["ctx_len"],
                         max_ctx=self.cfg.max_seq_len)
 
     def embed(self, m: int) -> None:
-        d = self.mb[m]
+        d = self._d(m)
         F.embed(d["ids"], self.embed_w, out=d["resid"])
 
     def layer(self, l: int, m: int) -> None:
@@ -161,7 +188,8 @@ class AttentionRank:
     def layer_attn(self, l: int, m: int) -> None:
         """[wait for the experts' combine] add + RMSNorm, QKV, RoPE / KV append, paged attention, o_proj. With tensor
         parallelism the o_proj partial sum goes to this rank's peer-visible buffer and the GEMM signals the TP peers."""
-        d, S, cfg = self.mb[m], self.shape, self.cfg
+        d, S, cfg = self._d(m), self.shape, self.cfg
+        T = self.active[m]
         parts = None
         if l > 0 and not cfg.is_dense_layer(l - 1):     # a dense-FFN layer sends nothing to the expert GPUs
             _lib.check(_lib.lib().dmoe_wait_flags(_vp(d["comb_flag"]), c_int(S.n_expert), _vp(d["wait_epoch"]),
@@ -179,7 +207,7 @@ class AttentionRank:
                          cfg.rope_theta)
         attn = F.paged_attention(qkv[:, :a.q_size], kv[0], kv[1], meta.block_tables, meta.bt_row, meta.ctx_len,
                                  a.num_heads, a.num_kv_heads, a.head_dim,
-                                 splits=F.pick_attn_splits(S.batch, a.num_kv_heads, cfg.max_seq_len, self.block_size))
+                                 splits=F.pick_attn_splits(T, a.num_kv_heads, cfg.max_seq_len, self.block_size))
         sig = gemm.GemmComm(signal_ptrs=d["oflag_ptrs"], n_signal=self.tp, signal_slot=self.tp_rank,
                             signal_epoch=d["o_signal_epoch"], done_ticket=d["o_ticket"])
         gemm.linear(attn, a.o_w, out=d["opart"][l % 2], comm=sig)
@@ -188,9 +216,10 @@ class AttentionRank:
         """Post-attention RMSNorm + router + dispatch. With tensor parallelism the router kernel first sums the TP
         ranks' o_proj partials straight out of their memory (the all-reduce), and this rank dispatches only its
         slice of the tokens."""
-        d, S, cfg = self.mb[m], self.shape, self.cfg
+        d, S, cfg = self._d(m), self.shape, self.cfg
+        T = self.active[m]
         a = self.layers[l]
-        lo, hi = 0, S.batch
+        lo, hi = 0, T
         if a.is_dense and self.tp == 1:
             a.dense_ffn(d["resid"])
             return
@@ -200,12 +229,12 @@ class AttentionRank:
         else:
             _lib.check(_lib.lib().dmoe_wait_flags(_vp(d["oflag"]), c_int(self.tp), _vp(d["o_wait_epoch"]),
                                                   _vp(self.status), c_vp(_lib.stream_ptr())), "dmoe_wait_flags")
-            per = S.batch // self.tp
-            lo, hi = self.tp_rank * per, (self.tp_rank + 1) * per
+            per = (T + self.tp - 1) // self.tp
+            lo, hi = min(T, self.tp_rank * per), min(T, (self.tp_rank + 1) * per)
             y, ids, w = d["y"], d["topk_ids"], d["topk_w"]
             _lib.check(_lib.lib().dmoe_route_ex(
                 _vp(d["resid"]), c_ll(S.hidden), _vp(a.post_ln), ctypes.c_float(cfg.rms_norm_eps), _vp(a.gate_w),
-                c_int(S.batch), c_int(S.hidden), c_int(S.num_experts), c_int(S.top_k), c_int(int(cfg.norm_topk_prob)),
+                c_int(T), c_int(S.hidden), c_int(S.num_experts), c_int(S.top_k), c_int(int(cfg.norm_topk_prob)),
                 _vp(y), c_ll(S.hidden), _vp(ids), _vp(w), _vp(d["ws"]), _vp(d["opart_ptrs"][l % 2]), c_int(self.tp),
                 c_ll(S.hidden), _vp(d["resid"]), c_ll(S.hidden), c_int(lo), c_int(hi), _vp(a.route_bias),
                 c_vp(_lib.stream_ptr())), "dmoe_route_ex")
@@ -215,7 +244,7 @@ class AttentionRank:
                 a.dense_ffn(d["resid"], h=y)
                 return
         _lib.check(_lib.lib().dmoe_dispatch_remote(
-            _vp(y), c_ll(y.stride(0)), _vp(ids), _vp(w), c_int(S.batch), c_int(S.top_k), c_int(S.hidden),
+            _vp(y), c_ll(y.stride(0)), _vp(ids), _vp(w), c_int(T), c_int(S.top_k), c_int(S.hidden),
             c_int(S.num_experts), c_int(S.experts_per_rank), c_int(S.n_expert), c_int(self.a), c_int(S.region_cap),
             _vp(d["ws"]), _vp(d["x_bases"]), c_ll(S.hidden), _vp(d["rec_bases"]), _vp(d["cnt_bases"]),
             _vp(d["flag_bases"]), _vp(d["disp_epoch"]), _vp(self.status), c_int(lo), c_int(hi),
@@ -225,7 +254,7 @@ class AttentionRank:
         a.shared_experts(y, d["resid"])
 
     def head(self, m: int) -> None:
-        d, S, cfg = self.mb[m], self.shape, self.cfg
+        d, S, cfg = self._d(m), self.shape, self.cfg
         _lib.check(_lib.lib().dmoe_wait_flags(_vp(d["comb_flag"]), c_int(S.n_expert), _vp(d["wait_epoch"]),
                                               _vp(self.status), c_vp(_lib.stream_ptr())), "dmoe_wait_flags")
         _, h = F.add_rmsnorm(d["resid"], d["parts"], self.norm_w, cfg.rms_norm_eps, resid_out=d["resid"])

@@ -1,0 +1,406 @@
+"""Continuous-batching serving on the fused disaggregated data plane (attention GPUs + expert GPUs, peer memory).
+
+One process per GPU. Ranks [0, A) are attention GPUs in TP groups of ``tp`` consecutive ranks; ranks [A, world) hold
+the routed experts. Every iteration of the job is one pass of two micro-batches through all layers
+(:class:`disagmoe_b200.parallel.disagg.AttentionRank` / ``ExpertRank``):
+
+* the **leader** of every attention group (its first rank) owns the group's requests: it admits arrivals, keeps the
+  paged-KV block manager, and builds the iteration's two micro-batches as flat token lists. A running sequence
+  contributes its next decode token; a newly admitted request contributes all its prompt tokens (position p attends
+  to the first p + 1 cached tokens of its own block-table row, so prompt and decode tokens share one kernel and one
+  batch: prefill never stalls the sequences that are decoding);
+* the other members of a TP group receive the leader's plan (token ids, positions, slots, block-table patches) over a
+  host-side broadcast and run the same launches on their head shard;
+* the expert GPUs replay one CUDA graph per iteration whatever the attention side scheduled: row counts travel with
+  the data (per-expert cursors in peer memory), so the expert side has no shape to agree on.
+
+Iterations are kept in lock step by one tiny host all-reduce per iteration (work left? any device status set?); token
+rows, router decisions and expert outputs never touch the host. Decode-sized iterations replay a CUDA graph captured
+for the padded micro-batch size; larger (prefill-heavy) iterations launch eagerly.
+
+The reference's counterpart is the whole host-scheduled loop: disagmoe/frontend/engine.py:614-871 (attention / expert
+loops), csrc/muhelper/muhelper.cpp (pools and dispatchers), disagmoe/frontend/controller.py:276-330 (request
+admission and results).
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..config import ModelConfig
+from ..frontend.datatypes import SloStat
+
+
+# ------------------------------------------------------------------------------------------------ scheduling (host)
+@dataclass
+class ServeSeq:
+    req_id: int
+    prompt: List[int]
+    max_new_tokens: int
+    t_arrival: float
+    mb: int = -1
+    length: int = 0                 # tokens whose K/V are cached
+    last_token: int = 0
+    outputs: List[int] = field(default_factory=list)
+    t_tokens: List[float] = field(default_factory=list)
+
+
+@dataclass
+class MicroBatchPlan:
+    ids: List[int] = field(default_factory=list)
+    pos: List[int] = field(default_factory=list)
+    rows: List[int] = field(default_factory=list)
+    slots: List[int] = field(default_factory=list)
+    # (row in the micro-batch, sequence whose next token that row produces, tokens the row's step adds to its cache)
+    emit: List[Tuple[int, ServeSeq, int]] = field(default_factory=list)
+
+    def __len__(self):
+        return len(self.ids)
+
+
+class FusedScheduler:
+    """Admission + micro-batch construction of one attention group (pure host logic, no GPU)."""
+
+    def __init__(self, block_mgr, block_size: int, n_mb: int, max_seqs_per_mb: int, max_tokens_per_mb: int,
+                 max_prefill_tokens_per_mb: Optional[int] = None):
+        self.bm, self.block_size, self.n_mb = block_mgr, block_size, n_mb
+        self.max_seqs, self.max_tokens = max_seqs_per_mb, max_tokens_per_mb
+        self.max_prefill = max_prefill_tokens_per_mb or max_tokens_per_mb
+        self.waiting: List[ServeSeq] = []                     # arrival order
+        self.running: List[Dict[int, ServeSeq]] = [dict() for _ in range(n_mb)]
+        self.finished: Dict[int, ServeSeq] = {}
+
+    def add_request(self, req_id: int, prompt: Sequence[int], max_new_tokens: int, t_arrival: float) -> None:
+        assert 1 <= len(prompt) <= self.max_prefill, "a prompt must fit one micro-batch"
+        self.waiting.append(ServeSeq(req_id, list(prompt), max_new_tokens, t_arrival))
+
+    def num_unfinished(self) -> int:
+        return len(self.waiting) + sum(len(r) for r in self.running)
+
+    def has_work(self, now: float) -> bool:
+        return any(len(r) for r in self.running) or bool(self.waiting and self.waiting[0].t_arrival <= now)
+
+    def build(self, now: float) -> List[MicroBatchPlan]:
+        plans = [MicroBatchPlan() for _ in range(self.n_mb)]
+        prefill = [0] * self.n_mb
+        for m in range(self.n_mb):
+            seqs = list(self.running[m].values())
+            if not seqs:
+                continue
+            lens = [s.length for s in seqs]
+            rs = self.bm.step_decode([s.req_id for s in seqs], lens)
+            n = len(seqs)
+            p = plans[m]
+            p.ids = [s.last_token for s in seqs]
+            p.pos = lens
+            p.rows = [int(r) for r in rs[:n]]
+            p.slots = [int(r) for r in rs[n:]]
+            p.emit = [(i, q, 1) for i, q in enumerate(seqs)]
+        # admission in arrival order; a request goes to the micro-batch with fewer tokens this iteration
+        while self.waiting and self.waiting[0].t_arrival <= now:
+            s = self.waiting[0]
+            n = len(s.prompt)
+            order = sorted(range(self.n_mb), key=lambda m: len(plans[m]))
+            m = next((m for m in order if len(self.running[m]) < self.max_seqs and len(plans[m]) + n <= self.max_tokens
+                      and prefill[m] + n <= self.max_prefill), None)
+            if m is None or not self.bm.can_allocate(n + 1):
+                break
+            self.waiting.pop(0)
+            self.bm.allocate(s.req_id, n + 1)
+            row = self.bm.row_of(s.req_id)
+            blocks = self.bm.get_seq_block_list(s.req_id)
+            bs = self.block_size
+            p = plans[m]
+            p.ids.extend(s.prompt)
+            p.pos.extend(range(n))
+            p.rows.extend([row] * n)
+            p.slots.extend(blocks[i // bs] * bs + i % bs for i in range(n))
+            p.emit.append((len(p.ids) - 1, s, n))          # only the last prompt row produces a token
+            s.mb = m
+            self.running[m][s.req_id] = s
+            prefill[m] += n
+        return plans
+
+    def commit(self, plans: List[MicroBatchPlan], next_ids: List[Sequence[int]], now: float) -> List[Tuple[int, int]]:
+        out = []
+        for m, p in enumerate(plans):
+            for row, s, grown in p.emit:
+                tok = int(next_ids[m][row])
+                s.length += grown
+                s.outputs.append(tok)
+                s.t_tokens.append(now)
+                s.last_token = tok
+                out.append((s.req_id, tok))
+                if len(s.outputs) >= s.max_new_tokens:
+                    self.bm.release(s.req_id)
+                    self.running[m].pop(s.req_id, None)
+                    self.finished[s.req_id] = s
+        return out
+
+
+# ------------------------------------------------------------------------------------------------ one rank of the job
+class FusedServingRank:
+    """One process of the fused disaggregated serving job (see the module docstring for the roles)."""
+
+    def __init__(self, cfg: ModelConfig, world: int, rank: int, local_rank: int, n_attn: int, tp: int = 1,
+                 max_seqs_per_mb: int = 128, max_tokens_per_mb: int = 2048, num_blocks: int = 8192,
+                 graph_sizes: Sequence[int] = (8, 32, 64, 128, 256), n_mb: int = 2, route_skew: float = 0.0,
+                 max_prefill_tokens_per_mb: Optional[int] = None, state_dict=None):
+        import torch.distributed as dist
+        from .. import disagmoe_c as C
+        from ..ops import _lib, gemm
+        from .disagg import AttentionRank, DisaggShape, ExpertRank, build_layout
+        from .peer import PeerArena
+        self.dist, self._lib, self._gemm = dist, _lib, gemm
+        A, X = n_attn, world - n_attn
+        assert 1 <= A < world and A % tp == 0
+        self.cfg, self.world, self.rank, self.A, self.X, self.tp, self.n_mb = cfg, world, rank, A, X, tp, n_mb
+        self.device = torch.device("cuda", local_rank)
+        self.is_attn = rank < A
+        self.is_leader = self.is_attn and rank % tp == 0
+        self.cap = max_tokens_per_mb
+        self.block_size = 16
+        self.shape = DisaggShape(A, X, n_mb, self.cap, cfg.top_k, cfg.hidden_size, cfg.num_experts, tp)
+        self.layout = build_layout(self.shape)
+        self.arena = PeerArena.create(self.layout.size, device=self.device)
+        # host control plane: gloo (keeps the CUDA streams free of control collectives)
+        self.ctl = dist.new_group(backend="gloo")
+        self.tp_groups = [dist.new_group(ranks=list(range(g, g + tp)), backend="gloo") for g in range(0, A, tp)] \
+            if tp > 1 else []
+        self.tp_group = self.tp_groups[rank // tp] if (tp > 1 and self.is_attn) else None
+        self.leader_rank = rank // tp * tp if self.is_attn else -1
+        self.graph_sizes = sorted(g for g in graph_sizes if g <= self.cap)
+        self.graphs: Dict[int, torch.cuda.CUDAGraph] = {}
+        self.iterations = 0
+        self.graph_iterations = 0
+        if self.is_attn:
+            # one block beyond the manager's range is the scratch page the padding rows write to
+            self.runner = AttentionRank(cfg, self.shape, self.arena, self.layout, rank, num_blocks + 1,
+                                        state_dict=state_dict)
+            for layer in self.runner.layers:
+                layer.set_route_skew(route_skew)
+            self.scratch_block = num_blocks
+            self.max_rows = n_mb * max_seqs_per_mb
+            self.dummy_row = self.max_rows                      # a block-table row that only names the scratch page
+            assert self.runner.block_tables.shape[0] > self.dummy_row
+            self.runner.block_tables[self.dummy_row].fill_(self.scratch_block)
+            self.sched = None
+            if self.is_leader:
+                self.bm = C.BlockManager(self.block_size, num_blocks, 0, self.max_rows)
+                self.sched = FusedScheduler(self.bm, self.block_size, n_mb, max_seqs_per_mb, self.cap,
+                                            max_prefill_tokens_per_mb)
+            n = n_mb * self.cap
+            pin = lambda dt: torch.zeros(n, dtype=dt).pin_memory()
+            self.h_ids, self.h_pos, self.h_ctx, self.h_row = (pin(torch.int32) for _ in range(4))
+            self.h_slots = pin(torch.int64)
+            self.h_out = pin(torch.int32)
+        else:
+            self.runner = ExpertRank(cfg, self.shape, self.arena, self.layout, rank - A, state_dict=state_dict)
+        torch.cuda.synchronize()
+        dist.barrier()
+        self._warm_up_and_capture()
+
+    # ---- set-up ------------------------------------------------------------------------------------------------
+    def _fill_padding(self, m: int, start: int, end: int) -> None:
+        """Rows [start, end) of micro-batch m become padding: token 0 at position 0 of the scratch page."""
+        sl = slice(m * self.cap + start, m * self.cap + end)
+        self.h_ids[sl] = 0
+        self.h_pos[sl] = 0
+        self.h_ctx[sl] = 1
+        self.h_row[sl] = self.dummy_row
+        self.h_slots[sl] = self.scratch_block * self.block_size
+
+    def _upload(self, m: int, T: int) -> None:
+        d = self.runner.mb[m]
+        sl = slice(m * self.cap, m * self.cap + T)
+        d["ids"][:T].copy_(self.h_ids[sl], non_blocking=True)
+        d["positions"][:T].copy_(self.h_pos[sl], non_blocking=True)
+        d["ctx_len"][:T].copy_(self.h_ctx[sl], non_blocking=True)
+        d["bt_row"][:T].copy_(self.h_row[sl], non_blocking=True)
+        d["slots"][:T].copy_(self.h_slots[sl], non_blocking=True)
+
+    def _warm_up_and_capture(self) -> None:
+        dist = self.dist
+        g0 = self.graph_sizes[0] if self.graph_sizes else 1
+        # eager iterations in lock step (scratch buffers, kernel attributes), then capture; capture runs no kernel,
+        # so the ranks need not agree on how many graphs each of them captures
+        for _ in range(2):
+            if self.is_attn:
+                for m in range(self.n_mb):
+                    self._fill_padding(m, 0, g0)
+                    self._upload(m, g0)
+                    self.runner.set_active(m, g0)
+            self.runner.iteration()
+            torch.cuda.synchronize()
+            dist.barrier()
+        side = torch.cuda.Stream(self.device)
+        side.wait_stream(torch.cuda.current_stream())
+        n0 = self._lib.LAUNCHES
+        if self.is_attn:
+            for g in self.graph_sizes:
+                for m in range(self.n_mb):
+                    self.runner.set_active(m, g)
+                gr = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gr, stream=side):
+                    self.runner.iteration()
+                self.graphs[g] = gr
+            self.launches_per_graph = (self._lib.LAUNCHES - n0) // max(1, len(self.graph_sizes))
+        else:
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr, stream=side):
+                self.runner.iteration()
+            self.graphs[0] = gr
+            self.launches_per_graph = self._lib.LAUNCHES - n0
+        torch.cuda.synchronize()
+        dist.barrier()
+
+    # ---- requests (leaders) --------------------------------------------------------------------------------------
+    def add_request(self, req_id: int, prompt: Sequence[int], max_new_tokens: int, t_arrival: float) -> None:
+        assert self.is_leader
+        self.sched.add_request(req_id, prompt, max_new_tokens, t_arrival)
+
+    # ---- one iteration -------------------------------------------------------------------------------------------
+    def _control(self, unfinished: int, ready: int, bad: int) -> Tuple[int, int, int]:
+        t = torch.tensor([unfinished, ready, bad], dtype=torch.int64)
+        self.dist.all_reduce(t, group=self.ctl)
+        return int(t[0]), int(t[1]), int(t[2])
+
+    def _plan_to_host(self, plans: List[MicroBatchPlan]) -> List[int]:
+        Ts = []
+        for m, p in enumerate(plans):
+            T = len(p)
+            o = m * self.cap
+            if T:
+                self.h_ids.numpy()[o:o + T] = p.ids
+                self.h_pos.numpy()[o:o + T] = p.pos
+                self.h_ctx.numpy()[o:o + T] = np.asarray(p.pos, dtype=np.int32) + 1
+                self.h_row.numpy()[o:o + T] = p.rows
+                self.h_slots.numpy()[o:o + T] = p.slots
+            Ts.append(T)
+        return Ts
+
+    def _share_plan(self, Ts: Optional[List[int]], patches: Optional[torch.Tensor]):
+        """Leader -> members of its TP group: sizes, the staged token arrays and the block-table patches."""
+        if self.tp_group is None:
+            return Ts, patches
+        dist = self.dist
+        hdr = torch.zeros(self.n_mb + 1, dtype=torch.int64)
+        if self.is_leader:
+            hdr[:self.n_mb] = torch.tensor(Ts)
+            hdr[self.n_mb] = 0 if patches is None else patches.shape[1]
+        dist.broadcast(hdr, src=self.leader_rank, group=self.tp_group)
+        Ts = [int(x) for x in hdr[:self.n_mb]]
+        n_patch = int(hdr[self.n_mb])
+        total = sum(Ts)
+        buf = torch.empty(5 * total + 3 * n_patch, dtype=torch.int64)
+        if self.is_leader:
+            o = 0
+            for m, T in enumerate(Ts):
+                sl = slice(m * self.cap, m * self.cap + T)
+                for h in (self.h_ids, self.h_pos, self.h_ctx, self.h_row, self.h_slots):
+                    buf[o:o + T] = h[sl]
+                    o += T
+            if n_patch:
+                buf[o:] = patches.reshape(-1)
+        dist.broadcast(buf, src=self.leader_rank, group=self.tp_group)
+        if not self.is_leader:
+            o = 0
+            for m, T in enumerate(Ts):
+                sl = slice(m * self.cap, m * self.cap + T)
+                for h in (self.h_ids, self.h_pos, self.h_ctx, self.h_row, self.h_slots):
+                    h[sl] = buf[o:o + T].to(h.dtype)
+                    o += T
+            patches = buf[o:].reshape(3, n_patch) if n_patch else None
+        return Ts, patches
+
+    def step(self, now: float) -> Optional[List[Tuple[int, int]]]:
+        """One lock-step iteration of the whole job. Returns None when the job is over (no request left anywhere, or
+        a device-side wait gave up), [] when nothing was ready to run, else the (request, token) pairs this rank's
+        group produced (leaders only)."""
+        unfinished = ready = 0
+        if self.is_leader:
+            unfinished = self.sched.num_unfinished()
+            ready = int(self.sched.has_work(now))
+        unfinished, ready, bad = self._control(unfinished, ready, 0)
+        if unfinished == 0:
+            return None
+        if ready == 0:
+            time.sleep(0.0005)
+            return []
+        self.iterations += 1
+        if not self.is_attn:
+            self.graphs[0].replay()
+            self._lib.add_launches(self.launches_per_graph)
+            torch.cuda.current_stream().synchronize()
+            return []
+        plans, Ts, patches = None, None, None
+        if self.is_leader:
+            plans = self.sched.build(now)
+            Ts = self._plan_to_host(plans)
+            ups = self.bm.drain_updates()
+            if ups:
+                patches = torch.tensor(ups, dtype=torch.int64).T.contiguous()
+        Ts, patches = self._share_plan(Ts, patches)
+        if patches is not None:
+            t = patches.pin_memory().to(self.device, non_blocking=True)
+            self.runner.block_tables.index_put_((t[0], t[1]), t[2].int())
+        # decode-sized iterations replay the graph of the padded size; bigger ones launch eagerly at the exact size
+        tmax = max(max(Ts), 1)
+        g = next((s for s in self.graph_sizes if s >= tmax), None)
+        for m, T in enumerate(Ts):
+            size = g if g is not None else min(self.cap, (max(T, 1) + 15) // 16 * 16)
+            self._fill_padding(m, T, size)
+            self._upload(m, size)
+            self.runner.set_active(m, size)
+        if g is not None:
+            self.graphs[g].replay()
+            self._lib.add_launches(self.launches_per_graph)
+            self.graph_iterations += 1
+        else:
+            self.runner.iteration()
+        for m, T in enumerate(Ts):
+            if T:
+                self.h_out[m * self.cap:m * self.cap + T].copy_(self.runner.mb[m]["next_ids"][:T], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        if not self.is_leader:
+            return []
+        outs = [self.h_out[m * self.cap:m * self.cap + T].tolist() for m, T in enumerate(Ts)]
+        return self.sched.commit(plans, outs, time.time())
+
+    def kernel_status(self) -> int:
+        return self._gemm.check_status(self.device)
+
+    # ---- a whole workload ----------------------------------------------------------------------------------------
+    def serve(self, requests: Sequence[Tuple[int, Sequence[int], int, float]], time_limit: float = 600.0
+              ) -> Dict[str, object]:
+        """Runs until every request of every group is finished. ``requests``: (req_id, prompt ids, output length,
+        arrival offset in seconds) of THIS rank's group (leaders; ignored elsewhere). Returns this rank's results."""
+        dist = self.dist
+        dist.barrier(group=self.ctl)
+        t0 = time.time()
+        if self.is_leader:
+            for rid, prompt, n_out, at in requests:
+                self.add_request(rid, prompt, n_out, t0 + at)
+        tokens = 0
+        while True:
+            now = time.time()
+            if now - t0 > time_limit:
+                raise TimeoutError("serving run exceeded its time limit")
+            out = self.step(now)
+            if out is None:
+                break
+            tokens += len(out)
+        torch.cuda.synchronize()
+        dt = time.time() - t0
+        res = {"rank": self.rank, "duration": dt, "tokens": tokens, "iterations": self.iterations,
+               "graph_iterations": self.graph_iterations, "kernel_status": self.kernel_status(), "slo": [], "arrivals": {}}
+        if self.is_leader:
+            for s in self.sched.finished.values():
+                res["slo"].append(SloStat(s.req_id, s.t_tokens[0], 0.0, s.t_tokens[-1], list(s.t_tokens)))
+                res["arrivals"][s.req_id] = s.t_arrival
+            res["outputs"] = {s.req_id: list(s.outputs) for s in self.sched.finished.values()}
+        return res

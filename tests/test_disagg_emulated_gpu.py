@@ -145,3 +145,64 @@ def test_emulated_tensor_parallel_attention(A, X, tp, n_mb, variant):
             got = attn[grp * tp + r].mb[m]["logits"]
             err = (got - lg).abs().max().item() / lg.abs().max().item()
             assert err < 0.03, f"group {grp} tp rank {r} mb {m}: rel err {err}"
+
+
+def test_emulated_mixed_prompt_and_decode_rows():
+    """A serving iteration: micro-batch 0 = one 12-token prompt + 2 decode tokens + padding rows, micro-batch 1 = 3 decode
+    tokens (fewer active rows than the buffers hold). Rows that produce a token must match the colocated executor's
+    prefill / decode logits."""
+    cfg, sd, _ = _model("mixtral", 2)
+    A, X, n_mb, cap = 1, 2, 2, 32
+    shape = DisaggShape(A, X, n_mb, cap, cfg.top_k, cfg.hidden_size, cfg.num_experts)
+    layout = build_layout(shape)
+    arenas = PeerArena.emulated(A + X, layout.size)
+    attn = AttentionRank(cfg, shape, arenas[0], layout, 0, num_blocks=64, state_dict=sd)
+    exps = [ExpertRank(cfg, shape, arenas[A + x], layout, x, state_dict=sd) for x in range(X)]
+    ref = FusedModelExecutor(cfg, CacheConfig(block_size=16), device="cuda", max_batch_size=8, max_prefill_tokens=32,
+                             state_dict=sd, num_blocks=64, enable_cuda_graph=False)
+    g = torch.Generator().manual_seed(1)
+    kv = torch.randn(ref.kv_cache.shape, generator=g).to(torch.bfloat16).cuda() * 0.5
+    attn.kv_cache.copy_(kv)
+    ref.kv_cache.copy_(kv)
+    bt = torch.arange(8 * 4, dtype=torch.int32).view(8, 4)          # sequence r owns blocks 4r .. 4r + 3
+    bt[7] = 63                                                       # row 7: padding rows, scratch page
+    attn.block_tables[:8, :4] = bt.cuda()
+    ref.block_tables[:8, :4] = bt.cuda()
+    slot = lambda r, p: int(bt[r, p // 16]) * 16 + p % 16
+    prompt = torch.randint(0, cfg.vocab_size, (12,), generator=g).tolist()
+    dec = {1: (int(torch.randint(0, cfg.vocab_size, (1,), generator=g)), 20), 2: (5, 9), 3: (6, 33), 4: (7, 1), 5: (8, 47)}
+    mb_rows = [[(0, t, p) for p, t in enumerate(prompt)] + [(r, *dec[r]) for r in (1, 2)] + [(7, 0, 0)] * 2,
+               [(r, *dec[r]) for r in (3, 4, 5)]]
+    for m, rows in enumerate(mb_rows):
+        T = len(rows)
+        attn.set_active(m, T)
+        d = attn.mb[m]
+        d["ids"][:T] = torch.tensor([t for _, t, _ in rows], dtype=torch.int32)
+        d["positions"][:T] = torch.tensor([p for _, _, p in rows], dtype=torch.int32)
+        d["ctx_len"][:T] = torch.tensor([p + 1 for _, _, p in rows], dtype=torch.int32)
+        d["bt_row"][:T] = torch.tensor([r for r, _, _ in rows], dtype=torch.int32)
+        d["slots"][:T] = torch.tensor([slot(r, p) for r, _, p in rows])
+    for m in range(n_mb):
+        attn.embed(m)
+    for l in range(cfg.num_layers):
+        for m in range(n_mb):
+            attn.layer(l, m)
+            for e in exps:
+                e.layer(l, m)
+    for m in range(n_mb):
+        attn.head(m)
+    torch.cuda.synchronize()
+    assert gemm.check_status() == 0
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32)
+    _, lg_p = ref.prefill(i32(prompt), i32(list(range(12))), torch.tensor([slot(0, p) for p in range(12)]),
+                          i32([p + 1 for p in range(12)]), i32([0] * 12), want_logits=True)
+    rs = [1, 2, 3, 4, 5]
+    _, lg_d = ref.decode(i32([dec[r][0] for r in rs]), i32([dec[r][1] for r in rs]),
+                         torch.tensor([slot(r, dec[r][1]) for r in rs]), i32([dec[r][1] + 1 for r in rs]), i32(rs),
+                         want_logits=True)
+    got = {"prompt": attn.mb[0]["logits"][11], 1: attn.mb[0]["logits"][12], 2: attn.mb[0]["logits"][13],
+           3: attn.mb[1]["logits"][0], 4: attn.mb[1]["logits"][1], 5: attn.mb[1]["logits"][2]}
+    want = {"prompt": lg_p[11], **{r: lg_d[i] for i, r in enumerate(rs)}}
+    for k in got:
+        err = (got[k] - want[k]).abs().max().item() / want[k].abs().max().item()
+        assert err < 0.03, f"{k}: rel err {err}"

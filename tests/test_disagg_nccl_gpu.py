@@ -41,3 +41,26 @@ def test_two_gpu_workers_over_nccl_channels():
         assert not [e for e in ctl.worker_errors().values() if e]
     finally:
         ctl.stop_workers()
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_two_gpu_fused_serving_matches_colocated():
+    """Continuous batching on the fused peer-memory path (1 attention + 1 expert GPU, one process each): Poisson
+    arrivals with real prefill; the generated tokens are compared with the single-GPU colocated engine."""
+    import json
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+           "127.0.0.1", "--master-port", "29655", os.path.join(root, "benchmark", "serve_fused.py"), "--model", "tiny",
+           "-r", "200", "-n", "24", "--min-input-len", "8", "-i", "40", "--min-output-len", "4", "-o", "12",
+           "--max-seqs-per-mb", "8", "--max-tokens-per-mb", "96", "--num-blocks", "512", "--time-limit", "120", "--check"]
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env)
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
+    lines = [json.loads(l) for l in out.stdout.splitlines() if l.startswith("{")]
+    info = next(l for l in lines if "iterations" in l)
+    check = next(l for l in lines if "check_tokens_agree" in l)
+    assert info["kernel_status"] == 0 and info["requests_finished"] == 24
+    assert check["check_first_tokens_agree"] >= 0.9, check
+    assert check["check_tokens_agree"] >= 0.7, check
