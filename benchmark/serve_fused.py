@@ -54,6 +54,10 @@ def main():
     args = ap.parse_args()
 
     rank, world, lr = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    if os.environ.get("DMOE_SERVE_DEBUG"):
+        # where is every rank if the job stops making progress: Python stacks of all threads to stderr, repeatedly
+        import faulthandler
+        faulthandler.dump_traceback_later(float(os.environ["DMOE_SERVE_DEBUG"]), repeat=True)
     torch.cuda.set_device(lr)
     dist.init_process_group("nccl", device_id=torch.device("cuda", lr))
     cfg = get_preset(args.model)

@@ -149,7 +149,10 @@ class FusedServingRank:
     def __init__(self, cfg: ModelConfig, world: int, rank: int, local_rank: int, n_attn: int, tp: int = 1,
                  max_seqs_per_mb: int = 128, max_tokens_per_mb: int = 2048, num_blocks: int = 8192,
                  graph_sizes: Sequence[int] = (8, 32, 64, 128, 256), n_mb: int = 2, route_skew: float = 0.0,
-                 max_prefill_tokens_per_mb: Optional[int] = None, state_dict=None):
+                 max_prefill_tokens_per_mb: Optional[int] = None, state_dict=None, host_only_runner=None):
+        """``host_only_runner(role, server)`` replaces the GPU side (peer arena, attention / expert ranks, CUDA graphs)
+        with a stand-in that offers the same buffers and ``iteration()``: the host protocol (control all-reduce, plan
+        sharing inside a TP group, scheduling, result collection) then runs as plain CPU processes."""
         import torch.distributed as dist
         from .. import disagmoe_c as C
         from ..ops import _lib, gemm
@@ -159,28 +162,29 @@ class FusedServingRank:
         A, X = n_attn, world - n_attn
         assert 1 <= A < world and A % tp == 0
         self.cfg, self.world, self.rank, self.A, self.X, self.tp, self.n_mb = cfg, world, rank, A, X, tp, n_mb
-        self.device = torch.device("cuda", local_rank)
+        self.host_only = host_only_runner is not None
+        self.device = torch.device("cpu") if self.host_only else torch.device("cuda", local_rank)
         self.is_attn = rank < A
         self.is_leader = self.is_attn and rank % tp == 0
         self.cap = max_tokens_per_mb
         self.block_size = 16
         self.shape = DisaggShape(A, X, n_mb, self.cap, cfg.top_k, cfg.hidden_size, cfg.num_experts, tp)
         self.layout = build_layout(self.shape)
-        self.arena = PeerArena.create(self.layout.size, device=self.device)
+        self.arena = None if self.host_only else PeerArena.create(self.layout.size, device=self.device)
         # host control plane: gloo (keeps the CUDA streams free of control collectives)
         self.ctl = dist.new_group(backend="gloo")
         self.tp_groups = [dist.new_group(ranks=list(range(g, g + tp)), backend="gloo") for g in range(0, A, tp)] \
             if tp > 1 else []
         self.tp_group = self.tp_groups[rank // tp] if (tp > 1 and self.is_attn) else None
         self.leader_rank = rank // tp * tp if self.is_attn else -1
-        self.graph_sizes = sorted(g for g in graph_sizes if g <= self.cap)
+        self.graph_sizes = [] if self.host_only else sorted(g for g in graph_sizes if g <= self.cap)
         self.graphs: Dict[int, torch.cuda.CUDAGraph] = {}
         self.iterations = 0
         self.graph_iterations = 0
         if self.is_attn:
             # one block beyond the manager's range is the scratch page the padding rows write to
-            self.runner = AttentionRank(cfg, self.shape, self.arena, self.layout, rank, num_blocks + 1,
-                                        state_dict=state_dict)
+            self.runner = host_only_runner("attention", self) if self.host_only else \
+                AttentionRank(cfg, self.shape, self.arena, self.layout, rank, num_blocks + 1, state_dict=state_dict)
             for layer in self.runner.layers:
                 layer.set_route_skew(route_skew)
             self.scratch_block = num_blocks
@@ -194,15 +198,32 @@ class FusedServingRank:
                 self.sched = FusedScheduler(self.bm, self.block_size, n_mb, max_seqs_per_mb, self.cap,
                                             max_prefill_tokens_per_mb)
             n = n_mb * self.cap
-            pin = lambda dt: torch.zeros(n, dtype=dt).pin_memory()
+            pin = lambda dt: torch.zeros(n, dtype=dt) if self.host_only else torch.zeros(n, dtype=dt).pin_memory()
             self.h_ids, self.h_pos, self.h_ctx, self.h_row = (pin(torch.int32) for _ in range(4))
             self.h_slots = pin(torch.int64)
             self.h_out = pin(torch.int32)
         else:
-            self.runner = ExpertRank(cfg, self.shape, self.arena, self.layout, rank - A, state_dict=state_dict)
-        torch.cuda.synchronize()
+            self.runner = host_only_runner("expert", self) if self.host_only else \
+                ExpertRank(cfg, self.shape, self.arena, self.layout, rank - A, state_dict=state_dict)
+        self._last_status = 0
+        self._sync()
         dist.barrier()
+        self._debug = bool(__import__("os").environ.get("DMOE_SERVE_DEBUG"))
+        self._log("set-up done")
         self._warm_up_and_capture()
+        self._log("graphs captured")
+
+    def _sync(self) -> None:
+        if not self.host_only:
+            torch.cuda.synchronize()
+
+    def _status_word(self) -> int:
+        return 0 if self.host_only else int(self._gemm.scratch(self.device).status.item())
+
+    def _log(self, msg: str) -> None:
+        if self._debug:
+            import sys
+            print(f"[serve rank {self.rank} it {self.iterations}] {msg}", file=sys.stderr, flush=True)
 
     # ---- set-up ------------------------------------------------------------------------------------------------
     def _fill_padding(self, m: int, start: int, end: int) -> None:
@@ -228,15 +249,20 @@ class FusedServingRank:
         g0 = self.graph_sizes[0] if self.graph_sizes else 1
         # eager iterations in lock step (scratch buffers, kernel attributes), then capture; capture runs no kernel,
         # so the ranks need not agree on how many graphs each of them captures
-        for _ in range(2):
+        # the first one runs at full capacity so that every scratch buffer reaches its final size before any capture
+        for size in (self.cap, g0):
             if self.is_attn:
                 for m in range(self.n_mb):
-                    self._fill_padding(m, 0, g0)
-                    self._upload(m, g0)
-                    self.runner.set_active(m, g0)
+                    self._fill_padding(m, 0, size)
+                    self._upload(m, size)
+                    self.runner.set_active(m, size)
             self.runner.iteration()
-            torch.cuda.synchronize()
+            self._sync()
+            self._log(f"eager warm-up iteration done, status {self._status_word()}")
             dist.barrier()
+        if self.host_only:
+            self.launches_per_graph = 0
+            return
         side = torch.cuda.Stream(self.device)
         side.wait_stream(torch.cuda.current_stream())
         n0 = self._lib.LAUNCHES
@@ -325,17 +351,23 @@ class FusedServingRank:
         if self.is_leader:
             unfinished = self.sched.num_unfinished()
             ready = int(self.sched.has_work(now))
-        unfinished, ready, bad = self._control(unfinished, ready, 0)
-        if unfinished == 0:
+        unfinished, ready, bad = self._control(unfinished, ready, int(self._last_status != 0))
+        if unfinished == 0 or bad:
             return None
         if ready == 0:
             time.sleep(0.0005)
             return []
         self.iterations += 1
+        if self._debug and self.iterations <= 3:
+            self._log(f"iteration starts (unfinished {unfinished}, ready {ready})")
         if not self.is_attn:
-            self.graphs[0].replay()
-            self._lib.add_launches(self.launches_per_graph)
-            torch.cuda.current_stream().synchronize()
+            if self.host_only:
+                self.runner.iteration()
+            else:
+                self.graphs[0].replay()
+                self._lib.add_launches(self.launches_per_graph)
+                torch.cuda.current_stream().synchronize()
+                self._last_status = self._status_word()
             return []
         plans, Ts, patches = None, None, None
         if self.is_leader:
@@ -346,7 +378,7 @@ class FusedServingRank:
                 patches = torch.tensor(ups, dtype=torch.int64).T.contiguous()
         Ts, patches = self._share_plan(Ts, patches)
         if patches is not None:
-            t = patches.pin_memory().to(self.device, non_blocking=True)
+            t = patches if self.host_only else patches.pin_memory().to(self.device, non_blocking=True)
             self.runner.block_tables.index_put_((t[0], t[1]), t[2].int())
         # decode-sized iterations replay the graph of the padded size; bigger ones launch eagerly at the exact size
         tmax = max(max(Ts), 1)
@@ -365,14 +397,16 @@ class FusedServingRank:
         for m, T in enumerate(Ts):
             if T:
                 self.h_out[m * self.cap:m * self.cap + T].copy_(self.runner.mb[m]["next_ids"][:T], non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        if not self.host_only:
+            torch.cuda.current_stream().synchronize()
+            self._last_status = self._status_word()
         if not self.is_leader:
             return []
         outs = [self.h_out[m * self.cap:m * self.cap + T].tolist() for m, T in enumerate(Ts)]
         return self.sched.commit(plans, outs, time.time())
 
     def kernel_status(self) -> int:
-        return self._gemm.check_status(self.device)
+        return 0 if self.host_only else (self._gemm.check_status(self.device) or self._last_status)
 
     # ---- a whole workload ----------------------------------------------------------------------------------------
     def serve(self, requests: Sequence[Tuple[int, Sequence[int], int, float]], time_limit: float = 600.0
@@ -394,7 +428,7 @@ class FusedServingRank:
             if out is None:
                 break
             tokens += len(out)
-        torch.cuda.synchronize()
+        self._sync()
         dt = time.time() - t0
         res = {"rank": self.rank, "duration": dt, "tokens": tokens, "iterations": self.iterations,
                "graph_iterations": self.graph_iterations, "kernel_status": self.kernel_status(), "slo": [], "arrivals": {}}

@@ -60,3 +60,101 @@ def test_admission_respects_limits():
     s.commit(plans, _fake_model(plans), 0.3)     # both finish (2 tokens) and release their blocks
     plans = s.build(0.4)
     assert [len(p) for p in plans] == [20, 20] and not s.waiting
+
+
+# ---- the host protocol of a whole job as CPU processes (gloo): control all-reduce, TP plan sharing, results ----------
+class _FakeAttention:
+    """Stands in for the GPU side of an attention rank: same buffers, next token = f(token, position)."""
+
+    def __init__(self, srv, vocab):
+        import torch
+        z = lambda n, dt=torch.int32: torch.zeros(n, dtype=dt)
+        self.mb = [dict(ids=z(srv.cap), positions=z(srv.cap), ctx_len=z(srv.cap), bt_row=z(srv.cap),
+                        slots=z(srv.cap, torch.int64), next_ids=z(srv.cap)) for _ in range(srv.n_mb)]
+        self.block_tables = torch.zeros(2 * srv.cap + 8, 64, dtype=torch.int32)
+        self.layers = []
+        self.active = [srv.cap] * srv.n_mb
+        self.vocab = vocab
+        self.seen_patches = 0
+
+    def set_active(self, m, T):
+        self.active[m] = T
+
+    def iteration(self):
+        for m, d in enumerate(self.mb):
+            T = self.active[m]
+            d["next_ids"][:T] = (d["ids"][:T] * 7 + d["positions"][:T] * 3 + 1) % self.vocab
+
+
+class _FakeExpert:
+    def iteration(self):
+        pass
+
+
+def _serving_worker(rank, world, n_attn, tp, port, q):
+    import os
+    import torch
+    import torch.distributed as dist
+    from disagmoe_b200.config import tiny_config
+    from disagmoe_b200.parallel.serving import FusedServingRank
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    cfg = tiny_config
+    mk = lambda role, srv: _FakeAttention(srv, cfg.vocab_size) if role == "attention" else _FakeExpert()
+    srv = FusedServingRank(cfg, world, rank, 0, n_attn, tp, max_seqs_per_mb=4, max_tokens_per_mb=64, num_blocks=128,
+                           host_only_runner=mk)
+    groups = n_attn // tp
+    g = torch.Generator().manual_seed(0)
+    reqs = [(i, torch.randint(0, cfg.vocab_size, (int(torch.randint(3, 30, (1,), generator=g)),), generator=g).tolist(),
+             int(torch.randint(2, 9, (1,), generator=g)), 0.002 * i) for i in range(20)]
+    mine = [r for r in reqs if srv.is_leader and r[0] % groups == rank // tp]
+    res = srv.serve(mine, time_limit=60)
+    # a TP member must have been handed exactly the block-table entries of its leader
+    res["table_sum"] = int(srv.runner.block_tables.sum()) if srv.is_attn else -1
+    res["slo"] = [(s.req_id, len(s.t_tokens)) for s in res["slo"]]
+    q.put((rank, res, reqs if rank == 0 else None))
+    dist.destroy_process_group()
+
+
+def _expected_tokens(prompt, n_out, vocab):
+    out, tok, pos = [], prompt[-1], len(prompt) - 1
+    for _ in range(n_out):
+        tok = (tok * 7 + pos * 3 + 1) % vocab
+        out.append(tok)
+        pos += 1
+    return out
+
+
+def _run_job(world, n_attn, tp, port):
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    ps = [ctx.Process(target=_serving_worker, args=(r, world, n_attn, tp, port, q)) for r in range(world)]
+    for p in ps:
+        p.start()
+    got = [q.get(timeout=120) for _ in ps]
+    for p in ps:
+        p.join(timeout=30)
+        assert p.exitcode == 0
+    return {r: res for r, res, _ in got}, next(x for _, _, x in got if x is not None)
+
+
+def test_host_protocol_two_dp_groups_cpu():
+    from disagmoe_b200.config import tiny_config
+    res, reqs = _run_job(world=3, n_attn=2, tp=1, port=29741)
+    outs = {**res[0]["outputs"], **res[1]["outputs"]}
+    assert len(outs) == 20 and "outputs" not in res[2]
+    for rid, prompt, n_out, _ in reqs:
+        assert outs[rid] == _expected_tokens(prompt, n_out, tiny_config.vocab_size), rid
+    assert res[0]["iterations"] == res[1]["iterations"] == res[2]["iterations"] > 0
+
+
+def test_host_protocol_tensor_parallel_group_cpu():
+    from disagmoe_b200.config import tiny_config
+    res, reqs = _run_job(world=4, n_attn=2, tp=2, port=29742)
+    outs = res[0]["outputs"]
+    assert len(outs) == 20 and "outputs" not in res[1]
+    for rid, prompt, n_out, _ in reqs:
+        assert outs[rid] == _expected_tokens(prompt, n_out, tiny_config.vocab_size), rid
+    assert res[0]["table_sum"] == res[1]["table_sum"] > 0
+    assert len({res[r]["iterations"] for r in range(4)}) == 1
