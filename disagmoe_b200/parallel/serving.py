@@ -173,9 +173,6 @@ class FusedServingRank:
         self.arena = None if self.host_only else PeerArena.create(self.layout.size, device=self.device)
         # host control plane: gloo (keeps the CUDA streams free of control collectives)
         self.ctl = dist.new_group(backend="gloo")
-        self.tp_groups = [dist.new_group(ranks=list(range(g, g + tp)), backend="gloo") for g in range(0, A, tp)] \
-            if tp > 1 else []
-        self.tp_group = self.tp_groups[rank // tp] if (tp > 1 and self.is_attn) else None
         self.leader_rank = rank // tp * tp if self.is_attn else -1
         self.graph_sizes = [] if self.host_only else sorted(g for g in graph_sizes if g <= self.cap)
         self.graphs: Dict[int, torch.cuda.CUDAGraph] = {}
@@ -290,10 +287,27 @@ class FusedServingRank:
         self.sched.add_request(req_id, prompt, max_new_tokens, t_arrival)
 
     # ---- one iteration -------------------------------------------------------------------------------------------
-    def _control(self, unfinished: int, ready: int, bad: int) -> Tuple[int, int, int]:
-        t = torch.tensor([unfinished, ready, bad], dtype=torch.int64)
-        self.dist.all_reduce(t, group=self.ctl)
-        return int(t[0]), int(t[1]), int(t[2])
+    def _pack_plan(self, Ts: List[int], patches: Optional[torch.Tensor]) -> torch.Tensor:
+        n_patch = 0 if patches is None else patches.shape[1]
+        buf = torch.empty(5 * sum(Ts) + 3 * n_patch, dtype=torch.int64)
+        o = 0
+        for m, T in enumerate(Ts):
+            sl = slice(m * self.cap, m * self.cap + T)
+            for h in (self.h_ids, self.h_pos, self.h_ctx, self.h_row, self.h_slots):
+                buf[o:o + T] = h[sl]
+                o += T
+        if n_patch:
+            buf[o:] = patches.reshape(-1)
+        return buf
+
+    def _unpack_plan(self, buf: torch.Tensor, Ts: List[int], n_patch: int) -> Optional[torch.Tensor]:
+        o = 0
+        for m, T in enumerate(Ts):
+            sl = slice(m * self.cap, m * self.cap + T)
+            for h in (self.h_ids, self.h_pos, self.h_ctx, self.h_row, self.h_slots):
+                h[sl] = buf[o:o + T].to(h.dtype)
+                o += T
+        return buf[o:].reshape(3, n_patch) if n_patch else None
 
     def _plan_to_host(self, plans: List[MicroBatchPlan]) -> List[int]:
         Ts = []
@@ -309,49 +323,36 @@ class FusedServingRank:
             Ts.append(T)
         return Ts
 
-    def _share_plan(self, Ts: Optional[List[int]], patches: Optional[torch.Tensor]):
-        """Leader -> members of its TP group: sizes, the staged token arrays and the block-table patches."""
-        if self.tp_group is None:
-            return Ts, patches
-        dist = self.dist
-        hdr = torch.zeros(self.n_mb + 1, dtype=torch.int64)
-        if self.is_leader:
-            hdr[:self.n_mb] = torch.tensor(Ts)
-            hdr[self.n_mb] = 0 if patches is None else patches.shape[1]
-        dist.broadcast(hdr, src=self.leader_rank, group=self.tp_group)
-        Ts = [int(x) for x in hdr[:self.n_mb]]
-        n_patch = int(hdr[self.n_mb])
-        total = sum(Ts)
-        buf = torch.empty(5 * total + 3 * n_patch, dtype=torch.int64)
-        if self.is_leader:
-            o = 0
-            for m, T in enumerate(Ts):
-                sl = slice(m * self.cap, m * self.cap + T)
-                for h in (self.h_ids, self.h_pos, self.h_ctx, self.h_row, self.h_slots):
-                    buf[o:o + T] = h[sl]
-                    o += T
-            if n_patch:
-                buf[o:] = patches.reshape(-1)
-        dist.broadcast(buf, src=self.leader_rank, group=self.tp_group)
-        if not self.is_leader:
-            o = 0
-            for m, T in enumerate(Ts):
-                sl = slice(m * self.cap, m * self.cap + T)
-                for h in (self.h_ids, self.h_pos, self.h_ctx, self.h_row, self.h_slots):
-                    h[sl] = buf[o:o + T].to(h.dtype)
-                    o += T
-            patches = buf[o:].reshape(3, n_patch) if n_patch else None
-        return Ts, patches
-
     def step(self, now: float) -> Optional[List[Tuple[int, int]]]:
         """One lock-step iteration of the whole job. Returns None when the job is over (no request left anywhere, or
         a device-side wait gave up), [] when nothing was ready to run, else the (request, token) pairs this rank's
-        group produced (leaders only)."""
-        unfinished = ready = 0
+        group produced (leaders only).
+
+        Host protocol, all over one gloo group of every rank (sub-groups are avoided on purpose: creating a gloo
+        sub-group under an eagerly initialised NCCL world blocked its members): one all-gather of a small header per
+        rank [requests unfinished, work ready now, device status set, rows of every micro-batch, block-table patches],
+        then, with tensor parallelism, one broadcast per TP group of the leader's staged token arrays, which the
+        members of that group keep and everybody else drops."""
+        n_mb = self.n_mb
+        hdr = torch.zeros(4 + n_mb, dtype=torch.int64)
+        plans, Ts, patches = None, [0] * n_mb, None
         if self.is_leader:
-            unfinished = self.sched.num_unfinished()
-            ready = int(self.sched.has_work(now))
-        unfinished, ready, bad = self._control(unfinished, ready, int(self._last_status != 0))
+            hdr[0] = self.sched.num_unfinished()
+            hdr[1] = int(self.sched.has_work(now))
+            if hdr[1]:
+                plans = self.sched.build(now)
+                Ts = self._plan_to_host(plans)
+                ups = self.bm.drain_updates()
+                if ups:
+                    patches = torch.tensor(ups, dtype=torch.int64).T.contiguous()
+                hdr[3:3 + n_mb] = torch.tensor(Ts)
+                hdr[3 + n_mb] = 0 if patches is None else patches.shape[1]
+        hdr[2] = int(self._last_status != 0)
+        every = [torch.zeros_like(hdr) for _ in range(self.world)]
+        self.dist.all_gather(every, hdr, group=self.ctl)
+        unfinished = sum(int(h[0]) for h in every)
+        ready = sum(int(h[1]) for h in every)
+        bad = sum(int(h[2]) for h in every)
         if unfinished == 0 or bad:
             return None
         if ready == 0:
@@ -360,6 +361,18 @@ class FusedServingRank:
         self.iterations += 1
         if self._debug and self.iterations <= 3:
             self._log(f"iteration starts (unfinished {unfinished}, ready {ready})")
+        if self.tp > 1:
+            for lead in range(0, self.A, self.tp):
+                h = every[lead]
+                lTs, n_patch = [int(x) for x in h[3:3 + n_mb]], int(h[3 + n_mb])
+                size = 5 * sum(lTs) + 3 * n_patch
+                if size == 0:
+                    continue
+                buf = self._pack_plan(Ts, patches) if self.rank == lead else torch.empty(size, dtype=torch.int64)
+                self.dist.broadcast(buf, src=lead, group=self.ctl)
+                if self.leader_rank == lead and not self.is_leader:
+                    Ts = lTs
+                    patches = self._unpack_plan(buf, lTs, n_patch)
         if not self.is_attn:
             if self.host_only:
                 self.runner.iteration()
@@ -369,14 +382,6 @@ class FusedServingRank:
                 torch.cuda.current_stream().synchronize()
                 self._last_status = self._status_word()
             return []
-        plans, Ts, patches = None, None, None
-        if self.is_leader:
-            plans = self.sched.build(now)
-            Ts = self._plan_to_host(plans)
-            ups = self.bm.drain_updates()
-            if ups:
-                patches = torch.tensor(ups, dtype=torch.int64).T.contiguous()
-        Ts, patches = self._share_plan(Ts, patches)
         if patches is not None:
             t = patches if self.host_only else patches.pin_memory().to(self.device, non_blocking=True)
             self.runner.block_tables.index_put_((t[0], t[1]), t[2].int())
@@ -401,6 +406,8 @@ class FusedServingRank:
             torch.cuda.current_stream().synchronize()
             self._last_status = self._status_word()
         if not self.is_leader:
+            return []
+        if plans is None:
             return []
         outs = [self.h_out[m * self.cap:m * self.cap + T].tolist() for m, T in enumerate(Ts)]
         return self.sched.commit(plans, outs, time.time())
