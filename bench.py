@@ -81,8 +81,8 @@ class ClockSampler:
 
 
 def reference_arm(args):
-    # The unmodified reference cannot be installed on this image: `pip install --no-index --no-build-isolation
-    # --find-links /opt/wheelhouse --target baseline/_ref /root/reference` stops at the C++ build (zmq.hpp and the
+    # The unmodified reference cannot be installed on this image: the offline `pip install --no-index
+    # --no-build-isolation --target baseline/_ref <reference checkout>` stops at the C++ build (zmq.hpp and the
     # cereal headers are missing: its third_party submodules are empty) and its Python side needs ray and vllm 0.6.2.
     print(json.dumps({"impl": "reference", "unavailable":
                       "reference does not build offline: third_party submodules (cereal, grouped_gemm) are empty, "

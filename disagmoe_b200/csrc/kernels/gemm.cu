@@ -74,6 +74,7 @@ struct GemmArgs {
   int group_regions;
   int clear_n;
   int* clear_ptr;
+  int epi_vec;   // plain epilogue may use 16-byte accesses on Y / R (alignment checked on the host)
 };
 
 template <int BN, int EPI>
@@ -82,11 +83,14 @@ struct Cfg {
   static constexpr int kABytes = kBM * kBK * 2;
   static constexpr int kBBytes = BN * kBK * 2;
   static constexpr int kStageBytes = kNumA * kABytes + kBBytes;
-  static constexpr int kStagesRaw = (kSmemBudget - 1024 - kTailBytes) / kStageBytes;
+  // plain epilogue: one 32-token x 128-feature fp32 chunk is transposed through shared memory, so that Y (and the
+  // residual) move as 16-byte row segments instead of one 2-byte element per thread
+  static constexpr int kEpiStageBytes = (EPI == EPI_PLAIN) ? 32 * kBM * 4 : 0;
+  static constexpr int kStagesRaw = (kSmemBudget - 1024 - kTailBytes - kEpiStageBytes) / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
   static constexpr int kAccCols = BN * kNumA;
   static constexpr int kTmemCols = (2 * kAccCols) < 32 ? 32 : 2 * kAccCols;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + kTailBytes;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + kTailBytes + kEpiStageBytes;
   static_assert(kTmemCols <= 512, "accumulators do not fit TMEM");
   static_assert((kTmemCols & (kTmemCols - 1)) == 0, "TMEM columns must be a power of two");
   static_assert(kStages >= 3, "pipeline too shallow");
@@ -167,6 +171,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
   int* last_flag = abort_word + 1;
   int* s_start = last_flag + 1;                                      // [S * G]
   int* s_cnt = s_start + kMaxSeg;                                    // [S * G]
+  float* epi_stage = reinterpret_cast<float*>(tail + kTailBytes);    // [32][kBM] (plain epilogue only)
   const int S = (a.S > 0 && !a.group_regions) ? a.S : 1;
 
   const int warp = threadIdx.x >> 5;
@@ -372,16 +377,39 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         float acc[32];
+        const int jmax = min(32, ntok - c * 32);
+        // Residual rows of this chunk are requested first, so that they travel together with the partial tiles /
+        // the TMEM read below instead of after them. Y may alias R (in-place update of the residual stream): all
+        // loads of a chunk are issued before its first store, and chunks cover disjoint tokens.
+        float r[32];
+        const bool vec = (EPI == EPI_PLAIN) && a.epi_vec != 0;
+        const bool has_r = (EPI == EPI_PLAIN) && a.R != nullptr && f_ok && !vec;
+        if (has_r) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const long long t = tok_base + c * 32 + j;
+            r[j] = (j < jmax) ? __bfloat162float(a.R[t * a.ldr + f]) : 0.f;
+          }
+        }
         if (a.splitk > 1) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) acc[j] = 0.f;
-          for (int s = 0; s < a.splitk; ++s) {
-            const float4* wsp = reinterpret_cast<const float4*>(a.ws) +
-                                (static_cast<size_t>(tile_mn) * a.splitk + s) * (BN / 4) * kBM;
+          // two splits' worth of loads (16 x 16 bytes per thread) are in flight before the first add: the chain of
+          // L2 round trips of the last arriver is half as long as with one split at a time
+          for (int s = 0; s < a.splitk; s += 2) {
+            const float4* w0 = reinterpret_cast<const float4*>(a.ws) +
+                               (static_cast<size_t>(tile_mn) * a.splitk + s) * (BN / 4) * kBM;
+            const bool two = s + 1 < a.splitk;
+            const float4* w1 = two ? w0 + (BN / 4) * kBM : w0;
+            float4 o0[8], o1[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o0[j] = __ldcg(&w0[(c * 8 + j) * kBM + row]);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o1[j] = two ? __ldcg(&w1[(c * 8 + j) * kBM + row]) : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-              const float4 o = __ldcg(&wsp[(c * 8 + j) * kBM + row]);
-              acc[4 * j] += o.x; acc[4 * j + 1] += o.y; acc[4 * j + 2] += o.z; acc[4 * j + 3] += o.w;
+              acc[4 * j] += o0[j].x + o1[j].x; acc[4 * j + 1] += o0[j].y + o1[j].y;
+              acc[4 * j + 2] += o0[j].z + o1[j].z; acc[4 * j + 3] += o0[j].w + o1[j].w;
             }
           }
         } else {
@@ -408,8 +436,58 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
             mbar_arrive(smem_u32(&tempty_bar[buf]));
           }
         }
+        if (EPI == EPI_PLAIN && vec) {
+          if (jmax <= 0) continue;                   // uniform over the CTA: no barrier is skipped by some threads only
+          // transpose the chunk: thread = feature row writes its 32 token values; then thread (token, 8 features)
+#pragma unroll
+          for (int j = 0; j < 32; ++j) epi_stage[j * kBM + row] = acc[j];
+          named_bar_sync(1, kEpiThreads);
+          const int fg = et & 15, tk0 = et >> 4;
+          const int f0 = m * kBM + fg * 8;
+          if (f0 < a.F) {                            // F is a multiple of 8 on this path
+            uint4 rr[4];
+            if (a.R != nullptr) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const int j = tk0 + q * 8;
+                const long long t = tok_base + c * 32 + j;
+                rr[q] = (j < jmax) ? *reinterpret_cast<const uint4*>(a.R + t * a.ldr + f0) : make_uint4(0, 0, 0, 0);
+              }
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const int j = tk0 + q * 8;
+              if (j >= jmax) continue;
+              const long long t = tok_base + c * 32 + j;
+              const float4 x0 = *reinterpret_cast<const float4*>(&epi_stage[j * kBM + fg * 8]);
+              const float4 x1 = *reinterpret_cast<const float4*>(&epi_stage[j * kBM + fg * 8 + 4]);
+              float o[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+              if (a.R != nullptr) {
+                const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&rr[q]);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const float2 rf = __bfloat1622float2(rp[i]);
+                  o[2 * i] += rf.x;
+                  o[2 * i + 1] += rf.y;
+                }
+              }
+              if (a.y_f32) {
+                float* yp = reinterpret_cast<float*>(a.Y) + t * a.ldy + f0;
+                *reinterpret_cast<float4*>(yp) = make_float4(o[0], o[1], o[2], o[3]);
+                *reinterpret_cast<float4*>(yp + 4) = make_float4(o[4], o[5], o[6], o[7]);
+              } else {
+                uint4 pk;
+                __nv_bfloat162* pp = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) pp[i] = __floats2bfloat162_rn(o[2 * i], o[2 * i + 1]);
+                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.Y) + t * a.ldy + f0) = pk;
+              }
+            }
+          }
+          named_bar_sync(1, kEpiThreads);            // the stage is free again for the next chunk / tile
+          continue;
+        }
         if (!f_ok) continue;
-        const int jmax = min(32, ntok - c * 32);
         if (EPI == EPI_COMBINE) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
@@ -427,15 +505,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
             }
           }
         } else {
-          if (a.R != nullptr) {
-            // all residual loads of the chunk are issued before the first store: Y may alias R (in-place update),
-            // so the compiler cannot hoist them itself, and one load -> store round trip per token would serialise
-            float r[32];
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const long long t = tok_base + c * 32 + j;
-              r[j] = (j < jmax) ? __bfloat162float(a.R[t * a.ldr + f]) : 0.f;
-            }
+          if (has_r) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) acc[j] += r[j];
           }
@@ -607,6 +677,12 @@ extern "C" int dmoe_gemm(const DmoeGemm* d, void* stream_) {
   a.signal_ptrs = reinterpret_cast<int* const*>(d->signal_ptrs); a.n_signal = d->n_signal;
   a.signal_slot = d->signal_slot; a.signal_epoch = d->signal_epoch; a.done_ticket = d->done_ticket;
   a.fanout = d->fanout; a.group_regions = d->group_regions; a.clear_n = d->clear_n; a.clear_ptr = d->clear_ptr;
+  {
+    const auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    const long long ymod = d->y_f32 ? 4 : 8;
+    a.epi_vec = (epi == EPI_PLAIN && d->F % 8 == 0 && d->ldy % ymod == 0 && al16(d->Y) &&
+                 (d->R == nullptr || (d->ldr % 8 == 0 && al16(d->R)))) ? 1 : 0;
+  }
   if (a.group_regions && (a.seg_cnt == nullptr || static_cast<long long>(a.G) * a.seg_cap > d->T)) return -16;
   if (!a.group_regions && a.S > 0 && (a.seg_cnt == nullptr || a.S * a.G > kMaxSeg || a.S * a.seg_cap > d->T)) return -16;
   if (a.S == 0 && a.G > kMaxSeg) return -16;
