@@ -369,6 +369,35 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("create_nccl_group_channel", [](int rank, int world, py::bytes uid) {
     return create_nccl_group_channel(rank, world, std::string(uid));
   });
+  // Name-compatible factories of the reference module (csrc/bindings.cpp:190-196): one group channel per local rank
+  // of an in-process party; a p2p channel whose id is picked from a {peer: id} map or given directly.
+  m.def("create_nccl_group_channels", [](int root, const std::vector<int>& party_all, py::bytes uid) {
+    DMOE_CHECK(root == 0, "the group root is rank 0");
+    std::vector<std::shared_ptr<NcclGroupChannel>> out;
+    const std::string id(uid);
+    for (size_t i = 0; i < party_all.size(); ++i)
+      out.push_back(create_nccl_group_channel(static_cast<int>(i), static_cast<int>(party_all.size()), id));
+    return out;
+  });
+  m.def("create_channel_py_map", [](int local, int peer, const std::map<int, py::bytes>& uids) {
+    auto it = uids.find(peer);
+    DMOE_CHECK(it != uids.end(), "no channel id for peer " << peer);
+    return create_channel(local, peer, std::string(it->second));
+  });
+  m.def("create_channel_py_single", [](int local, int peer, py::bytes uid) {
+    return create_channel(local, peer, std::string(uid));
+  });
+  // Row scatter out[mappings[i]] = tokens[i / k], k = len(mappings) / len(tokens) (reference: csrc/permute.cu:53-112,
+  // bound under the same name). This entry runs on any device through tensor ops; the sm_100a kernel of the same
+  // operation is dmoe_permute_rows in the kernel library (disagmoe_b200.ops.memory.permute_tokens_cuda).
+  m.def("permute_tokens_cuda", [](const torch::Tensor& tokens, const torch::Tensor& mappings, uintptr_t /*stream*/) {
+    const int64_t n_out = mappings.numel();
+    const int64_t k = std::max<int64_t>(1, n_out / std::max<int64_t>(1, tokens.size(0)));
+    auto src = k > 1 ? tokens.repeat_interleave(k, 0) : tokens;
+    auto out = torch::empty({n_out, tokens.size(1)}, tokens.options());
+    out.index_copy_(0, mappings.to(torch::kLong).to(tokens.device()), src.slice(0, 0, n_out));
+    return out;
+  }, py::arg("tokens"), py::arg("mappings"), py::arg("stream") = 0);
   m.def("instantiate_channels", &instantiate_channels, py::call_guard<py::gil_scoped_release>());
   m.def("get_nccl_unique_id", [] { return py::bytes(get_nccl_unique_id()); });
   m.def("set_gpu_library_paths", &GpuApi::set_library_paths);

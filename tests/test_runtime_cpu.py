@@ -215,3 +215,21 @@ def test_dp_scheduler_max_blocks_until_release():
         rr = get_dp_scheduler(3, 64, 16, "RR")
         assert rr.schedule([10, 11, 12, 13]) == [0, 1, 2, 0]
     asyncio.run(run())
+
+
+def test_native_module_keeps_the_reference_api_surface():
+    """Every class / function name the reference binds in its disagmoe_c module (csrc/bindings.cpp:24-221) exists."""
+    classes = ("MuHelper Scheduler AttentionScheduler MuDispatcher Tokenizer Sampler TopKSampler TensorBatch ChannelInfo "
+               "Channel NcclGroupChannel TokenMetadata ParallelConfig AttentionBatch SloStat SamplerStepInfo "
+               "AttentionBatchMetadata Metadata NcclChannel BlockManager TraceContext").split()
+    functions = ("prepare_batch_infos permute_tokens_cuda recorder_output recorder_create range_push range_pop "
+                 "create_channel create_nccl_group_channel create_nccl_group_channels create_channel_py_map "
+                 "create_channel_py_single get_nccl_unique_id instantiate_channels init_engine init_engine_colocate "
+                 "start_engine init_sampler init_tokenizer set_hosts").split()
+    missing = [n for n in classes + functions if not hasattr(C, n)]
+    assert not missing, missing
+    x = torch.arange(12.0).view(4, 3)
+    m = torch.tensor([3, 0, 2, 1, 7, 4, 6, 5])
+    out = C.permute_tokens_cuda(x, m)
+    for i in range(8):
+        assert torch.equal(out[m[i]], x[i // 2])
