@@ -437,6 +437,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("wait_for_new_requests", &Scheduler::wait_for_new_requests, py::arg("timeout_ms") = 100,
            py::call_guard<py::gil_scoped_release>())
       .def("get_pool_snapshot", &Scheduler::get_pool_snapshot)
+      .def("get_cur_queueing_delay", &Scheduler::get_cur_queueing_delay)
       .def("set_max_batch_size", &Scheduler::set_max_batch_size)
       .def("set_schedule_policy", &Scheduler::set_schedule_policy)
       .def("set_schedule_block", &Scheduler::set_schedule_block);
@@ -445,6 +446,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("wait_for_new_requests", &AttentionScheduler::wait_for_new_requests, py::arg("timeout_ms") = 100,
            py::call_guard<py::gil_scoped_release>())
       .def("get_pool_snapshot", &AttentionScheduler::get_pool_snapshot)
+      .def("get_cur_queueing_delay", &AttentionScheduler::get_cur_queueing_delay)
       .def("set_max_batch_size", &AttentionScheduler::set_max_batch_size)
       .def("set_schedule_policy", &AttentionScheduler::set_schedule_policy)
       .def("set_schedule_block", &AttentionScheduler::set_schedule_block)

@@ -313,7 +313,7 @@ void MuPool::process_batch(torch::Tensor tensor, metadata_t meta, int kind) {
   const int cell = local * num_groups_ + group;
   {
     std::lock_guard<std::mutex> lk(batch_mu_);
-    queues_[cell].push_back(TensorBatch{tensor, meta});
+    queues_[cell].push_back(TensorBatch{tensor, meta, now_ms()});
     tokens_per_cell_[cell] += n;
     layer_scheduler_->add_tokens_to_layer(cell, n);
   }
@@ -335,6 +335,7 @@ std::vector<TensorBatch> MuPool::fetch_largest_batch(int* layer_out) {
     out.push_back(std::move(q.front()));
     q.pop_front();
   }
+  if (!out.empty()) last_delay_ms_.store(static_cast<float>(now_ms() - out.front().t_queued_ms));   // FIFO: oldest first
   tokens_per_cell_[cell] -= taken;
   if (tokens_per_cell_[cell] > 0) layer_scheduler_->add_tokens_to_layer(cell, tokens_per_cell_[cell]);
   return out;
@@ -384,6 +385,7 @@ void MuAttentionPool::process_batch(torch::Tensor tensor, metadata_t meta, int k
         TokenTopKInfo info;
         info.seq_id = tm.req_id; info.position = tm.position; info.init_prefill_len = tm.init_prefill_len;
         info.attn_dp_rank = tm.attn_dp_rank; info.token_id = meta->tok.token_ids.at(i);
+        info.t_ready_ms = now_ms();
         ready_[local].push_back(std::move(info));
         ++completed;
         continue;
@@ -396,6 +398,7 @@ void MuAttentionPool::process_batch(torch::Tensor tensor, metadata_t meta, int k
       }
       info.parts.emplace_back(tm.topk_slot, tensor[i]);
       if (info.count() >= needed) {
+        info.t_ready_ms = now_ms();
         ready_[local].push_back(std::move(info));
         partial_[local].erase(key);
         ++completed;
@@ -493,6 +496,9 @@ AttentionBatch MuAttentionPool::fetch_attention_batch() {
     if (!q.empty()) layer_scheduler_->add_tokens_to_layer(local, static_cast<int>(q.size()));
   }
   if (toks.empty()) return AttentionBatch{};
+  double oldest = toks.front().t_ready_ms;
+  for (auto& t : toks) oldest = std::min(oldest, t.t_ready_ms);
+  last_delay_ms_.store(static_cast<float>(now_ms() - oldest));
   return pack(local, toks);
 }
 

@@ -38,6 +38,7 @@ struct MsgHeader {
 struct TensorBatch {
   torch::Tensor data;     // [tokens, hidden] (undefined for token-id batches)
   metadata_t metadata;
+  double t_queued_ms = 0;  // steady-clock time at which a pool queued the batch (0: never queued)
   // Merges batches of one layer into one expert-sorted batch (stable counting sort + row gather).
   static TensorBatch merge(const std::vector<TensorBatch>& batches);
   static TensorBatch concat(const std::vector<TensorBatch>& batches);
@@ -149,6 +150,8 @@ class MuPool : public MuHelper {
   bool wait_for_tokens(int timeout_ms);
   // Test hook: injects a batch as if it had been received.
   virtual void process_batch(torch::Tensor tensor, metadata_t meta, int kind);
+  // How long the oldest row of the most recently fetched batch had been runnable in this pool (milliseconds).
+  float last_queueing_delay_ms() const { return last_delay_ms_.load(); }
   int local_layer(int layer_id) const;
   int global_layer(int local) const { return layer_ids_.at(local); }
   int num_local_layers() const { return static_cast<int>(layer_ids_.size()); }
@@ -170,6 +173,7 @@ class MuPool : public MuHelper {
   std::vector<int> tokens_per_cell_;
   std::map<int, int> layer_to_local_;
   std::shared_ptr<MuPool> forward_;
+  std::atomic<float> last_delay_ms_{0.f};
   bool owns_mailbox_ = true;
 };
 
@@ -177,6 +181,7 @@ class MuPool : public MuHelper {
 struct TokenTopKInfo {
   int seq_id = 0, position = 0, init_prefill_len = -1, attn_dp_rank = 0, token_id = -1;
   std::vector<std::pair<int, torch::Tensor>> parts;   // (slot, row [hidden])
+  double t_ready_ms = 0;                                // when the last part arrived and the token became runnable
   int count() const { return static_cast<int>(parts.size()); }
 };
 
@@ -216,6 +221,9 @@ class Scheduler {
   TensorBatch schedule();
   bool wait_for_new_requests(int timeout_ms = 100) { return pool_->wait_for_tokens(timeout_ms); }
   std::vector<int> get_pool_snapshot() { return pool_->get_pool_snapshot(); }
+  // Queueing delay (ms) of the batch the last schedule() returned (reference: Scheduler::get_cur_queueing_delay,
+  // csrc/include/scheduler.h:54, where the measurement itself is commented out and the value stays 0).
+  float get_cur_queueing_delay() const { return pool_->last_queueing_delay_ms(); }
   void set_max_batch_size(int n) { pool_->set_max_batch_size(n); }
   void set_schedule_policy(const std::string& p) { pool_->set_layer_schedule_type(p); }
   void set_schedule_block(int step) { pool_->set_scheduler_block(step); }
@@ -233,6 +241,7 @@ class AttentionScheduler {
   virtual AttentionBatch schedule();
   bool wait_for_new_requests(int timeout_ms = 100) { return pool_->wait_for_tokens(timeout_ms); }
   std::vector<int> get_pool_snapshot() { return pool_->get_pool_snapshot(); }
+  float get_cur_queueing_delay() const { return pool_->last_queueing_delay_ms(); }
   void set_max_batch_size(int n) { pool_->set_max_batch_size(n); }
   void set_schedule_policy(const std::string& p) { pool_->set_layer_schedule_type(p); }
   void set_schedule_block(int step) { pool_->set_scheduler_block(step); }

@@ -354,6 +354,45 @@ class Controller:
                 res.tokens = self.sampler.get_output_tokens(s.req_id)
                 res.event.set()
 
+    # ---- names of the reference controller (controller.py:131-136, 323-358, 388-390) ------------------------------
+    @property
+    def all_workers(self) -> List[object]:
+        return list(self.workers.values()) + [self.sampler, self.tokenizer]
+
+    @property
+    def all_device_ids(self) -> List[int]:
+        from ..utils.constants import SAMPLER_DEV_ID, TOKENIZER_DEV_ID
+        return list(self.workers) + [SAMPLER_DEV_ID, TOKENIZER_DEV_ID]
+
+    def determine_worker_type(self, device_id: int) -> str:
+        from ..utils.constants import SAMPLER_DEV_ID, TOKENIZER_DEV_ID
+        if device_id == SAMPLER_DEV_ID:
+            return "sampler"
+        if device_id == TOKENIZER_DEV_ID:
+            return "tokenizer"
+        if self.placement.is_hybrid:
+            return "hybrid"
+        return "attention" if self.placement.has_attn(device_id) else "expert"
+
+    def fetch_queueing_delays(self) -> Tuple[List[List[float]], List[List[float]]]:
+        """Per-step queueing delays (ms) of every attention worker and of every expert worker."""
+        attn, exp = [], []
+        for d, res in self._all("fetch_queueing_delays").items():
+            (attn if self.placement.has_attn(d) else exp).append(res)
+        return attn, exp
+
+    def fetch_submitted_time(self) -> Dict[int, float]:
+        return self.tokenizer.fetch_submitted_time()
+
+    def reset_workers(self) -> None:
+        self._all("reset")
+
+    def start_polling_results(self) -> None:
+        if self._poll_thread is None or not self._poll_thread.is_alive():
+            self._end = False
+            self._poll_thread = threading.Thread(target=self._poll_loop, daemon=True, name="controller-poll")
+            self._poll_thread.start()
+
     def release_kv_cache(self, req_ids: List[int]) -> None:
         for d, w in self.workers.items():
             if self.placement.has_attn(d) and d not in self.suspect_workers and w.alive():

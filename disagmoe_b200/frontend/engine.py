@@ -33,6 +33,7 @@ from ..models.attention import AttnMeta, MoEAttention
 from ..models.experts import MoEExperts
 from ..ops import functional as F
 from ..ops import gemm
+from .datatypes import SloStat
 from ..utils.logger import get_logger
 from ..utils.metrics import Metric
 from ..utils.placement import ModelPlacement
@@ -79,6 +80,8 @@ class Engine:
         self._logger = get_logger(f"engine{device_id}")
         self.error: Optional[str] = None
         self._max_rows = 1024
+        self._queueing_delays: List[float] = []      # per executed step: how long its oldest row waited (ms)
+        self.has_attn = self.has_expert = False
 
     # ---- set-up ---------------------------------------------------------------------------------------------
     def set_hosts(self, pid_tag: int, hosts: Dict[int, str]) -> None:
@@ -208,7 +211,15 @@ class Engine:
             self.error = traceback.format_exc()
             self._logger.error(self.error)
 
+    # names of the reference's loops (engine.py:832-904): one loop serves both kinds of worker here
+    def single_module_loop(self) -> None:
+        self._loop()
+
+    def dual_module_loop(self) -> None:
+        self._loop()
+
     def _timed_step(self, fn, layer_id, n_tokens, t_sched, sched) -> None:
+        self._queueing_delays.append(sched.get_cur_queueing_delay())
         t0 = time_ms()
         self.timer.start("step")
         with nvtx_range("engine.step"):
@@ -361,6 +372,42 @@ class Engine:
             self.block_mgr.batch_release(held)
             self.handles.attn_pool.release_seqs(seq_ids)
 
+    def fetch_queueing_delays(self) -> List[float]:
+        """Milliseconds the oldest row of every executed batch had waited in this worker's pool (reference:
+        engine.py:919-920, where the underlying measurement is disabled)."""
+        return list(self._queueing_delays)
+
+    def set_device_id(self, device_id: int) -> None:
+        self.device_id = device_id
+
+    def get_node_ip(self) -> str:
+        from ..utils.utils import get_ip
+        return get_ip()
+
+    @property
+    def is_attn_driver(self) -> bool:
+        return self.has_attn and self.model_config.tp_size > 1 and self.model_config.rank == 0
+
+    @property
+    def is_attn_worker(self) -> bool:
+        return self.has_attn and self.model_config.tp_size > 1 and self.model_config.rank > 0
+
+    def get_configured_kv_cache_blocks(self) -> int:
+        return self.cache_config.num_gpu_blocks
+
+    def determine_kv_cache_blocks(self, gpu_memory_utilization: float = 0.9) -> int:
+        """Paged-KV blocks that fit next to the weights already resident: (total * utilisation - used) / bytes of
+        one block over this worker's attention layers (reference: engine.py:328-348; no profile run is needed here
+        because the activation buffers of a step are a few MB)."""
+        cfg, cc = self.model_config, self.cache_config
+        n_layers = max(1, len(self.attn_layers))
+        kvh = next(iter(self.attn_layers.values())).num_kv_heads if self.attn_layers else cfg.num_kv_heads
+        block_bytes = n_layers * 2 * cc.block_size * kvh * cfg.head_dim * torch.empty(0, dtype=self.dtype).element_size()
+        if self.device.type != "cuda":
+            return cc.num_gpu_blocks or 1024
+        free, total = torch.cuda.mem_get_info(self.device)
+        return max(0, int((total * gpu_memory_utilization - (total - free)) // block_bytes))
+
     def num_free_blocks(self) -> int:
         return self.block_mgr.num_free_blocks() if self.block_mgr is not None else 0
 
@@ -411,6 +458,7 @@ class Engine:
     def reset(self) -> None:
         self.metric = Metric()
         self.step_infos = []
+        self._queueing_delays = []
 
     def terminate(self) -> None:
         self.end_flag = True
@@ -444,6 +492,15 @@ class TokenizerEngine:
         for r, p, d in zip(req_ids, prompts, dp_ranks):
             self.put_single_request(r, p, d)
 
+    put_requests = put_request          # the reference's name (engine.py:1068)
+    process_request = put_single_request
+
+    def fetch_submitted_time(self) -> Dict[int, float]:
+        return dict(self.t_submitted)
+
+    def reset(self) -> None:
+        self.t_submitted.clear()
+
     def terminate(self) -> None:
         self.tokenizer.terminate()
 
@@ -461,6 +518,19 @@ class SamplerEngine:
 
     def set_request_output_len(self, req_id: int, n: int) -> None:
         self.sampler.set_request_output_len(req_id, n)
+
+    def wait_for_n_requests(self, n_request: int, timeout: float = 600.0) -> Dict[int, SloStat]:
+        """Blocks until ``n_request`` requests have finished; their SLO timestamps by request id (reference:
+        engine.py:1035-1043)."""
+        t0, out = time.time(), {}
+        while len(out) < n_request:
+            for s in self.sampler.fetch_finished_slo_stats():
+                out[s.req_id] = SloStat.from_c(s)
+            if time.time() - t0 > timeout:
+                raise TimeoutError(f"{len(out)} of {n_request} requests finished within {timeout} s")
+            if len(out) < n_request:
+                time.sleep(0.002)
+        return out
 
     def fetch_finished_results(self):
         return self.sampler.fetch_finished_slo_stats()

@@ -49,3 +49,6 @@ def permute_tokens_cuda(tokens: torch.Tensor, mappings: torch.Tensor) -> torch.T
 
 
 permute_tokens = permute_tokens_cuda
+# The reference also ships a Triton version of the same scatter (ops/memory.py:71-91, used by its tests only). This
+# code base has no Triton path: the name resolves to the sm_100a kernel.
+permute_tokens_triton = permute_tokens_cuda

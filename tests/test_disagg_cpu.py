@@ -41,6 +41,13 @@ def _run(cfg, placement_args, n_dev, in_process, n_req, prompt_len, n_new, strat
         assert worst < 1e-4, f"max logit error {worst}"
         errs = [e for e in ctl.worker_errors().values() if e]
         assert not errs, errs
+        # bookkeeping the reference controller exposes under the same names
+        attn_q, exp_q = ctl.fetch_queueing_delays()
+        assert attn_q and all(len(q) > 0 and min(q) >= 0.0 for q in attn_q)
+        if strategy != "colocate":
+            assert exp_q and all(len(q) > 0 for q in exp_q) and max(max(q) for q in attn_q + exp_q) > 0.0
+        assert set(ctl.fetch_submitted_time()) == {r.req_id for r in res}
+        assert ctl.determine_worker_type(0) in ("attention", "hybrid") and len(ctl.all_device_ids) == n_dev + 2
     finally:
         ctl.stop_workers()
 
