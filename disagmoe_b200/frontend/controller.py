@@ -164,6 +164,10 @@ class Controller:
         self._free_blocks: Dict[int, int] = {}
         self._req_rank: Dict[int, int] = {}
         self._lock = threading.Lock()
+        self._init_args = None                       # arguments of init_engine, kept for recover()
+        self._req_info: Dict[int, Tuple[List[int], int]] = {}   # request -> (original prompt, output length)
+        self._prefix: Dict[int, List[int]] = {}      # tokens a request had produced before a recovery
+        self._pending_args: Dict[int, InitCoreArgs] = {}
 
     # ---- workers --------------------------------------------------------------------------------------------
     def _device_of(self, device_id: int) -> str:
@@ -204,6 +208,9 @@ class Controller:
                     sampling_config: Optional[SamplingConfig] = None, state_dict_path: Optional[str] = None,
                     keep_logits: bool = False, dtype=None, ignore_eos: bool = True) -> None:
         self.placement, self.model_config = placement, model_config
+        self._init_args = (placement, model_config, cache_config, sampling_config, state_dict_path, keep_logits, dtype,
+                           ignore_eos)
+        self._pending_args = {}
         cache_config = cache_config or CacheConfig()
         sampling_config = sampling_config or SamplingConfig(1, 2)
         L = model_config.num_layers
@@ -256,7 +263,6 @@ class Controller:
                 local_attn_dp_rank=placement.attn_dp_rank_at(d) if d in placement.attn else 0,
                 expert_ids=list(placement.expert_ids_at(d)), hosts=hosts, port_shift=self.port_shift,
                 state_dict_path=state_dict_path, keep_logits=keep_logits)
-            self._pending_args = getattr(self, "_pending_args", {})
             self._pending_args[d] = args
         # in-edges are the transpose of the (extended) out-edges
         for d, a in self._pending_args.items():
@@ -311,16 +317,21 @@ class Controller:
             prompt = [rnd.randrange(3, cfg.vocab_size) for _ in range(prompt)]
         rid = req_id if req_id is not None else self.get_new_req_id()
         max_out = output_len if output_len is not None else self.sampling_config.max_output_len
-        need = (len(prompt) + max_out + self.cache_config.block_size - 1) // self.cache_config.block_size
-        rank = self._pick_dp_rank(need)
         res = AsyncResult(rid, threading.Event())
         with self._lock:
             self.results[rid] = res
-            self._req_rank[rid] = (rank, need)
-        if output_len is not None:
-            self.sampler.set_request_output_len(rid, output_len)
-        self.tokenizer.put_single_request(rid, prompt, rank)
+            self._req_info[rid] = (list(prompt), max_out)
+        self._submit(rid, list(prompt), max_out, explicit_len=output_len is not None)
         return res
+
+    def _submit(self, rid: int, prompt: List[int], max_out: int, explicit_len: bool = True) -> None:
+        need = (len(prompt) + max_out + self.cache_config.block_size - 1) // self.cache_config.block_size
+        rank = self._pick_dp_rank(need)
+        with self._lock:
+            self._req_rank[rid] = (rank, need)
+        if explicit_len:
+            self.sampler.set_request_output_len(rid, max_out)
+        self.tokenizer.put_single_request(rid, prompt, rank)
 
     def put_requests(self, prompts: List, output_lens: Optional[List[int]] = None) -> List[AsyncResult]:
         return [self.put_single_request(p, None if output_lens is None else output_lens[i])
@@ -351,7 +362,7 @@ class Controller:
                     self._free_blocks[rank_need[0]] += rank_need[1]
             if res is not None:
                 res.slo = SloStat.from_c(s)
-                res.tokens = self.sampler.get_output_tokens(s.req_id)
+                res.tokens = self._prefix.get(s.req_id, []) + list(self.sampler.get_output_tokens(s.req_id))
                 res.event.set()
 
     # ---- names of the reference controller (controller.py:131-136, 323-358, 388-390) ------------------------------
@@ -445,6 +456,41 @@ class Controller:
                     if e:
                         return f"worker {d}: {e}"
         return None
+
+    def recover(self) -> List[int]:
+        """Recovery after a worker failure by full restart and re-admission: every worker is torn down and rebuilt
+        with the placement / configuration of the last ``init_engine`` (fresh ports, fresh channels), and every
+        request that had not finished is submitted again as prompt + the tokens the sampler had already recorded for it
+        (its KV is rebuilt by a prefill of that longer prompt), for the remaining number of tokens. The
+        ``AsyncResult`` objects handed out before stay valid and receive the complete token list. Returns the ids of
+        the re-admitted requests. The reference has no recovery path (errors are fatal there)."""
+        assert self._init_args is not None, "init_engine has not run"
+        with self._lock:
+            unfinished = [rid for rid, r in self.results.items() if not r.event.is_set()]
+        for rid in unfinished:
+            self._prefix[rid] = self._prefix.get(rid, []) + list(self.sampler.get_output_tokens(rid))
+        self.stop_workers()
+        self.workers.clear()
+        self.suspect_workers.clear()
+        with self._lock:
+            self._req_rank.clear()
+        self.port_shift = (self.port_shift + 16 * 4 * 11) % 6000        # the old sockets may linger in TIME_WAIT
+        self.init_engine(*self._init_args)
+        self.start_engine()
+        again = []
+        for rid in unfinished:
+            prompt, max_out = self._req_info[rid]
+            done = self._prefix[rid]
+            remaining = max_out - len(done)
+            res = self.results[rid]
+            if remaining <= 0:
+                res.tokens = list(done)
+                res.event.set()
+                continue
+            self._submit(rid, prompt + done, remaining)
+            again.append(rid)
+        self._logger.info(f"recovered: {len(again)} request(s) re-admitted")
+        return again
 
     # ---- stats / control ------------------------------------------------------------------------------------
     def fetch_step_stats(self):

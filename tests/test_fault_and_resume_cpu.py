@@ -97,3 +97,43 @@ def test_serving_state_snapshot_resumes_with_identical_tokens():
     b.load_state(path)
     got = b.run_until_done(100)
     assert got == want
+
+
+def test_recover_restarts_workers_and_readmits_unfinished_requests():
+    """The expert worker process dies while requests are decoding. ``Controller.recover`` rebuilds every worker and
+    re-admits the unfinished requests as prompt + tokens produced so far; the final token lists equal the oracle's."""
+    import os
+    import tempfile
+    from disagmoe_b200.models.oracle import OracleModel
+    from disagmoe_b200.models.weights import init_state_dict, save_state_dict
+    cfg = tiny_config.clone(ep_size=1)
+    sd = init_state_dict(cfg)
+    path = os.path.join(tempfile.mkdtemp(), "tiny.pt")
+    save_state_dict(sd, path)
+    place = get_model_placement(cfg, ClusterConfig(1, 2), "pipeline", 1, 1)
+    ctl = init_controller(1, 2, device="cpu")
+    n_new = 40
+    try:
+        ctl.init_engine(place, cfg, CacheConfig(block_size=16, num_gpu_blocks=128), SamplingConfig(n_new, n_new + 1),
+                        state_dict_path=path, dtype=torch.float32)
+        ctl.start_engine()
+        g = torch.Generator().manual_seed(3)
+        prompts = [torch.randint(3, cfg.vocab_size, (10,), generator=g).tolist() for _ in range(4)]
+        res = [ctl.put_single_request(p, output_len=n_new) for p in prompts]
+        t0 = time.time()
+        while len(ctl.sampler.get_output_tokens(res[0].req_id)) < 3:
+            assert time.time() - t0 < 60
+            time.sleep(0.001)
+        ctl.workers[1].proc.terminate()           # between two of its steps as far as the GPU-less worker is concerned
+        ctl.workers[1].proc.join(timeout=10)
+        assert ctl.check_workers() == [1]
+        again = ctl.recover()
+        assert again, "the worker died before the requests had finished, so some must be re-admitted"
+        assert ctl.check_workers() == []
+        ctl.wait_for_requests(4, timeout=120)
+        oracle = OracleModel(cfg, sd)
+        for r, p in zip(res, prompts):
+            want, _ = oracle.generate(r.req_id, p, n_new)
+            assert r.tokens == want, f"request {r.req_id}"
+    finally:
+        ctl.stop_workers()
