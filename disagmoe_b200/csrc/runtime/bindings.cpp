@@ -408,6 +408,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("get_zmq_addr", &get_zmq_addr, py::arg("device_id"), py::arg("is_gpu") = true, py::arg("offset") = 0,
         py::arg("group_hash") = 0);
   m.def("set_inproc_transport", &set_inproc_transport);
+  m.def("set_send_fault", &set_send_fault, py::arg("kind"), py::arg("nth"), py::arg("delay_ms") = 0);
+  m.def("send_faults_fired", &send_faults_fired);
+  m.attr("SEND_FAULT_DROP") = static_cast<int>(SEND_FAULT_DROP);
+  m.attr("SEND_FAULT_DUPLICATE") = static_cast<int>(SEND_FAULT_DUPLICATE);
+  m.attr("SEND_FAULT_DELAY") = static_cast<int>(SEND_FAULT_DELAY);
   m.def("set_port_base", &set_port_base);
   m.def("is_embedding_node", &is_embedding_node);
 

@@ -56,6 +56,7 @@ void Sampler::recv_loop() {
     MsgHeader h;
     from_bytes(f[0], h);
     if (h.kind == MSG_STOP) continue;
+    if (seq_filter_.seen(h.sender, h.seq)) continue;   // a duplicated message must not count a token twice
     Metadata meta;
     from_bytes(f[1], meta);
     try {

@@ -59,6 +59,7 @@ class Sampler : public MuDispatcher {
   bool ignore_eos_;
   std::mt19937 rng_;
   PullSocket mailbox_;
+  SeqFilter seq_filter_;
   std::thread recv_thread_;
   std::mutex result_mu_;
   std::map<int, int> output_lens_, required_lens_;

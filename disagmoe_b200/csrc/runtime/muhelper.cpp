@@ -132,6 +132,7 @@ void MuDispatcher::send_batch(Endpoint& ep, const torch::Tensor& rows, const Met
   const bool has_rows = rows.defined() && rows.numel() > 0;
   const bool inline_payload = !ep.channel || ep.channel->inline_payload();
   h.has_payload = (has_rows && inline_payload) ? 1 : 0;
+  h.seq = next_message_seq();
   if (has_rows && !inline_payload) h.ticket = ep.channel->stash(rows);
   std::unique_lock<std::mutex> pair_lock;
   if (ep.channel) pair_lock = std::unique_lock<std::mutex>(ep.channel->send_mutex());
@@ -280,6 +281,10 @@ void MuPool::run() {
     MsgHeader h;
     from_bytes(f[0], h);
     if (h.kind == MSG_STOP) continue;
+    if (seq_filter_.seen(h.sender, h.seq)) {
+      DMOE_LOG(WARN) << "pool@" << device_id_ << ": duplicate message " << h.seq << " from " << h.sender << " dropped";
+      continue;
+    }
     auto meta = std::make_shared<Metadata>();
     from_bytes(f[1], *meta);
     torch::Tensor t;

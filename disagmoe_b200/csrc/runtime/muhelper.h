@@ -31,8 +31,9 @@ struct MsgHeader {
   int has_payload = 0;
   int dst_role = 0;   // 0 = attention role, 1 = expert role of the receiving device (colocated workers run both)
   uint64_t ticket = 0;  // same-process edges: the tensor waits in the LocalChannel under this ticket
+  uint64_t seq = 0;     // process-wide message number of the sender; receivers drop a (sender, seq) seen before
   template <class A>
-  void io(A& a) { a(sender, kind, has_payload, dst_role, ticket); }
+  void io(A& a) { a(sender, kind, has_payload, dst_role, ticket, seq); }
 };
 
 struct TensorBatch {
@@ -173,6 +174,7 @@ class MuPool : public MuHelper {
   std::vector<int> tokens_per_cell_;
   std::map<int, int> layer_to_local_;
   std::shared_ptr<MuPool> forward_;
+  SeqFilter seq_filter_;
   std::atomic<float> last_delay_ms_{0.f};
   bool owns_mailbox_ = true;
 };

@@ -1,4 +1,7 @@
 #include "net.h"
+#include <chrono>
+#include <thread>
+#include <atomic>
 
 #include <arpa/inet.h>
 #include <fcntl.h>
@@ -188,7 +191,63 @@ void PushSocket::connect(const std::string& addr, int timeout_ms) {
   }
 }
 
+namespace {
+std::mutex g_fault_mu;
+int g_fault_kind = SEND_FAULT_NONE, g_fault_countdown = 0, g_fault_delay_ms = 0, g_faults_fired = 0;
+std::atomic<uint64_t> g_msg_seq{0};
+
+// Which fault (if any) applies to the message being sent now.
+int take_send_fault(int* delay_ms) {
+  std::lock_guard<std::mutex> lk(g_fault_mu);
+  if (g_fault_kind == SEND_FAULT_NONE || --g_fault_countdown > 0) return SEND_FAULT_NONE;
+  const int k = g_fault_kind;
+  *delay_ms = g_fault_delay_ms;
+  g_fault_kind = SEND_FAULT_NONE;
+  ++g_faults_fired;
+  return k;
+}
+}  // namespace
+
+void set_send_fault(int kind, int nth, int delay_ms) {
+  std::lock_guard<std::mutex> lk(g_fault_mu);
+  g_fault_kind = kind;
+  g_fault_countdown = nth < 1 ? 1 : nth;
+  g_fault_delay_ms = delay_ms;
+}
+
+int send_faults_fired() {
+  std::lock_guard<std::mutex> lk(g_fault_mu);
+  return g_faults_fired;
+}
+
+uint64_t next_message_seq() { return ++g_msg_seq; }
+
+bool SeqFilter::seen(int sender, uint64_t seq) {
+  if (seq == 0) return false;
+  auto& p = s_[sender];
+  if (p.have.count(seq)) {
+    ++dups_;
+    return true;
+  }
+  p.have.insert(seq);
+  p.order.push_back(seq);
+  if (p.order.size() > kWindow) {
+    p.have.erase(p.order.front());
+    p.order.pop_front();
+  }
+  return false;
+}
+
 void PushSocket::send(const Frames& frames) {
+  int delay_ms = 0;
+  const int fault = take_send_fault(&delay_ms);
+  if (fault == SEND_FAULT_DROP) return;
+  if (fault == SEND_FAULT_DELAY) std::this_thread::sleep_for(std::chrono::milliseconds(delay_ms));
+  send_now(frames);
+  if (fault == SEND_FAULT_DUPLICATE) send_now(frames);
+}
+
+void PushSocket::send_now(const Frames& frames) {
   if (inproc_) {
     {
       std::lock_guard<std::mutex> lk(inproc_->mu);

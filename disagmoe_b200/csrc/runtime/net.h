@@ -6,6 +6,8 @@
 // any number of pushers. Receives take a timeout so that a helper thread can always be stopped (the reference
 // joins threads that are blocked in recv). Port scheme of get_zmq_addr (csrc/include/distributed.hpp:52-59).
 #pragma once
+#include <map>
+#include <set>
 #include <condition_variable>
 #include <deque>
 
@@ -52,10 +54,36 @@ class PushSocket {
   bool connected() const { return fd_ >= 0 || inproc_ != nullptr; }
 
  private:
+  void send_now(const Frames& frames);
   std::mutex mu_;
   int fd_ = -1;
   std::shared_ptr<InprocQueue> inproc_;
 };
+
+// Host-side fault injection for tests of the failure paths (no GPU is involved): the `nth` message sent by this
+// process from now on (1 = the next one) is dropped, sent twice, or held back for `delay_ms`. One shot.
+enum SendFault { SEND_FAULT_NONE = 0, SEND_FAULT_DROP = 1, SEND_FAULT_DUPLICATE = 2, SEND_FAULT_DELAY = 3 };
+void set_send_fault(int kind, int nth, int delay_ms = 0);
+int send_faults_fired();
+
+// Receiver-side duplicate filter: remembers the last `window` sequence numbers seen per sender.
+class SeqFilter {
+ public:
+  // True when (sender, seq) was seen before (the caller then drops the message). seq 0 = unnumbered, never a duplicate.
+  bool seen(int sender, uint64_t seq);
+  uint64_t duplicates() const { return dups_; }
+
+ private:
+  struct PerSender {
+    std::deque<uint64_t> order;
+    std::set<uint64_t> have;
+  };
+  std::map<int, PerSender> s_;
+  uint64_t dups_ = 0;
+  static constexpr size_t kWindow = 8192;
+};
+// Process-wide message numbering (strictly increasing, never 0).
+uint64_t next_message_seq();
 
 // device id -> ip table (persisted so that helper processes of the same job can read it)
 void set_hosts(int pid_tag, const std::map<int, std::string>& device_ip);

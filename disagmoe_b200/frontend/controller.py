@@ -168,6 +168,7 @@ class Controller:
         self._req_info: Dict[int, Tuple[List[int], int]] = {}   # request -> (original prompt, output length)
         self._prefix: Dict[int, List[int]] = {}      # tokens a request had produced before a recovery
         self._pending_args: Dict[int, InitCoreArgs] = {}
+        self._progress: Dict[int, Tuple[int, float]] = {}   # request -> (tokens seen, time of the last new token)
 
     # ---- workers --------------------------------------------------------------------------------------------
     def _device_of(self, device_id: int) -> str:
@@ -347,7 +348,29 @@ class Controller:
             if time.time() - last_beat > max(1.0, self.heartbeat_timeout_s / 3):
                 last_beat = time.time()
                 self.check_workers()
+            self._note_progress()
             time.sleep(0.002)
+
+    def _note_progress(self, period_s: float = 0.05) -> None:
+        now = time.time()
+        if now - getattr(self, "_last_progress_scan", 0.0) < period_s:
+            return
+        self._last_progress_scan = now
+        with self._lock:
+            pending = [rid for rid, r in self.results.items() if not r.event.is_set()]
+        for rid in pending:
+            n = len(self.sampler.get_output_tokens(rid))
+            seen = self._progress.get(rid)
+            if seen is None or seen[0] != n:
+                self._progress[rid] = (n, now)
+
+    def stalled_requests(self, deadline_s: float) -> List[int]:
+        """Unfinished requests that have produced no token for ``deadline_s`` seconds (a lost message leaves the
+        tokens of a request waiting for a part that never comes; nothing else in the system would notice)."""
+        now = time.time()
+        with self._lock:
+            pending = [rid for rid, r in self.results.items() if not r.event.is_set()]
+        return [rid for rid in pending if rid in self._progress and now - self._progress[rid][1] > deadline_s]
 
     def process_finished_results(self, stats) -> None:
         if not stats:
@@ -472,6 +495,7 @@ class Controller:
         self.stop_workers()
         self.workers.clear()
         self.suspect_workers.clear()
+        self._progress.clear()
         with self._lock:
             self._req_rank.clear()
         self.port_shift = (self.port_shift + 16 * 4 * 11) % 6000        # the old sockets may linger in TIME_WAIT

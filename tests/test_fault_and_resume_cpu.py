@@ -137,3 +137,65 @@ def test_recover_restarts_workers_and_readmits_unfinished_requests():
             assert r.tokens == want, f"request {r.req_id}"
     finally:
         ctl.stop_workers()
+
+
+def _tiny_job(n_new, **init_kw):
+    import os
+    import tempfile
+    from disagmoe_b200.models.oracle import OracleModel
+    from disagmoe_b200.models.weights import init_state_dict, save_state_dict
+    cfg = tiny_config.clone(ep_size=1)
+    sd = init_state_dict(cfg)
+    path = os.path.join(tempfile.mkdtemp(), "tiny.pt")
+    save_state_dict(sd, path)
+    place = get_model_placement(cfg, ClusterConfig(1, 2), "pipeline", 1, 1)
+    ctl = init_controller(1, 2, device="cpu", in_process=True)
+    ctl.init_engine(place, cfg, CacheConfig(block_size=16, num_gpu_blocks=128), SamplingConfig(n_new, n_new + 1),
+                    state_dict_path=path, dtype=torch.float32)
+    ctl.start_engine()
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(3, cfg.vocab_size, (9,), generator=g).tolist() for _ in range(3)]
+    return cfg, ctl, prompts, OracleModel(cfg, sd)
+
+
+@pytest.mark.parametrize("kind", ["duplicate", "delay"])
+def test_duplicated_or_delayed_message_does_not_change_the_result(kind):
+    """Host-side fault hook on the message layer: one message is sent twice (the receiver's sequence filter drops the
+    copy) or held back for 150 ms. The generated tokens still equal the oracle's."""
+    from disagmoe_b200 import disagmoe_c as C
+    n_new = 6
+    cfg, ctl, prompts, oracle = _tiny_job(n_new)
+    try:
+        fired0 = C.send_faults_fired()
+        C.set_send_fault(C.SEND_FAULT_DUPLICATE if kind == "duplicate" else C.SEND_FAULT_DELAY, 7, 150)
+        res = [ctl.put_single_request(p, output_len=n_new) for p in prompts]
+        ctl.wait_for_requests(3, timeout=120)
+        assert C.send_faults_fired() == fired0 + 1
+        for r, p in zip(res, prompts):
+            assert r.tokens == oracle.generate(r.req_id, p, n_new)[0]
+        assert not [e for e in ctl.worker_errors().values() if e]
+    finally:
+        ctl.stop_workers()
+
+
+def test_dropped_message_is_noticed_by_the_deadline_and_recovered():
+    """One message is dropped on the host: the tokens it carried never arrive, the affected requests stop making
+    progress. The controller's per-request deadline reports them and recover() finishes every request."""
+    from disagmoe_b200 import disagmoe_c as C
+    n_new = 8
+    cfg, ctl, prompts, oracle = _tiny_job(n_new)
+    try:
+        C.set_send_fault(C.SEND_FAULT_DROP, 9)
+        res = [ctl.put_single_request(p, output_len=n_new) for p in prompts]
+        t0 = time.time()
+        while not ctl.stalled_requests(0.5):
+            assert time.time() - t0 < 30, "the stall was not reported"
+            time.sleep(0.05)
+        stalled = ctl.stalled_requests(0.5)
+        assert set(stalled) <= {r.req_id for r in res}
+        ctl.recover()
+        ctl.wait_for_requests(3, timeout=120)
+        for r, p in zip(res, prompts):
+            assert r.tokens == oracle.generate(r.req_id, p, n_new)[0]
+    finally:
+        ctl.stop_workers()
