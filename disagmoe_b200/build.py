@@ -82,11 +82,26 @@ def runtime_lib_path():
     return os.path.join(ROOT, "disagmoe_c" + suffix)
 
 
-def build_runtime(force=False, verbose=False):
-    """Compile csrc/runtime/*.cpp into the pybind11 module disagmoe_b200.disagmoe_c."""
+def variant_lib_path(sanitize):
+    suffix = sysconfig.get_config_var("EXT_SUFFIX") or ".so"
+    return os.path.join(ROOT, "_variants", sanitize, "disagmoe_c" + suffix)
+
+
+def sanitizer_runtime(sanitize):
+    """Path of gcc's runtime library of a sanitizer (to be LD_PRELOADed into the Python process), or None."""
+    name = {"address": "libasan.so", "thread": "libtsan.so"}[sanitize]
+    p = subprocess.run(["gcc", "-print-file-name=" + name], capture_output=True, text=True).stdout.strip()
+    return p if os.path.isabs(p) and os.path.exists(p) else None
+
+
+def build_runtime(force=False, verbose=False, sanitize=None):
+    """Compile csrc/runtime/*.cpp into the pybind11 module disagmoe_b200.disagmoe_c. ``sanitize`` = "address" or
+    "thread" builds an instrumented copy under _variants/<sanitize>/ instead (-fsanitize=..., -O1 -g), which the
+    package loads in place of the normal module when DMOE_RUNTIME_VARIANT=<sanitize> is set."""
     srcs = sorted(glob.glob(os.path.join(RUNTIME_DIR, "*.cpp")))
     hdrs = sorted(glob.glob(os.path.join(RUNTIME_DIR, "*.h")) + glob.glob(os.path.join(RUNTIME_DIR, "*.hpp")))
-    out = runtime_lib_path()
+    out = variant_lib_path(sanitize) if sanitize else runtime_lib_path()
+    os.makedirs(os.path.dirname(out), exist_ok=True)
     if not srcs:
         return None
     if not force and not _newer(srcs + hdrs, out):
@@ -101,9 +116,13 @@ def build_runtime(force=False, verbose=False):
     abi = int(torch._C._GLIBCXX_USE_CXX11_ABI)
     cflags = ["-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-DTORCH_EXTENSION_NAME=disagmoe_c",
               "-D_GLIBCXX_USE_CXX11_ABI=%d" % abi, "-DTORCH_API_INCLUDE_EXTENSION_H", "-Wno-unused-variable"]
+    san_flags = []
+    if sanitize:
+        san_flags = ["-fsanitize=" + sanitize, "-fno-omit-frame-pointer", "-g"]
+        cflags = ["-O1" if f == "-O2" else f for f in cflags] + san_flags
     objs, jobs = [], []
     for s in srcs:
-        o = os.path.join(OBJ_DIR, "rt_" + os.path.basename(s)[:-4] + ".o")
+        o = os.path.join(OBJ_DIR, ("rt_%s_" % sanitize if sanitize else "rt_") + os.path.basename(s)[:-4] + ".o")
         objs.append(o)
         if force or _newer([s] + hdrs, o):
             jobs.append((["g++"] + cflags + inc + ["-c", s, "-o", o], o + ".log"))
@@ -112,7 +131,7 @@ def build_runtime(force=False, verbose=False):
             if verbose:
                 print(res)
     torch_lib = os.path.join(os.path.dirname(torch.__file__), "lib")
-    _run(["g++", "-shared", "-o", out] + objs + ["-L" + torch_lib, "-Wl,-rpath," + torch_lib, "-ltorch", "-ltorch_cpu",
+    _run(["g++", "-shared", "-o", out] + san_flags + objs + ["-L" + torch_lib, "-Wl,-rpath," + torch_lib, "-ltorch", "-ltorch_cpu",
                                                   "-lc10", "-ltorch_python", "-lpthread", "-ldl"])
     return out
 
