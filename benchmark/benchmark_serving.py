@@ -188,9 +188,17 @@ def generate_step_trace(step_stats, path_prefix: str) -> None:
         pickle.dump(queues, f)
 
 
-def write_ttft_and_throughput(stats: List[SloStat], arrivals, sampler_steps, prefix: str) -> None:
+def write_ttft_and_throughput(stats: List[SloStat], arrivals, sampler_steps, prefix: str, queueing_delays=None) -> None:
+    """ttft.csv, sampler_step.csv, req_finish_time.csv (seconds since the first arrival) and one
+    ``<worker>_queueing_delay.csv`` per worker: the inputs of benchmark/plotter/*."""
     import pandas as pd
     os.makedirs(os.path.dirname(os.path.abspath(prefix)) or ".", exist_ok=True)
+    t0 = min(arrivals.values()) if arrivals else 0.0
+    pd.DataFrame({"finish_time_s": sorted(s.t_decode - t0 for s in stats)}).to_csv(prefix + "req_finish_time.csv",
+                                                                                   index=False)
+    for kind, lists in (queueing_delays or {}).items():
+        for i, delays in enumerate(lists):
+            pd.DataFrame({"queueing_delay_ms": delays}).to_csv(prefix + f"{kind}{i}_queueing_delay.csv", index=False)
     pd.DataFrame({"req_id": [s.req_id for s in stats],
                   "ttft_ms": [(s.t_prefill - arrivals.get(s.req_id, s.t_prefill)) * 1e3 for s in stats]}
                  ).to_csv(prefix + "ttft.csv", index=False)
@@ -208,7 +216,7 @@ def main(argv=None):
         if args.backend == "colocated":
             cfg = model_config_from_args(args)
             stats, arrivals, dur = run_benchmark_colocated(cfg, wl, args)
-            sampler_steps = []
+            sampler_steps, queueing = [], {}
         else:
             master, cfg = launch(args)
             try:
@@ -217,6 +225,8 @@ def main(argv=None):
                 stats, arrivals, dur = run_benchmark_controller(master, cfg, wl, args)
                 from disagmoe_b200.frontend.datatypes import SamplerStepInfo
                 sampler_steps = [SamplerStepInfo.from_c(s) for s in master.fetch_sampler_step_infos()]
+                attn_q, exp_q = master.fetch_queueing_delays()
+                queueing = {"attn": attn_q, "expert": exp_q}
                 if args.trace:
                     generate_step_trace(master.fetch_step_stats(), prefix)
                 if args.profile_dir:
@@ -225,7 +235,10 @@ def main(argv=None):
                 master.stop_workers()
         metrics = analyze_results(stats, arrivals, dur)
         if args.analyze_throughput:
-            write_ttft_and_throughput(stats, arrivals, sampler_steps, prefix)
+            write_ttft_and_throughput(stats, arrivals, sampler_steps, prefix, queueing)
+            # the same files under the run's own directory (reports/<settings>/), where the plotters look for them
+            from benchmark.plotter.namer import get_dir_path
+            write_ttft_and_throughput(stats, arrivals, sampler_steps, os.path.join(get_dir_path(args), ""), queueing)
     except Exception as e:   # a failed run still leaves a row, as the reference does
         print("benchmark failed:", repr(e))
         metrics = BenchmarkMetrics()

@@ -27,13 +27,26 @@ def test_analyze_results():
     assert abs(m.ttft_mean_ms - 550) < 1e-6
 
 
-def test_end_to_end_tiny_cpu(tmp_path):
+def test_end_to_end_tiny_cpu(tmp_path, monkeypatch):
+    monkeypatch.setenv("DMOE_REPORTS_DIR", str(tmp_path / "reports"))
     out = tmp_path / "bench.csv"
     m = main(["--device", "cpu", "--model", "tiny", "-g", "2", "--ep-size", "1", "--step-attn", "1", "--step-expert", "1",
               "-n", "6", "-r", "200", "--min-input-len", "4", "-i", "9", "--min-output-len", "3", "-o", "5", "-K", "2",
               "--trace", "--analyze-throughput", "-f", str(out), "--num-blocks", "128"])
     assert m.token_throughput > 0 and m.itl_latency_p99_ms >= 0
     assert out.exists() and (tmp_path / "trace.json.gz").exists() and (tmp_path / "ttft.csv").exists()
+    # the run's own directory holds what the plotters read; every plotter runs on it (CSV fallback without matplotlib)
+    runs = list((tmp_path / "reports").iterdir())
+    assert len(runs) == 1 and runs[0].name.startswith("rate=200")
+    run = runs[0]
+    for name in ("ttft.csv", "sampler_step.csv", "req_finish_time.csv", "attn0_queueing_delay.csv",
+                 "expert0_queueing_delay.csv"):
+        assert (run / name).exists(), name
+    from benchmark.plotter import output_req, queue_length_interact, queueing_delay, sampler_step, ttft
+    for mod in (output_req, sampler_step, ttft, queueing_delay):
+        assert mod.main([str(run)])
+    html = queue_length_interact.main([str(tmp_path / "queue_length.pkl"), "--worker", "0"])
+    assert os.path.getsize(html) > 200
 
 
 def test_colocated_backend_cpu(tmp_path):
@@ -41,3 +54,19 @@ def test_colocated_backend_cpu(tmp_path):
               "-i", "8", "--min-output-len", "2", "-o", "4", "-f", str(tmp_path / "b.csv"), "--num-blocks", "64",
               "--max-batch-size-attn", "4"])
     assert m.req_throughput > 0
+
+
+def test_remote_comm_latency_socket_pair():
+    """sender.py / recver.py as two processes on this host over the runtime's TCP channel."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    args = ["--transport", "socket", "--iters", "4", "--warmup", "1", "--rows", "64", "--hidden", "256", "--port-base", "3200"]
+    rx = subprocess.Popen([sys.executable, os.path.join(root, "benchmark/remote_comm_latency/recver.py")] + args,
+                          stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    tx = subprocess.run([sys.executable, os.path.join(root, "benchmark/remote_comm_latency/sender.py")] + args,
+                        capture_output=True, text=True, timeout=120)
+    out_rx, _ = rx.communicate(timeout=60)
+    assert tx.returncode == 0, tx.stdout + tx.stderr
+    assert rx.returncode == 0, out_rx
+    assert "one way in" in tx.stdout and "receiver done: 10 transfers" in out_rx
