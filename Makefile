@@ -22,5 +22,5 @@ bench: build
 	$(PY) bench.py --gpus 1 --steps 20 --warmup 3
 
 clean:
-	rm -rf disagmoe_b200/lib disagmoe_b200/_variants disagmoe_b200/csrc/obj
+	rm -rf disagmoe_b200/lib disagmoe_b200/_variants disagmoe_b200/build
 	rm -f disagmoe_b200/disagmoe_c*.so
