@@ -226,17 +226,28 @@ NcclGroupChannel::~NcclGroupChannel() {
   auto& a = GpuApi::get();
   if (comm_ != nullptr && a.available()) a.ncclCommDestroy(comm_);
   if (stream_ != nullptr && a.available()) a.cudaStreamDestroy(stream_);
+  if (fence_ != nullptr && a.available()) a.cudaEventDestroy(fence_);
+}
+
+// Tensors handed to this channel are produced (or were last used) on the default stream, and the channel's stream
+// is non-blocking: every collective first waits for an event recorded on the default stream.
+void NcclGroupChannel::wait_for_compute() {
+  auto& a = gpu_or_throw();
+  CUDA_OK(a.cudaEventRecord(fence_, nullptr));
+  CUDA_OK(a.cudaStreamWaitEvent(stream_, fence_, 0));
 }
 
 void NcclGroupChannel::instantiate() {
   auto& a = gpu_or_throw();
   CUDA_OK(a.cudaStreamCreateWithFlags(&stream_, 1));
+  CUDA_OK(a.cudaEventCreateWithFlags(&fence_, 2 /*cudaEventDisableTiming*/));
   NCCL_OK(a.ncclCommInitRank(&comm_, world_, uid_, local_));
   staging_ = torch::empty({1 << 16}, torch::TensorOptions().dtype(torch::kUInt8).device(torch::kCUDA));
   barrier();
 }
 
 void NcclGroupChannel::broadcast(const void* send_buf, void* recv_buf, size_t count, int dtype, int root) {
+  wait_for_compute();
   NCCL_OK(gpu_or_throw().ncclBroadcast(send_buf, recv_buf, count, dtype, root, comm_, stream_));
   sync();
 }
@@ -282,11 +293,13 @@ void NcclGroupChannel::recv_metadata(Metadata& meta) {
 
 void NcclGroupChannel::all_reduce(torch::Tensor& t) {
   DMOE_CHECK(t.is_cuda() && t.is_contiguous(), "all_reduce needs a contiguous CUDA tensor");
+  wait_for_compute();
   NCCL_OK(gpu_or_throw().ncclAllReduce(t.data_ptr(), t.data_ptr(), t.numel(), nccl_dtype_of(t), 0 /*sum*/, comm_, stream_));
 }
 
 void NcclGroupChannel::barrier() {
   auto one = torch::ones({1}, torch::TensorOptions().dtype(torch::kInt32).device(torch::kCUDA));
+  wait_for_compute();
   NCCL_OK(gpu_or_throw().ncclAllReduce(one.data_ptr(), one.data_ptr(), 1, 2, 0, comm_, stream_));
   sync();
 }

@@ -159,10 +159,12 @@ class NcclGroupChannel : public Channel {
   void barrier();
 
  private:
+  void wait_for_compute();  // orders stream_ after everything enqueued so far on the default (compute) stream
   int world_;
   NcclId uid_;
   void* comm_ = nullptr;
   void* stream_ = nullptr;
+  void* fence_ = nullptr;
   torch::Tensor staging_;   // device buffer for object broadcasts
 };
 
