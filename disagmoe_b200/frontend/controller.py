@@ -8,7 +8,6 @@ devices; CPU workers use the socket transport (the tensor bytes ride in the cont
 """
 from __future__ import annotations
 
-import asyncio
 import multiprocessing as mp
 import os
 import random
@@ -143,7 +142,7 @@ class AsyncResult:
 
 class Controller:
     def __init__(self, n_node: int, n_gpu_per_node: int, device: str = "cuda", in_process: bool = False,
-                 heartbeat_timeout_s: float = 30.0):
+                 heartbeat_timeout_s: float = 30.0, dp_policy: str = "max"):
         self.n_node, self.n_gpu_per_node = n_node, n_gpu_per_node
         self.device_kind = device
         self.in_process = in_process
@@ -155,6 +154,7 @@ class Controller:
         self.req_counter = 0
         self.results: Dict[int, AsyncResult] = {}
         self.dp_scheduler = None
+        self.dp_policy = dp_policy          # "max": replica with the most free KV blocks (waits for room); "RR"
         self.port_shift = random.randint(0, 400) * 16 * 4 % 6000
         self.heartbeat_timeout_s = heartbeat_timeout_s
         self.suspect_workers: List[int] = []
@@ -284,6 +284,8 @@ class Controller:
         self.sampling_config = sampling_config
         self.cache_config = cache_config
         self.dp_size = len(layer0)
+        self.dp_scheduler = get_dp_scheduler(self.dp_size, model_config.max_seq_len, cache_config.block_size,
+                                             self.dp_policy)
         self._free_blocks = {r: self.workers[dev].call("num_free_blocks") for r, dev in layer0.items()}
         self.attn_peer = attn_peer
 
@@ -301,7 +303,13 @@ class Controller:
         return self.req_counter
 
     def _pick_dp_rank(self, need_blocks: int) -> int:
-        # admission by free KV blocks (the "max" policy of the DP scheduler); waits while no replica has room
+        if self.dp_policy == "RR":
+            with self._lock:
+                r = self.dp_scheduler._schedule()
+                self._free_blocks[r] -= need_blocks
+                return r
+        # admission by free KV blocks (the "max" policy of the DP scheduler, with the request's own block need
+        # instead of a fixed worst case); waits while no replica has room
         while True:
             with self._lock:
                 r = max(self._free_blocks, key=lambda k: (self._free_blocks[k], -k))

@@ -2,7 +2,7 @@
 from __future__ import annotations
 
 import pickle
-from typing import List, Optional, Tuple
+from typing import List
 
 import torch
 import torch.distributed as dist

@@ -6,7 +6,7 @@ from __future__ import annotations
 
 import ctypes
 import math
-from typing import List, Optional, Tuple
+from typing import Optional, Tuple
 
 import torch
 

@@ -28,7 +28,7 @@ from typing import Dict, List, Optional
 import torch
 
 from .. import disagmoe_c as C
-from ..config import CacheConfig, ModelConfig
+from ..config import ModelConfig
 from ..models import weights as W
 from ..models.attention import AttnMeta, MoEAttention
 from ..models.experts import MoEExperts
