@@ -230,9 +230,21 @@ class Controller:
         expert_ranks = [(l, e, r) for (l, e), r in placement.expert_ranks.items()]
         hosts = {d: "127.0.0.1" for d in list(self.workers) + [TOKENIZER_DEV_ID, SAMPLER_DEV_ID]}
         self._all("setup_engine", model_config, cache_config, dtype, self.in_process)
+        # attention TP: only the driver of a group is part of the token flow; it broadcasts its batches to the workers
+        tp_workers = {d for d in self.workers if placement.is_worker_device(d)}
+        assert not (tp_workers and self.in_process), "attention TP needs one process per device"
         for d, w in self.workers.items():
-            outs = list(placement.out_device_ids.get(d, []))
-            ins = list(placement.in_device_ids.get(d, []))
+            group = (placement.device_groups or {}).get(d, [d]) if placement.has_attn(d) else [d]
+            tp = dict(tp_rank=group.index(d), tp_size=len(group),
+                      tp_master_port=20000 + (self.port_shift + 97 * group[0]) % 20000)
+            if d in tp_workers:
+                self._pending_args[d] = InitCoreArgs(
+                    layer_ids=placement.layer_ids_at(d), in_device_ids=[], out_device_ids=[], out_channel_infos=[],
+                    attn_peer=attn_peer, expert_ranks=expert_ranks, hosts=hosts, port_shift=self.port_shift,
+                    state_dict_path=state_dict_path, **tp)
+                continue
+            outs = [o for o in placement.out_device_ids.get(d, []) if o not in tp_workers]
+            ins = [i for i in placement.in_device_ids.get(d, []) if i not in tp_workers]
             if placement.has_attn(d):
                 # the residual stream goes to the attention worker of the next layer; the head step reports to the sampler
                 dp = placement.attn_dp_rank_at(d)
@@ -263,7 +275,7 @@ class Controller:
                 attn_peer=attn_peer, expert_ranks=expert_ranks,
                 local_attn_dp_rank=placement.attn_dp_rank_at(d) if d in placement.attn else 0,
                 expert_ids=list(placement.expert_ids_at(d)), hosts=hosts, port_shift=self.port_shift,
-                state_dict_path=state_dict_path, keep_logits=keep_logits)
+                state_dict_path=state_dict_path, keep_logits=keep_logits, **tp)
             self._pending_args[d] = args
         # in-edges are the transpose of the (extended) out-edges
         for d, a in self._pending_args.items():
@@ -420,6 +432,8 @@ class Controller:
         """Per-step queueing delays (ms) of every attention worker and of every expert worker."""
         attn, exp = [], []
         for d, res in self._all("fetch_queueing_delays").items():
+            if self.placement.is_worker_device(d):
+                continue                      # a TP worker has no queue: it runs what its driver broadcasts
             (attn if self.placement.has_attn(d) else exp).append(res)
         return attn, exp
 

@@ -58,6 +58,11 @@ class InitCoreArgs:
     port_shift: int = 0
     state_dict_path: Optional[str] = None
     keep_logits: bool = False
+    # attention tensor parallelism of the host-scheduled path: rank 0 of a group (the driver) takes part in the token
+    # flow and broadcasts every attention batch it schedules to the other ranks (the workers) of its group
+    tp_rank: int = 0
+    tp_size: int = 1
+    tp_master_port: int = 0
 
 
 class Engine:
@@ -80,6 +85,7 @@ class Engine:
         self._logger = get_logger(f"engine{device_id}")
         self.error: Optional[str] = None
         self._max_rows = 1024
+        self.tp_rank, self.tp_size = 0, 1
         self._queueing_delays: List[float] = []      # per executed step: how long its oldest row waited (ms)
         self.has_attn = self.has_expert = False
 
@@ -102,6 +108,9 @@ class Engine:
         if args.hosts:
             C.set_hosts(os.getpid(), args.hosts)
         self.args = args
+        self.tp_rank, self.tp_size = args.tp_rank, args.tp_size
+        if self.tp_size > 1:
+            self._init_tp_group(args)
         self.has_attn = placement.has_attn(self.device_id)
         self.has_expert = placement.has_expert(self.device_id)
         self.dp_rank = args.local_attn_dp_rank
@@ -141,13 +150,26 @@ class Engine:
             self.handles.scheduler.set_max_batch_size(cfg.max_batch_size_expert)
         self._build_executor(attn_layers)
 
+    def _init_tp_group(self, args: InitCoreArgs) -> None:
+        """One process group per attention TP group (gloo on CPU, NCCL on GPUs) for the driver's batch broadcast and
+        the o_proj all-reduce (reference: engine.py:253-256, where the TP group is a ``torch.distributed`` group too)."""
+        import torch.distributed as dist
+        from ..models import distributed as D
+        assert not dist.is_initialized(), "attention TP needs one worker process per device"
+        backend = "nccl" if self.device.type == "cuda" else "gloo"
+        kw = {"device_id": self.device} if backend == "nccl" else {}
+        dist.init_process_group(backend, init_method=f"tcp://127.0.0.1:{args.tp_master_port}", rank=self.tp_rank,
+                                world_size=self.tp_size, **kw)
+        D.set_tensor_model_parallel_config(self.model_config.clone(tp_size=self.tp_size, rank=self.tp_rank))
+        self._dist = dist
+
     def _build_executor(self, attn_layers: List[int]) -> None:
         cfg, dev, dt = self.model_config, self.device, self.dtype
         sd = None
         if self.args.state_dict_path:
             sd = W.load_state_dict(self.args.state_dict_path)
         for l in attn_layers:
-            m = MoEAttention(cfg, l, device=dev, dtype=dt)
+            m = MoEAttention(cfg, l, getattr(self, "tp_size", 1), getattr(self, "tp_rank", 0), device=dev, dtype=dt)
             m.load_weights(sd) if sd is not None else m.init_weights()
             self.attn_layers[l] = m
         for l, experts in self.local_experts.items():
@@ -176,7 +198,8 @@ class Engine:
     def start(self) -> None:
         C.start_engine(self.handles)
         self.end_flag = False
-        self.loop_thread = threading.Thread(target=self._loop, daemon=True, name=f"engine-loop-{self.device_id}")
+        target = self.attn_worker_loop if (self.tp_size > 1 and self.tp_rank > 0) else self._loop
+        self.loop_thread = threading.Thread(target=target, daemon=True, name=f"engine-loop-{self.device_id}")
         self.loop_thread.start()
 
     def _loop(self) -> None:
@@ -207,6 +230,53 @@ class Engine:
                     if self.has_expert:
                         self.handles.scheduler.wait_for_new_requests(5 if self.has_attn else 20)
         except Exception as e:   # surfaced through check_error(); the worker stays up for diagnosis
+            import traceback
+            self.error = traceback.format_exc()
+            self._logger.error(self.error)
+
+    # ---- attention TP (host-scheduled path) ----------------------------------------------------------------------
+    def _tp_broadcast_batch(self, layer: int, token_ids, parts, meta: AttnMeta) -> None:
+        """Driver -> workers of its TP group: what it is about to run (layer, token ids or partial rows, positions,
+        slots, block table of the batch), as one pickled header and one tensor broadcast."""
+        from ..models.utils import broadcast_pyobj
+        dev = "cpu" if self.device.type == "cpu" else self.device
+        hdr = dict(layer=layer, token_ids=token_ids, shape=None if parts is None else tuple(parts.shape),
+                   pos=meta.positions.tolist(), slots=meta.slots.tolist(), table=meta.block_tables.tolist(),
+                   bt_row=meta.bt_row.tolist(), ctx=meta.ctx_len.tolist(), n_prefill=meta.num_prefill_tokens,
+                   n_decode=meta.num_decode_tokens, max_ctx=meta.max_ctx)
+        broadcast_pyobj(hdr, 0, device=dev)
+        if parts is not None:
+            self._dist.broadcast(parts.contiguous(), 0)
+
+    def attn_worker_loop(self) -> None:
+        """Loop of a TP worker (a non-driver rank of an attention TP group): it takes no part in the token flow, it
+        runs what the driver broadcasts on its own head shard and KV shard; the all-reduce inside the layer makes
+        every rank hold the full result, and only the driver routes and dispatches it (reference:
+        engine.py:538-612,757-772, asserted off there)."""
+        from ..models.utils import broadcast_pyobj
+        dev = self.device
+        pdev = "cpu" if dev.type == "cpu" else dev
+        t = lambda x, dt=torch.int32: torch.tensor(x, dtype=dt).to(dev)
+        try:
+            while True:
+                hdr = broadcast_pyobj(None, 0, device=pdev)
+                if hdr.get("stop"):
+                    return
+                layer = hdr["layer"]
+                resid = parts = None
+                if hdr["token_ids"] is not None:
+                    resid = F.embed(t(hdr["token_ids"]), self.embed_w)
+                else:
+                    parts = torch.empty(hdr["shape"], dtype=self.dtype, device=dev)
+                    self._dist.broadcast(parts, 0)
+                    resid = parts[:, 0].contiguous()
+                    parts = parts[:, 1:] if parts.shape[1] > 1 else None
+                meta = AttnMeta(t(hdr["pos"]), t(hdr["slots"], torch.int64), t(hdr["table"]), t(hdr["bt_row"]),
+                                t(hdr["ctx"]), num_prefill_tokens=hdr["n_prefill"], num_decode_tokens=hdr["n_decode"],
+                                max_ctx=hdr["max_ctx"])
+                self.attn_layers[layer].forward(resid, parts, (self.kv_cache[layer][0], self.kv_cache[layer][1]), meta)
+                self.metric.step()
+        except Exception:
             import traceback
             self.error = traceback.format_exc()
             self._logger.error(self.error)
@@ -281,6 +351,8 @@ class Engine:
             self.timer.stop("preprocess")
             return self._head_step(m, parts)
         meta = self._attn_meta(m)
+        if self.tp_size > 1:
+            self._tp_broadcast_batch(layer, list(m.token_ids) if batch.data is None else None, parts, meta)
         self.timer.stop("preprocess")
         self.timer.start("execute")
         if resid is None:
@@ -462,8 +534,15 @@ class Engine:
 
     def terminate(self) -> None:
         self.end_flag = True
-        if self.loop_thread is not None:
+        tp_worker = getattr(self, "tp_size", 1) > 1 and self.tp_rank > 0
+        if self.loop_thread is not None and not tp_worker:      # a TP worker's loop waits for its driver's stop message
             self.loop_thread.join(timeout=10)
+        if getattr(self, "tp_size", 1) > 1 and self.tp_rank == 0 and self.error is None:
+            from ..models.utils import broadcast_pyobj
+            try:
+                broadcast_pyobj({"stop": True}, 0, device="cpu" if self.device.type == "cpu" else self.device)
+            except Exception:
+                pass
         if self.handles is not None:
             C.stop_engine(self.handles)
 

@@ -73,3 +73,11 @@ def test_four_processes_ep2_striped_attention():
     """2 attention stages (layers striped) + EP=2 expert workers: residual stream crosses attention workers."""
     cfg = tiny_config.clone(ep_size=2)
     _run(cfg, (2, 1), 4, False, n_req=6, prompt_len=10, n_new=5)
+
+
+def test_three_processes_attention_tp2():
+    """Attention tensor parallelism on the host-scheduled path: a TP group of two attention processes (the driver takes
+    part in the token flow and broadcasts every batch it schedules; both run their head / KV shard and all-reduce the
+    o_proj partial sums over gloo) + one expert process; logits against the single-process oracle."""
+    cfg = tiny_config.clone(ep_size=1, tp_size=2)
+    _run(cfg, (1, 1), 3, False, n_req=5, prompt_len=11, n_new=6)
