@@ -23,18 +23,18 @@ POLICIES = ("mbfs", "flfs", "mbflfs", "mbtfs", "bin")
 
 
 def create_app(args):
+    from contextlib import asynccontextmanager
     from fastapi import FastAPI, HTTPException
-    app = FastAPI(title="disagmoe_b200 benchmark server")
     state = {"master": None, "cfg": None, "args": args}
 
-    @app.on_event("startup")
-    def _startup():
-        state["master"], state["cfg"] = launch(args)
-
-    @app.on_event("shutdown")
-    def _shutdown():
-        if state["master"] is not None:
+    @asynccontextmanager
+    async def lifespan(_app):
+        state["master"], state["cfg"] = launch(args)      # workers come up with the server ...
+        yield
+        if state["master"] is not None:                   # ... and go down with it
             state["master"].stop_workers()
+
+    app = FastAPI(title="disagmoe_b200 benchmark server", lifespan=lifespan)
 
     @app.post("/run_once")
     def run_once(body: dict):

@@ -70,3 +70,35 @@ def test_remote_comm_latency_socket_pair():
     assert tx.returncode == 0, tx.stdout + tx.stderr
     assert rx.returncode == 0, out_rx
     assert "one way in" in tx.stdout and "receiver done: 10 transfers" in out_rx
+
+
+def test_http_server_run_once_and_policy_switch():
+    """The benchmark server in-process: start-up launches the workers, /run_once runs a small workload, /set_schedule
+    switches the layer-scheduling policy of every worker, bad input is rejected with 400."""
+    from fastapi.testclient import TestClient
+    from benchmark.server import create_app
+    from benchmark.utils import get_parser_base
+    args = get_parser_base().parse_args(
+        ["--device", "cpu", "--model", "tiny", "-g", "2", "--ep-size", "1", "--step-attn", "1", "--step-expert", "1",
+         "--min-input-len", "4", "-i", "8", "--min-output-len", "2", "-o", "4", "-K", "2", "--num-blocks", "128"])
+    with TestClient(create_app(args)) as client:
+        assert client.get("/health").json() == {"suspect_workers": [], "workers": 2}
+        assert client.post("/set_schedule", json={"policy": "flfs", "step": 2}).json() == {"ok": True}
+        assert client.post("/set_schedule", json={"policy": "nonsense"}).status_code == 400
+        assert client.post("/set_schedule", json={}).status_code == 400
+        m = client.post("/run_once", json={"rate": 40, "time": 0.2, "distribution": "poisson"}).json()
+        assert m["token_throughput"] > 0 and m["req_throughput"] > 0
+
+
+def test_queueing_simulator_policies():
+    from simulator.queueing import simulate
+    for policy in ("largest", "fcfs", "first"):
+        out = simulate(rate=30, n_layers=4, step_ms=3.0, duration_s=2.0, policy=policy, out_len=4, seed=1)
+        # a token passes 4 layers of 3 ms each between two outputs of its request, whatever the policy
+        assert out["steps"] > 0 and out["itl_mean_ms"] >= 3.0 * 4 - 1e-6 and out["itl_p99_ms"] >= out["itl_p50_ms"], (policy, out)
+
+
+def test_preprocess_microbenchmark_runs():
+    from benchmark import benchmark_preprocess
+    out = benchmark_preprocess.main(["--iters", "3"])
+    assert out is None or out
