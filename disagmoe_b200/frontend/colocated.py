@@ -96,14 +96,23 @@ class ColocatedEngine:
         return 3 * 8 * n
 
     # ---- steps --------------------------------------------------------------------------------------------------
+    def _blocks(self, tokens: int) -> int:
+        return (tokens + self.block_size - 1) // self.block_size
+
     def _prefill(self) -> List[Tuple[int, int]]:
         ex = self.executor
         batch: List[_Seq] = []
         total = 0
+        # blocks the running sequences will still take before they finish stay free: a decode step never finds the
+        # pool empty (there is no preemption)
+        reserve = sum(max(0, self._blocks(max(len(s.prompt), s.length) + s.max_new_tokens - len(s.outputs)) -
+                          len(self.block_mgr.get_seq_block_list(s.req_id))) for s in self.running.values())
         while self.waiting and len(self.running) + len(batch) < self.max_batch_size:
             s = self.waiting[0]
-            if total + len(s.prompt) > ex.prefill_buf.cap or not self.block_mgr.can_allocate(len(s.prompt) + 1):
+            need = self._blocks(len(s.prompt) + s.max_new_tokens)
+            if total + len(s.prompt) > ex.prefill_buf.cap or self.block_mgr.num_free_blocks() - reserve < need:
                 break
+            reserve += need - self._blocks(len(s.prompt) + 1)
             self.waiting.pop(0)
             self.block_mgr.allocate(s.req_id, len(s.prompt) + 1)
             batch.append(s)

@@ -84,6 +84,15 @@ class FusedScheduler:
     def has_work(self, now: float) -> bool:
         return any(len(r) for r in self.running) or bool(self.waiting and self.waiting[0].t_arrival <= now)
 
+    def _blocks(self, tokens: int) -> int:
+        return (tokens + self.block_size - 1) // self.block_size
+
+    def _growth_reserve(self) -> int:
+        """KV blocks the running sequences will still take before they finish. Admission leaves them free, so that a
+        decode step can never find the pool empty (there is no preemption)."""
+        return sum(max(0, self._blocks(len(s.prompt) + s.max_new_tokens) - len(self.bm.get_seq_block_list(s.req_id)))
+                   for r in self.running for s in r.values())
+
     def build(self, now: float) -> List[MicroBatchPlan]:
         plans = [MicroBatchPlan() for _ in range(self.n_mb)]
         prefill = [0] * self.n_mb
@@ -107,7 +116,7 @@ class FusedScheduler:
             order = sorted(range(self.n_mb), key=lambda m: len(plans[m]))
             m = next((m for m in order if len(self.running[m]) < self.max_seqs and len(plans[m]) + n <= self.max_tokens
                       and prefill[m] + n <= self.max_prefill), None)
-            if m is None or not self.bm.can_allocate(n + 1):
+            if m is None or self.bm.num_free_blocks() - self._growth_reserve() < self._blocks(n + s.max_new_tokens):
                 break
             self.waiting.pop(0)
             self.bm.allocate(s.req_id, n + 1)

@@ -25,3 +25,20 @@ def test_engine_generates_oracle_tokens():
         assert out[i] == ref, f"request {i}"
     # every KV block went back to the allocator
     assert eng.block_mgr.num_free_blocks() == 64 and eng.block_mgr.num_seqs() == 0
+
+
+def test_tight_kv_pool_admission_waits_instead_of_failing():
+    """More requests than the KV pool can hold at once: admission reserves the blocks running sequences will grow into,
+    so the engine works through the queue without ever running out of blocks."""
+    import torch
+    from disagmoe_b200.config import CacheConfig, tiny_config
+    from disagmoe_b200.frontend.colocated import ColocatedEngine
+    cfg = tiny_config.clone(dtype=torch.float32, num_layers=1)
+    eng = ColocatedEngine(cfg, CacheConfig(block_size=16), device="cpu", max_batch_size=8, max_prefill_tokens=128,
+                          num_blocks=14, enable_cuda_graph=False)
+    g = torch.Generator().manual_seed(0)
+    for i in range(10):
+        n = int(torch.randint(5, 40, (1,), generator=g))
+        eng.add_request(i, torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist(), 30)
+    out = eng.run_until_done(5000)
+    assert len(out) == 10 and all(len(v) == 30 for v in out.values())

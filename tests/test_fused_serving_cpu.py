@@ -158,3 +158,22 @@ def test_host_protocol_tensor_parallel_group_cpu():
         assert outs[rid] == _expected_tokens(prompt, n_out, tiny_config.vocab_size), rid
     assert res[0]["table_sum"] == res[1]["table_sum"] > 0
     assert len({res[r]["iterations"] for r in range(4)}) == 1
+
+
+def test_tight_kv_pool_never_runs_dry():
+    """Admission keeps the blocks free that the running sequences will still grow into: with a pool far smaller than
+    the total demand, decode steps never hit 'out of KV blocks' and every request finishes."""
+    import random
+    bm = C.BlockManager(16, 24, 0, 64)
+    s = FusedScheduler(bm, 16, n_mb=2, max_seqs_per_mb=8, max_tokens_per_mb=256)
+    rnd = random.Random(0)
+    for i in range(30):
+        s.add_request(i, [1] * rnd.randint(5, 60), rnd.randint(10, 70), 0.0)
+    steps = 0
+    while s.num_unfinished():
+        plans = s.build(1.0)
+        assert any(len(p) for p in plans), "nothing runnable although requests are pending"
+        s.commit(plans, [[7] * len(p) for p in plans], 1.0)
+        steps += 1
+        assert steps < 5000
+    assert len(s.finished) == 30 and bm.num_free_blocks() == 24
