@@ -207,9 +207,51 @@ def write_ttft_and_throughput(stats: List[SloStat], arrivals, sampler_steps, pre
                       "num_tokens": [s.num_tokens for s in sampler_steps]}).to_csv(prefix + "sampler_step.csv", index=False)
 
 
+def fused_command(args) -> List[str]:
+    """The torchrun command line that serves the same workload on the fused peer-memory path
+    (``benchmark/serve_fused.py``, one process per GPU): attention GPUs = tp x dp, the other GPUs hold the experts."""
+    n_gpu = args.num_nodes * args.num_gpus
+    n_attn = args.tp_size * args.dp_size
+    assert 1 <= n_attn < n_gpu, "--tp-size x --dp-size attention GPUs must leave at least one expert GPU"
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(n_gpu),
+           "--master-addr", "127.0.0.1", "--master-port", str(29700 + args.seed % 200),
+           os.path.join(os.path.dirname(os.path.abspath(__file__)), "serve_fused.py"), "--model", args.model,
+           "--n-attn", str(n_attn), "--attn-tp", str(args.tp_size), "-r", str(args.rate), "-n", str(args.num_requests),
+           "--min-input-len", str(args.min_input_len), "-i", str(args.max_input_len),
+           "--min-output-len", str(args.min_output_len), "-o", str(args.max_output_len),
+           "--generator-type", args.generator_type, "--seed", str(args.seed),
+           "--max-seqs-per-mb", str(max(1, args.max_batch_size_attn // 2))]
+    if args.num_blocks:
+        cmd += ["--num-blocks", str(args.num_blocks)]
+    if args.model in ("mixtral", "duo") and args.num_layers != 32:
+        cmd += ["-L", str(args.num_layers)]
+    return cmd
+
+
+def run_benchmark_fused(args) -> BenchmarkMetrics:
+    """Runs ``fused_command`` and reads the metrics line it appends to a JSON-lines file."""
+    import subprocess
+    import tempfile
+    out = os.path.join(tempfile.mkdtemp(), "fused.jsonl")
+    proc = subprocess.run(fused_command(args) + ["-f", out], capture_output=True, text=True)
+    if proc.returncode != 0 or not os.path.exists(out):
+        raise RuntimeError("fused serving run failed:\n" + (proc.stdout + proc.stderr)[-2000:])
+    row = json.loads(open(out).read().strip().splitlines()[-1])
+    return BenchmarkMetrics(**{k: row[k] for k in BenchmarkMetrics.__dataclass_fields__ if k in row})
+
+
 def main(argv=None):
     args = get_parser_base().parse_args(argv)
     np.random.seed(args.seed)
+    if args.backend == "fused":
+        try:
+            metrics = run_benchmark_fused(args)
+        except Exception as e:
+            print("benchmark failed:", repr(e))
+            metrics = BenchmarkMetrics()
+        print(metrics)
+        metrics.write_to_file(args)
+        return metrics
     wl = make_workload(args)
     prefix = os.path.join(os.path.dirname(os.path.abspath(args.file)), "")
     try:

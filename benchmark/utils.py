@@ -50,6 +50,7 @@ def get_parser_base() -> ArgumentParser:
     p.add_argument("--step-expert", type=int, default=1)
     # this implementation
     p.add_argument("--backend", type=str, default="controller",
-                   help="controller (one process per device, host-scheduled) | colocated (one GPU, fused executor)")
+                   help="controller (one process per device, host-scheduled) | colocated (one GPU, fused executor) | "
+                        "fused (one process per GPU on the peer-memory path: tp-size x dp-size attention GPUs, the rest experts)")
     p.add_argument("--device", type=str, default="cuda", help="cuda | cpu")
     return p

@@ -102,3 +102,17 @@ def test_preprocess_microbenchmark_runs():
     from benchmark import benchmark_preprocess
     out = benchmark_preprocess.main(["--iters", "3"])
     assert out is None or out
+
+
+def test_fused_backend_command_line():
+    """--backend fused maps the benchmark flags onto the torchrun job of benchmark/serve_fused.py."""
+    from benchmark.benchmark_serving import fused_command
+    from benchmark.utils import get_parser_base
+    a = get_parser_base().parse_args(["--backend", "fused", "-g", "8", "--tp-size", "4", "--dp-size", "1", "-r", "16", "-n",
+                                      "96", "--min-input-len", "128", "-i", "1024", "--min-output-len", "64", "-o", "512",
+                                      "--num-blocks", "16384", "--max-batch-size-attn", "256"])
+    cmd = fused_command(a)
+    joined = " ".join(cmd)
+    assert "--nproc-per-node 8" in joined and "serve_fused.py" in joined
+    assert "--n-attn 4 --attn-tp 4" in joined and "-r 16.0 -n 96" in joined and "--max-seqs-per-mb 128" in joined
+    assert "--num-blocks 16384" in joined
