@@ -55,7 +55,8 @@ class MicroBatchPlan:
     pos: List[int] = field(default_factory=list)
     rows: List[int] = field(default_factory=list)
     slots: List[int] = field(default_factory=list)
-    # (row in the micro-batch, sequence whose next token that row produces, tokens the row's step adds to its cache)
+    # (row in the micro-batch or -1, sequence, tokens this step adds to its cache): row >= 0 produces the sequence's next
+    # token; row == -1 is a prompt chunk that is not the last one (cache grows, nothing is sampled)
     emit: List[Tuple[int, ServeSeq, int]] = field(default_factory=list)
 
     def __len__(self):
@@ -63,19 +64,27 @@ class MicroBatchPlan:
 
 
 class FusedScheduler:
-    """Admission + micro-batch construction of one attention group (pure host logic, no GPU)."""
+    """Admission + micro-batch construction of one attention group (pure host logic, no GPU).
+
+    Every iteration a micro-batch holds one decode token per running sequence plus prompt tokens up to two budgets:
+    ``max_tokens_per_mb`` rows in total and ``max_prefill_tokens_per_mb`` prompt rows. A prompt that does not fit is
+    processed in chunks over several iterations (chunk i attends to the K/V the earlier chunks cached; only the last
+    chunk samples a token), so long prompts neither starve behind decode tokens nor stall them."""
+
+    MIN_CHUNK = 16      # do not start or continue a prompt with fewer rows than this unless that finishes it
 
     def __init__(self, block_mgr, block_size: int, n_mb: int, max_seqs_per_mb: int, max_tokens_per_mb: int,
                  max_prefill_tokens_per_mb: Optional[int] = None):
         self.bm, self.block_size, self.n_mb = block_mgr, block_size, n_mb
         self.max_seqs, self.max_tokens = max_seqs_per_mb, max_tokens_per_mb
         self.max_prefill = max_prefill_tokens_per_mb or max_tokens_per_mb
+        assert self.max_tokens > self.max_seqs, "a micro-batch must have room for prompt rows next to its decode rows"
         self.waiting: List[ServeSeq] = []                     # arrival order
         self.running: List[Dict[int, ServeSeq]] = [dict() for _ in range(n_mb)]
         self.finished: Dict[int, ServeSeq] = {}
 
     def add_request(self, req_id: int, prompt: Sequence[int], max_new_tokens: int, t_arrival: float) -> None:
-        assert 1 <= len(prompt) <= self.max_prefill, "a prompt must fit one micro-batch"
+        assert len(prompt) >= 1 and max_new_tokens >= 1
         self.waiting.append(ServeSeq(req_id, list(prompt), max_new_tokens, t_arrival))
 
     def num_unfinished(self) -> int:
@@ -93,53 +102,66 @@ class FusedScheduler:
         return sum(max(0, self._blocks(len(s.prompt) + s.max_new_tokens) - len(self.bm.get_seq_block_list(s.req_id)))
                    for r in self.running for s in r.values())
 
+    def _add_prompt_rows(self, p: MicroBatchPlan, s: ServeSeq, budget: int) -> int:
+        """Appends the next prompt rows of ``s`` (at most ``budget``) to the plan; returns how many."""
+        n, done = len(s.prompt), s.length
+        take = min(n - done, budget)
+        if take <= 0 or (take < self.MIN_CHUNK and take < n - done):
+            return 0
+        row = self.bm.row_of(s.req_id)
+        blocks = self.bm.get_seq_block_list(s.req_id)
+        bs = self.block_size
+        p.ids.extend(s.prompt[done:done + take])
+        p.pos.extend(range(done, done + take))
+        p.rows.extend([row] * take)
+        p.slots.extend(blocks[i // bs] * bs + i % bs for i in range(done, done + take))
+        last = done + take == n
+        p.emit.append((len(p.ids) - 1 if last else -1, s, take))
+        return take
+
     def build(self, now: float) -> List[MicroBatchPlan]:
         plans = [MicroBatchPlan() for _ in range(self.n_mb)]
         prefill = [0] * self.n_mb
+        budget = lambda m: min(self.max_tokens - len(plans[m]), self.max_prefill - prefill[m])
         for m in range(self.n_mb):
-            seqs = list(self.running[m].values())
-            if not seqs:
-                continue
-            lens = [s.length for s in seqs]
-            rs = self.bm.step_decode([s.req_id for s in seqs], lens)
-            n = len(seqs)
-            p = plans[m]
-            p.ids = [s.last_token for s in seqs]
-            p.pos = lens
-            p.rows = [int(r) for r in rs[:n]]
-            p.slots = [int(r) for r in rs[n:]]
-            p.emit = [(i, q, 1) for i, q in enumerate(seqs)]
-        # admission in arrival order; a request goes to the micro-batch with fewer tokens this iteration
+            seqs = [s for s in self.running[m].values() if s.length >= len(s.prompt)]      # fully prefilled
+            if seqs:
+                lens = [s.length for s in seqs]
+                rs = self.bm.step_decode([s.req_id for s in seqs], lens)
+                n = len(seqs)
+                p = plans[m]
+                p.ids = [s.last_token for s in seqs]
+                p.pos = lens
+                p.rows = [int(r) for r in rs[:n]]
+                p.slots = [int(r) for r in rs[n:]]
+                p.emit = [(i, q, 1) for i, q in enumerate(seqs)]
+            # prompts that are part-way through, oldest first
+            for s in [s for s in self.running[m].values() if s.length < len(s.prompt)]:
+                prefill[m] += self._add_prompt_rows(plans[m], s, budget(m))
+        # admission in arrival order; a request goes to the micro-batch with more room this iteration
         while self.waiting and self.waiting[0].t_arrival <= now:
             s = self.waiting[0]
             n = len(s.prompt)
-            order = sorted(range(self.n_mb), key=lambda m: len(plans[m]))
-            m = next((m for m in order if len(self.running[m]) < self.max_seqs and len(plans[m]) + n <= self.max_tokens
-                      and prefill[m] + n <= self.max_prefill), None)
+            order = sorted(range(self.n_mb), key=lambda m: (-budget(m), len(plans[m]), len(self.running[m])))
+            m = next((m for m in order if len(self.running[m]) < self.max_seqs
+                      and budget(m) >= min(n, self.MIN_CHUNK)), None)
             if m is None or self.bm.num_free_blocks() - self._growth_reserve() < self._blocks(n + s.max_new_tokens):
                 break
             self.waiting.pop(0)
             self.bm.allocate(s.req_id, n + 1)
-            row = self.bm.row_of(s.req_id)
-            blocks = self.bm.get_seq_block_list(s.req_id)
-            bs = self.block_size
-            p = plans[m]
-            p.ids.extend(s.prompt)
-            p.pos.extend(range(n))
-            p.rows.extend([row] * n)
-            p.slots.extend(blocks[i // bs] * bs + i % bs for i in range(n))
-            p.emit.append((len(p.ids) - 1, s, n))          # only the last prompt row produces a token
             s.mb = m
             self.running[m][s.req_id] = s
-            prefill[m] += n
+            prefill[m] += self._add_prompt_rows(plans[m], s, budget(m))
         return plans
 
     def commit(self, plans: List[MicroBatchPlan], next_ids: List[Sequence[int]], now: float) -> List[Tuple[int, int]]:
         out = []
         for m, p in enumerate(plans):
             for row, s, grown in p.emit:
-                tok = int(next_ids[m][row])
                 s.length += grown
+                if row < 0:
+                    continue
+                tok = int(next_ids[m][row])
                 s.outputs.append(tok)
                 s.t_tokens.append(now)
                 s.last_token = tok

@@ -54,7 +54,8 @@ def test_two_gpu_fused_serving_matches_colocated():
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
            "127.0.0.1", "--master-port", "29655", os.path.join(root, "benchmark", "serve_fused.py"), "--model", "tiny",
            "-r", "200", "-n", "24", "--min-input-len", "8", "-i", "40", "--min-output-len", "4", "-o", "12",
-           "--max-seqs-per-mb", "8", "--max-tokens-per-mb", "96", "--num-blocks", "512", "--time-limit", "120", "--check"]
+           "--max-seqs-per-mb", "8", "--max-tokens-per-mb", "96", "--max-prefill-tokens-per-mb", "24", "--num-blocks", "512",
+           "--time-limit", "120", "--check"]       # prompts of up to 40 tokens against a 24-token budget: chunked prefill
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env)
     assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]

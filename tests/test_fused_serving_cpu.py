@@ -177,3 +177,35 @@ def test_tight_kv_pool_never_runs_dry():
         steps += 1
         assert steps < 5000
     assert len(s.finished) == 30 and bm.num_free_blocks() == 24
+
+
+def test_long_prompt_is_prefilled_in_chunks_next_to_decode_rows():
+    """A prompt longer than the per-iteration prompt budget is split over iterations: positions continue where the last
+    chunk stopped, only the last chunk samples, and the sequences that are decoding get their token every iteration."""
+    bm = C.BlockManager(16, 64, 0, 8)
+    s = FusedScheduler(bm, 16, n_mb=1, max_seqs_per_mb=4, max_tokens_per_mb=40, max_prefill_tokens_per_mb=32)
+    s.add_request(0, list(range(100, 105)), 6, t_arrival=0.0)      # short: decoding from the 2nd iteration on
+    s.add_request(1, list(range(200, 290)), 2, t_arrival=0.0)      # 90 prompt tokens: 27 + 32 + 31
+    plans = s.build(0.0)
+    p = plans[0]
+    assert len(p) == 32 and p.ids[:5] == list(range(100, 105)) and p.ids[5:] == list(range(200, 227))
+    assert [(r, q.req_id, g) for r, q, g in p.emit] == [(4, 0, 5), (-1, 1, 27)]
+    out = s.commit(plans, _fake_model(plans), 0.1)
+    assert [r for r, _ in out] == [0] and s.running[0][1].length == 27 and not s.running[0][1].outputs
+    plans = s.build(0.2)                                               # 1 decode row + the next 32 prompt rows
+    p = plans[0]
+    assert len(p) == 33 and p.pos[0] == 5 and p.pos[1:] == list(range(27, 59)) and p.ids[1] == 227
+    blocks = bm.get_seq_block_list(1)
+    assert p.slots[1:] == [blocks[i // 16] * 16 + i % 16 for i in range(27, 59)]
+    assert [(r, q.req_id, g) for r, q, g in p.emit] == [(0, 0, 1), (-1, 1, 32)]
+    s.commit(plans, _fake_model(plans), 0.3)
+    plans = s.build(0.4)                                               # last chunk: 31 rows, its last row samples
+    p = plans[0]
+    assert len(p) == 32 and p.pos[1:] == list(range(59, 90))
+    assert [(r, q.req_id, g) for r, q, g in p.emit] == [(0, 0, 1), (31, 1, 31)]
+    out = s.commit(plans, _fake_model(plans), 0.5)
+    assert sorted(r for r, _ in out) == [0, 1] and s.running[0][1].length == 90
+    while s.num_unfinished():
+        plans = s.build(1.0)
+        s.commit(plans, _fake_model(plans), 1.0)
+    assert len(s.finished[0].outputs) == 6 and len(s.finished[1].outputs) == 2 and bm.num_free_blocks() == 64
