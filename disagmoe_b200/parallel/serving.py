@@ -6,9 +6,10 @@ the routed experts. Every iteration of the job is one pass of two micro-batches 
 
 * the **leader** of every attention group (its first rank) owns the group's requests: it admits arrivals, keeps the
   paged-KV block manager, and builds the iteration's two micro-batches as flat token lists. A running sequence
-  contributes its next decode token; a newly admitted request contributes all its prompt tokens (position p attends
-  to the first p + 1 cached tokens of its own block-table row, so prompt and decode tokens share one kernel and one
-  batch: prefill never stalls the sequences that are decoding);
+  contributes its next decode token; a newly admitted request contributes prompt tokens, all of them or, under the
+  per-iteration prompt budget, one chunk per iteration (position p attends to the first p + 1 cached tokens of its own
+  block-table row, so prompt and decode tokens share one kernel and one batch: prefill never stalls the sequences that
+  are decoding, and a long prompt never waits for a micro-batch to empty);
 * the other members of a TP group receive the leader's plan (token ids, positions, slots, block-table patches) over a
   host-side broadcast and run the same launches on their head shard;
 * the expert GPUs replay one CUDA graph per iteration whatever the attention side scheduled: row counts travel with
@@ -24,6 +25,8 @@ admission and results).
 """
 from __future__ import annotations
 
+import os
+import sys
 import time
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
@@ -236,7 +239,7 @@ class FusedServingRank:
         self._last_status = 0
         self._sync()
         dist.barrier()
-        self._debug = bool(__import__("os").environ.get("DMOE_SERVE_DEBUG"))
+        self._debug = bool(os.environ.get("DMOE_SERVE_DEBUG"))
         self._log("set-up done")
         self._warm_up_and_capture()
         self._log("graphs captured")
@@ -250,7 +253,6 @@ class FusedServingRank:
 
     def _log(self, msg: str) -> None:
         if self._debug:
-            import sys
             print(f"[serve rank {self.rank} it {self.iterations}] {msg}", file=sys.stderr, flush=True)
 
     # ---- set-up ------------------------------------------------------------------------------------------------
