@@ -338,6 +338,8 @@ class Controller:
             prompt = [rnd.randrange(3, cfg.vocab_size) for _ in range(prompt)]
         rid = req_id if req_id is not None else self.get_new_req_id()
         max_out = output_len if output_len is not None else self.sampling_config.max_output_len
+        if len(prompt) + max_out > cfg.max_seq_len:
+            raise ValueError(f"{len(prompt)} prompt + {max_out} new tokens exceed max_seq_len {cfg.max_seq_len}")
         res = AsyncResult(rid, threading.Event())
         with self._lock:
             self.results[rid] = res

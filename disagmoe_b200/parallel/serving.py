@@ -317,6 +317,10 @@ class FusedServingRank:
     # ---- requests (leaders) --------------------------------------------------------------------------------------
     def add_request(self, req_id: int, prompt: Sequence[int], max_new_tokens: int, t_arrival: float) -> None:
         assert self.is_leader
+        if len(prompt) + max_new_tokens > self.cfg.max_seq_len:
+            # the block table has max_seq_len / block_size columns: a longer sequence must be refused here, on the host
+            raise ValueError(f"request {req_id}: {len(prompt)} prompt + {max_new_tokens} new tokens exceed "
+                             f"max_seq_len {self.cfg.max_seq_len}")
         self.sched.add_request(req_id, prompt, max_new_tokens, t_arrival)
 
     # ---- one iteration -------------------------------------------------------------------------------------------
