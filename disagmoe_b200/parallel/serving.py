@@ -205,8 +205,11 @@ class FusedServingRank:
         self.shape = DisaggShape(A, X, n_mb, self.cap, cfg.top_k, cfg.hidden_size, cfg.num_experts, tp)
         self.layout = build_layout(self.shape)
         self.arena = None if self.host_only else PeerArena.create(self.layout.size, device=self.device)
-        # host control plane: gloo (keeps the CUDA streams free of control collectives)
-        self.ctl = dist.new_group(backend="gloo")
+        # host control plane: gloo (keeps the CUDA streams free of control collectives). Every rank calls it at least
+        # every iteration (idle ranks poll), so a collective that waits two minutes means a rank is gone: the others
+        # then fail with a timeout instead of waiting forever
+        import datetime
+        self.ctl = dist.new_group(backend="gloo", timeout=datetime.timedelta(seconds=120))
         self.leader_rank = rank // tp * tp if self.is_attn else -1
         self.graph_sizes = [] if self.host_only else sorted(g for g in graph_sizes if g <= self.cap)
         self.graphs: Dict[int, torch.cuda.CUDAGraph] = {}
