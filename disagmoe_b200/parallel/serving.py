@@ -88,6 +88,8 @@ class FusedScheduler:
 
     def add_request(self, req_id: int, prompt: Sequence[int], max_new_tokens: int, t_arrival: float) -> None:
         assert len(prompt) >= 1 and max_new_tokens >= 1
+        if self._blocks(len(prompt) + max_new_tokens) > self.bm.num_total_blocks():
+            raise ValueError(f"request {req_id} needs more KV blocks than the pool has")
         self.waiting.append(ServeSeq(req_id, list(prompt), max_new_tokens, t_arrival))
 
     def num_unfinished(self) -> int:

@@ -209,3 +209,51 @@ def test_long_prompt_is_prefilled_in_chunks_next_to_decode_rows():
         plans = s.build(1.0)
         s.commit(plans, _fake_model(plans), 1.0)
     assert len(s.finished[0].outputs) == 6 and len(s.finished[1].outputs) == 2 and bm.num_free_blocks() == 64
+
+
+def test_scheduler_invariants_on_random_streams():
+    """Random request streams against random budgets: every iteration respects the row and prompt budgets and the
+    per-micro-batch sequence limit, every sequence's positions advance without gaps, only the last prompt row and the
+    decode rows sample, every request finishes with its length, and no KV block leaks."""
+    from hypothesis import given, settings, strategies as st
+
+    @settings(max_examples=40, deadline=None)
+    @given(st.integers(0, 10_000), st.integers(1, 3), st.integers(1, 6), st.integers(24, 96), st.integers(16, 64))
+    def run(seed, n_mb, max_seqs, max_tokens, max_prefill):
+        import random
+        rnd = random.Random(seed)
+        bm = C.BlockManager(16, 96, 0, 64)
+        s = FusedScheduler(bm, 16, n_mb, max_seqs, max(max_tokens, max_seqs + 16), max_prefill)
+        reqs = {i: (rnd.randint(1, 120), rnd.randint(1, 12), rnd.random() * 3) for i in range(rnd.randint(1, 14))}
+        for i, (n_in, n_out, at) in sorted(reqs.items(), key=lambda kv: kv[1][2]):
+            s.add_request(i, [rnd.randrange(1000) for _ in range(n_in)], n_out, at)
+        next_pos = {i: 0 for i in reqs}
+        now, steps = 0.0, 0
+        while s.num_unfinished():
+            now += 0.25
+            plans = s.build(now)
+            for m, p in enumerate(plans):
+                assert len(p) <= s.max_tokens and len(s.running[m]) <= max_seqs
+                assert len(p.ids) == len(p.pos) == len(p.rows) == len(p.slots)
+                sampled = {row for row, _, _ in p.emit if row >= 0}
+                assert len(sampled) == len([e for e in p.emit if e[0] >= 0])
+                prompt_rows = 0
+                cursor = 0
+                for row, q, grown in p.emit:                       # emit entries are in row order
+                    first = (row - grown + 1) if row >= 0 else cursor
+                    for k in range(grown):
+                        assert p.pos[first + k] == next_pos[q.req_id] + k
+                    if not (row >= 0 and grown == 1 and q.length >= len(q.prompt)):
+                        prompt_rows += grown
+                    next_pos[q.req_id] += grown
+                    cursor = first + grown
+                assert prompt_rows <= max_prefill
+            s.commit(plans, [[1] * len(p) for p in plans], now)
+            steps += 1
+            assert steps < 4000
+        assert set(s.finished) == set(reqs)
+        for i, (n_in, n_out, _) in reqs.items():
+            assert len(s.finished[i].outputs) == n_out and s.finished[i].length == n_in + n_out - 1
+        assert bm.num_free_blocks() == 96
+
+    run()
