@@ -85,10 +85,11 @@ class FusedScheduler:
         self.waiting: List[ServeSeq] = []                     # arrival order
         self.running: List[Dict[int, ServeSeq]] = [dict() for _ in range(n_mb)]
         self.finished: Dict[int, ServeSeq] = {}
+        self.pool_blocks = block_mgr.num_free_blocks()        # the scheduler is created on an empty pool
 
     def add_request(self, req_id: int, prompt: Sequence[int], max_new_tokens: int, t_arrival: float) -> None:
         assert len(prompt) >= 1 and max_new_tokens >= 1
-        if self._blocks(len(prompt) + max_new_tokens) > self.bm.num_total_blocks():
+        if self._blocks(len(prompt) + max_new_tokens) > self.pool_blocks:
             raise ValueError(f"request {req_id} needs more KV blocks than the pool has")
         self.waiting.append(ServeSeq(req_id, list(prompt), max_new_tokens, t_arrival))
 
