@@ -466,9 +466,18 @@ class FusedServingRank:
         dist = self.dist
         dist.barrier(group=self.ctl)
         t0 = time.time()
+        problem = ""
         if self.is_leader:
-            for rid, prompt, n_out, at in requests:
-                self.add_request(rid, prompt, n_out, t0 + at)
+            try:
+                for rid, prompt, n_out, at in requests:
+                    self.add_request(rid, prompt, n_out, t0 + at)
+            except ValueError as e:
+                problem = str(e)
+        # a request one leader has to refuse ends the job on every rank, before anybody waits for anybody
+        flag = torch.tensor([1 if problem else 0], dtype=torch.int64)
+        dist.all_reduce(flag, group=self.ctl)
+        if int(flag) > 0:
+            raise ValueError(problem or "another attention group refused one of its requests")
         tokens = 0
         while True:
             now = time.time()
