@@ -30,7 +30,7 @@ from .. import disagmoe_c as C
 from ..config import CacheConfig, ModelConfig
 from ..models import weights as W
 from ..models.attention import AttnMeta, MoEAttention
-from ..models.experts import MoEExperts
+from ..models.experts import MoEExperts, MoEExpertsSerial
 from ..ops import functional as F
 from ..ops import gemm
 from .datatypes import SloStat
@@ -175,8 +175,10 @@ class Engine:
         for l, experts in self.local_experts.items():
             experts.sort()
             assert experts == list(range(experts[0], experts[-1] + 1)), "a worker holds a contiguous expert range"
-            e = MoEExperts(cfg, l, experts[0], experts[-1] + 1, device=dev, dtype=dt,
-                           max_batch_size=cfg.max_batch_size_expert if dev.type == "cuda" else 0)
+            # --serial-gemm: one dense GEMM per expert instead of the grouped GEMM (the reference's non-grouped mode)
+            cls = MoEExperts if cfg.enable_grouped_gemm else MoEExpertsSerial
+            e = cls(cfg, l, experts[0], experts[-1] + 1, device=dev, dtype=dt,
+                    max_batch_size=cfg.max_batch_size_expert if dev.type == "cuda" else 0)
             e.load_weights(sd) if sd is not None else e.init_weights()
             self.expert_layers[l] = e
         if self.has_attn:

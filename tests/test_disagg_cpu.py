@@ -81,3 +81,9 @@ def test_three_processes_attention_tp2():
     o_proj partial sums over gloo) + one expert process; logits against the single-process oracle."""
     cfg = tiny_config.clone(ep_size=1, tp_size=2)
     _run(cfg, (1, 1), 3, False, n_req=5, prompt_len=11, n_new=6)
+
+
+def test_serial_expert_gemm_mode_matches_oracle():
+    """enable_grouped_gemm = False: expert workers run one dense GEMM per expert; same logits."""
+    cfg = tiny_config.clone(ep_size=1, enable_grouped_gemm=False)
+    _run(cfg, (1, 1), 2, True, n_req=3, prompt_len=7, n_new=3)
