@@ -14,6 +14,7 @@ _defaults = {
     "LD_LIBRARY_PATH": "",
     "ENABLE_NVTX": "0",                 # enables the native range recorder
     "DMOE_WEIGHTED_ROUTER_FILE": "",    # per-layer expert popularity used for trace-weighted routing
+    "DMOE_WEIGHTED_ROUTER_CATEGORY": "",  # which trace category of that file to use (default closed_qa)
     "DMOE_DATA_PLANE": "",              # "peer" (fused NVSwitch kernels), "nccl" (reference-style), "" = auto
 }
 

@@ -59,10 +59,38 @@ class MoEAttention(torch.nn.Module):
         self.q_size = self.num_heads * self.head_dim
         self.kv_size = self.num_kv_heads * self.head_dim
         self.is_dense = cfg.is_dense_layer(layer_id)
-        self.weighted_router: Optional[torch.Tensor] = None   # expert popularity for trace-weighted routing
+        # expert popularity for trace-weighted routing: set from the file named by DMOE_WEIGHTED_ROUTER_FILE
+        self.weighted_router: Optional[torch.Tensor] = None if self.is_dense else self._load_weighted_router()
         self._gen: Optional[torch.Generator] = None
         self.counts: Optional[torch.Tensor] = None            # device histogram fed to the dispatch kernel
         self.route_bias: Optional[torch.Tensor] = None        # fp32 [E] added to the gate logits (popularity skew)
+
+    def _load_weighted_router(self) -> Optional[torch.Tensor]:
+        """Per-expert popularity of this layer from a routing trace (reference: attention.py:169-182). The file is a
+        CSV with a ``layer_id`` column, optionally a ``category`` column (DMOE_WEIGHTED_ROUTER_CATEGORY, default
+        ``closed_qa``), and one count column per expert as its last ``num_experts`` columns; the rows of this layer are
+        summed and normalised. With it set, the router samples expert ids from the popularity vector instead of
+        using the gate (synthetic load studies); ``use_popularity_as_logit_bias`` keeps the gate and skews it."""
+        import os
+        path = os.environ.get("DMOE_WEIGHTED_ROUTER_FILE", "")
+        if not path:
+            return None
+        assert os.path.exists(path), f"weighted router file {path} does not exist"
+        import pandas as pd
+        df = pd.read_csv(path)
+        if "category" in df.columns:
+            df = df[df["category"] == os.environ.get("DMOE_WEIGHTED_ROUTER_CATEGORY", "closed_qa")]
+        df = df[df["layer_id"] == self.layer_id]
+        counts = torch.tensor(df.iloc[:, -self.cfg.num_experts:].to_numpy(dtype="float64")).sum(0)
+        assert counts.numel() == self.cfg.num_experts and float(counts.sum()) > 0, "no trace rows for this layer"
+        return (counts / counts.sum()).float()
+
+    def use_popularity_as_logit_bias(self) -> None:
+        """Turns the loaded popularity vector into a device-side logit bias (log popularity): the gate still decides,
+        skewed towards the popular experts, and routing stays on the device (usable inside CUDA graphs)."""
+        if self.weighted_router is not None:
+            self.route_bias = torch.log(self.weighted_router.clamp_min(1e-6)).float().to(self.device)
+            self.weighted_router = None
 
     # ---- weights ------------------------------------------------------------------------------------------
     def param_names(self):

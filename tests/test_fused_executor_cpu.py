@@ -52,3 +52,38 @@ def test_shared_expert_and_dense_layer_match_oracle():
     torch.manual_seed(1)
     prompts = [torch.randint(0, 1024, (n,)).tolist() for n in (9, 21)]
     _run(cfg, prompts, 3)
+
+
+def test_trace_weighted_router_file(tmp_path, monkeypatch):
+    """DMOE_WEIGHTED_ROUTER_FILE: per-layer expert popularity from a routing-trace CSV; the router then samples expert
+    ids from it, or (use_popularity_as_logit_bias) keeps the gate and skews its logits."""
+    import pandas as pd
+    import torch
+    from disagmoe_b200.config import tiny_config
+    from disagmoe_b200.models.attention import MoEAttention
+    E = tiny_config.num_experts
+    rows = []
+    for layer in range(2):
+        for cat in ("closed_qa", "other"):
+            for _ in range(3):
+                counts = [0] * E
+                counts[layer] = 90 if cat == "closed_qa" else 1         # layer l prefers expert l
+                counts[E - 1] = 10
+                rows.append({"category": cat, "layer_id": layer, **{f"e{i}": c for i, c in enumerate(counts)}})
+    path = tmp_path / "trace.csv"
+    pd.DataFrame(rows).to_csv(path, index=False)
+    monkeypatch.setenv("DMOE_WEIGHTED_ROUTER_FILE", str(path))
+    a = MoEAttention(tiny_config, 1)
+    a.init_weights()
+    assert torch.allclose(a.weighted_router, torch.tensor([0, 0.9, 0, 0, 0, 0, 0, 0.1]), atol=1e-6)
+    x = torch.randn(200, tiny_config.hidden_size)
+    _, ids, w, _ = a.route(x)
+    assert set(ids.reshape(-1).tolist()) == {1, E - 1}                 # only experts with non-zero popularity
+    assert torch.allclose(w.sum(1), torch.ones(200))
+    a.use_popularity_as_logit_bias()
+    assert a.weighted_router is None and a.route_bias.argmax().item() == 1
+    _, ids, _, _ = a.route(x)
+    hist = torch.bincount(ids.reshape(-1).long(), minlength=E)
+    assert hist[1] >= 190 and hist[E - 1] >= 150                       # the gate decides, heavily skewed
+    monkeypatch.delenv("DMOE_WEIGHTED_ROUTER_FILE")
+    assert MoEAttention(tiny_config, 1).weighted_router is None
