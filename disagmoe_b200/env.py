@@ -15,7 +15,6 @@ _defaults = {
     "ENABLE_NVTX": "0",                 # enables the native range recorder
     "DMOE_WEIGHTED_ROUTER_FILE": "",    # per-layer expert popularity used for trace-weighted routing
     "DMOE_WEIGHTED_ROUTER_CATEGORY": "",  # which trace category of that file to use (default closed_qa)
-    "DMOE_DATA_PLANE": "",              # "peer" (fused NVSwitch kernels), "nccl" (reference-style), "" = auto
 }
 
 ENV_VARS = {k: os.environ.get(k, v) for k, v in _defaults.items()}

@@ -514,6 +514,7 @@ class Engine:
         return time.time()
 
     def start_profile(self, profile_dir: Optional[str] = None) -> None:
+        profile_dir = profile_dir or os.environ.get("DMOE_PROFILE_DIR") or None
         C.recorder_enable(True)
         self._torch_prof = None
         if profile_dir:
