@@ -29,6 +29,22 @@ from disagmoe_b200.config import CacheConfig, get_preset
 from disagmoe_b200.parallel.serving import FusedServingRank
 
 
+def write_trace(results, path: str) -> str:
+    """Chrome trace: one process per attention rank, one event per iteration carrying the rows of its micro-batches
+    and whether it replayed a CUDA graph."""
+    import gzip
+    events = []
+    for r in results:
+        for t0, t1, Ts, g in r.get("step_log", []):
+            events.append({"name": ("graph %d" % g) if g else "eager", "cat": "iteration", "ph": "X", "ts": t0 * 1e6,
+                           "dur": (t1 - t0) * 1e6, "pid": r["rank"], "tid": 0,
+                           "args": {"rows_per_micro_batch": list(Ts)}})
+    os.makedirs(os.path.dirname(os.path.abspath(path)) or ".", exist_ok=True)
+    with gzip.open(path, "wt") as f:
+        json.dump(events, f)
+    return path
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", default="mixtral")
@@ -51,6 +67,7 @@ def main():
     ap.add_argument("--time-limit", type=float, default=600.0)
     ap.add_argument("--check", action="store_true")
     ap.add_argument("-f", "--file", default="", help="append the metrics as one JSON line")
+    ap.add_argument("--trace", default="", help="write a Chrome trace (json.gz) of every attention rank's iterations")
     args = ap.parse_args()
 
     rank, world, lr = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
@@ -98,6 +115,8 @@ def main():
                  "kernel_status": max(g["kernel_status"] for g in gathered), "requests_finished": len(slo),
                  "layout": f"{groups} attention group(s) x tp{tp} + {world - A} expert GPUs"}
         print(json.dumps(extra))
+        if args.trace:
+            write_trace(gathered, args.trace)
         if args.check:
             from disagmoe_b200.frontend.colocated import ColocatedEngine
             outs = {k: v for g in gathered for k, v in g.get("outputs", {}).items()}

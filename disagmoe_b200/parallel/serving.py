@@ -218,6 +218,8 @@ class FusedServingRank:
         self.graphs: Dict[int, torch.cuda.CUDAGraph] = {}
         self.iterations = 0
         self.graph_iterations = 0
+        # per iteration: (start s, end s, rows of every micro-batch, graph size or 0 for an eager launch)
+        self.step_log: List[Tuple[float, float, Tuple[int, ...], int]] = []
         if self.is_attn:
             # one block beyond the manager's range is the scratch page the padding rows write to
             self.runner = host_only_runner("attention", self) if self.host_only else \
@@ -428,6 +430,7 @@ class FusedServingRank:
         if patches is not None:
             t = patches if self.host_only else patches.pin_memory().to(self.device, non_blocking=True)
             self.runner.block_tables.index_put_((t[0], t[1]), t[2].int())
+        t_begin = time.time()
         # decode-sized iterations replay the graph of the padded size; bigger ones launch eagerly at the exact size
         tmax = max(max(Ts), 1)
         g = next((s for s in self.graph_sizes if s >= tmax), None)
@@ -448,6 +451,7 @@ class FusedServingRank:
         if not self.host_only:
             torch.cuda.current_stream().synchronize()
             self._last_status = self._status_word()
+        self.step_log.append((t_begin, time.time(), tuple(Ts), g or 0))
         if not self.is_leader:
             return []
         if plans is None:
@@ -490,7 +494,8 @@ class FusedServingRank:
         self._sync()
         dt = time.time() - t0
         res = {"rank": self.rank, "duration": dt, "tokens": tokens, "iterations": self.iterations,
-               "graph_iterations": self.graph_iterations, "kernel_status": self.kernel_status(), "slo": [], "arrivals": {}}
+               "graph_iterations": self.graph_iterations, "kernel_status": self.kernel_status(), "slo": [], "arrivals": {},
+               "step_log": list(self.step_log)}
         if self.is_leader:
             for s in self.sched.finished.values():
                 res["slo"].append(SloStat(s.req_id, s.t_tokens[0], 0.0, s.t_tokens[-1], list(s.t_tokens)))

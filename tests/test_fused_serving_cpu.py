@@ -147,6 +147,17 @@ def test_host_protocol_two_dp_groups_cpu():
     for rid, prompt, n_out, _ in reqs:
         assert outs[rid] == _expected_tokens(prompt, n_out, tiny_config.vocab_size), rid
     assert res[0]["iterations"] == res[1]["iterations"] == res[2]["iterations"] > 0
+    # every attention rank logs its iterations; the benchmark turns the logs into a Chrome trace
+    assert len(res[0]["step_log"]) == res[0]["iterations"] and not res[2]["step_log"]
+    import gzip
+    import json
+    import os
+    import tempfile
+    from benchmark.serve_fused import write_trace
+    path = write_trace(list(res.values()), os.path.join(tempfile.mkdtemp(), "t.json.gz"))
+    ev = json.load(gzip.open(path, "rt"))
+    assert len(ev) == 2 * res[0]["iterations"] and {e["pid"] for e in ev} == {0, 1}
+    assert all(e["dur"] >= 0 and len(e["args"]["rows_per_micro_batch"]) == 2 for e in ev)
 
 
 def test_host_protocol_tensor_parallel_group_cpu():
