@@ -36,6 +36,7 @@ import torch
 
 from ..config import ModelConfig
 from ..frontend.datatypes import SloStat
+from ..utils.constants import EOS_TOKEN_ID
 
 
 # ------------------------------------------------------------------------------------------------ scheduling (host)
@@ -77,8 +78,9 @@ class FusedScheduler:
     MIN_CHUNK = 16      # do not start or continue a prompt with fewer rows than this unless that finishes it
 
     def __init__(self, block_mgr, block_size: int, n_mb: int, max_seqs_per_mb: int, max_tokens_per_mb: int,
-                 max_prefill_tokens_per_mb: Optional[int] = None):
+                 max_prefill_tokens_per_mb: Optional[int] = None, ignore_eos: bool = True):
         self.bm, self.block_size, self.n_mb = block_mgr, block_size, n_mb
+        self.ignore_eos = ignore_eos          # False: a sampled EOS token (id 2) ends the request early
         self.max_seqs, self.max_tokens = max_seqs_per_mb, max_tokens_per_mb
         self.max_prefill = max_prefill_tokens_per_mb or max_tokens_per_mb
         assert self.max_tokens > self.max_seqs, "a micro-batch must have room for prompt rows next to its decode rows"
@@ -172,7 +174,7 @@ class FusedScheduler:
                 s.t_tokens.append(now)
                 s.last_token = tok
                 out.append((s.req_id, tok))
-                if len(s.outputs) >= s.max_new_tokens:
+                if len(s.outputs) >= s.max_new_tokens or (not self.ignore_eos and tok == EOS_TOKEN_ID):
                     self.bm.release(s.req_id)
                     self.running[m].pop(s.req_id, None)
                     self.finished[s.req_id] = s
@@ -186,7 +188,8 @@ class FusedServingRank:
     def __init__(self, cfg: ModelConfig, world: int, rank: int, local_rank: int, n_attn: int, tp: int = 1,
                  max_seqs_per_mb: int = 128, max_tokens_per_mb: int = 2048, num_blocks: int = 8192,
                  graph_sizes: Sequence[int] = (8, 32, 64, 128, 256), n_mb: int = 2, route_skew: float = 0.0,
-                 max_prefill_tokens_per_mb: Optional[int] = None, state_dict=None, host_only_runner=None):
+                 max_prefill_tokens_per_mb: Optional[int] = None, state_dict=None, host_only_runner=None,
+                 ignore_eos: bool = True):
         """``host_only_runner(role, server)`` replaces the GPU side (peer arena, attention / expert ranks, CUDA graphs)
         with a stand-in that offers the same buffers and ``iteration()``: the host protocol (control all-reduce, plan
         sharing inside a TP group, scheduling, result collection) then runs as plain CPU processes."""
@@ -235,7 +238,7 @@ class FusedServingRank:
             if self.is_leader:
                 self.bm = C.BlockManager(self.block_size, num_blocks, 0, self.max_rows)
                 self.sched = FusedScheduler(self.bm, self.block_size, n_mb, max_seqs_per_mb, self.cap,
-                                            max_prefill_tokens_per_mb)
+                                            max_prefill_tokens_per_mb, ignore_eos)
             n = n_mb * self.cap
             pin = lambda dt: torch.zeros(n, dtype=dt) if self.host_only else torch.zeros(n, dtype=dt).pin_memory()
             self.h_ids, self.h_pos, self.h_ctx, self.h_row = (pin(torch.int32) for _ in range(4))

@@ -268,3 +268,15 @@ def test_scheduler_invariants_on_random_streams():
         assert bm.num_free_blocks() == 96
 
     run()
+
+
+def test_eos_ends_a_request_when_not_ignored():
+    from disagmoe_b200.utils.constants import EOS_TOKEN_ID
+    bm = C.BlockManager(16, 16, 0, 4)
+    s = FusedScheduler(bm, 16, 1, 2, 64, ignore_eos=False)
+    s.add_request(0, [5, 6, 7], 10, 0.0)
+    plans = s.build(0.0)
+    s.commit(plans, [[9] * len(plans[0])], 0.1)                 # first token: not EOS
+    plans = s.build(0.2)
+    s.commit(plans, [[EOS_TOKEN_ID]], 0.3)                      # second token: EOS
+    assert s.finished[0].outputs == [9, EOS_TOKEN_ID] and s.num_unfinished() == 0 and bm.num_free_blocks() == 16
