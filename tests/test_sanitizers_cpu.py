@@ -15,7 +15,10 @@ TARGETS = ["tests/test_runtime_cpu.py",
            "tests/test_disagg_cpu.py::test_disaggregated_in_process_1attn_1expert",
            "tests/test_disagg_cpu.py::test_colocated_in_process",
            "tests/test_fused_serving_cpu.py::test_mixed_prefill_decode_micro_batches",
-           "tests/test_fault_and_resume_cpu.py::test_duplicated_or_delayed_message_does_not_change_the_result"]
+           "tests/test_fault_and_resume_cpu.py::test_duplicated_or_delayed_message_does_not_change_the_result",
+           # worker processes inherit the preloaded sanitizer: TCP sockets between processes, the TP group, recovery
+           "tests/test_disagg_cpu.py::test_three_processes_attention_tp2",
+           "tests/test_fault_and_resume_cpu.py::test_recover_restarts_workers_and_readmits_unfinished_requests"]
 
 
 @pytest.mark.parametrize("kind", ["address", "thread"])
