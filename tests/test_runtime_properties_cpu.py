@@ -100,3 +100,52 @@ def test_block_manager_against_a_python_model(seq):
             assert [cols[c] for c in range(len(blocks))] == blocks
     bm.batch_release(list(lens))
     assert bm.num_free_blocks() == total and bm.num_seqs() == 0
+
+
+def test_attention_pool_is_insensitive_to_arrival_order():
+    """Partial rows of decode tokens arrive in random order and random groupings: a token is released exactly when its
+    top-k + residual parts are all there, with every part in its own slot, whatever the order."""
+    import random
+
+    import torch
+    K = 3                                                     # parts per token (top-2 + residual)
+    C.set_inproc_transport(True)
+    try:
+        for seed in range(8):
+            rnd = random.Random(seed)
+            args = C.EngineArgs()
+            args.local_id, args.has_attn, args.top_k = 710 + seed, True, K - 1
+            args.attn_layer_ids = [1]
+            args.parts_needed = {1: K}
+            h = C.init_engine(args)
+            p = h.attn_pool
+            n_tok = rnd.randint(1, 9)
+            parts = [(t, s) for t in range(n_tok) for s in range(K)]
+            rnd.shuffle(parts)
+            value = lambda t, s: torch.full((4,), float(10 * t + s))
+            released, arrived = set(), {t: 0 for t in range(n_tok)}
+            while parts:
+                group = [parts.pop() for _ in range(min(len(parts), rnd.randint(1, 4)))]
+                m = C.Metadata([len(group), 4])
+                m.layer_id = 1
+                m.req_ids = [100 + t for t, _ in group]
+                m.exp_ids, m.attn_dp_ranks = [0] * len(group), [0] * len(group)
+                m.init_prefill_lens, m.positions = [-1] * len(group), [7] * len(group)
+                m.topk_slots = [s for _, s in group]
+                p.process_batch(torch.stack([value(t, s) for t, s in group]), m, 0)
+                for t, _ in group:
+                    arrived[t] += 1
+                b = p.fetch_attention_batch()
+                complete = {t for t in arrived if arrived[t] == K} - released
+                if not complete:
+                    assert b.metadata is None
+                    continue
+                assert sorted(b.metadata.seq_ids) == sorted(100 + t for t in complete) and b.num_parts == K
+                for row, sid in enumerate(b.metadata.seq_ids):
+                    got = sorted(b.data[row, :, 0].tolist())
+                    assert got == [float(10 * (sid - 100) + s) for s in range(K)]
+                released |= complete
+            assert released == set(range(n_tok)) and p.num_pending_tokens() == 0
+            C.stop_engine(h)
+    finally:
+        C.set_inproc_transport(False)
