@@ -96,6 +96,16 @@ def make_workload(args) -> Workload:
     return gen.generate_duration(args.duration) if args.duration > 0 else gen.generate_num(args.num_requests)
 
 
+def parse_worker_addresses(spec: str):
+    """'3=10.0.0.2:7700,4=10.0.0.2:7700' -> {3: ('10.0.0.2', 7700), 4: ('10.0.0.2', 7700)}"""
+    out = {}
+    for item in filter(None, (x.strip() for x in spec.split(","))):
+        dev, addr = item.split("=")
+        host, port = addr.rsplit(":", 1)
+        out[int(dev)] = (host, int(port))
+    return out
+
+
 def launch(args):
     """Builds the placement and the controller, starts every worker (reference: benchmark_serving.py:88-131)."""
     from disagmoe_b200.frontend.controller import init_controller
@@ -105,7 +115,8 @@ def launch(args):
         place = get_model_placement(cfg, cluster, "pipeline", args.step_attn, args.step_expert, args.zigzag_attn)
     else:
         place = get_model_placement(cfg, cluster, args.placement)
-    master = init_controller(args.num_nodes, args.num_gpus, device=args.device)
+    master = init_controller(args.num_nodes, args.num_gpus, device=args.device,
+                             worker_addresses=parse_worker_addresses(getattr(args, "worker_addresses", "")))
     master.init_engine(place, cfg, CacheConfig(block_size=args.block_size, gpu_memory_utilization=args.gpu_usage,
                                                num_gpu_blocks=args.num_blocks or 4096),
                        SamplingConfig(args.min_output_len, args.max_output_len))

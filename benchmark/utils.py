@@ -53,4 +53,7 @@ def get_parser_base() -> ArgumentParser:
                    help="controller (one process per device, host-scheduled) | colocated (one GPU, fused executor) | "
                         "fused (one process per GPU on the peer-memory path: tp-size x dp-size attention GPUs, the rest experts)")
     p.add_argument("--device", type=str, default="cuda", help="cuda | cpu")
+    p.add_argument("--worker-addresses", type=str, default="",
+                   help="multi-node: 'device=host:port,...' of the node agents (python -m disagmoe_b200.frontend.node_agent) "
+                        "that host those devices' workers; devices not listed run on this machine")
     return p

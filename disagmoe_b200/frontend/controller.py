@@ -142,7 +142,8 @@ class AsyncResult:
 
 class Controller:
     def __init__(self, n_node: int, n_gpu_per_node: int, device: str = "cuda", in_process: bool = False,
-                 heartbeat_timeout_s: float = 30.0, dp_policy: str = "max"):
+                 heartbeat_timeout_s: float = 30.0, dp_policy: str = "max",
+                 worker_addresses: Optional[Dict[int, Tuple[str, int]]] = None):
         self.n_node, self.n_gpu_per_node = n_node, n_gpu_per_node
         self.device_kind = device
         self.in_process = in_process
@@ -155,6 +156,10 @@ class Controller:
         self.results: Dict[int, AsyncResult] = {}
         self.dp_scheduler = None
         self.dp_policy = dp_policy          # "max": replica with the most free KV blocks (waits for room); "RR"
+        # device id -> (host, port) of the node agent that hosts that device's worker (multi-node deployments);
+        # devices not listed get a worker process on this machine
+        self.worker_addresses = dict(worker_addresses or {})
+        self.controller_host = "127.0.0.1"   # the address workers on other nodes use to reach tokenizer / sampler
         self.port_shift = random.randint(0, 400) * 16 * 4 % 6000
         self.heartbeat_timeout_s = heartbeat_timeout_s
         self.suspect_workers: List[int] = []
@@ -182,6 +187,10 @@ class Controller:
         for d in placement.device_ids():
             if self.in_process:
                 self.workers[d] = LocalWorker(d, self._device_of(d))
+            elif d in self.worker_addresses:
+                from .node_agent import RemoteWorkerHandle
+                env = {"CUDA_VISIBLE_DEVICES": str(d % self.n_gpu_per_node)} if self.device_kind == "cuda" else {}
+                self.workers[d] = RemoteWorkerHandle(d, self._device_of(d), self.worker_addresses[d], env)
             else:
                 env = {}
                 if self.device_kind == "cuda":
@@ -228,7 +237,10 @@ class Controller:
                 attn_peer.setdefault(l, {})[placement.attn_dp_rank_at(d)] = d
         attn_peer[L] = dict(attn_peer[0])
         expert_ranks = [(l, e, r) for (l, e), r in placement.expert_ranks.items()]
-        hosts = {d: "127.0.0.1" for d in list(self.workers) + [TOKENIZER_DEV_ID, SAMPLER_DEV_ID]}
+        # every worker learns where every other one lives; tokenizer and sampler live with the controller
+        hosts = {d: self.worker_addresses.get(d, (self.controller_host, 0))[0]
+                 for d in list(self.workers) + [TOKENIZER_DEV_ID, SAMPLER_DEV_ID]}
+        C.set_hosts(os.getpid(), hosts)
         self._all("setup_engine", model_config, cache_config, dtype, self.in_process)
         # attention TP: only the driver of a group is part of the token flow; it broadcasts its batches to the workers
         tp_workers = {d for d in self.workers if placement.is_worker_device(d)}
@@ -592,5 +604,6 @@ class Controller:
             w.stop()
 
 
-def init_controller(n_node: int, n_gpu_per_node: int, device: str = "cuda", in_process: bool = False) -> Controller:
-    return Controller(n_node, n_gpu_per_node, device=device, in_process=in_process)
+def init_controller(n_node: int, n_gpu_per_node: int, device: str = "cuda", in_process: bool = False,
+                    **kwargs) -> Controller:
+    return Controller(n_node, n_gpu_per_node, device=device, in_process=in_process, **kwargs)

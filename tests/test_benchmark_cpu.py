@@ -116,3 +116,9 @@ def test_fused_backend_command_line():
     assert "--nproc-per-node 8" in joined and "serve_fused.py" in joined
     assert "--n-attn 4 --attn-tp 4" in joined and "-r 16.0 -n 96" in joined and "--max-seqs-per-mb 128" in joined
     assert "--num-blocks 16384" in joined
+
+
+def test_worker_address_flag():
+    from benchmark.benchmark_serving import parse_worker_addresses
+    assert parse_worker_addresses("") == {}
+    assert parse_worker_addresses("3=10.0.0.2:7700, 4=node-b:7701") == {3: ("10.0.0.2", 7700), 4: ("node-b", 7701)}

