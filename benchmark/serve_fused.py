@@ -5,8 +5,8 @@
         --min-input-len 128 -i 1024 --min-output-len 64 -o 512
 
 Every rank builds the same synthetic workload from the seed (Poisson arrivals, uniform prompt / output lengths,
-uniform random token ids); request i belongs to attention group i mod (number of groups), so no request ever travels
-between processes. Rank 0 gathers the per-request timestamps and prints the same metrics as
+uniform random token ids) and the same request -> attention group assignment (least outstanding KV demand at arrival,
+``assign_requests``), so no request ever travels between processes. Rank 0 gathers the per-request timestamps and prints the same metrics as
 ``benchmark.benchmark_serving`` (request / token throughput, request latency, inter-token latency and time to first
 token: mean / median / p99), the share of iterations that replayed a CUDA graph, and the device status word.
 ``--check`` replays the same requests through the single-GPU colocated engine on rank 0 afterwards and reports the
@@ -27,6 +27,22 @@ from benchmark.benchmark_serving import analyze_results
 from benchmark.workload import get_generator
 from disagmoe_b200.config import CacheConfig, get_preset
 from disagmoe_b200.parallel.serving import FusedServingRank
+
+
+def assign_requests(reqs, groups: int):
+    """Request -> attention group, computed identically on every rank from the workload alone: in arrival order, each
+    request goes to the group with the least KV demand (prompt + output tokens) still outstanding at its arrival time,
+    assuming a request holds its tokens from arrival until ``output length`` inter-token steps later. The same idea as
+    the DP admission policy of the host-scheduled path (most free KV blocks first), without any communication."""
+    load = [[] for _ in range(groups)]            # per group: (release time estimate, tokens)
+    owner = {}
+    step = 0.02                                   # nominal seconds per token, only used to age out old requests
+    for rid, prompt, n_out, at in sorted(reqs, key=lambda r: (r[3], r[0])):
+        cur = [sum(t for rel, t in g if rel > at) for g in load]
+        g = min(range(groups), key=lambda i: (cur[i], i))
+        owner[rid] = g
+        load[g].append((at + n_out * step, len(prompt) + n_out))
+    return owner
 
 
 def write_trace(results, path: str) -> str:
@@ -100,7 +116,8 @@ def main():
                            max_tokens_per_mb=args.max_tokens_per_mb, num_blocks=args.num_blocks,
                            route_skew=args.route_skew,
                            max_prefill_tokens_per_mb=args.max_prefill_tokens_per_mb or None)
-    mine = [r for r in reqs if srv.is_leader and r[0] % groups == rank // tp]
+    owner = assign_requests(reqs, groups)
+    mine = [r for r in reqs if srv.is_leader and owner[r[0]] == rank // tp]
     res = srv.serve(mine, time_limit=args.time_limit)
     gathered = [None] * world if rank == 0 else None
     dist.gather_object(res, gathered, dst=0, group=srv.ctl)

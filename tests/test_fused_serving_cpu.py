@@ -280,3 +280,17 @@ def test_eos_ends_a_request_when_not_ignored():
     plans = s.build(0.2)
     s.commit(plans, [[EOS_TOKEN_ID]], 0.3)                      # second token: EOS
     assert s.finished[0].outputs == [9, EOS_TOKEN_ID] and s.num_unfinished() == 0 and bm.num_free_blocks() == 16
+
+
+def test_request_assignment_balances_groups_deterministically():
+    import random
+    from benchmark.serve_fused import assign_requests
+    rnd = random.Random(0)
+    reqs = [(i, [0] * rnd.randint(100, 1000), rnd.randint(50, 500), i * 0.05) for i in range(200)]
+    owner = assign_requests(reqs, 4)
+    assert owner == assign_requests(list(reversed(reqs)), 4)          # a function of the workload, not of its order
+    work = [0] * 4
+    for rid, prompt, n_out, _ in reqs:
+        work[owner[rid]] += len(prompt) + n_out
+    assert max(work) / min(work) < 1.25
+    assert set(assign_requests(reqs, 1).values()) == {0}
