@@ -149,12 +149,18 @@ def run_benchmark_colocated(cfg, wl: Workload, args):
     """One GPU, fused executor: the driver loop admits arrived requests and steps the engine."""
     import torch
     from disagmoe_b200.frontend.colocated import ColocatedEngine
-    eng = ColocatedEngine(cfg, CacheConfig(block_size=args.block_size, gpu_memory_utilization=args.gpu_usage,
-                                           num_gpu_blocks=args.num_blocks), device=args.device,
-                          max_batch_size=args.max_batch_size_attn,
-                          max_prefill_tokens=max(args.max_input_len, args.max_batch_size_attn, 2048),
-                          enable_cuda_graph=args.cuda_graph_attn,
-                          dtype=torch.float32 if args.device == "cpu" else None)
+    from disagmoe_b200.frontend.colocated_mixed import MixedBatchEngine
+    budget = getattr(args, "prefill_budget", 0)
+    kw = dict(prefill_budget=budget) if budget > 0 else {}
+    # --prefill-budget N: mixed batches (decode tokens + at most N prompt rows per step, chunked prefill) instead of
+    # alternating whole-prompt prefill steps and decode steps
+    Engine = MixedBatchEngine if budget > 0 else ColocatedEngine
+    eng = Engine(cfg, CacheConfig(block_size=args.block_size, gpu_memory_utilization=args.gpu_usage,
+                                  num_gpu_blocks=args.num_blocks), device=args.device,
+                 max_batch_size=args.max_batch_size_attn,
+                 max_prefill_tokens=max(args.max_input_len, args.max_batch_size_attn, 2048) + (budget if budget > 0 else 0),
+                 enable_cuda_graph=args.cuda_graph_attn,
+                 dtype=torch.float32 if args.device == "cpu" else None, **kw)
     if args.cuda_graph_attn:
         eng.executor.capture()
     rng = np.random.default_rng(args.seed)

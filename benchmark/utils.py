@@ -53,6 +53,9 @@ def get_parser_base() -> ArgumentParser:
                    help="controller (one process per device, host-scheduled) | colocated (one GPU, fused executor) | "
                         "fused (one process per GPU on the peer-memory path: tp-size x dp-size attention GPUs, the rest experts)")
     p.add_argument("--device", type=str, default="cuda", help="cuda | cpu")
+    p.add_argument("--prefill-budget", type=int, default=0,
+                   help="colocated backend: prompt rows per step next to the decode tokens (chunked prefill); "
+                        "0 = alternate whole-prompt prefill steps and decode steps")
     p.add_argument("--worker-addresses", type=str, default="",
                    help="multi-node: 'device=host:port,...' of the node agents (python -m disagmoe_b200.frontend.node_agent) "
                         "that host those devices' workers; devices not listed run on this machine")

@@ -54,6 +54,11 @@ def test_colocated_backend_cpu(tmp_path):
               "-i", "8", "--min-output-len", "2", "-o", "4", "-f", str(tmp_path / "b.csv"), "--num-blocks", "64",
               "--max-batch-size-attn", "4"])
     assert m.req_throughput > 0
+    # the same workload with mixed batches (8 prompt rows per step)
+    m2 = main(["--device", "cpu", "--model", "tiny", "--backend", "colocated", "-n", "5", "-r", "0", "--min-input-len", "4",
+               "-i", "8", "--min-output-len", "2", "-o", "4", "-f", str(tmp_path / "b.csv"), "--num-blocks", "64",
+               "--max-batch-size-attn", "4", "--prefill-budget", "8"])
+    assert m2.req_throughput > 0 and m2.token_throughput > 0
 
 
 def test_remote_comm_latency_socket_pair():
