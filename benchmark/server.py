@@ -3,6 +3,7 @@
     python -m benchmark.server --device cpu --model tiny -g 2 --ep-size 1 --step-attn 1 --port 6699
 
 POST /run_once     {"rate": 10, "time": 10, "distribution": "poisson"}  runs one open-loop workload, returns its metrics
+POST /generate     {"prompt_ids": [...], "max_new_tokens": 16}          one request; returns the generated token ids
 POST /set_schedule {"policy": "mbflfs", "step": 8}                     switches the layer-scheduling policy / block size
                                                                        of every worker at run time
 GET  /health       worker liveness
@@ -63,6 +64,23 @@ def create_app(args):
             state["master"].set_schedule_block(int(step))
             state["args"].layer_scheduler_step = int(step)
         return {"ok": True}
+
+    @app.post("/generate")
+    def generate(body: dict):
+        """One request through the serving system: {"prompt_ids": [...], "max_new_tokens": n} -> generated token ids
+        and the request's timestamps (seconds)."""
+        prompt, n_new = body.get("prompt_ids"), body.get("max_new_tokens", 16)
+        if not isinstance(prompt, list) or not prompt or not all(isinstance(t, int) for t in prompt):
+            raise HTTPException(400, "prompt_ids must be a non-empty list of token ids")
+        cfg = state["cfg"]
+        if not all(0 <= t < cfg.vocab_size for t in prompt) or not isinstance(n_new, int) or n_new < 1:
+            raise HTTPException(400, "token ids must be inside the vocabulary and max_new_tokens >= 1")
+        try:
+            res = state["master"].put_single_request(prompt, output_len=n_new)
+            slo = res.get(timeout=600)
+        except ValueError as e:
+            raise HTTPException(400, str(e))
+        return {"req_id": res.req_id, "tokens": res.tokens, "t_tokens": slo.t_tokens}
 
     @app.get("/health")
     def health():

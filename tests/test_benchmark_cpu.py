@@ -93,6 +93,12 @@ def test_http_server_run_once_and_policy_switch():
         assert client.post("/set_schedule", json={}).status_code == 400
         m = client.post("/run_once", json={"rate": 40, "time": 0.2, "distribution": "poisson"}).json()
         assert m["token_throughput"] > 0 and m["req_throughput"] > 0
+        g = client.post("/generate", json={"prompt_ids": [5, 6, 7, 8], "max_new_tokens": 3}).json()
+        assert len(g["tokens"]) == 3 and len(g["t_tokens"]) == 3
+        again = client.post("/generate", json={"prompt_ids": [5, 6, 7, 8], "max_new_tokens": 3}).json()
+        assert again["tokens"] == g["tokens"]                         # greedy decoding is deterministic
+        assert client.post("/generate", json={"prompt_ids": []}).status_code == 400
+        assert client.post("/generate", json={"prompt_ids": [10 ** 9]}).status_code == 400
 
 
 def test_queueing_simulator_policies():
