@@ -186,7 +186,7 @@ def generate_step_trace(step_stats, path_prefix: str) -> None:
     running metrics, and the queue-length history (reference: benchmark_serving.py:187-259)."""
     events, metrics, queues = [], {}, {}
     for pid, (infos, traces, metric) in step_stats.items():
-        metrics[pid] = asdict(metric) if hasattr(metric, "__dataclass_fields__") else metric
+        metrics[pid] = metric.as_dict() if hasattr(metric, "as_dict") else metric
         queues[pid] = [(s.start_timestamp_ms, s.pool_snapshot) for s in infos]
         for s in infos:
             events.append({"name": f"layer {s.layer_id}, batch {s.batch_size}", "cat": "step", "ph": "X",
