@@ -47,6 +47,12 @@ def test_end_to_end_tiny_cpu(tmp_path, monkeypatch):
         assert mod.main([str(run)])
     html = queue_length_interact.main([str(tmp_path / "queue_length.pkl"), "--worker", "0"])
     assert os.path.getsize(html) > 200
+    from benchmark.plotter import latency_cdf, queue_length
+    heat = queue_length.main([str(tmp_path / "queue_length.pkl"), "--out-dir", str(tmp_path / "plots")])
+    assert len(heat) == 2 and all(os.path.exists(f) for f in heat)           # one heat map per worker
+    cdfs = latency_cdf.main(["--ttft", str(run / "ttft.csv"), "--sampler", str(run / "sampler_step.csv"),
+                             "--out-dir", str(tmp_path / "plots")])
+    assert len(cdfs) == 3 and all(os.path.exists(f) for f in cdfs)
 
 
 def test_colocated_backend_cpu(tmp_path):
