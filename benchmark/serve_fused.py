@@ -26,7 +26,7 @@ import torch.distributed as dist
 from benchmark.benchmark_serving import analyze_results
 from benchmark.workload import get_generator
 from disagmoe_b200.config import CacheConfig, get_preset
-from disagmoe_b200.parallel.serving import FusedServingRank
+from disagmoe_b200.parallel.serving import FusedServingRank, HostOnlyAttention, host_only_runner
 
 
 def assign_requests(reqs, groups: int):
@@ -82,6 +82,9 @@ def main():
     ap.add_argument("--route-skew", type=float, default=0.0)
     ap.add_argument("--time-limit", type=float, default=600.0)
     ap.add_argument("--check", action="store_true")
+    ap.add_argument("--host-only", action="store_true",
+                    help="dry run of the host side (scheduling, lock-step protocol, result collection) as CPU processes "
+                         "over gloo with a stand-in for the GPU side; --check then verifies the stand-in's tokens")
     ap.add_argument("-f", "--file", default="", help="append the metrics as one JSON line")
     ap.add_argument("--trace", default="", help="write a Chrome trace (json.gz) of every attention rank's iterations")
     args = ap.parse_args()
@@ -91,8 +94,11 @@ def main():
         # where is every rank if the job stops making progress: Python stacks of all threads to stderr, repeatedly
         import faulthandler
         faulthandler.dump_traceback_later(float(os.environ["DMOE_SERVE_DEBUG"]), repeat=True)
-    torch.cuda.set_device(lr)
-    dist.init_process_group("nccl", device_id=torch.device("cuda", lr))
+    if args.host_only:
+        dist.init_process_group("gloo")
+    else:
+        torch.cuda.set_device(lr)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", lr))
     cfg = get_preset(args.model)
     if args.num_layers:
         cfg = cfg.clone(num_layers=args.num_layers)
@@ -115,7 +121,8 @@ def main():
     srv = FusedServingRank(cfg, world, rank, lr, A, tp, max_seqs_per_mb=args.max_seqs_per_mb,
                            max_tokens_per_mb=args.max_tokens_per_mb, num_blocks=args.num_blocks,
                            route_skew=args.route_skew,
-                           max_prefill_tokens_per_mb=args.max_prefill_tokens_per_mb or None)
+                           max_prefill_tokens_per_mb=args.max_prefill_tokens_per_mb or None,
+                           host_only_runner=host_only_runner(cfg.vocab_size) if args.host_only else None)
     owner = assign_requests(reqs, groups)
     mine = [r for r in reqs if srv.is_leader and owner[r[0]] == rank // tp]
     res = srv.serve(mine, time_limit=args.time_limit)
@@ -134,7 +141,18 @@ def main():
         print(json.dumps(extra))
         if args.trace:
             write_trace(gathered, args.trace)
-        if args.check:
+        if args.check and args.host_only:
+            outs = {k: v for g in gathered for k, v in g.get("outputs", {}).items()}
+            ok = 0
+            for rid, prompt, n_out, _ in reqs:
+                tok, pos, want = prompt[-1], len(prompt) - 1, []
+                for _ in range(n_out):
+                    tok = HostOnlyAttention.next_token(tok, pos, cfg.vocab_size)
+                    want.append(tok)
+                    pos += 1
+                ok += int(outs.get(rid) == want)
+            print(json.dumps({"check_requests_exact": ok, "requests": len(reqs)}))
+        elif args.check:
             from disagmoe_b200.frontend.colocated import ColocatedEngine
             outs = {k: v for g in gathered for k, v in g.get("outputs", {}).items()}
             del srv

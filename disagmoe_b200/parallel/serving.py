@@ -181,6 +181,43 @@ class FusedScheduler:
         return out
 
 
+# ------------------------------------------------------------------------------------------------ host-only stand-ins
+class HostOnlyAttention:
+    """Stands in for the GPU side of an attention rank in host-only runs (CPU processes, no kernels): the same buffers
+    as ``AttentionRank``; the "model" maps (token, position) to the next token deterministically."""
+
+    def __init__(self, srv: "FusedServingRank", vocab: int):
+        z = lambda n, dt=torch.int32: torch.zeros(n, dtype=dt)
+        self.mb = [dict(ids=z(srv.cap), positions=z(srv.cap), ctx_len=z(srv.cap), bt_row=z(srv.cap),
+                        slots=z(srv.cap, torch.int64), next_ids=z(srv.cap)) for _ in range(srv.n_mb)]
+        self.block_tables = torch.zeros(2 * srv.cap + 8, 64, dtype=torch.int32)
+        self.layers: List = []
+        self.active = [srv.cap] * srv.n_mb
+        self.vocab = vocab
+
+    @staticmethod
+    def next_token(token: int, position: int, vocab: int) -> int:
+        return (token * 7 + position * 3 + 1) % vocab
+
+    def set_active(self, m: int, T: int) -> None:
+        self.active[m] = T
+
+    def iteration(self) -> None:
+        for m, d in enumerate(self.mb):
+            T = self.active[m]
+            d["next_ids"][:T] = (d["ids"][:T] * 7 + d["positions"][:T] * 3 + 1) % self.vocab
+
+
+class HostOnlyExpert:
+    def iteration(self) -> None:
+        pass
+
+
+def host_only_runner(vocab: int):
+    """``host_only_runner`` argument of :class:`FusedServingRank` for dry runs of the host protocol on CPU."""
+    return lambda role, srv: HostOnlyAttention(srv, vocab) if role == "attention" else HostOnlyExpert()
+
+
 # ------------------------------------------------------------------------------------------------ one rank of the job
 class FusedServingRank:
     """One process of the fused disaggregated serving job (see the module docstring for the roles)."""

@@ -294,3 +294,28 @@ def test_request_assignment_balances_groups_deterministically():
         work[owner[rid]] += len(prompt) + n_out
     assert max(work) / min(work) < 1.5                                  # total work stays roughly even too
     assert set(assign_requests(reqs, 1).values()) == {0}
+
+
+def test_serve_fused_script_host_only_dry_run(tmp_path):
+    """benchmark/serve_fused.py end to end as CPU processes (2 attention groups + 1 expert rank): workload, request
+    assignment, lock-step serving with chunked prefill, result collection, metrics file, Chrome trace."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out, trace = tmp_path / "m.jsonl", tmp_path / "t.json.gz"
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "3", "--master-addr",
+           "127.0.0.1", "--master-port", "29771", os.path.join(root, "benchmark", "serve_fused.py"), "--host-only",
+           "--model", "tiny", "--n-attn", "2", "-r", "300", "-n", "30", "--min-input-len", "5", "-i", "60",
+           "--min-output-len", "2", "-o", "9", "--max-seqs-per-mb", "4", "--max-tokens-per-mb", "48",
+           "--max-prefill-tokens-per-mb", "20", "--num-blocks", "256", "--time-limit", "60", "--check", "-f", str(out),
+           "--trace", str(trace)]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=240)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+    lines = [json.loads(l) for l in res.stdout.splitlines() if l.startswith("{")]
+    assert next(l for l in lines if "check_requests_exact" in l) == {"check_requests_exact": 30, "requests": 30}
+    info = next(l for l in lines if "iterations" in l)
+    assert info["requests_finished"] == 30 and info["kernel_status"] == 0
+    row = json.loads(out.read_text().strip().splitlines()[-1])
+    assert row["token_throughput"] > 0 and trace.exists()
