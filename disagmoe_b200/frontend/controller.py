@@ -49,16 +49,16 @@ def _worker_main(conn, device_id: int, device: str, env: Dict[str, str]) -> None
         pass
 
 
-class WorkerHandle:
-    """RPC stub of one worker process."""
+class ConnWorker:
+    """Method-call stub over a ``multiprocessing`` connection: one request in flight at a time (``call_async`` takes
+    the lock, ``wait`` returns it). Sub-classes say how the worker was started and how to tell whether it is alive."""
 
-    def __init__(self, device_id: int, device: str, env: Optional[Dict[str, str]] = None):
-        ctx = mp.get_context("spawn")
-        self.device_id = device_id
-        self.conn, child = ctx.Pipe()
-        self.proc = ctx.Process(target=_worker_main, args=(child, device_id, device, env or {}), daemon=True)
-        self.proc.start()
+    device_id: int
+
+    def _init_conn(self, conn) -> None:
+        self.conn = conn
         self.lock = threading.Lock()
+        self._dead = False
 
     def call_async(self, method: str, *args, **kwargs) -> None:
         self.lock.acquire()
@@ -66,6 +66,7 @@ class WorkerHandle:
             self.conn.send((method, args, kwargs))
         except (OSError, ValueError) as e:
             self.lock.release()
+            self._dead = True
             raise RuntimeError(f"worker {self.device_id} is gone: {e}")
 
     def wait(self, timeout: float = 300.0):
@@ -75,6 +76,7 @@ class WorkerHandle:
             try:
                 status, res = self.conn.recv()
             except (EOFError, OSError) as e:
+                self._dead = True
                 raise RuntimeError(f"worker {self.device_id} is gone: {e}")
         finally:
             self.lock.release()
@@ -86,10 +88,7 @@ class WorkerHandle:
         self.call_async(method, *args, **kwargs)
         return self.wait(timeout)
 
-    def alive(self) -> bool:
-        return self.proc.is_alive()
-
-    def stop(self) -> None:
+    def _send_stop(self) -> None:
         try:
             if self.lock.acquire(timeout=5):
                 try:
@@ -98,6 +97,24 @@ class WorkerHandle:
                     self.lock.release()
         except Exception:
             pass
+
+
+class WorkerHandle(ConnWorker):
+    """A worker process on this machine, reached through a pipe."""
+
+    def __init__(self, device_id: int, device: str, env: Optional[Dict[str, str]] = None):
+        ctx = mp.get_context("spawn")
+        self.device_id = device_id
+        conn, child = ctx.Pipe()
+        self.proc = ctx.Process(target=_worker_main, args=(child, device_id, device, env or {}), daemon=True)
+        self.proc.start()
+        self._init_conn(conn)
+
+    def alive(self) -> bool:
+        return self.proc.is_alive()
+
+    def stop(self) -> None:
+        self._send_stop()
         self.proc.join(timeout=10)
         if self.proc.is_alive():
             self.proc.terminate()

@@ -15,6 +15,8 @@ import threading
 from multiprocessing.connection import Client, Listener
 from typing import Dict, Optional, Tuple
 
+from .controller import ConnWorker
+
 DEFAULT_AUTHKEY = b"disagmoe_b200"
 
 
@@ -65,53 +67,24 @@ class NodeAgent:
                 p.terminate()
 
 
-class RemoteWorkerHandle:
-    """RPC stub of a worker hosted by a :class:`NodeAgent` (same interface as ``controller.WorkerHandle``)."""
+class RemoteWorkerHandle(ConnWorker):
+    """A worker hosted by a :class:`NodeAgent`, reached over TCP (same interface as ``controller.WorkerHandle``)."""
 
     def __init__(self, device_id: int, device: str, address: Tuple[str, int], env: Optional[Dict[str, str]] = None,
                  authkey: bytes = DEFAULT_AUTHKEY):
         self.device_id = device_id
         self.address = address
-        self.conn = Client(tuple(address), authkey=authkey)
-        self.conn.send((device_id, device, env or {}))
-        status, _ = self.conn.recv()
+        conn = Client(tuple(address), authkey=authkey)
+        conn.send((device_id, device, env or {}))
+        status, _ = conn.recv()
         assert status == "ok"
-        self.lock = threading.Lock()
-        self._dead = False
-
-    def call_async(self, method: str, *args, **kwargs) -> None:
-        self.lock.acquire()
-        try:
-            self.conn.send((method, args, kwargs))
-        except (OSError, ValueError) as e:
-            self.lock.release()
-            self._dead = True
-            raise RuntimeError(f"worker {self.device_id} is gone: {e}")
-
-    def wait(self, timeout: float = 300.0):
-        try:
-            if not self.conn.poll(timeout):
-                raise TimeoutError(f"worker {self.device_id} did not answer within {timeout} s")
-            try:
-                status, res = self.conn.recv()
-            except (EOFError, OSError) as e:
-                self._dead = True
-                raise RuntimeError(f"worker {self.device_id} is gone: {e}")
-        finally:
-            self.lock.release()
-        if status != "ok":
-            raise RuntimeError(f"worker {self.device_id} failed:\n{res}")
-        return res
-
-    def call(self, method: str, *args, timeout: float = 300.0, **kwargs):
-        self.call_async(method, *args, **kwargs)
-        return self.wait(timeout)
+        self._init_conn(conn)
 
     def alive(self) -> bool:
         if self._dead:
             return False
         try:
-            # a closed peer shows up as a readable connection that raises EOF on recv
+            # between two calls nothing is expected on the connection: readable + EOF means the peer closed it
             if self.lock.acquire(blocking=False):
                 try:
                     if self.conn.poll(0):
@@ -124,14 +97,7 @@ class RemoteWorkerHandle:
             return False
 
     def stop(self) -> None:
-        try:
-            if self.lock.acquire(timeout=5):
-                try:
-                    self.conn.send(None)
-                finally:
-                    self.lock.release()
-        except Exception:
-            pass
+        self._send_stop()
         try:
             self.conn.close()
         except Exception:
