@@ -84,8 +84,39 @@ class MixedBatchEngine(ColocatedEngine):
             n += 1
         return {r: s.outputs for r, s in self.sched.finished.items()}
 
+    # ---- serving-state snapshot ----------------------------------------------------------------------------------
     def save_state(self, path: str) -> None:
-        raise NotImplementedError("serving-state snapshots are implemented by ColocatedEngine")
+        """Request table (running sequences with their prefill progress, waiting and finished requests) and the KV
+        pages of every running sequence, taken between two steps. ``load_state`` on a fresh engine with the same weights
+        continues with identical tokens."""
+        import os
+        running = []
+        for s in self.sched.running[0].values():
+            blocks = self.block_mgr.get_seq_block_list(s.req_id)
+            pages = self.executor.kv_cache[:, :, torch.tensor(blocks, device=self.device)].cpu()
+            running.append(dict(req_id=s.req_id, prompt=s.prompt, max_new_tokens=s.max_new_tokens, length=s.length,
+                                last_token=s.last_token, outputs=list(s.outputs), t_arrival=s.t_arrival, pages=pages))
+        waiting = [dict(req_id=s.req_id, prompt=s.prompt, max_new_tokens=s.max_new_tokens, t_arrival=s.t_arrival)
+                   for s in self.sched.waiting]
+        finished = {r: list(s.outputs) for r, s in self.sched.finished.items()}
+        tmp = path + ".tmp"
+        torch.save(dict(running=running, waiting=waiting, finished=finished, block_size=self.block_size), tmp)
+        os.replace(tmp, path)
 
     def load_state(self, path: str) -> None:
-        raise NotImplementedError("serving-state snapshots are implemented by ColocatedEngine")
+        st = torch.load(path, map_location="cpu", weights_only=False)
+        assert st["block_size"] == self.block_size and self.sched.num_unfinished() == 0
+        for d in st["running"]:
+            s = ServeSeq(d["req_id"], d["prompt"], d["max_new_tokens"], d["t_arrival"], mb=0, length=d["length"],
+                         last_token=d["last_token"], outputs=list(d["outputs"]))
+            # the same reservation a fresh admission makes: room for the whole prompt, the rest grows step by step
+            self.block_mgr.allocate(s.req_id, max(len(s.prompt), s.length) + 1)
+            blocks = self.block_mgr.get_seq_block_list(s.req_id)
+            n = min(d["pages"].shape[2], len(blocks))
+            self.executor.kv_cache[:, :, torch.tensor(blocks[:n], device=self.device)] = d["pages"][:, :, :n].to(self.device)
+            self.sched.running[0][s.req_id] = s
+        for d in st["waiting"]:
+            self.sched.add_request(d["req_id"], d["prompt"], d["max_new_tokens"], d["t_arrival"])
+        for r, outs in st["finished"].items():
+            self.sched.finished[r] = ServeSeq(r, [], len(outs), 0.0, outputs=list(outs))
+        self._apply_block_table_patches()

@@ -76,3 +76,31 @@ def test_mixed_batch_engine_matches_alternating_engine():
     assert got == want
     assert saw_mixed, "the workload was meant to overlap a chunked prompt with running sequences"
     assert b.block_mgr.num_free_blocks() == a.block_mgr.num_free_blocks()
+
+
+def test_mixed_batch_engine_snapshot_resumes_with_identical_tokens(tmp_path):
+    """Snapshot in the middle of a chunked prefill and of decoding sequences; a fresh engine continues identically."""
+    import torch
+    from disagmoe_b200.config import CacheConfig, tiny_config
+    from disagmoe_b200.frontend.colocated_mixed import MixedBatchEngine
+    from disagmoe_b200.models.weights import init_state_dict
+    cfg = tiny_config.clone(dtype=torch.float32)
+    sd = init_state_dict(cfg)
+    g = torch.Generator().manual_seed(9)
+    reqs = [(i, torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist(), 7) for i, n in enumerate([6, 50, 9, 44])]
+    kw = dict(device="cpu", max_batch_size=4, max_prefill_tokens=64, num_blocks=96, enable_cuda_graph=False, state_dict=sd,
+              prefill_budget=16)
+    ref = MixedBatchEngine(cfg, CacheConfig(block_size=16), **kw)
+    a = MixedBatchEngine(cfg, CacheConfig(block_size=16), **kw)
+    for r in reqs:
+        ref.add_request(*r)
+        a.add_request(*r)
+    want = ref.run_until_done(500)
+    for _ in range(3):
+        a.step()
+    assert any(s.length < len(s.prompt) for s in a.sched.running[0].values()), "a prompt should be part-way through"
+    path = str(tmp_path / "state.pt")
+    a.save_state(path)
+    b = MixedBatchEngine(cfg, CacheConfig(block_size=16), **kw)
+    b.load_state(path)
+    assert b.run_until_done(500) == want
