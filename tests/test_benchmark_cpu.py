@@ -139,3 +139,20 @@ def test_worker_address_flag():
     from benchmark.benchmark_serving import parse_worker_addresses
     assert parse_worker_addresses("") == {}
     assert parse_worker_addresses("3=10.0.0.2:7700, 4=node-b:7701") == {3: ("10.0.0.2", 7700), 4: ("node-b", 7701)}
+
+
+def test_pipeline_model_regimes():
+    """The event model of the fused pipeline: the slower side sets the step, hops only matter when there is no slack,
+    and a single micro-batch serialises the two sides."""
+    from simulator.pipeline import simulate
+    kw = dict(experts=8, layers=32, jitter=0.0, head_us=0.0)
+    attn_bound = simulate(4, 4, micro_batches=2, attn_us=300, expert_us_per_expert=100, hop_us=5, **kw)     # experts 200 us
+    assert abs(attn_bound["step_ms"] - 64 * 0.300) < 0.5 and attn_bound["attention_busy"] > 0.97
+    exp_bound = simulate(2, 2, micro_batches=2, attn_us=200, expert_us_per_expert=100, hop_us=5, **kw)      # experts 400 us
+    assert abs(exp_bound["step_ms"] - 64 * 0.400) < 0.7 and exp_bound["expert_busy"] > 0.95
+    serial = simulate(4, 4, micro_batches=1, attn_us=300, expert_us_per_expert=100, hop_us=5, **kw)
+    assert abs(serial["step_ms"] - 32 * (0.300 + 0.200 + 0.010)) < 0.3
+    slow_hops = simulate(4, 4, micro_batches=2, attn_us=300, expert_us_per_expert=100, hop_us=80, **kw)
+    assert slow_hops["step_ms"] > attn_bound["step_ms"] + 1.0          # 200 + 2 x 80 > 300: the attention side now waits
+    uneven = simulate(5, 3, micro_batches=2, attn_us=300, expert_us_per_expert=100, hop_us=5, **kw)
+    assert uneven["experts_per_gpu_max"] == 3
