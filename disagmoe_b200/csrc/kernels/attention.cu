@@ -271,12 +271,12 @@ static int launch_attn(const void* q, long long ld_q, const void* kc, const void
   const size_t merge_b = static_cast<size_t>(kAttnWarps) * GQ * HD * sizeof(float);
   const size_t ring_b = static_cast<size_t>(kAttnWarps) * kAttnStages * 2 * kAttnStageTok * HD * 2;
   const size_t smem = merge_b > ring_b ? merge_b : ring_b;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(paged_attn_kernel<HD, GQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
-  }
+  static PerDeviceOnce configured;
+  const int crc = configured.run([] {
+    return static_cast<int>(cudaFuncSetAttribute(paged_attn_kernel<HD, GQ>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 160 * 1024));
+  });
+  if (crc != 0) return crc;
   dim3 grid(T, n_kv, splits);
   paged_attn_kernel<HD, GQ><<<grid, kAttnThreads, smem, stream>>>(
       static_cast<const __nv_bfloat16*>(q), ld_q, static_cast<const __nv_bfloat16*>(kc),

@@ -164,7 +164,7 @@ extern "C" int dmoe_dispatch_remote(const void* y, long long ld_y, const int* to
   a.tok_lo = tok_lo; a.tok_hi = tok_hi;
   const int npairs = (tok_hi - tok_lo) * K;
   int grid = (npairs + 7) / 8;
-  if (grid > 148 * 2) grid = 148 * 2;
+  if (grid > device_num_sms() * 2) grid = device_num_sms() * 2;
   if (grid < 1) grid = 1;   // an empty batch still publishes its flag
   reserve_kernel<<<(E + 63) / 64, 64, 0, static_cast<cudaStream_t>(stream)>>>(ws, E, experts_per_rank, a.cnt_bases,
                                                                                ws + 2 * E + 8);

@@ -24,6 +24,14 @@
 //     (every element that is read was written by the same call). Two calls that overlap on the GPU (different
 //     streams without an ordering between them) race on the array: serialise them.
 //   * No cudaMalloc, cudaFree, or allocating library routine (PyTorch's included) is called.
+//   * Host threads: the entry points may be called from several host threads (the per-device tables are guarded by a
+//     mutex and dmoe_noalloc_last_error() is per thread), but the GPU work of two calls must still not overlap.
+//   * dmoe_noalloc_last_status() reads the word on the stream that the last dmoe_linear_noalloc call on the current
+//     device was given and synchronises that stream, so it is ordered behind that call whatever kind of stream it is.
+//     Do not call it while that stream is being captured.
+//   * Every non-zero return fills dmoe_noalloc_last_error(). Besides the three codes below, a positive value is a
+//     cudaError_t and other negative values come from the GEMM's own argument checks (for example a tensor-map
+//     encoding that the driver refused).
 #pragma once
 
 #ifdef __cplusplus
@@ -36,12 +44,13 @@ extern "C" {
 #define DMOE_NOALLOC_E_BAD_ARG (-31)
 #define DMOE_NOALLOC_E_SETUP (-32)
 
-// W [F, K] bf16 K-contiguous, X [T, K] bf16 with row stride ldx elements (0 = K), Y [T, F] bf16 with row stride ldy
-// (0 = F). bn: token tile 32/64/128/256 (0 = pick); splitk >= 1 (0 = pick). Returns 0, a positive cudaError_t, or
+// W [F, K] bf16 K-contiguous and 16-byte aligned, X [T, K] bf16, 16-byte aligned, with row stride ldx elements
+// (0 = K; >= K and a multiple of 8), Y [T, F] bf16 with row stride ldy (0 = F; >= F). bn: token tile 32/64/128/256 (0 = pick); splitk >= 1 (0 = pick). Returns 0, a positive cudaError_t, or
 // one of the negative codes above.
 int dmoe_linear_noalloc(const void* W, const void* X, void* Y, int T, int F, int K, long long ldx, long long ldy,
                         int bn, int splitk, void* stream);
-// Blocking read of the status word the last call on the current device left (0 = every bounded wait completed).
+// Blocking read of the status word the last call on the current device left (0 = every bounded wait completed),
+// ordered behind that call on its stream.
 int dmoe_noalloc_last_status(int* status_out);
 const char* dmoe_noalloc_last_error(void);
 

@@ -270,7 +270,7 @@ extern "C" int dmoe_permute_rows(const void* src, long long ld_src, void* dst, l
                                  int H, int repeat, int gather, void* stream) {
   if (H % 8 != 0 || repeat < 1) return -10;
   if (n == 0) return 0;
-  const int grid = n < 148 * 16 ? n : 148 * 16;
+  const int grid = n < device_num_sms() * 16 ? n : device_num_sms() * 16;
   permute_rows_kernel<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(src), ld_src, static_cast<__nv_bfloat16*>(dst), ld_dst, map, n, H, repeat, gather);
   return static_cast<int>(cudaGetLastError());
@@ -279,7 +279,7 @@ extern "C" int dmoe_permute_rows(const void* src, long long ld_src, void* dst, l
 extern "C" int dmoe_gather_ptrs(const void* ptrs, void* dst, long long ld_dst, int n, int H, void* stream) {
   if (H % 8 != 0) return -10;
   if (n == 0) return 0;
-  const int grid = n < 148 * 16 ? n : 148 * 16;
+  const int grid = n < device_num_sms() * 16 ? n : device_num_sms() * 16;
   gather_ptrs_kernel<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16* const*>(ptrs), static_cast<__nv_bfloat16*>(dst), ld_dst, n, H);
   return static_cast<int>(cudaGetLastError());

@@ -594,28 +594,18 @@ static int make_map_2d(CUtensorMap* map, const void* ptr, long long rows, long l
   return r == CUDA_SUCCESS ? 0 : -2;
 }
 
-static int g_num_sms = 0;
-static int num_sms() {
-  if (g_num_sms == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
-    if (g_num_sms <= 0) g_num_sms = 148;
-  }
-  return g_num_sms;
-}
+static int num_sms() { return device_num_sms(); }
 
 template <int BN, int EPI>
 static int launch(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmArgs& a, int max_tiles,
                   cudaStream_t stream) {
   using C = Cfg<BN, EPI>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         C::kSmemBytes);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
-  }
+  static PerDeviceOnce configured;
+  const int crc = configured.run([] {
+    return static_cast<int>(cudaFuncSetAttribute(gemm_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 C::kSmemBytes));
+  });
+  if (crc != 0) return crc;
   int grid = num_sms();
   if (max_tiles < grid) grid = max_tiles;
   if (grid < 1) grid = 1;
@@ -731,6 +721,8 @@ extern "C" int dmoe_gemm(const DmoeGemm* d, void* stream_) {
 // Allocation-free entry point (see dmoe_noalloc.h): the split-K scratch is a file-scope device array.
 #include <stdio.h>
 
+#include <mutex>
+
 #include "dmoe_noalloc.h"
 
 constexpr long long kNoallocCounterBytes = DMOE_NOALLOC_MAX_TILES * 4ll;
@@ -740,22 +732,28 @@ static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoallocBytes];
 
 namespace {
 
-constexpr int kMaxDevices = 64;
+constexpr int kMaxDevices = kMaxDevicesPerProcess;
+std::mutex g_noalloc_mu;                                 // guards the two tables below
 unsigned char* g_noalloc_ptr[kMaxDevices] = {nullptr};   // device address of the array, per device
-char g_noalloc_error[256] = "";
+cudaStream_t g_noalloc_stream[kMaxDevices] = {nullptr};  // stream of the last call, per device
+thread_local char g_noalloc_error[256] = "";             // message of this thread's last failing call
+
+#define NOALLOC_FAIL(code, ...)                                          \
+  do {                                                                   \
+    snprintf(g_noalloc_error, sizeof(g_noalloc_error), __VA_ARGS__);     \
+    return (code);                                                       \
+  } while (0)
 
 // In host code `g_noalloc_scratch` is only a handle of the symbol, not a device address: the address a kernel may
 // use has to be asked for, once per device, with that device current.
 int noalloc_setup(int dev, unsigned char** out) {
-  if (dev < 0 || dev >= kMaxDevices) return DMOE_NOALLOC_E_SETUP;
+  if (dev < 0 || dev >= kMaxDevices) NOALLOC_FAIL(DMOE_NOALLOC_E_SETUP, "device index %d is out of range", dev);
+  std::lock_guard<std::mutex> lock(g_noalloc_mu);
   if (g_noalloc_ptr[dev] == nullptr) {
     void* p = nullptr;
     const cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
-    if (e != cudaSuccess || p == nullptr) {
-      snprintf(g_noalloc_error, sizeof(g_noalloc_error), "cudaGetSymbolAddress failed on device %d: %s", dev,
-               cudaGetErrorString(e));
-      return DMOE_NOALLOC_E_SETUP;
-    }
+    if (e != cudaSuccess || p == nullptr)
+      NOALLOC_FAIL(DMOE_NOALLOC_E_SETUP, "cudaGetSymbolAddress failed on device %d: %s", dev, cudaGetErrorString(e));
     g_noalloc_ptr[dev] = static_cast<unsigned char*>(p);
   }
   *out = g_noalloc_ptr[dev];
@@ -768,27 +766,32 @@ extern "C" const char* dmoe_noalloc_last_error(void) { return g_noalloc_error; }
 extern "C" int dmoe_linear_noalloc(const void* W, const void* X, void* Y, int T, int F, int K, long long ldx,
                                    long long ldy, int bn, int splitk, void* stream_) {
   g_noalloc_error[0] = 0;
-  if (W == nullptr || X == nullptr || Y == nullptr || T < 0 || F < 1 || K < 8 || K % 8 != 0) {
-    snprintf(g_noalloc_error, sizeof(g_noalloc_error), "bad argument (T=%d F=%d K=%d; K must be a multiple of 8)", T, F, K);
-    return DMOE_NOALLOC_E_BAD_ARG;
-  }
+  if (W == nullptr || X == nullptr || Y == nullptr || T < 0 || F < 1 || K < 8 || K % 8 != 0)
+    NOALLOC_FAIL(DMOE_NOALLOC_E_BAD_ARG, "bad argument (T=%d F=%d K=%d; K must be a multiple of 8)", T, F, K);
+  if (ldx <= 0) ldx = K;
+  if (ldy <= 0) ldy = F;
+  if (ldx < K || ldy < F || ldx % 8 != 0)
+    NOALLOC_FAIL(DMOE_NOALLOC_E_BAD_ARG, "bad row stride (ldx=%lld needs >= K=%d and a multiple of 8; ldy=%lld needs >= F=%d)",
+                 ldx, K, ldy, F);
+  if ((reinterpret_cast<uintptr_t>(W) & 15) != 0 || (reinterpret_cast<uintptr_t>(X) & 15) != 0)
+    NOALLOC_FAIL(DMOE_NOALLOC_E_BAD_ARG, "W and X must be 16-byte aligned (TMA)");
   if (T == 0) return 0;
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return DMOE_NOALLOC_E_SETUP;
+  if (cudaGetDevice(&dev) != cudaSuccess) NOALLOC_FAIL(DMOE_NOALLOC_E_SETUP, "cudaGetDevice failed");
   unsigned char* base = nullptr;
   const int rc = noalloc_setup(dev, &base);
   if (rc != 0) return rc;
   if (bn == 0) bn = dmoe_gemm_pick_bn(T, DMOE_EPI_PLAIN);
-  if (bn != 32 && bn != 64 && bn != 128 && bn != 256) {
-    snprintf(g_noalloc_error, sizeof(g_noalloc_error), "token tile %d is not one of 32/64/128/256", bn);
-    return DMOE_NOALLOC_E_BAD_ARG;
-  }
+  if (bn != 32 && bn != 64 && bn != 128 && bn != 256)
+    NOALLOC_FAIL(DMOE_NOALLOC_E_BAD_ARG, "token tile %d is not one of 32/64/128/256", bn);
+  if (splitk < 0) NOALLOC_FAIL(DMOE_NOALLOC_E_BAD_ARG, "splitk=%d is negative", splitk);
   const int kblocks = (K + 63) / 64;
   const long long tiles = static_cast<long long>((F + 127) / 128) * ((T + bn - 1) / bn);
   if (splitk == 0) {
     splitk = 1;
-    if (tiles < 74 && kblocks >= 8) {
-      splitk = static_cast<int>(148 / tiles);
+    const int sms = num_sms();
+    if (tiles < sms / 2 && kblocks >= 8) {
+      splitk = static_cast<int>(sms / tiles);
       if (splitk > kblocks / 4) splitk = kblocks / 4;
       if (splitk > 16) splitk = 16;
       if (splitk < 1) splitk = 1;
@@ -796,37 +799,53 @@ extern "C" int dmoe_linear_noalloc(const void* W, const void* X, void* Y, int T,
   }
   if (splitk > kblocks) splitk = kblocks;
   const long long need = dmoe_gemm_workspace_bytes(T, F, bn, splitk);
-  if (need > DMOE_NOALLOC_WS_BYTES || (splitk > 1 && tiles > DMOE_NOALLOC_MAX_TILES)) {
-    snprintf(g_noalloc_error, sizeof(g_noalloc_error),
-             "problem too large for the built-in scratch: T=%d F=%d tile=%d splitk=%d needs %lld bytes of partial tiles "
-             "and %lld counters; the limits are %lld bytes and %d counters",
-             T, F, bn, splitk, need, tiles, static_cast<long long>(DMOE_NOALLOC_WS_BYTES), DMOE_NOALLOC_MAX_TILES);
-    return DMOE_NOALLOC_E_TOO_LARGE;
-  }
+  if (need > DMOE_NOALLOC_WS_BYTES || (splitk > 1 && tiles > DMOE_NOALLOC_MAX_TILES))
+    NOALLOC_FAIL(DMOE_NOALLOC_E_TOO_LARGE,
+                 "problem too large for the built-in scratch: T=%d F=%d tile=%d splitk=%d needs %lld bytes of partial tiles "
+                 "and %lld counters; the limits are %lld bytes and %d counters",
+                 T, F, bn, splitk, need, tiles, static_cast<long long>(DMOE_NOALLOC_WS_BYTES), DMOE_NOALLOC_MAX_TILES);
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  {
+    std::lock_guard<std::mutex> lock(g_noalloc_mu);
+    g_noalloc_stream[dev] = stream;
+  }
   unsigned char* counters = base + DMOE_NOALLOC_WS_BYTES;
   // the counters and the status word must start at zero; the array keeps whatever the previous call left behind
   cudaError_t e = cudaMemsetAsync(counters, 0, static_cast<size_t>(kNoallocCounterBytes + 256), stream);
-  if (e != cudaSuccess) return static_cast<int>(e);
+  if (e != cudaSuccess) NOALLOC_FAIL(static_cast<int>(e), "cudaMemsetAsync of the counters failed: %s", cudaGetErrorString(e));
   DmoeGemm d;
   memset(&d, 0, sizeof(d));
   d.W = W; d.X = X; d.Y = Y;
   d.ws = base; d.ws_bytes = DMOE_NOALLOC_WS_BYTES;
   d.counters = reinterpret_cast<int*>(counters);
   d.status = reinterpret_cast<int*>(counters + kNoallocCounterBytes);
-  d.ldx = ldx > 0 ? ldx : K;
-  d.ldy = ldy > 0 ? ldy : F;
+  d.ldx = ldx;
+  d.ldy = ldy;
   d.G = 1; d.T = T; d.F = F; d.K = K;
   d.epi = DMOE_EPI_PLAIN; d.bn = bn; d.splitk = splitk; d.y_f32 = 0;
-  return dmoe_gemm(&d, stream_);
+  const int grc = dmoe_gemm(&d, stream_);
+  if (grc > 0) NOALLOC_FAIL(grc, "launch failed: %s", cudaGetErrorString(static_cast<cudaError_t>(grc)));
+  if (grc < 0) NOALLOC_FAIL(grc, "the GEMM rejected the problem with code %d (tensor-map encoding or argument check)", grc);
+  return 0;
 }
 
 extern "C" int dmoe_noalloc_last_status(int* status_out) {
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || status_out == nullptr) return DMOE_NOALLOC_E_SETUP;
+  if (cudaGetDevice(&dev) != cudaSuccess || status_out == nullptr)
+    NOALLOC_FAIL(DMOE_NOALLOC_E_SETUP, "cudaGetDevice failed or status_out is NULL");
   unsigned char* base = nullptr;
   const int rc = noalloc_setup(dev, &base);
   if (rc != 0) return rc;
-  return static_cast<int>(cudaMemcpy(status_out, base + DMOE_NOALLOC_WS_BYTES + kNoallocCounterBytes, sizeof(int),
-                                     cudaMemcpyDeviceToHost));
+  cudaStream_t stream;
+  {
+    std::lock_guard<std::mutex> lock(g_noalloc_mu);
+    stream = g_noalloc_stream[dev];
+  }
+  // read on the stream of the last call, behind its memset and kernel: a copy on the legacy default stream would not
+  // be ordered behind work on a non-blocking or per-thread stream
+  cudaError_t e = cudaMemcpyAsync(status_out, base + DMOE_NOALLOC_WS_BYTES + kNoallocCounterBytes, sizeof(int),
+                                  cudaMemcpyDeviceToHost, stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+  if (e != cudaSuccess) NOALLOC_FAIL(static_cast<int>(e), "status read failed: %s", cudaGetErrorString(e));
+  return 0;
 }

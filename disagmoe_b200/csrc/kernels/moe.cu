@@ -276,16 +276,20 @@ dispatch_kernel(const __nv_bfloat16* __restrict__ y, long long ld_y, const int* 
 
 using namespace dmoe;
 
+// route_kernel keeps one fp32 row in dynamic shared memory (up to 32 KB): opt in once per device.
+static int configure_route() {
+  static PerDeviceOnce once;
+  return once.run([] {
+    return static_cast<int>(cudaFuncSetAttribute(route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 8192 * 4));
+  });
+}
+
 extern "C" int dmoe_route(const void* x, long long ld_x, const void* norm_w, float eps, const void* gate_w, int T, int H,
                           int E, int K, int renorm, void* y, long long ld_y, int* topk_ids, float* topk_w,
                           float* logits_out, int* counts, const float* logit_bias, void* stream) {
   if (H % 8 != 0 || H > kRouteThreads * kRouteMaxVec * 8 || E > kMaxExperts || K > kMaxTopK || K > E) return -10;
   if (T == 0) return 0;
-  static bool configured = false;
-  if (!configured) {
-    cudaFuncSetAttribute(route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 8192 * 4);
-    configured = true;
-  }
+  if (const int rc = configure_route()) return rc;
   route_kernel<<<T, kRouteThreads, H * sizeof(float), static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), ld_x, static_cast<const __nv_bfloat16*>(norm_w), eps,
       static_cast<const __nv_bfloat16*>(gate_w), H, E, K, renorm, static_cast<__nv_bfloat16*>(y), ld_y, topk_ids, topk_w,
@@ -304,7 +308,7 @@ extern "C" int dmoe_route_ex(const void* x, long long ld_x, const void* norm_w, 
   if (H % 8 != 0 || H > kRouteThreads * kRouteMaxVec * 8) return -10;
   if (gate_w != nullptr && (E > kMaxExperts || K > kMaxTopK || K > E)) return -10;
   if (T == 0) return 0;
-  cudaFuncSetAttribute(route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 8192 * 4);
+  if (const int rc = configure_route()) return rc;
   route_kernel<<<T, kRouteThreads, H * sizeof(float), static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), ld_x, static_cast<const __nv_bfloat16*>(norm_w), eps,
       static_cast<const __nv_bfloat16*>(gate_w), H, E, K, renorm, static_cast<__nv_bfloat16*>(y), ld_y, topk_ids, topk_w,
@@ -321,7 +325,7 @@ extern "C" int dmoe_dispatch_local(const void* y, long long ld_y, const int* top
   if (T == 0) return 0;
   const int npairs = T * K;
   int grid = (npairs + 7) / 8;
-  if (grid > 148 * 4) grid = 148 * 4;
+  if (grid > device_num_sms() * 4) grid = device_num_sms() * 4;
   dispatch_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(y), ld_y, topk_ids, topk_w, T, K, H, E, experts_per_rank, my_rank, ws, offs,
       static_cast<void* const*>(x_bases), ld_dst, static_cast<void* const*>(rec_bases), dst_capacity, status);

@@ -183,6 +183,37 @@ __host__ __device__ constexpr uint32_t umma_idesc_bf16(int M, int N) {
          (static_cast<uint32_t>(M >> 4) << 24);
 }
 
+// ---------------------------------------------------------------- host helpers
+// cudaFuncSetAttribute applies to the current device only, so "already configured" has to be remembered per
+// device: one process may drive several GPUs.
+constexpr int kMaxDevicesPerProcess = 64;
+struct PerDeviceOnce {
+  bool done[kMaxDevicesPerProcess] = {};
+  // Runs fn() the first time it is called with each device current; returns fn's error code or 0.
+  template <typename Fn>
+  int run(Fn fn) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevicesPerProcess) return fn();
+    if (done[dev]) return 0;
+    const int rc = fn();
+    if (rc == 0) done[dev] = true;
+    return rc;
+  }
+};
+
+// Number of SMs of the current device (cached per device).
+inline int device_num_sms() {
+  static int cache[kMaxDevicesPerProcess] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevicesPerProcess) return 148;
+  if (cache[dev] == 0) {
+    int n = 0;
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    cache[dev] = n > 0 ? n : 148;
+  }
+  return cache[dev];
+}
+
 // ---------------------------------------------------------------- misc
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");

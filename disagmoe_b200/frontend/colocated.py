@@ -224,7 +224,7 @@ class ColocatedEngine:
         os.replace(tmp, path)
 
     def load_state(self, path: str) -> None:
-        st = torch.load(path, map_location="cpu", weights_only=False)
+        st = torch.load(path, map_location="cpu", weights_only=True)   # plain containers + tensors only
         assert st["block_size"] == self.block_size and not self.running and not self.waiting
         for d in st["running"]:
             s = _Seq(d["req_id"], d["prompt"], d["max_new_tokens"], length=d["length"], last_token=d["last_token"],

@@ -104,7 +104,7 @@ class MixedBatchEngine(ColocatedEngine):
         os.replace(tmp, path)
 
     def load_state(self, path: str) -> None:
-        st = torch.load(path, map_location="cpu", weights_only=False)
+        st = torch.load(path, map_location="cpu", weights_only=True)   # plain containers + tensors only
         assert st["block_size"] == self.block_size and self.sched.num_unfinished() == 0
         for d in st["running"]:
             s = ServeSeq(d["req_id"], d["prompt"], d["max_new_tokens"], d["t_arrival"], mb=0, length=d["length"],

@@ -45,17 +45,17 @@ class MoEExperts(torch.nn.Module):
         self.w2_weight = w2.to(device=self.device, dtype=self.dtype).contiguous()
 
     def init_weights(self) -> None:
-        """Seeded random weights drawn directly in the runtime layout on the target device, expert by expert
-        (no checkpoint-layout copy of a multi-GB tensor is ever made)."""
+        """Seeded random weights created on the target device expert by expert (no copy of the multi-GB stacked
+        tensor is ever made) and transposed into the runtime layout. The values equal
+        ``load_weights(init_state_dict(cfg))`` for a state dict drawn on the same kind of device."""
         cfg, H, I = self.cfg, self.hidden_size, self.intermediate_size
         E = self.num_experts
         self.w13_weight = torch.empty(E, 2 * I, H, dtype=self.dtype, device=self.device)
         self.w2_weight = torch.empty(E, H, I, dtype=self.dtype, device=self.device)
         for i, e in enumerate(range(self.e_lo, self.e_hi)):
-            n13 = f"layers.{self.layer_id}.experts.w13_weight.{e}"
-            n2 = f"layers.{self.layer_id}.experts.w2_weight.{e}"
-            self.w13_weight[i] = W.init_tensor(cfg, n13, (2 * I, H), self.device, self.dtype)
-            self.w2_weight[i] = W.init_tensor(cfg, n2, (H, I), self.device, self.dtype)
+            w13, w2 = W.init_expert(cfg, self.layer_id, e, self.device, self.dtype)
+            self.w13_weight[i].copy_(w13.T)
+            self.w2_weight[i].copy_(w2.T)
 
     def forward(self, bs: int, hiddens: torch.Tensor, offs: torch.Tensor, out: Optional[torch.Tensor] = None
                 ) -> torch.Tensor:

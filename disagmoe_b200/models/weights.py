@@ -68,18 +68,36 @@ def _name_seed(seed: int, name: str) -> int:
     return (h ^ (seed * 0x9E3779B97F4A7C15)) & 0x7FFFFFFFFFFFFFFF
 
 
+def is_expert_stack(name: str) -> bool:
+    return name.endswith(".experts.w13_weight") or name.endswith(".experts.w2_weight")
+
+
 def init_tensor(cfg: ModelConfig, name: str, shape: Tuple[int, ...], device="cpu", dtype=None) -> torch.Tensor:
     """One parameter, N(0, init_std) (norm weights = 1), drawn from a generator seeded by (cfg.seed, name): the
     value of a tensor does not depend on which other tensors a process creates, so every worker can materialise
-    only its shard's names and still agree with a single-process model."""
+    only its shard's names and still agree with a single-process model. The stacked expert tensors are drawn expert
+    by expert from (cfg.seed, name + "." + expert index), so an expert-parallel worker that creates only its own
+    experts (:func:`init_expert`) gets exactly the slices of the full tensor. Draws on a CUDA device come from a
+    different generator than CPU draws: compare models initialised on the same kind of device."""
     dtype = dtype or cfg.dtype
     if name.endswith("layernorm.weight") or name == "norm.weight":
         return torch.ones(shape, dtype=dtype, device=device)
+    if is_expert_stack(name) and len(shape) == 3:
+        return torch.stack([init_tensor(cfg, f"{name}.{e}", tuple(shape[1:]), device, dtype) for e in range(shape[0])])
     gen = torch.Generator(device=device)
     gen.manual_seed(_name_seed(cfg.seed, name))
     t = torch.empty(shape, dtype=torch.float32 if torch.device(device).type == "cpu" else dtype, device=device)
     t.normal_(0.0, cfg.init_std, generator=gen)
     return t.to(dtype)
+
+
+def init_expert(cfg: ModelConfig, layer_id: int, e: int, device="cpu", dtype=None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Checkpoint-layout (w13 [H, 2I], w2 [I, H]) weights of global expert ``e`` of layer ``layer_id``: the same values
+    as ``init_state_dict(cfg)["layers.<l>.experts.w13_weight"][e]`` / ``w2_weight[e]`` on the same kind of device."""
+    p = f"layers.{layer_id}.experts."
+    H, I = cfg.hidden_size, cfg.intermediate_size
+    return (init_tensor(cfg, f"{p}w13_weight.{e}", (H, 2 * I), device, dtype),
+            init_tensor(cfg, f"{p}w2_weight.{e}", (I, H), device, dtype))
 
 
 def init_state_dict(cfg: ModelConfig, device="cpu", dtype=None, names: Optional[Iterable[str]] = None) -> StateDict:

@@ -84,10 +84,12 @@ def rope_kv_append(qkv: torch.Tensor, positions: torch.Tensor, slots: Optional[t
 
 
 def pick_attn_splits(T: int, n_kv: int, max_ctx: int, block_size: int) -> int:
+    from .gemm import num_sms
+    sms = num_sms()
     ctas = max(1, T * n_kv)
-    if ctas >= 2 * 148 or max_ctx <= 256:
+    if ctas >= 2 * sms or max_ctx <= 256:
         return 1
-    want = (4 * 148 + ctas - 1) // ctas
+    want = (4 * sms + ctas - 1) // ctas
     return max(1, min(want, (max_ctx + 255) // 256, 64))
 
 

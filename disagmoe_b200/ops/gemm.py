@@ -19,7 +19,17 @@ import torch
 from . import _lib
 
 EPI_PLAIN, EPI_SWIGLU, EPI_COMBINE = 0, 1, 2
-_NUM_SMS = 148
+_num_sms_cache = {}
+
+
+def num_sms(device=None) -> int:
+    """SM count of a CUDA device (read once per device)."""
+    idx = torch.device(device).index if device is not None else None
+    if idx is None:
+        idx = torch.cuda.current_device() if torch.cuda.is_available() else -1
+    if idx not in _num_sms_cache:
+        _num_sms_cache[idx] = torch.cuda.get_device_properties(idx).multi_processor_count if idx >= 0 else 148
+    return _num_sms_cache[idx]
 
 
 class _Scratch:
@@ -55,14 +65,15 @@ def check_status(device=None) -> int:
     return v
 
 
-def pick_splitk(T: int, F: int, K: int, bn: int) -> int:
-    """Split-K factor of a dense GEMM: enough (tile, split) work items to occupy most of the 148 SMs when the output
+def pick_splitk(T: int, F: int, K: int, bn: int, sms: int = 0) -> int:
+    """Split-K factor of a dense GEMM: enough (tile, split) work items to occupy most of the SMs when the output
     has few tiles (decode-size token counts), never more than one split per 4 K-blocks."""
+    sms = sms or num_sms()
     tiles = ((F + 127) // 128) * ((T + bn - 1) // bn)
     kblocks = (K + 63) // 64
-    if tiles >= 80 or kblocks < 8:
+    if tiles >= sms * 80 // 148 or kblocks < 8:
         return 1
-    return max(1, min((128 + tiles // 2) // tiles, kblocks // 4, 16))
+    return max(1, min((sms * 128 // 148 + tiles // 2) // tiles, kblocks // 4, 16))
 
 
 def pick_bn(tokens_per_group: int, epi: int) -> int:
@@ -157,9 +168,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor] = 
         return out
     if not bn:
         bn = pick_bn(T, EPI_PLAIN)
-        if bn == 256 and ((F + 127) // 128) * ((T + 255) // 256) < 74:
+        if bn == 256 and ((F + 127) // 128) * ((T + 255) // 256) < num_sms(x.device) // 2:
             bn = 128     # too few 256-wide tiles to fill the GPU: halve the tile instead of splitting K further
-    splitk = splitk or pick_splitk(T, F, K, bn)
+    splitk = splitk or pick_splitk(T, F, K, bn, num_sms(x.device))
     _launch(w, x, out, residual, None, None, None, 1, T, F, K, EPI_PLAIN, bn, splitk, out.stride(0),
             out.dtype == torch.float32, comm)
     return out

@@ -87,3 +87,20 @@ def test_trace_weighted_router_file(tmp_path, monkeypatch):
     assert hist[1] >= 190 and hist[E - 1] >= 150                       # the gate decides, heavily skewed
     monkeypatch.delenv("DMOE_WEIGHTED_ROUTER_FILE")
     assert MoEAttention(tiny_config, 1).weighted_router is None
+
+
+def test_expert_shard_init_equals_slices_of_the_full_state_dict():
+    """An expert-parallel worker started without a state dict draws only its own experts; they must be the
+    transposed slices of the tensors a single-process model (or the oracle) is initialised with."""
+    import torch
+    from disagmoe_b200.config import tiny_config
+    from disagmoe_b200.models import weights as W
+    from disagmoe_b200.models.experts import MoEExperts
+    cfg = tiny_config.clone(dtype=torch.float32)
+    sd = W.init_state_dict(cfg)
+    for lo, hi in [(0, cfg.num_experts), (2, 5)]:
+        a = MoEExperts(cfg, 1, lo, hi)
+        a.init_weights()
+        b = MoEExperts(cfg, 1, lo, hi)
+        b.load_weights(sd)
+        assert torch.equal(a.w13_weight, b.w13_weight) and torch.equal(a.w2_weight, b.w2_weight)
