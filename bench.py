@@ -8,9 +8,13 @@ requests) on N GPUs of one node.
 
 A "step" is one decode iteration: every running sequence gets one new token through all 32 layers (attention on
 the attention GPUs, routed experts on the expert GPUs), the LM head and greedy sampling. N = 1 runs the colocated
-engine; N = 2/4/8 run N/2 attention GPUs (data-parallel replicas) + N/2 expert GPUs (expert parallel) with the fused
-peer-memory dispatch/combine kernels. Per-GPU work is fixed as N grows (weak scaling): every attention GPU holds
-``--batch`` sequences.
+engine; N = 2/4/8 run N/2 attention GPUs, by default as ONE tensor-parallel group (N = 8: 4 attention GPUs with TP 4 +
+4 expert GPUs with 2 experts each; ``--attn-tp 1`` makes them data-parallel replicas instead), + N/2 expert GPUs
+(expert parallel) with the fused peer-memory dispatch / combine / all-gather / reduce-scatter kernels. Per-GPU work is
+fixed as N grows (weak scaling): ``--batch`` sequences per attention GPU and micro-batch.
+
+``--impl baseline`` runs the reference-style restatement (NCCL + library kernels, benchmark/reference_style.py) on the
+same shapes; its recorded numbers (baseline/reference_style_measured.json) are what ``vs_baseline`` divides by.
 
 Timing: CUDA events on the launching stream, max over ranks. ``value`` counts the device time of the steps (input
 copy + kernels + result copy); ``e2e`` is the same K steps through the public engine API including the host-side
@@ -90,21 +94,48 @@ def reference_arm(args):
     return 0
 
 
+BASELINE_FILE = os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline", "reference_style_measured.json")
+
+
+def baseline_number(n_gpus: int, model: str):
+    """tokens/s of the reference-style baseline (``--impl baseline``) recorded for this GPU count, or None."""
+    try:
+        with open(BASELINE_FILE) as f:
+            return float(json.load(f)[model][str(n_gpus)]["value"])
+    except Exception:
+        return None
+
+
+def percentile(xs, q):
+    xs = sorted(xs)
+    if not xs:
+        return None
+    i = min(len(xs) - 1, max(0, int(round(q * (len(xs) - 1)))))
+    return xs[i]
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "baseline"],
+                    help="ours: this package's engine; baseline: the reference-style restatement with NCCL and library "
+                         "kernels (benchmark/reference_style.py); reference: the unmodified reference (unavailable here)")
     ap.add_argument("--batch", type=int, default=256, help="decode sequences per attention GPU")
     ap.add_argument("--ctx-min", type=int, default=192)
     ap.add_argument("--ctx-max", type=int, default=1536)
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (the result is then marked invalid)")
     ap.add_argument("--model", default="mixtral")
-    ap.add_argument("--attn-tp", type=int, default=1, help="tensor-parallel degree of the attention GPUs (N >= 4)")
+    ap.add_argument("--attn-tp", type=int, default=0,
+                    help="tensor-parallel degree of the attention GPUs; 0 = all attention GPUs form one TP group (the "
+                         "layout of the headline configuration: 4 attention GPUs TP4 + 4 expert GPUs at N = 8); 1 = "
+                         "data-parallel attention replicas")
     ap.add_argument("--n-attn", type=int, default=0, help="attention GPUs out of N (default N/2); the rest hold experts")
+    ap.add_argument("--micro-batches", type=int, default=2)
     ap.add_argument("--route-skew", type=float, default=0.0,
                     help="Zipf exponent of a synthetic expert-popularity skew added to the router logits (0 = none)")
+    ap.add_argument("--no-selfcheck", action="store_true", help="skip the tiny-model correctness run at N >= 2")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -127,12 +158,26 @@ def main():
     cfg.max_seq_len = max(4096, (args.ctx_max + K + W + 2 + 15) // 16 * 16)
     g = torch.Generator().manual_seed(1234 + rank)
     B = args.batch
+    selfcheck = None
+    ours = args.impl == "ours"
 
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-        from disagmoe_b200.parallel.disagg import DisaggDecodeBench
-        runner = DisaggDecodeBench(cfg, world, rank, local_rank, B, args.ctx_min, args.ctx_max, K + W, g, tp=args.attn_tp,
-                                   n_attn=args.n_attn, route_skew=args.route_skew)
+    if not ours:
+        from benchmark.reference_style import ReferenceStyleDecode
+        runner = ReferenceStyleDecode(cfg, world, rank, local_rank, B, args.ctx_min, args.ctx_max, K + W, g)
+        par = [runner.parallelism if rank == 0 else None]
+        parallelism = par[0]
+    elif world > 1:
+        from disagmoe_b200.parallel.disagg import DisaggDecodeBench, selfcheck_against_colocated
+        A = args.n_attn or world // 2
+        tp = args.attn_tp or A
+        while A % tp or cfg.num_heads % tp:
+            tp -= 1
+        if not args.no_selfcheck:
+            selfcheck = selfcheck_against_colocated(world, rank, local_rank, A, tp, args.micro_batches)
+        runner = DisaggDecodeBench(cfg, world, rank, local_rank, B, args.ctx_min, args.ctx_max, K + W, g, tp=tp,
+                                   n_attn=A, route_skew=args.route_skew, n_mb=args.micro_batches)
         parallelism = runner.parallelism
     else:
         from disagmoe_b200.frontend.colocated import ColocatedEngine
@@ -178,19 +223,24 @@ def main():
     sync_all()
     clocks = sampler.stop()
     e2e_ms = t_start.elapsed_time(t_end)
-    dev_ms = sum(a.elapsed_time(b) for a, b in runner.event_pairs)
+    step_ms = [a.elapsed_time(b) for a, b in runner.event_pairs]
+    dev_ms = sum(step_ms)
     launches = (runner.launch_count() - launches0) if hasattr(runner, "launch_count") else 0
 
     tokens_local = runner.tokens_per_step() if hasattr(runner, "tokens_per_step") else B
-    from disagmoe_b200.ops import gemm as _gemm
-    kstatus = _gemm.check_status(torch.device("cuda", local_rank))   # non-zero: a bounded device wait gave up
+    kstatus = 0
+    if ours:
+        from disagmoe_b200.ops import gemm as _gemm
+        kstatus = _gemm.check_status(torch.device("cuda", local_rank))   # non-zero: a bounded device wait gave up
     t = torch.tensor([dev_ms, e2e_ms, float(tokens_local), float(launches), float(h2d), float(d2h), float(kstatus)],
                      device="cuda", dtype=torch.float64)
+    steps_t = torch.tensor(step_ms, device="cuda", dtype=torch.float64)
     if world > 1:
         mx = t.clone()
         dist.all_reduce(mx, op=dist.ReduceOp.MAX)
         sm = t.clone()
         dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        dist.all_reduce(steps_t, op=dist.ReduceOp.MAX)      # per step: the slowest rank
         dev_ms, e2e_ms, kstatus = float(mx[0]), float(mx[1]), int(mx[6])
         tokens_step, launches, h2d, d2h = float(sm[2]), int(sm[3]), float(sm[4]), float(sm[5])
     else:
@@ -198,21 +248,43 @@ def main():
     value = tokens_step * K / (dev_ms / 1e3)
     e2e = tokens_step * K / (e2e_ms / 1e3)
     if rank == 0:
+        # a decode step gives every running sequence one token, so the time per output token of a sequence is the step time
+        per_step = steps_t.tolist()
+        base = baseline_number(world, cfg.name) if ours and not args.layers else None
+        mhz, mhz_max = clocks.get("sm_mhz"), clocks.get("sm_max_mhz")
         out = {
             "metric": METRIC, "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
-            "ms_per_step": round(dev_ms / K, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "ms_per_step": round(dev_ms / K, 3), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": round(e2e / base, 3) if base else None,
             "dtype": "bf16", "data": "synthetic (random-init weights, random token ids, randn KV history)",
-            "impl": "ours",
+            "impl": args.impl,
             "config": {"model": cfg.name + ("" if not args.layers else f" TRUNCATED to {args.layers} layers (invalid)"),
                        "global_batch": int(tokens_step), "seq_len": f"context uniform[{args.ctx_min},{args.ctx_max}]",
                        "parallelism": parallelism, "kv_block_size": 16,
                        "l2": "no flush: every step streams all expert weights (>> 126 MB L2)"},
             "clocks": clocks,
+            "tpot_ms": {"p50": round(percentile(per_step, 0.5), 3), "p99": round(percentile(per_step, 0.99), 3),
+                        "max": round(max(per_step), 3), "how": "device time of each decode step, max over ranks"},
             "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms / K, 3),
                     "h2d_bytes_per_step": int(h2d / K), "d2h_bytes_per_step": int(d2h / K)},
             "gpu_launches": int(launches),
             "kernel_status": int(kstatus),
         }
+        if mhz and mhz_max:
+            # the same work at the clock the GPU could not hold: value scaled by median / max SM clock, and the step in
+            # millions of SM cycles (a clock-independent figure for compute-bound parts)
+            out["clock_normalised"] = {"value_x_mhz_over_max": round(value * mhz / mhz_max, 1),
+                                       "mcycles_per_step": round(dev_ms / K * mhz / 1e3, 2)}
+        if base:
+            out["baseline"] = {"what": "reference-style baseline (ours): bench.py --impl baseline, e2e tokens/s measured "
+                                       "on this pool, recorded in baseline/reference_style_measured.json",
+                               "value": base, "vs_baseline_is": "e2e.value / baseline value"}
+        if selfcheck is not None:
+            out["selfcheck"] = selfcheck
+        if not ours:
+            out["gpu_launches"] = 0
+            out["note"] = "library kernels only (cuBLAS, torch._grouped_mm, library attention, NCCL): none of this package's kernels"
+            out.pop("kernel_status")
         if kstatus != 0:
             out["invalid"] = "a device-side wait timed out (kernel status %d): results are not valid" % kstatus
         print(json.dumps(out))

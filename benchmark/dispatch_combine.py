@@ -8,9 +8,10 @@ router top-k -> dispatch -> expert GEMM-1 + SwiGLU -> GEMM-2 -> weighted combine
 ``--tokens`` is per attention GPU. Ranks [0, A) are attention GPUs, ranks [A, N) expert GPUs (N - A must divide 8).
 
 Variants:
-  fused   peer-memory kernels of this package: route_kernel, dispatch_remote_kernel (remote stores + records + counts +
-          release flag), gated multi-source grouped tcgen05 GEMM-1, GEMM-2 with the combine epilogue (remote stores into
-          the owner's partial buffer + completion flag), bounded flag wait + fused add/RMSNorm at the consumer.
+  fused   peer-memory kernels of this package: route_dispatch_kernel (norm + gate + top-k + row reservation + remote
+          stores + records + release flag in one launch), gated grouped tcgen05 GEMM-1, GEMM-2 with the combine
+          epilogue (remote stores into the owner's partial buffer + completion flag), and norm_gather_kernel (bounded
+          flag wait + add + RMSNorm in one launch) at the consumer: 4 launches per round trip.
   nccl    the reference-style path restated with library pieces: torch.topk, argsort + row permute, NCCL all-to-all of
           counts and rows (rows + metadata), torch._grouped_mm / SiLU-mul / torch._grouped_mm, NCCL all-to-all back,
           un-permute + weighted sum.
@@ -56,33 +57,33 @@ def load_peaks():
 
 
 class FusedAttnSide:
-    """Router + dispatch + (wait, add + RMSNorm) of one attention GPU, on the package's kernels."""
+    """Router + dispatch (one kernel) and wait + add + RMSNorm (one kernel) of one attention GPU."""
 
     def __init__(self, cfg, shape, arena, layout, a, x, gate_w, norm_w):
         self.cfg, self.S, self.a, self.x, self.gate_w, self.norm_w = cfg, shape, a, x, gate_w, norm_w
         dev = x.device
         z = lambda *s: torch.zeros(*s, dtype=torch.int32, device=dev)
         ex = [shape.n_attn + i for i in range(shape.n_expert)]
-        self.ws, self.disp_epoch, self.wait_epoch = z(3 * cfg.num_experts + 8), z(1), z(1)
+        self.disp_epoch, self.wait_epoch, self.ticket = z(1), z(1), z(1)
         self.parts = arena.view(layout.offset("parts0"), (shape.batch, cfg.top_k, cfg.hidden_size), torch.bfloat16)
         self.comb_flag = arena.view(layout.offset("comb_flag0"), (shape.n_expert,), torch.int32)
         self.tables = [arena.ptr_table(ex, layout.offset(n)) for n in ("recv_rows0", "recv_recs0", "recv_cnt0", "disp_flag0")]
         self.status = gemm.scratch(dev).status
+        self.resid = x.clone()
         self.y = torch.empty_like(x)
         self.out = torch.empty_like(x)
+        self.y_ptr = torch.tensor([self.y.data_ptr()], dtype=torch.int64, device=dev)
 
     def run(self):
         cfg, S = self.cfg, self.S
-        y, ids, w, _ = F.route(self.x, self.norm_w, 1e-5, self.gate_w, cfg.top_k, True, y=self.y, counts=self.ws[:cfg.num_experts])
-        _lib.check(_lib.lib().dmoe_dispatch_remote(
-            _vp(y), c_ll(y.stride(0)), _vp(ids), _vp(w), c_int(S.batch), c_int(cfg.top_k), c_int(cfg.hidden_size),
-            c_int(cfg.num_experts), c_int(S.experts_per_rank), c_int(S.n_expert), c_int(self.a), c_int(S.region_cap),
-            _vp(self.ws), _vp(self.tables[0]), c_ll(cfg.hidden_size), _vp(self.tables[1]), _vp(self.tables[2]),
-            _vp(self.tables[3]), _vp(self.disp_epoch), _vp(self.status), c_int(0), c_int(S.batch), c_vp(_lib.stream_ptr())),
-            "dispatch_remote")
-        _lib.check(_lib.lib().dmoe_wait_flags(_vp(self.comb_flag), c_int(S.n_expert), _vp(self.wait_epoch),
-                                              _vp(self.status), c_vp(_lib.stream_ptr())), "wait_flags")
-        F.add_rmsnorm(self.x, self.parts, self.norm_w, 1e-5, resid_out=self.out, y=self.y)
+        H = cfg.hidden_size
+        F.route_dispatch(self.resid, self.norm_w, 1e-5, self.gate_w, cfg.top_k, True, S.batch, x_bases=self.tables[0],
+                         rec_bases=self.tables[1], cnt_bases=self.tables[2], flag_bases=self.tables[3], ld_dst=H,
+                         experts_per_rank=S.experts_per_rank, n_dst=S.n_expert, my_rank=self.a,
+                         region_cap=S.region_cap, disp_epoch=self.disp_epoch, ticket=self.ticket, status=self.status)
+        F.norm_gather(self.x, self.parts, self.norm_w, 1e-5, self.out, self.y_ptr, 1, 0, H, S.batch, H,
+                      wait_flags=self.comb_flag, n_wait=S.n_expert, wait_epoch=self.wait_epoch, ticket=self.ticket,
+                      status=self.status)
         return self.out
 
 

@@ -172,16 +172,19 @@ extern "C" int dmoe_dispatch_remote(const void* y, long long ld_y, const int* to
   return static_cast<int>(cudaGetLastError());
 }
 
-static long long g_flag_wait_cycles = 4 * DMOE_WAIT_CYCLES;
+// Cycle budget of every peer-flag wait of the library (wait_flags, the GEMM's arrival gates, the sender kernels);
+// kernels launched later use the new value. <= 0 restores the default of about 4 s.
+namespace dmoe {
+long long g_dmoe_flag_wait_cycles = 4 * DMOE_WAIT_CYCLES;
+}
 
-// Cycle budget of every later flag wait launched through dmoe_wait_flags (<= 0 restores the default of ~4 s).
 extern "C" void dmoe_set_flag_wait_cycles(long long cycles) {
-  g_flag_wait_cycles = cycles > 0 ? cycles : 4 * DMOE_WAIT_CYCLES;
+  g_dmoe_flag_wait_cycles = cycles > 0 ? cycles : 4 * DMOE_WAIT_CYCLES;
 }
 
 extern "C" int dmoe_wait_flags(const int* flags, int n, int* epoch, int* status, void* stream) {
   if (n < 0 || n > 256 || epoch == nullptr) return -10;
-  wait_flags_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(flags, n, epoch, status, g_flag_wait_cycles);
+  wait_flags_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(flags, n, epoch, status, g_dmoe_flag_wait_cycles);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -41,6 +41,23 @@ typedef struct DmoeGemm {
   int bn;             // token tile: 32/64/128/256, 0 = pick from T/G
   int splitk;         // >= 1; > 1 only for dense plain / combine GEMMs
   int y_f32;
+  // --- tensor-parallel attention fusion (plain epilogue with 16-byte aligned Y; all optional) ---
+  // all-gather prologue: rows [s * shard_rows, (s + 1) * shard_rows) of X are pushed by peer s, which then sets
+  // wait_flags[s]; a token tile is fetched as soon as the shards it covers have landed (n_wait = number of shards)
+  int shard_rows;
+  // reduce-scatter epilogue: row t is stored to row rs_slot * rs_cap + t % rs_rows of buffer rs_bases[t / rs_rows]
+  // (device array of peer pointers, row stride ldy) instead of Y
+  const void* rs_bases;
+  int rs_rows, rs_slot, rs_cap;
+  // QKV epilogue: neox RoPE on the n_q + n_kv leading heads of head size hd (64 / 128) from rope_table
+  // ([rope_max_pos][hd / 2] float2 = (cos, sin), see dmoe_rope_table), K / V rows appended to the paged caches
+  // ([blocks, block_size, n_kv, hd]) at slots[t] (< 0: skip); only the q columns are written to Y. F = (n_q + 2 n_kv) hd.
+  const void* rope_table;
+  const int* positions;
+  const long long* slots;
+  void* kcache;
+  void* vcache;
+  int n_q, n_kv, hd, rope_max_pos;
 } DmoeGemm;
 
 int dmoe_gemm(const DmoeGemm* desc, void* stream);
@@ -55,6 +72,8 @@ int dmoe_add_rmsnorm(const void* resid_in, const void* add, int n_add, long long
 // neox RoPE on the q and k heads of qkv rows [q | k | v] in place, then K/V append at slots[t] (slot < 0: no append).
 int dmoe_rope_kv_append(void* qkv, long long ld, const int* positions, const long long* slots, void* kcache,
                         void* vcache, int T, int n_q, int n_kv, int hd, float theta, void* stream);
+// (cos, sin) of pos * theta^(-2 d / hd) for pos < max_pos, d < hd / 2: the table the QKV epilogue rotates with.
+int dmoe_rope_table(void* table, int max_pos, int hd, float theta, void* stream);
 int dmoe_embed(const int* ids, const void* table, void* out, int T, int H, int vocab, long long ld_out, void* stream);
 int dmoe_argmax(const void* logits, int is_f32, long long ld, int T, int V, int* ids, void* stream);
 int dmoe_permute_rows(const void* src, long long ld_src, void* dst, long long ld_dst, const int* map, int n, int H,
@@ -92,8 +111,40 @@ int dmoe_dispatch_remote(const void* y, long long ld_y, const int* topk_ids, con
                          int E, int experts_per_rank, int n_dst, int my_rank, int region_cap, int* ws,
                          const void* x_bases, long long ld_dst, const void* rec_bases, const void* cnt_bases,
                          const void* flag_bases, int* epoch, int* status, int tok_lo, int tok_hi, void* stream);
+// ---- fused attention-side senders (sender.cu) --------------------------------------------------------
+// [wait] resid_out = resid_in + sum of n_add partial rows; y = rmsnorm(resid_out) * w is stored to row dst_row0 + t of
+// EVERY buffer in dst_ptrs (device array of n_dst pointers: this GPU's and, for a tensor-parallel group, its peers'
+// QKV staging buffers); then slot signal_slot of every flag array in signal_ptrs gets *signal_epoch + 1.
+// The wait (flags[i] >= *wait_epoch + 1 for i < n_wait, bounded) runs inside the kernel. ticket: one zeroed int.
+typedef struct DmoeNormGather {
+  const void* resid_in; const void* add; const void* w; void* resid_out; const void* dst_ptrs;
+  const int* wait_flags; int* wait_epoch; const void* signal_ptrs; int* signal_epoch; int* ticket; int* status;
+  long long ld_in, add_row_stride, add_part_stride, ld_out, dst_row0, ld_dst;
+  float eps;
+  int n_add, n_dst, T, H, n_wait, n_signal, signal_slot;
+} DmoeNormGather;
+int dmoe_norm_gather(const DmoeNormGather* desc, void* stream);
+
+// [wait] resid += sum of the n_add partial-row slots (add + s * add_slot_stride, row stride ld_add); y = rmsnorm(resid);
+// gate -> softmax -> top-k; every (token, k) pair reserves a row in its expert's region on the owning GPU (atomic on
+// cnt_bases[dst][local expert]) and stores row + record there; the last CTA sets flag_bases[d][my_rank] = *disp_epoch + 1
+// for every d. gate_w == NULL: reduction and normalisation only. x_bases == NULL: route without dispatching.
+typedef struct DmoeRouteDispatch {
+  void* resid; const void* add; const void* norm_w; const void* gate_w; const float* logit_bias; void* y;
+  int* topk_ids; float* topk_w; const void* x_bases; const void* rec_bases; const void* cnt_bases;
+  const void* flag_bases; int* disp_epoch; const int* wait_flags; int* wait_epoch; int* ticket; int* status;
+  long long ld_resid, add_slot_stride, ld_add, ld_y, ld_dst;
+  float eps;
+  int n_add, T, H, E, K, renorm, experts_per_rank, n_dst, my_rank, region_cap, n_wait;
+} DmoeRouteDispatch;
+int dmoe_route_dispatch(const DmoeRouteDispatch* desc, void* stream);
+// dst_ptrs[d][dst0 + i] = src[i] (i < n) for every d < n_dst, then signal_ptrs[d][signal_slot] = *signal_epoch + 1.
+int dmoe_ids_gather(const int* src, int n, const void* dst_ptrs, int n_dst, int dst0, const void* signal_ptrs,
+                    int signal_slot, int* signal_epoch, void* stream);
+
 // Waits (bounded) until flags[i] >= *epoch + 1 for i < n, then advances *epoch.
 int dmoe_wait_flags(const int* flags, int n, int* epoch, int* status, void* stream);
+// Cycle budget of every peer-flag wait in kernels launched from now on (<= 0: the default, about 4 s).
 void dmoe_set_flag_wait_cycles(long long cycles);
 int dmoe_enable_peer_access(int peer_device);
 // Peer arena: a zeroed cudaMalloc block + its 64-byte CUDA IPC handle; dmoe_peer_open maps a peer's block into

@@ -148,6 +148,19 @@ __global__ void rope_kv_append_kernel(__nv_bfloat16* __restrict__ qkv, long long
   }
 }
 
+// table[pos][d] = (cos, sin)(pos * theta^(-2 d / hd)): the same arithmetic as rope_kv_append_kernel, so that the QKV
+// GEMM's rotating epilogue and the stand-alone kernel produce identical bits.
+__global__ void rope_table_kernel(float2* __restrict__ table, int max_pos, int hd, float theta_log2) {
+  const int half = hd / 2;
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= static_cast<long long>(max_pos) * half) return;
+  const int pos = static_cast<int>(i / half), d = static_cast<int>(i % half);
+  const float inv_freq = exp2f(-theta_log2 * (2.f * d) / static_cast<float>(hd));
+  float s, c;
+  sincosf(static_cast<float>(pos) * inv_freq, &s, &c);
+  table[i] = make_float2(c, s);
+}
+
 // out[t] = table[ids[t]]
 __global__ void embed_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
                              __nv_bfloat16* __restrict__ out, int H, int vocab, long long ld_out) {
@@ -244,6 +257,14 @@ extern "C" int dmoe_rope_kv_append(void* qkv, long long ld, const int* positions
   rope_kv_append_kernel<<<T, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<__nv_bfloat16*>(qkv), ld, positions, slots, static_cast<__nv_bfloat16*>(kcache),
       static_cast<__nv_bfloat16*>(vcache), n_q, n_kv, hd, log2f(theta));
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int dmoe_rope_table(void* table, int max_pos, int hd, float theta, void* stream) {
+  if (hd % 16 != 0 || max_pos < 1) return -10;
+  const long long n = static_cast<long long>(max_pos) * (hd / 2);
+  rope_table_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<float2*>(table), max_pos, hd, log2f(theta));
   return static_cast<int>(cudaGetLastError());
 }
 

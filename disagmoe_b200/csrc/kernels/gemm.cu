@@ -75,6 +75,22 @@ struct GemmArgs {
   int clear_n;
   int* clear_ptr;
   int epi_vec;   // plain epilogue may use 16-byte accesses on Y / R (alignment checked on the host)
+  // all-gather prologue: X rows [s * shard_rows, (s + 1) * shard_rows) are pushed by peer s; a token tile is loaded
+  // once wait_flags[s] carries this call's epoch for every shard it touches (0 = one gate for the whole launch)
+  int shard_rows;
+  // reduce-scatter epilogue: row t belongs to rank t / rs_rows and is stored to row rs_slot * rs_cap + t % rs_rows of
+  // that rank's buffer rs_bases[t / rs_rows] (row stride ldy); the owner sums the slots
+  void* const* rs_bases;
+  int rs_rows, rs_slot, rs_cap;
+  // QKV epilogue: neox RoPE on the q and k heads from a (cos, sin) table [pos][hd / 2], K / V append to the paged
+  // cache at slots[t] (< 0: none); only the q columns are written to Y
+  const float2* rope_table;
+  const int* positions;
+  const long long* slots;
+  __nv_bfloat16* kcache;
+  __nv_bfloat16* vcache;
+  int n_q, n_kv, hd, rope_max_pos;
+  long long flag_cycles;   // budget of the peer-flag waits
 };
 
 template <int BN, int EPI>
@@ -179,6 +195,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
   const int MT = (a.F + kBM - 1) / kBM;
   const int kblocks = (a.K + kBK - 1) / kBK;
   const int kb_per = (kblocks + a.splitk - 1) / a.splitk;
+  // the producer may legitimately sit in a peer-flag wait (all-gather prologue): the warps behind it must outlast it
+  const long long bar_budget = DMOE_WAIT_CYCLES + (a.shard_rows > 0 ? a.flag_cycles : 0);
 
   if (threadIdx.x == 0) {
     *abort_word = 0;
@@ -195,14 +213,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
     tma_prefetch_desc(&tmW);
     tma_prefetch_desc(&tmX);
   }
-  if (a.n_wait > 0) {
+  if (a.n_wait > 0 && a.shard_rows == 0) {
     // arrival gate: the senders' rows, counts and records are complete once their flag carries this call's epoch
     if (threadIdx.x < a.n_wait) {
       const int want = *a.wait_epoch + 1;
       const bool poisoned = a.status != nullptr && *reinterpret_cast<volatile int*>(a.status) != kStatusOk;
       const long long t0 = clock64();
       while (!poisoned && ld_acquire_sys(a.wait_flags + threadIdx.x) < want) {
-        if (clock64() - t0 > 4 * DMOE_WAIT_CYCLES) {
+        if (clock64() - t0 > a.flag_cycles) {
           if (a.status != nullptr) atomicCAS(a.status, kStatusOk, kStatusFlagTimeout);
           break;
         }
@@ -259,6 +277,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      unsigned long long shard_ready = 0;     // bit s: shard s of X has landed (all-gather prologue)
+      const int shard_want = (a.shard_rows > 0) ? *a.wait_epoch + 1 : 0;
       for (int tile = blockIdx.x; ok; tile += gridDim.x) {
         int m, n, ks, xrow, ntok_;
         if (!tw.seek(tile, m, n, ks, xrow, ntok_)) break;
@@ -272,6 +292,31 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
           mbar_expect_tx(fb, C::kStageBytes);
           tma_load_2d(smem_u32(st), &tmW, kb * kBK, wrow, fb, pol_w);
           if (EPI == EPI_SWIGLU) tma_load_2d(smem_u32(st + C::kABytes), &tmW, kb * kBK, wrow + a.F, fb, pol_w);
+          if (a.shard_rows > 0 && kb == kb0) {
+            // the weight tile is already on its way; the token tile may only be fetched once every peer whose rows
+            // it covers has published them (the peers' stores are generic-proxy writes: fence before the TMA read)
+            const int s0 = xrow / a.shard_rows;
+            const int s1 = min((xrow + ntok_ - 1) / a.shard_rows, a.n_wait - 1);
+            for (int sh = s0; sh <= s1 && ok; ++sh) {
+              if ((shard_ready >> sh) & 1ull) continue;
+              const long long t0 = clock64();
+              while (ld_acquire_sys(a.wait_flags + sh) < shard_want) {
+                if (*reinterpret_cast<volatile int*>(abort_word) != 0 || clock64() - t0 > a.flag_cycles ||
+                    (a.status != nullptr && *reinterpret_cast<volatile int*>(a.status) != kStatusOk)) {
+                  if (a.status != nullptr) atomicCAS(a.status, kStatusOk, kStatusFlagTimeout);
+                  *abort_word = 1;
+                  ok = false;
+                  break;
+                }
+                __nanosleep(64);
+              }
+              if (ok) {
+                shard_ready |= 1ull << sh;
+                asm volatile("fence.proxy.async;" ::: "memory");
+              }
+            }
+            if (!ok) break;
+          }
           tma_load_2d(smem_u32(st + C::kNumA * C::kABytes), &tmX, kb * kBK, xrow, fb, pol_x);
           if (++stage == C::kStages) { stage = 0; phase ^= 1; }
         }
@@ -292,13 +337,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
         if (!tw.seek(tile, m, n, ks, row0_, ntok_)) break;
         const int buf = it & 1;
         const uint32_t bphase = (it >> 1) & 1;
-        if (!mbar_wait(smem_u32(&tempty_bar[buf]), bphase ^ 1, abort_word)) { ok = false; break; }
+        if (!mbar_wait(smem_u32(&tempty_bar[buf]), bphase ^ 1, abort_word, bar_budget)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d0 = tmem_base + buf * C::kAccCols;
         const int kb0 = ks * kb_per;
         const int kb1 = min(kblocks, kb0 + kb_per);
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait(smem_u32(&full_bar[stage]), phase, abort_word)) { ok = false; break; }
+          if (!mbar_wait(smem_u32(&full_bar[stage]), phase, abort_word, bar_budget)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + stage * C::kStageBytes);
           const uint64_t da = umma_desc_sw128(sa);
@@ -333,7 +378,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
       if (!tw.seek(tile, m, n, ks, tok_base, ntok)) break;
       const int buf = it & 1;
       const uint32_t bphase = (it >> 1) & 1;
-      if (!mbar_wait(smem_u32(&tfull_bar[buf]), bphase, abort_word)) { ok = false; break; }
+      if (!mbar_wait(smem_u32(&tfull_bar[buf]), bphase, abort_word, bar_budget)) { ok = false; break; }
       tc_fence_after();
       const uint32_t t0 = tmem_base + buf * C::kAccCols + (static_cast<uint32_t>(q * 32) << 16);
       const int f = m * kBM + row;
@@ -454,6 +499,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
                 rr[q] = (j < jmax) ? *reinterpret_cast<const uint4*>(a.R + t * a.ldr + f0) : make_uint4(0, 0, 0, 0);
               }
             }
+            // QKV epilogue geometry: a 128-feature tile holds whole heads (hd = 64 or 128), so the rotation partner
+            // of a feature (d +- hd / 2) sits in the same shared-memory chunk
+            const bool rope = a.rope_table != nullptr;
+            const int half = a.hd >> 1;
+            const int d0 = rope ? f0 % a.hd : 0;               // first of this thread's 8 features inside its head
+            const int head = rope ? f0 / a.hd : 0;
+            const bool rot = rope && head < a.n_q + a.n_kv;
+            const bool lower = d0 < half;
+            const int pf = fg * 8 + (lower ? half : -half);     // partner features inside the tile
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
               const int j = tk0 + q * 8;
@@ -471,6 +525,24 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
                   o[2 * i + 1] += rf.y;
                 }
               }
+              if (rot) {
+                const float4 p0 = *reinterpret_cast<const float4*>(&epi_stage[j * kBM + pf]);
+                const float4 p1 = *reinterpret_cast<const float4*>(&epi_stage[j * kBM + pf + 4]);
+                const float pr[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+                int pos = a.positions[t];
+                pos = pos < 0 ? 0 : (pos >= a.rope_max_pos ? a.rope_max_pos - 1 : pos);
+                const float4* cs = reinterpret_cast<const float4*>(a.rope_table + static_cast<long long>(pos) * half +
+                                                                   (lower ? d0 : d0 - half));
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const float4 v = __ldg(cs + i);      // (cos, sin) of two consecutive rotation pairs
+                  // the accumulator is rounded to bf16 before the rotation, as the unfused path stores and re-reads it
+                  const float a0 = __bfloat162float(__float2bfloat16(o[2 * i])), b0 = __bfloat162float(__float2bfloat16(pr[2 * i]));
+                  const float a1 = __bfloat162float(__float2bfloat16(o[2 * i + 1])), b1 = __bfloat162float(__float2bfloat16(pr[2 * i + 1]));
+                  o[2 * i] = lower ? a0 * v.x - b0 * v.y : a0 * v.x + b0 * v.y;
+                  o[2 * i + 1] = lower ? a1 * v.z - b1 * v.w : a1 * v.z + b1 * v.w;
+                }
+              }
               if (a.y_f32) {
                 float* yp = reinterpret_cast<float*>(a.Y) + t * a.ldy + f0;
                 *reinterpret_cast<float4*>(yp) = make_float4(o[0], o[1], o[2], o[3]);
@@ -480,7 +552,25 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
                 __nv_bfloat162* pp = reinterpret_cast<__nv_bfloat162*>(&pk);
 #pragma unroll
                 for (int i = 0; i < 4; ++i) pp[i] = __floats2bfloat162_rn(o[2 * i], o[2 * i + 1]);
-                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.Y) + t * a.ldy + f0) = pk;
+                if (rope) {
+                  if (head < a.n_q) {
+                    *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.Y) + t * a.ldy + f0) = pk;
+                  } else {
+                    const long long slot = a.slots != nullptr ? a.slots[t] : -1;
+                    if (slot >= 0) {
+                      const int kvh = head - a.n_q;
+                      __nv_bfloat16* cache = kvh < a.n_kv ? a.kcache : a.vcache;
+                      const int hh = kvh < a.n_kv ? kvh : kvh - a.n_kv;
+                      *reinterpret_cast<uint4*>(cache + (slot * a.n_kv + hh) * a.hd + d0) = pk;
+                    }
+                  }
+                } else if (a.rs_bases != nullptr) {
+                  const int owner = static_cast<int>(t) / a.rs_rows;
+                  const long long lrow = static_cast<long long>(a.rs_slot) * a.rs_cap + (static_cast<int>(t) - owner * a.rs_rows);
+                  *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(a.rs_bases[owner]) + lrow * a.ldy + f0) = pk;
+                } else {
+                  *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.Y) + t * a.ldy + f0) = pk;
+                }
               }
             }
           }
@@ -673,6 +763,26 @@ extern "C" int dmoe_gemm(const DmoeGemm* d, void* stream_) {
     a.epi_vec = (epi == EPI_PLAIN && d->F % 8 == 0 && d->ldy % ymod == 0 && al16(d->Y) &&
                  (d->R == nullptr || (d->ldr % 8 == 0 && al16(d->R)))) ? 1 : 0;
   }
+  a.shard_rows = d->shard_rows;
+  a.flag_cycles = g_dmoe_flag_wait_cycles;
+  a.rs_bases = static_cast<void* const*>(d->rs_bases);
+  a.rs_rows = d->rs_rows; a.rs_slot = d->rs_slot; a.rs_cap = d->rs_cap;
+  a.rope_table = static_cast<const float2*>(d->rope_table);
+  a.positions = d->positions; a.slots = d->slots;
+  a.kcache = static_cast<__nv_bfloat16*>(d->kcache); a.vcache = static_cast<__nv_bfloat16*>(d->vcache);
+  a.n_q = d->n_q; a.n_kv = d->n_kv; a.hd = d->hd; a.rope_max_pos = d->rope_max_pos;
+  if (a.shard_rows < 0 || (a.shard_rows > 0 && (a.n_wait < 1 || a.n_wait > 64 || epi == EPI_SWIGLU || d->offs != nullptr ||
+                                                 d->S > 0 || d->group_regions)))
+    return -18;
+  if (a.rs_bases != nullptr && (!a.epi_vec || d->y_f32 || a.rs_rows < 1 || a.rs_cap < a.rs_rows || a.rs_slot < 0 ||
+                                d->R != nullptr || a.rope_table != nullptr))
+    return -18;
+  if (a.rope_table != nullptr &&
+      (!a.epi_vec || d->y_f32 || d->R != nullptr || a.positions == nullptr || a.kcache == nullptr || a.vcache == nullptr ||
+       (a.hd != 64 && a.hd != 128) || a.n_q < 1 || a.n_kv < 1 || (a.n_q + 2 * a.n_kv) * a.hd != d->F ||
+       a.rope_max_pos < 1 || (reinterpret_cast<uintptr_t>(a.rope_table) & 15) != 0 ||
+       (reinterpret_cast<uintptr_t>(a.kcache) & 15) != 0 || (reinterpret_cast<uintptr_t>(a.vcache) & 15) != 0))
+    return -19;
   if (a.group_regions && (a.seg_cnt == nullptr || static_cast<long long>(a.G) * a.seg_cap > d->T)) return -16;
   if (!a.group_regions && a.S > 0 && (a.seg_cnt == nullptr || a.S * a.G > kMaxSeg || a.S * a.seg_cap > d->T)) return -16;
   if (a.S == 0 && a.G > kMaxSeg) return -16;

@@ -57,7 +57,8 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 
 // Bounded mbarrier wait. `abort_word` is a CTA-shared int: once any waiter gives up it is set, and every
 // other waiter of the CTA leaves at its next poll.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_word) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_word,
+                                          long long budget = DMOE_WAIT_CYCLES) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   for (;;) {
@@ -66,7 +67,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       if (mbar_try_wait(bar, parity)) return true;
     }
     if (*abort_word) return false;
-    if (clock64() - t0 > DMOE_WAIT_CYCLES) {
+    if (clock64() - t0 > budget) {
       *abort_word = 1;
       return false;
     }
@@ -184,6 +185,9 @@ __host__ __device__ constexpr uint32_t umma_idesc_bf16(int M, int N) {
 }
 
 // ---------------------------------------------------------------- host helpers
+// Cycle budget of the peer-flag waits (set with dmoe_set_flag_wait_cycles; defined in comm.cu).
+extern long long g_dmoe_flag_wait_cycles;
+
 // cudaFuncSetAttribute applies to the current device only, so "already configured" has to be remembered per
 // device: one process may drive several GPUs.
 constexpr int kMaxDevicesPerProcess = 64;

@@ -150,10 +150,17 @@ class MoEAttention(torch.nn.Module):
         cfg = self.cfg
         # the residual stream is updated in place: `resid` is owned by the caller's step buffers
         resid, h = F.add_rmsnorm(resid, parts, self.pre_ln, cfg.rms_norm_eps, resid_out=resid)
-        qkv = gemm.linear(h, self.qkv_w)
         kc, vc = kv_cache
-        F.rope_kv_append(qkv, meta.positions, meta.slots, kc, vc, self.num_heads, self.num_kv_heads, self.head_dim,
-                         cfg.rope_theta)
+        if h.is_cuda:
+            # RoPE and the paged K / V append run in the QKV GEMM's epilogue (only the q columns of `qkv` are written)
+            table = gemm.rope_table(cfg.max_seq_len, self.head_dim, cfg.rope_theta, h.device)   # positions < max_seq_len
+            rope = gemm.RopeAppend(table, meta.positions, meta.slots, kc, vc, self.num_heads, self.num_kv_heads,
+                                   self.head_dim)
+            qkv = gemm.linear(h, self.qkv_w, comm=gemm.GemmComm(rope=rope))
+        else:
+            qkv = gemm.linear(h, self.qkv_w)
+            F.rope_kv_append(qkv, meta.positions, meta.slots, kc, vc, self.num_heads, self.num_kv_heads,
+                             self.head_dim, cfg.rope_theta)
         T = qkv.shape[0]
         splits = 1
         if qkv.is_cuda:

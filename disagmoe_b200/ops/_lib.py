@@ -32,7 +32,33 @@ class DmoeGemm(ctypes.Structure):
         ("clear_ptr", ctypes.c_void_p), ("fanout", ctypes.c_int),
         ("G", ctypes.c_int), ("T", ctypes.c_int), ("F", ctypes.c_int), ("K", ctypes.c_int),
         ("epi", ctypes.c_int), ("bn", ctypes.c_int), ("splitk", ctypes.c_int), ("y_f32", ctypes.c_int),
+        ("shard_rows", ctypes.c_int), ("rs_bases", ctypes.c_void_p),
+        ("rs_rows", ctypes.c_int), ("rs_slot", ctypes.c_int), ("rs_cap", ctypes.c_int),
+        ("rope_table", ctypes.c_void_p), ("positions", ctypes.c_void_p), ("slots", ctypes.c_void_p),
+        ("kcache", ctypes.c_void_p), ("vcache", ctypes.c_void_p),
+        ("n_q", ctypes.c_int), ("n_kv", ctypes.c_int), ("hd", ctypes.c_int), ("rope_max_pos", ctypes.c_int),
     ]
+
+
+_vp, _ll, _i, _f = ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_float
+
+
+class DmoeNormGather(ctypes.Structure):
+    _fields_ = [(n, _vp) for n in ("resid_in", "add", "w", "resid_out", "dst_ptrs", "wait_flags", "wait_epoch",
+                                   "signal_ptrs", "signal_epoch", "ticket", "status")] + \
+               [(n, _ll) for n in ("ld_in", "add_row_stride", "add_part_stride", "ld_out", "dst_row0", "ld_dst")] + \
+               [("eps", _f)] + \
+               [(n, _i) for n in ("n_add", "n_dst", "T", "H", "n_wait", "n_signal", "signal_slot")]
+
+
+class DmoeRouteDispatch(ctypes.Structure):
+    _fields_ = [(n, _vp) for n in ("resid", "add", "norm_w", "gate_w", "logit_bias", "y", "topk_ids", "topk_w",
+                                   "x_bases", "rec_bases", "cnt_bases", "flag_bases", "disp_epoch", "wait_flags",
+                                   "wait_epoch", "ticket", "status")] + \
+               [(n, _ll) for n in ("ld_resid", "add_slot_stride", "ld_add", "ld_y", "ld_dst")] + \
+               [("eps", _f)] + \
+               [(n, _i) for n in ("n_add", "T", "H", "E", "K", "renorm", "experts_per_rank", "n_dst", "my_rank",
+                                  "region_cap", "n_wait")]
 
 
 def lib_path() -> str:
@@ -54,6 +80,10 @@ def lib():
         _LIB.dmoe_gemm.argtypes = [ctypes.POINTER(DmoeGemm), ctypes.c_void_p]
         _LIB.dmoe_gemm.restype = ctypes.c_int
         _LIB.dmoe_gemm_workspace_bytes.restype = ctypes.c_longlong
+        _LIB.dmoe_norm_gather.argtypes = [ctypes.POINTER(DmoeNormGather), ctypes.c_void_p]
+        _LIB.dmoe_route_dispatch.argtypes = [ctypes.POINTER(DmoeRouteDispatch), ctypes.c_void_p]
+        _LIB.dmoe_set_flag_wait_cycles.argtypes = [ctypes.c_longlong]
+        _LIB.dmoe_set_flag_wait_cycles.restype = None
     return _LIB
 
 

@@ -256,3 +256,70 @@ def dispatch_local(y: torch.Tensor, topk_ids: torch.Tensor, topk_w: torch.Tensor
         _vp(y), c_ll(y.stride(0)), _vp(topk_ids), _vp(topk_w), c_int(T), c_int(K), c_int(buf.H), c_int(buf.E),
         c_int(buf.E), c_int(0), _vp(buf.ws), _vp(buf.offs), _vp(buf.x_bases), c_ll(buf.xs.stride(0)),
         _vp(buf.rec_bases), c_int(buf.capacity), _vp(s.status), _st()), "dmoe_dispatch_local")
+
+
+# ---- fused attention-side senders (csrc/kernels/sender.cu); CUDA only -------------------------------------------------
+def norm_gather(resid: Optional[torch.Tensor], add: Optional[torch.Tensor], w: torch.Tensor, eps: float,
+                resid_out: Optional[torch.Tensor], dst_ptrs: torch.Tensor, n_dst: int, dst_row0: int, ld_dst: int,
+                T: int, H: int, wait_flags: Optional[torch.Tensor] = None, n_wait: int = 0,
+                wait_epoch: Optional[torch.Tensor] = None, signal_ptrs: Optional[torch.Tensor] = None,
+                n_signal: int = 0, signal_slot: int = 0, signal_epoch: Optional[torch.Tensor] = None,
+                ticket: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None) -> None:
+    """[wait for ``wait_flags``] resid_out = resid + add.sum(1); rmsnorm(resid_out) * w is stored to rows
+    [dst_row0, dst_row0 + T) of every buffer named in ``dst_ptrs`` (int64 device tensor of n_dst addresses, peers
+    included); then the flags in ``signal_ptrs`` are released. ``add`` is [T, P, H] (or [T, H]) bf16."""
+    d = _lib.DmoeNormGather()
+    if add is not None and add.dim() == 2:
+        add = add.unsqueeze(1)
+    d.resid_in, d.add, d.w, d.resid_out = _lib.ptr(resid), _lib.ptr(add), w.data_ptr(), _lib.ptr(resid_out)
+    d.dst_ptrs, d.n_dst, d.dst_row0, d.ld_dst = dst_ptrs.data_ptr(), n_dst, dst_row0, ld_dst
+    d.ld_in = resid.stride(0) if resid is not None else 0
+    d.ld_out = resid_out.stride(0) if resid_out is not None else 0
+    d.n_add = 0 if add is None else add.shape[1]
+    d.add_row_stride = add.stride(0) if add is not None else 0
+    d.add_part_stride = add.stride(1) if add is not None else 0
+    d.eps, d.T, d.H = eps, T, H
+    d.wait_flags, d.n_wait, d.wait_epoch = _lib.ptr(wait_flags), n_wait, _lib.ptr(wait_epoch)
+    d.signal_ptrs, d.n_signal, d.signal_slot = _lib.ptr(signal_ptrs), n_signal, signal_slot
+    d.signal_epoch, d.ticket, d.status = _lib.ptr(signal_epoch), _lib.ptr(ticket), _lib.ptr(status)
+    _lib.check(_lib.lib().dmoe_norm_gather(ctypes.byref(d), _st()), "dmoe_norm_gather")
+
+
+def route_dispatch(resid: torch.Tensor, norm_w: torch.Tensor, eps: float, gate_w: Optional[torch.Tensor], top_k: int,
+                   renormalize: bool, T: int, *, add: Optional[torch.Tensor] = None, n_add: int = 0,
+                   add_slot_stride: int = 0, ld_add: int = 0, y: Optional[torch.Tensor] = None,
+                   topk_ids: Optional[torch.Tensor] = None, topk_w: Optional[torch.Tensor] = None,
+                   logit_bias: Optional[torch.Tensor] = None, x_bases=None, rec_bases=None, cnt_bases=None,
+                   flag_bases=None, ld_dst: int = 0, experts_per_rank: int = 1, n_dst: int = 0, my_rank: int = 0,
+                   region_cap: int = 0, disp_epoch=None, wait_flags=None, n_wait: int = 0, wait_epoch=None, ticket=None,
+                   status=None) -> None:
+    """One launch for the post-attention half of a layer on an attention GPU: [wait for the TP peers' o_proj flags]
+    resid[:T] += the ``n_add`` partial-row slots of ``add``; RMSNorm; gate; softmax; top-k; dispatch of every routed row
+    into its expert's receive region on the owning GPU (peer stores) with a release flag per expert GPU."""
+    H = resid.shape[1]
+    d = _lib.DmoeRouteDispatch()
+    d.resid, d.ld_resid, d.add, d.n_add = resid.data_ptr(), resid.stride(0), _lib.ptr(add), n_add
+    d.add_slot_stride, d.ld_add = add_slot_stride, ld_add
+    d.norm_w, d.eps, d.gate_w, d.logit_bias = norm_w.data_ptr(), eps, _lib.ptr(gate_w), _lib.ptr(logit_bias)
+    d.T, d.H, d.E, d.K, d.renorm = T, H, (gate_w.shape[0] if gate_w is not None else 0), top_k, int(renormalize)
+    d.y, d.ld_y = _lib.ptr(y), (y.stride(0) if y is not None else 0)
+    d.topk_ids, d.topk_w = _lib.ptr(topk_ids), _lib.ptr(topk_w)
+    d.x_bases, d.rec_bases, d.cnt_bases, d.flag_bases = (_lib.ptr(t) for t in (x_bases, rec_bases, cnt_bases, flag_bases))
+    d.ld_dst, d.experts_per_rank, d.n_dst, d.my_rank, d.region_cap = ld_dst, experts_per_rank, n_dst, my_rank, region_cap
+    d.disp_epoch, d.wait_flags, d.n_wait, d.wait_epoch = _lib.ptr(disp_epoch), _lib.ptr(wait_flags), n_wait, _lib.ptr(wait_epoch)
+    d.ticket, d.status = _lib.ptr(ticket), _lib.ptr(status)
+    _lib.check(_lib.lib().dmoe_route_dispatch(ctypes.byref(d), _st()), "dmoe_route_dispatch")
+
+
+def ids_gather(src: torch.Tensor, n: int, dst_ptrs: torch.Tensor, n_dst: int, dst0: int,
+               signal_ptrs: Optional[torch.Tensor] = None, signal_slot: int = 0,
+               signal_epoch: Optional[torch.Tensor] = None) -> None:
+    """The first n int32 of ``src`` are stored at offset dst0 of every buffer in ``dst_ptrs``; then one flag per
+    destination is released (the all-gather of a TP group's sampled ids)."""
+    _lib.check(_lib.lib().dmoe_ids_gather(_vp(src), c_int(n), _vp(dst_ptrs), c_int(n_dst), c_int(dst0), _vp(signal_ptrs),
+                                          c_int(signal_slot), _vp(signal_epoch), _st()), "dmoe_ids_gather")
+
+
+def wait_flags(flags: torch.Tensor, n: int, epoch: torch.Tensor, status: Optional[torch.Tensor]) -> None:
+    """Stand-alone bounded wait: flags[i] >= epoch + 1 for i < n; advances the device-resident epoch."""
+    _lib.check(_lib.lib().dmoe_wait_flags(_vp(flags), c_int(n), _vp(epoch), _vp(status), _st()), "dmoe_wait_flags")

@@ -101,12 +101,17 @@ class GemmComm:
 
     def __init__(self, seg_cnt=None, S=0, seg_cap=0, wait_flags=None, n_wait=0, wait_epoch=None, signal_ptrs=None,
                  n_signal=0, signal_slot=0, signal_epoch=None, done_ticket=None, fanout=0, group_regions=False,
-                 clear=None):
+                 clear=None, shard_rows=0, rs_bases=None, rs_rows=0, rs_slot=0, rs_cap=0, rope: "Optional[RopeAppend]" = None):
         self.seg_cnt, self.S, self.seg_cap = seg_cnt, S, seg_cap
         self.wait_flags, self.n_wait, self.wait_epoch = wait_flags, n_wait, wait_epoch
         self.signal_ptrs, self.n_signal, self.signal_slot = signal_ptrs, n_signal, signal_slot
         self.signal_epoch, self.done_ticket = signal_epoch, done_ticket
         self.fanout, self.group_regions, self.clear = fanout, group_regions, clear
+        # tensor-parallel attention: all-gather prologue (X arrives in shards of shard_rows rows, one wait flag per
+        # shard), reduce-scatter epilogue (row t -> rank t // rs_rows, slot rs_slot of its partial buffer)
+        self.shard_rows = shard_rows
+        self.rs_bases, self.rs_rows, self.rs_slot, self.rs_cap = rs_bases, rs_rows, rs_slot, rs_cap
+        self.rope = rope
 
     def fill(self, d):
         d.seg_cnt, d.S, d.seg_cap = _lib.ptr(self.seg_cnt), self.S, self.seg_cap
@@ -116,6 +121,46 @@ class GemmComm:
         d.fanout = self.fanout
         d.group_regions = int(self.group_regions)
         d.clear_ptr, d.clear_n = _lib.ptr(self.clear), (0 if self.clear is None else self.clear.numel())
+        d.shard_rows = self.shard_rows
+        d.rs_bases, d.rs_rows, d.rs_slot, d.rs_cap = _lib.ptr(self.rs_bases), self.rs_rows, self.rs_slot, self.rs_cap
+        if self.rope is not None:
+            r = self.rope
+            d.rope_table, d.positions, d.slots = r.table.data_ptr(), r.positions.data_ptr(), _lib.ptr(r.slots)
+            d.kcache, d.vcache = r.kcache.data_ptr(), r.vcache.data_ptr()
+            d.n_q, d.n_kv, d.hd, d.rope_max_pos = r.n_q, r.n_kv, r.hd, r.table.shape[0]
+
+
+class RopeAppend:
+    """QKV epilogue: neox RoPE on the q / k heads and K / V append to the paged cache (see ``DmoeGemm``).
+
+    table: fp32 [max_pos, hd / 2, 2] from :func:`rope_table`; positions int32 [T]; slots int64 [T] or None;
+    kcache / vcache [blocks, block_size, n_kv, hd] bf16."""
+
+    def __init__(self, table, positions, slots, kcache, vcache, n_q, n_kv, hd):
+        assert table.dtype == torch.float32 and table.is_contiguous() and table.shape[1] == hd // 2
+        assert positions.dtype == torch.int32 and (slots is None or slots.dtype == torch.int64)
+        assert kcache.is_contiguous() and vcache.is_contiguous() and kcache.dtype == torch.bfloat16
+        self.table, self.positions, self.slots, self.kcache, self.vcache = table, positions, slots, kcache, vcache
+        self.n_q, self.n_kv, self.hd = n_q, n_kv, hd
+
+
+_rope_tables = {}
+
+
+def rope_table(max_pos: int, hd: int, theta: float, device) -> torch.Tensor:
+    """fp32 [max_pos, hd / 2, 2] = (cos, sin)(pos * theta^(-2 d / hd)), computed on the device with the arithmetic
+    of the stand-alone RoPE kernel; cached per (device, max_pos, hd, theta)."""
+    device = torch.device(device)
+    key = (device.index or 0, max_pos, hd, float(theta))
+    t = _rope_tables.get(key)
+    if t is None:
+        t = torch.empty(max_pos, hd // 2, 2, dtype=torch.float32, device=device)
+        with torch.cuda.device(device):
+            _lib.check(_lib.lib().dmoe_rope_table(ctypes.c_void_p(t.data_ptr()), ctypes.c_int(max_pos), ctypes.c_int(hd),
+                                                  ctypes.c_float(theta), ctypes.c_void_p(_lib.stream_ptr())),
+                       "dmoe_rope_table")
+        _rope_tables[key] = t
+    return t
 
 
 def _launch(W, X, Y, R, offs, recs, bases, G, T, F, K, epi, bn, splitk, ldy, y_f32, comm: Optional[GemmComm] = None):
@@ -161,9 +206,10 @@ def linear(x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor] = 
     _check_x(x)
     assert w.is_contiguous() and w.dtype == torch.bfloat16 and w.shape[1] == K
     odt = out_dtype or torch.bfloat16
-    if out is None:
+    scatter = comm is not None and comm.rs_bases is not None      # reduce-scatter epilogue: rows go to the peers
+    if out is None and not scatter:
         out = torch.empty(T, F, dtype=odt, device=x.device)
-    assert out.stride(1) == 1 and out.dtype in (torch.bfloat16, torch.float32)
+    assert scatter or (out.stride(1) == 1 and out.dtype in (torch.bfloat16, torch.float32))
     if T == 0:
         return out
     if not bn:
@@ -171,8 +217,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor] = 
         if bn == 256 and ((F + 127) // 128) * ((T + 255) // 256) < num_sms(x.device) // 2:
             bn = 128     # too few 256-wide tiles to fill the GPU: halve the tile instead of splitting K further
     splitk = splitk or pick_splitk(T, F, K, bn, num_sms(x.device))
-    _launch(w, x, out, residual, None, None, None, 1, T, F, K, EPI_PLAIN, bn, splitk, out.stride(0),
-            out.dtype == torch.float32, comm)
+    _launch(w, x, out, residual, None, None, None, 1, T, F, K, EPI_PLAIN, bn, splitk,
+            F if scatter else out.stride(0), (not scatter) and out.dtype == torch.float32, comm)
     return out
 
 

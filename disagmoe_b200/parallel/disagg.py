@@ -1,15 +1,17 @@
 """Device-driven disaggregated decode: attention GPUs and expert GPUs exchange tokens through peer memory.
 
-Ranks [0, A) are attention replicas (data parallel, each with its own sequences and KV cache); ranks [A, A + X) hold
-the routed experts (expert parallel, ``num_experts / X`` experts each). One decode iteration of a micro-batch is,
-per layer:
+Ranks [0, A) are attention GPUs, in groups of ``tp`` consecutive ranks that share their sequences (tensor parallel:
+heads and KV cache split over the group, residual stream sharded by rows) — groups are data-parallel replicas of
+one another; ranks [A, A + X) hold the routed experts (expert parallel, ``num_experts / X`` experts each). One decode
+iteration of a micro-batch is, per layer:
 
-    attention rank   [wait combine flags]  add+RMSNorm -> QKV -> RoPE/KV append -> paged attention -> o_proj+residual
-                     -> RMSNorm+gate+top-k -> dispatch: a block of rows per expert is reserved on the owning expert GPU
-                     (one system-scope atomic per expert), then rows, records and a release flag are stored there
+    attention rank   [wait combine flags] add+RMSNorm (+ all-gather push) -> QKV (+ RoPE, KV append) -> paged attention
+                     -> o_proj (+ residual, or + reduce-scatter push) -> [wait o_proj flags] reduce + RMSNorm + gate +
+                     top-k + dispatch: every routed row reserves a slot in its expert's region on the owning expert GPU
+                     (one system-scope atomic), then row, record and finally a release flag are stored there
     expert rank      grouped GEMM-1 (+SwiGLU), gated on the arrival flags, reads the rows where they landed
                      -> grouped GEMM-2 whose epilogue scales by the router weight and stores every row into the
-                     source attention GPU's partial-output buffer, then signals that GPU
+                     partial-output buffer of the attention GPU that owns the row, then signals that GPU
 
 Nothing in this chain returns to the host: flags carry device-resident epoch counters, so the whole iteration of a
 rank is one CUDA graph. Every attention rank runs two micro-batches through the layers in lock-step order
@@ -49,7 +51,7 @@ class DisaggShape:
     n_attn: int
     n_expert: int
     n_mb: int           # micro-batches per attention rank
-    batch: int          # sequences per micro-batch
+    batch: int          # token rows per micro-batch of one attention group (a TP group shares them)
     top_k: int
     hidden: int
     num_experts: int
@@ -61,8 +63,18 @@ class DisaggShape:
         return (self.num_experts + self.n_expert - 1) // self.n_expert
 
     @property
+    def rows_cap(self) -> int:
+        """Rows of the residual stream one attention rank owns at full batch (the sequence shard of a TP rank)."""
+        return (self.batch + self.tp - 1) // self.tp
+
+    @property
     def region_cap(self) -> int:   # rows of one expert's receive region: every sender could route all its pairs to it
-        return self.n_attn * (self.batch // self.tp) * self.top_k
+        return self.n_attn * self.rows_cap * self.top_k
+
+
+def shard_rows(T: int, tp: int) -> int:
+    """Rows per TP rank when T rows are split over tp ranks: rank r owns [r * per, min(T, (r + 1) * per))."""
+    return max(1, (T + tp - 1) // tp)
 
 
 def build_layout(s: DisaggShape) -> ArenaLayout:
@@ -73,21 +85,42 @@ def build_layout(s: DisaggShape) -> ArenaLayout:
         L.add(f"recv_recs{m}", rows * 16)
         L.add(f"recv_cnt{m}", s.experts_per_rank * 4)      # per-expert row cursors, advanced by the senders
         L.add(f"disp_flag{m}", s.n_attn * 4)
-        L.add(f"parts{m}", s.batch * s.top_k * s.hidden * 2)
+        L.add(f"parts{m}", s.rows_cap * s.top_k * s.hidden * 2)
         L.add(f"comb_flag{m}", s.n_expert * 4)
         if s.tp > 1:
-            # this rank's o_proj partial sums, read by its TP peers. Two buffers used by layer parity: a peer may
-            # still read layer l's partials while this rank already writes layer l + 1's (nothing else orders the two
-            # when layer l has a dense FFN and so no round trip through the expert GPUs); by layer l + 2 the peer's
-            # own layer l + 1 signal proves it is done with layer l
-            L.add(f"opart{m}_0", s.batch * s.hidden * 2)
-            L.add(f"opart{m}_1", s.batch * s.hidden * 2)
+            # all-gather target: the normalised rows of the whole group, every rank pushes its shard to every member
+            L.add(f"hs{m}", s.batch * s.hidden * 2)
+            L.add(f"hsflag{m}", s.tp * 4)
+            # reduce-scatter target: slot p holds TP rank p's o_proj partial sums of THIS rank's rows. One buffer is
+            # enough: a peer writes layer l + 1's partials only after its QKV GEMM saw this rank's layer l + 1 shard,
+            # which this rank pushes after it has consumed layer l's partials
+            L.add(f"opart{m}", s.tp * s.rows_cap * s.hidden * 2)
             L.add(f"oflag{m}", s.tp * 4)
+            L.add(f"nid{m}", s.batch * 4)                  # sampled ids of the whole group
+            L.add(f"nidflag{m}", s.tp * 4)
     return L
 
 
 class AttentionRank:
-    """All attention layers + embedding + LM head of one DP replica, with its KV cache and micro-batch buffers."""
+    """All attention layers + embedding + LM head of one attention GPU, with its KV cache and micro-batch buffers.
+
+    Per layer and micro-batch this rank launches five kernels (six when the attention runs split-KV):
+
+        norm_gather      [wait: experts' combine flags] resid += expert partials; pre-norm; the normalised rows go
+                         to the QKV staging buffer of every member of the TP group (all-gather by peer stores)
+        QKV GEMM         tcgen05; token tiles gated shard by shard on the members' flags (all-gather prologue);
+                         epilogue rotates q / k (RoPE) and appends K / V to the paged cache
+        paged attention  this rank's heads, all rows of the group
+        o_proj GEMM      tcgen05; with TP the epilogue scatters every row's partial sum to the rank that owns the row
+                         (reduce-scatter by peer stores) and signals; without TP it adds the residual in place
+        route_dispatch   [wait: members' o_proj flags] ordered sum of the partials + residual; post-norm; gate; top-k;
+                         row reservation on the expert GPUs; remote stores of rows + records; release flags
+
+    With tensor parallelism the residual stream is sharded by rows: rank r of a group owns rows [r * per, (r + 1) *
+    per) of the group's micro-batch (per = ceil(T / tp)), runs both norms, the router, the dispatch, shared experts /
+    dense FFN and the LM head on those rows only, and receives the experts' combine output for those rows only.
+    Replaces, for TP groups, the reference's broadcast of inputs (disagmoe/frontend/engine.py:494-535) and its
+    all-reduce after o_proj (disagmoe/models/linear.py:1064-1089, csrc/muhelper/comm.cpp:399-416)."""
 
     def __init__(self, cfg: ModelConfig, shape: DisaggShape, arena: PeerArena, layout: ArenaLayout, attn_rank: int,
                  num_blocks: int, block_size: int = 16, state_dict: Optional[W.StateDict] = None, device=None):
@@ -98,7 +131,6 @@ class AttentionRank:
         self.tp = shape.tp
         self.tp_rank = attn_rank % shape.tp
         self.group0 = attn_rank // shape.tp * shape.tp      # first attention rank of this TP group
-        assert shape.batch % shape.tp == 0
         self.layers: List[MoEAttention] = []
         for l in range(cfg.num_layers):
             m = MoEAttention(cfg, l, tp_size=self.tp, tp_rank=self.tp_rank, device=dev, dtype=dt)
@@ -110,21 +142,30 @@ class AttentionRank:
         self.norm_w = sd["norm.weight"].to(device=dev, dtype=dt)
         self.lm_head_w = sd["lm_head.weight"].to(device=dev, dtype=dt).contiguous()
         S = shape
-        B, k, H, E = S.batch, S.top_k, S.hidden, S.num_experts
+        B, R, k, H, E = S.batch, S.rows_cap, S.top_k, S.hidden, S.num_experts
+        a0 = self.layers[0]
         self.block_size = block_size
         self.max_blocks = (cfg.max_seq_len + block_size - 1) // block_size
-        self.kv_cache = torch.zeros(cfg.num_layers, 2, num_blocks, block_size, self.layers[0].num_kv_heads, cfg.head_dim,
+        self.kv_cache = torch.zeros(cfg.num_layers, 2, num_blocks, block_size, a0.num_kv_heads, cfg.head_dim,
                                     dtype=dt, device=dev)
         self.block_tables = torch.zeros(S.n_mb * B, self.max_blocks, dtype=torch.int32, device=dev)
+        self.rope = gemm.rope_table(cfg.max_seq_len, cfg.head_dim, cfg.rope_theta, dev)
+        self.qkv_features = a0.q_size + 2 * a0.kv_size
         z = lambda *s, dt_=torch.int32: torch.zeros(*s, dtype=dt_, device=dev)
         self.mb = []
         expert_ranks = [S.n_attn + x for x in range(S.n_expert)]
+        group = [self.group0 + i for i in range(self.tp)]
         for m in range(S.n_mb):
             d = dict(
                 ids=z(B), positions=z(B), slots=z(B, dt_=torch.int64), ctx_len=z(B), bt_row=z(B),
-                resid=torch.zeros(B, H, dtype=dt, device=dev), ws=z(3 * E + 8), disp_epoch=z(1), wait_epoch=z(1),
-                next_ids=z(B), logits=torch.zeros(B, cfg.vocab_size, dtype=torch.float32, device=dev),
-                parts=arena.view(layout.offset(f"parts{m}"), (B, k, H), dt),
+                resid=torch.zeros(R, H, dtype=dt, device=dev), y=torch.zeros(R, H, dtype=dt, device=dev),
+                hfin=torch.zeros(R, H, dtype=dt, device=dev),
+                qkv=torch.zeros(B, self.qkv_features, dtype=dt, device=dev),
+                attn=torch.zeros(B, a0.q_size, dtype=dt, device=dev),
+                disp_epoch=z(1), comb_epoch=z(1), ticket=z(1),
+                next_local=z(R), logits=torch.zeros(R, cfg.vocab_size, dtype=torch.float32, device=dev),
+                topk_ids=z(R, k), topk_w=torch.zeros(R, k, dtype=torch.float32, device=dev),
+                parts=arena.view(layout.offset(f"parts{m}"), (R, k, H), dt),
                 comb_flag=arena.view(layout.offset(f"comb_flag{m}"), (S.n_expert,), torch.int32),
                 x_bases=arena.ptr_table(expert_ranks, layout.offset(f"recv_rows{m}")),
                 rec_bases=arena.ptr_table(expert_ranks, layout.offset(f"recv_recs{m}")),
@@ -132,22 +173,29 @@ class AttentionRank:
                 flag_bases=arena.ptr_table(expert_ranks, layout.offset(f"disp_flag{m}")),
             )
             if self.tp > 1:
-                group = [self.group0 + i for i in range(self.tp)]
                 d.update(
-                    opart=[arena.view(layout.offset(f"opart{m}_{p}"), (B, H), dt) for p in range(2)],
+                    hs=arena.view(layout.offset(f"hs{m}"), (B, H), dt),
+                    hs_ptrs=arena.ptr_table(group, layout.offset(f"hs{m}")),
+                    hsflag=arena.view(layout.offset(f"hsflag{m}"), (self.tp,), torch.int32),
+                    hsflag_ptrs=arena.ptr_table(group, layout.offset(f"hsflag{m}")),
+                    opart=arena.view(layout.offset(f"opart{m}"), (self.tp, R, H), dt),
+                    opart_ptrs=arena.ptr_table(group, layout.offset(f"opart{m}")),
                     oflag=arena.view(layout.offset(f"oflag{m}"), (self.tp,), torch.int32),
-                    opart_ptrs=[arena.ptr_table(group, layout.offset(f"opart{m}_{p}")) for p in range(2)],
                     oflag_ptrs=arena.ptr_table(group, layout.offset(f"oflag{m}")),
-                    o_signal_epoch=z(1), o_wait_epoch=z(1), o_ticket=z(1),
-                    y=torch.zeros(B, H, dtype=dt, device=dev), topk_ids=z(B, k),
-                    topk_w=torch.zeros(B, k, dtype=torch.float32, device=dev))
+                    next_ids=arena.view(layout.offset(f"nid{m}"), (B,), torch.int32),
+                    nid_ptrs=arena.ptr_table(group, layout.offset(f"nid{m}")),
+                    nidflag=arena.view(layout.offset(f"nidflag{m}"), (self.tp,), torch.int32),
+                    nidflag_ptrs=arena.ptr_table(group, layout.offset(f"nidflag{m}")),
+                    hs_sig_epoch=z(1), hs_wait_epoch=z(1), o_sig_epoch=z(1), o_wait_epoch=z(1),
+                    nid_sig_epoch=z(1), nid_wait_epoch=z(1), gemm_ticket=z(1))
+            else:
+                d["hs"] = torch.zeros(B, H, dtype=dt, device=dev)
+                d["hs_ptrs"] = torch.tensor([d["hs"].data_ptr()], dtype=torch.int64, device=dev)
+                d["next_ids"] = d["next_local"]
+            d["hfin_ptrs"] = torch.tensor([d["hfin"].data_ptr()], dtype=torch.int64, device=dev)
             self.mb.append(d)
         self.status = gemm.scratch(dev).status
         self.active = [B] * S.n_mb      # rows of every micro-batch that the next launches process (<= B)
-        self._views: Dict[tuple, dict] = {}
-
-    _ROW_KEYS = ("ids", "positions", "slots", "ctx_len", "bt_row", "resid", "next_ids", "logits", "parts", "y",
-                 "topk_ids", "topk_w")
 
     def set_active(self, m: int, T: int) -> None:
         """The next launches of micro-batch m process its first T rows (1 <= T <= batch): a serving step fills the
@@ -155,111 +203,128 @@ class AttentionRank:
         assert 1 <= T <= self.shape.batch
         self.active[m] = T
 
-    def _d(self, m: int) -> dict:
+    def rows(self, m: int):
+        """(T, rows per TP rank, first own row, one past the last own row) of micro-batch m as currently active."""
         T = self.active[m]
-        full = self.mb[m]
-        if T == self.shape.batch:
-            return full
-        v = self._views.get((m, T))
-        if v is None:
-            v = dict(full)
-            for k in self._ROW_KEYS:
-                if k in full:
-                    v[k] = full[k][:T]
-            if "opart" in full:
-                v["opart"] = [t[:T] for t in full["opart"]]
-            self._views[(m, T)] = v
-        return v
+        per = shard_rows(T, self.tp)
+        return T, per, min(T, self.tp_rank * per), min(T, (self.tp_rank + 1) * per)
 
     def _meta(self, m: int) -> AttnMeta:
-        d = self._d(m)
-        return AttnMeta(d["positions"], d["slots"], self.block_tables, d["bt_row"], d["ctx_len"],
+        d, T = self.mb[m], self.active[m]
+        return AttnMeta(d["positions"][:T], d["slots"][:T], self.block_tables, d["bt_row"][:T], d["ctx_len"][:T],
                         max_ctx=self.cfg.max_seq_len)
 
     def embed(self, m: int) -> None:
-        d = self._d(m)
-        F.embed(d["ids"], self.embed_w, out=d["resid"])
+        d = self.mb[m]
+        _, _, lo, hi = self.rows(m)
+        if hi > lo:
+            F.embed(d["ids"][lo:hi], self.embed_w, out=d["resid"][:hi - lo])
 
     def layer(self, l: int, m: int) -> None:
         """Attention half of layer l for micro-batch m, ending with the peer-memory dispatch."""
+        self.layer_pre(l, m)
         self.layer_attn(l, m)
         self.layer_route_dispatch(l, m)
 
-    def layer_attn(self, l: int, m: int) -> None:
-        """[wait for the experts' combine] add + RMSNorm, QKV, RoPE / KV append, paged attention, o_proj. With tensor
-        parallelism the o_proj partial sum goes to this rank's peer-visible buffer and the GEMM signals the TP peers."""
-        d, S, cfg = self._d(m), self.shape, self.cfg
-        T = self.active[m]
-        parts = None
-        if l > 0 and not cfg.is_dense_layer(l - 1):     # a dense-FFN layer sends nothing to the expert GPUs
-            _lib.check(_lib.lib().dmoe_wait_flags(_vp(d["comb_flag"]), c_int(S.n_expert), _vp(d["wait_epoch"]),
-                                                  _vp(self.status), c_vp(_lib.stream_ptr())), "dmoe_wait_flags")
-            parts = d["parts"]
+    def _expert_parts(self, l: int) -> bool:
+        """Does layer l start by adding the routed experts' output of layer l - 1? (Not after a dense-FFN layer, which
+        sends nothing to the expert GPUs.)"""
+        return l > 0 and not self.cfg.is_dense_layer(l - 1)
+
+    def layer_pre(self, l: int, m: int) -> None:
+        """[wait for the experts' combine] add + pre-attention RMSNorm on this rank's rows; the normalised rows land in
+        the QKV staging buffer of every member of the TP group."""
+        d, S, cfg = self.mb[m], self.shape, self.cfg
+        T, per, lo, hi = self.rows(m)
+        Tm = hi - lo
         a = self.layers[l]
-        kv = (self.kv_cache[l, 0], self.kv_cache[l, 1])
-        if self.tp == 1:
-            d["resid2"] = a.attention(d["resid"], parts, kv, self._meta(m))
-            return
+        wait = self._expert_parts(l)
+        tp = self.tp
+        F.norm_gather(d["resid"][:Tm], d["parts"][:Tm] if wait else None, a.pre_ln, cfg.rms_norm_eps,
+                      d["resid"][:Tm] if wait else None, d["hs_ptrs"], tp, lo, S.hidden, Tm, S.hidden,
+                      wait_flags=d["comb_flag"] if wait else None, n_wait=S.n_expert if wait else 0,
+                      wait_epoch=d["comb_epoch"] if wait else None,
+                      signal_ptrs=d["hsflag_ptrs"] if tp > 1 else None, n_signal=tp if tp > 1 else 0,
+                      signal_slot=self.tp_rank, signal_epoch=d.get("hs_sig_epoch"), ticket=d["ticket"],
+                      status=self.status)
+
+    def layer_attn(self, l: int, m: int) -> None:
+        """QKV (+ RoPE + KV append in the epilogue), paged attention, o_proj. With tensor parallelism the QKV GEMM
+        consumes the all-gathered rows shard by shard and the o_proj epilogue scatters the partial sums to the rows'
+        owners; without it o_proj adds the residual in place."""
+        d, S, cfg = self.mb[m], self.shape, self.cfg
+        T, per, lo, hi = self.rows(m)
+        a = self.layers[l]
+        kc, vc = self.kv_cache[l, 0], self.kv_cache[l, 1]
         meta = self._meta(m)
-        resid, h = F.add_rmsnorm(d["resid"], parts, a.pre_ln, cfg.rms_norm_eps, resid_out=d["resid"])
-        qkv = gemm.linear(h, a.qkv_w)
-        F.rope_kv_append(qkv, meta.positions, meta.slots, kv[0], kv[1], a.num_heads, a.num_kv_heads, a.head_dim,
-                         cfg.rope_theta)
-        attn = F.paged_attention(qkv[:, :a.q_size], kv[0], kv[1], meta.block_tables, meta.bt_row, meta.ctx_len,
-                                 a.num_heads, a.num_kv_heads, a.head_dim,
+        rope = gemm.RopeAppend(self.rope, meta.positions, meta.slots, kc, vc, a.num_heads, a.num_kv_heads, a.head_dim)
+        if self.tp > 1:
+            comm = gemm.GemmComm(shard_rows=per, wait_flags=d["hsflag"], n_wait=self.tp, wait_epoch=d["hs_wait_epoch"],
+                                 done_ticket=d["gemm_ticket"], rope=rope)
+        else:
+            comm = gemm.GemmComm(rope=rope)
+        qkv = gemm.linear(d["hs"][:T], a.qkv_w, out=d["qkv"][:T], comm=comm)
+        attn = F.paged_attention(qkv[:, :a.q_size], kc, vc, meta.block_tables, meta.bt_row, meta.ctx_len,
+                                 a.num_heads, a.num_kv_heads, a.head_dim, out=d["attn"][:T],
                                  splits=F.pick_attn_splits(T, a.num_kv_heads, cfg.max_seq_len, self.block_size))
-        sig = gemm.GemmComm(signal_ptrs=d["oflag_ptrs"], n_signal=self.tp, signal_slot=self.tp_rank,
-                            signal_epoch=d["o_signal_epoch"], done_ticket=d["o_ticket"])
-        gemm.linear(attn, a.o_w, out=d["opart"][l % 2], comm=sig)
+        if self.tp == 1:
+            gemm.linear(attn, a.o_w, residual=d["resid"][:T], out=d["resid"][:T])
+            return
+        sig = gemm.GemmComm(rs_bases=d["opart_ptrs"], rs_rows=per, rs_slot=self.tp_rank, rs_cap=S.rows_cap,
+                            signal_ptrs=d["oflag_ptrs"], n_signal=self.tp, signal_slot=self.tp_rank,
+                            signal_epoch=d["o_sig_epoch"], done_ticket=d["gemm_ticket"])
+        gemm.linear(attn, a.o_w, comm=sig)
 
     def layer_route_dispatch(self, l: int, m: int) -> None:
-        """Post-attention RMSNorm + router + dispatch. With tensor parallelism the router kernel first sums the TP
-        ranks' o_proj partials straight out of their memory (the all-reduce), and this rank dispatches only its
-        slice of the tokens."""
-        d, S, cfg = self._d(m), self.shape, self.cfg
-        T = self.active[m]
+        """[wait for the TP members' o_proj] reduce + residual, post-attention RMSNorm, router, dispatch of this
+        rank's rows: one kernel. Shared experts and dense FFN layers follow on this rank's rows."""
+        d, S, cfg = self.mb[m], self.shape, self.cfg
+        T, per, lo, hi = self.rows(m)
+        Tm = hi - lo
         a = self.layers[l]
-        lo, hi = 0, T
-        if a.is_dense and self.tp == 1:
-            a.dense_ffn(d["resid"])
+        tp = self.tp
+        kw = {}
+        if tp > 1:
+            kw = dict(add=d["opart"], n_add=tp, add_slot_stride=S.rows_cap * S.hidden, ld_add=S.hidden,
+                      wait_flags=d["oflag"], n_wait=tp, wait_epoch=d["o_wait_epoch"])
+        if not a.is_dense:
+            kw.update(x_bases=d["x_bases"], rec_bases=d["rec_bases"], cnt_bases=d["cnt_bases"],
+                      flag_bases=d["flag_bases"], ld_dst=S.hidden, experts_per_rank=S.experts_per_rank,
+                      n_dst=S.n_expert, my_rank=self.a, region_cap=S.region_cap, disp_epoch=d["disp_epoch"],
+                      logit_bias=a.route_bias, topk_ids=d["topk_ids"], topk_w=d["topk_w"])
+        F.route_dispatch(d["resid"], a.post_ln, cfg.rms_norm_eps, None if a.is_dense else a.gate_w, S.top_k,
+                         cfg.norm_topk_prob, Tm, y=d["y"], ticket=d["ticket"], status=self.status, **kw)
+        if Tm == 0:
             return
-        if self.tp == 1:
-            a.counts = d["ws"][:S.num_experts]
-            y, ids, w, _ = a.route(d["resid2"])
-        else:
-            _lib.check(_lib.lib().dmoe_wait_flags(_vp(d["oflag"]), c_int(self.tp), _vp(d["o_wait_epoch"]),
-                                                  _vp(self.status), c_vp(_lib.stream_ptr())), "dmoe_wait_flags")
-            per = (T + self.tp - 1) // self.tp
-            lo, hi = min(T, self.tp_rank * per), min(T, (self.tp_rank + 1) * per)
-            y, ids, w = d["y"], d["topk_ids"], d["topk_w"]
-            _lib.check(_lib.lib().dmoe_route_ex(
-                _vp(d["resid"]), c_ll(S.hidden), _vp(a.post_ln), ctypes.c_float(cfg.rms_norm_eps), _vp(a.gate_w),
-                c_int(T), c_int(S.hidden), c_int(S.num_experts), c_int(S.top_k), c_int(int(cfg.norm_topk_prob)),
-                _vp(y), c_ll(S.hidden), _vp(ids), _vp(w), _vp(d["ws"]), _vp(d["opart_ptrs"][l % 2]), c_int(self.tp),
-                c_ll(S.hidden), _vp(d["resid"]), c_ll(S.hidden), c_int(lo), c_int(hi), _vp(a.route_bias),
-                c_vp(_lib.stream_ptr())), "dmoe_route_ex")
-            if a.is_dense:
-                # the router kernel ran without a gate: it summed the TP partials into the residual stream and
-                # normalised it; every TP rank then applies the (replicated) dense FFN to all rows
-                a.dense_ffn(d["resid"], h=y)
-                return
-        _lib.check(_lib.lib().dmoe_dispatch_remote(
-            _vp(y), c_ll(y.stride(0)), _vp(ids), _vp(w), c_int(T), c_int(S.top_k), c_int(S.hidden),
-            c_int(S.num_experts), c_int(S.experts_per_rank), c_int(S.n_expert), c_int(self.a), c_int(S.region_cap),
-            _vp(d["ws"]), _vp(d["x_bases"]), c_ll(S.hidden), _vp(d["rec_bases"]), _vp(d["cnt_bases"]),
-            _vp(d["flag_bases"]), _vp(d["disp_epoch"]), _vp(self.status), c_int(lo), c_int(hi),
-            c_vp(_lib.stream_ptr())), "dmoe_dispatch_remote")
+        if a.is_dense:
+            a.dense_ffn(d["resid"][:Tm], h=d["y"][:Tm])
+            return
         # shared experts stay on the attention GPU and run while the expert GPUs work on the rows just sent
-        # (replicated over the ranks of a TP group)
-        a.shared_experts(y, d["resid"])
+        a.shared_experts(d["y"][:Tm], d["resid"][:Tm])
 
     def head(self, m: int) -> None:
-        d, S, cfg = self._d(m), self.shape, self.cfg
-        _lib.check(_lib.lib().dmoe_wait_flags(_vp(d["comb_flag"]), c_int(S.n_expert), _vp(d["wait_epoch"]),
-                                              _vp(self.status), c_vp(_lib.stream_ptr())), "dmoe_wait_flags")
-        _, h = F.add_rmsnorm(d["resid"], d["parts"], self.norm_w, cfg.rms_norm_eps, resid_out=d["resid"])
-        logits = gemm.linear(h, self.lm_head_w, out=d["logits"], out_dtype=torch.float32)
-        F.argmax(logits, out=d["next_ids"])
+        """[wait for the last layer's combine] final norm, LM head and greedy sampling on this rank's rows; a TP group
+        then exchanges the sampled ids so that every member holds all of them."""
+        d, S, cfg = self.mb[m], self.shape, self.cfg
+        T, per, lo, hi = self.rows(m)
+        Tm = hi - lo
+        wait = self._expert_parts(cfg.num_layers)
+        F.norm_gather(d["resid"][:Tm], d["parts"][:Tm] if wait else None, self.norm_w, cfg.rms_norm_eps,
+                      d["resid"][:Tm] if wait else None, d["hfin_ptrs"], 1, 0, S.hidden, Tm, S.hidden,
+                      wait_flags=d["comb_flag"] if wait else None, n_wait=S.n_expert if wait else 0,
+                      wait_epoch=d["comb_epoch"] if wait else None, ticket=d["ticket"], status=self.status)
+        if Tm > 0:
+            logits = gemm.linear(d["hfin"][:Tm], self.lm_head_w, out=d["logits"][:Tm], out_dtype=torch.float32)
+            F.argmax(logits, out=d["next_local"][:Tm])
+        if self.tp > 1:
+            F.ids_gather(d["next_local"], Tm, d["nid_ptrs"], self.tp, lo, d["nidflag_ptrs"], self.tp_rank,
+                         d["nid_sig_epoch"])
+
+    def head_wait(self, m: int) -> None:
+        """A TP group's iteration ends when every member's sampled ids have landed in this rank's id buffer."""
+        if self.tp > 1:
+            d = self.mb[m]
+            F.wait_flags(d["nidflag"], self.tp, d["nid_wait_epoch"], self.status)
 
     def iteration(self) -> None:
         S = self.shape
@@ -270,6 +335,8 @@ class AttentionRank:
                 self.layer(l, m)
         for m in range(S.n_mb):
             self.head(m)
+        for m in range(S.n_mb):
+            self.head_wait(m)
 
 
 class ExpertRank:
@@ -307,7 +374,7 @@ class ExpertRank:
                 parts_bases=arena.ptr_table(attn_ranks, layout.offset(f"parts{m}")),
                 signal_ptrs=arena.ptr_table(attn_ranks, layout.offset(f"comb_flag{m}")),
             ))
-        pairs = S.n_attn * (S.batch // S.tp) * S.top_k       # (token, k) pairs arriving per launch, all experts
+        pairs = S.n_attn * S.rows_cap * S.top_k              # (token, k) pairs arriving per launch, all experts
         self.bn = gemm.pick_bn(gemm._group_hint(pairs, S.num_experts), gemm.EPI_SWIGLU)
 
     def layer(self, l: int, m: int) -> None:
@@ -321,13 +388,81 @@ class ExpertRank:
         # the last CTA clears the row cursors before it signals: the senders reserve again only after that signal
         sig = gemm.GemmComm(seg_cnt=d["cnt"], seg_cap=S.region_cap, group_regions=True, signal_ptrs=d["signal_ptrs"],
                             n_signal=S.n_attn, signal_slot=self.x, signal_epoch=d["signal_epoch"],
-                            done_ticket=self.ticket, fanout=S.tp, clear=d["cnt"])
+                            done_ticket=self.ticket, clear=d["cnt"])
         gemm.grouped_combine(self.act, e.w2_weight, None, d["recs"], d["parts_bases"], S.hidden, bn=self.bn, comm=sig)
 
     def iteration(self) -> None:
         for l in range(self.cfg.num_layers):
             for m in range(self.shape.n_mb):
                 self.layer(l, m)
+
+
+def selfcheck_against_colocated(world: int, rank: int, local_rank: int, n_attn: int, tp: int, n_mb: int = 2,
+                                batch: int = 8) -> Dict[str, float]:
+    """Correctness line of a multi-GPU job: a tiny model (2 layers, hidden 256, 8 experts) runs one decode iteration
+    through the fused pipeline on the job's real GPUs with the job's layout (attention groups, TP degree, expert
+    GPUs), and every attention rank compares the logits of the rows it owns with the single-GPU colocated executor
+    fed the same weights, KV history and inputs. Collective over the world; returns the worst relative error
+    (max |diff| / max |ref|) and the worst fraction of rows whose arg-max agrees, over all ranks."""
+    import torch.distributed as dist
+    from ..config import CacheConfig, tiny_config
+    from ..executor.fused import FusedModelExecutor
+    A, X = n_attn, world - n_attn
+    cfg = tiny_config.clone(dtype=torch.bfloat16, num_layers=2)
+    dev = torch.device("cuda", local_rank)
+    sd = {k: v.to(torch.bfloat16) for k, v in W.init_state_dict(cfg, dtype=torch.float32).items()}
+    B = batch * tp
+    shape = DisaggShape(A, X, n_mb, B, cfg.top_k, cfg.hidden_size, cfg.num_experts, tp)
+    layout = build_layout(shape)
+    arena = PeerArena.create(layout.size, device=dev)
+    nb, bs = 4 * n_mb * B + 1, 16
+    err, agree = 0.0, 1.0
+    if rank < A:
+        grp = rank // tp
+        g = torch.Generator().manual_seed(99 + grp)
+        r = AttentionRank(cfg, shape, arena, layout, rank, nb, state_dict=sd, device=dev)
+        kvh = cfg.num_kv_heads // tp if cfg.num_kv_heads >= tp else 1
+        kv = torch.randn(cfg.num_layers, 2, nb, bs, cfg.num_kv_heads, cfg.head_dim, generator=g).to(torch.bfloat16) * 0.5
+        k0 = (rank % tp) * kvh if cfg.num_kv_heads >= tp else (rank % tp) // (tp // cfg.num_kv_heads)
+        r.kv_cache.copy_(kv[..., k0:k0 + kvh, :])
+        inputs = []
+        for m in range(n_mb):
+            ids = torch.randint(0, cfg.vocab_size, (B,), generator=g).int()
+            ctx = torch.randint(3, 60, (B,), generator=g).int()
+            bt = (torch.arange(B * 4, dtype=torch.int32) + m * B * 4).view(B, 4)
+            slots = torch.tensor([int(bt[i, int(ctx[i]) // bs]) * bs + int(ctx[i]) % bs for i in range(B)])
+            rows = torch.arange(B, dtype=torch.int32) + m * B
+            r.block_tables[m * B:(m + 1) * B, :4] = bt.to(dev)
+            d = r.mb[m]
+            d["ids"].copy_(ids); d["positions"].copy_(ctx); d["ctx_len"].copy_(ctx + 1)
+            d["bt_row"].copy_(rows); d["slots"].copy_(slots)
+            inputs.append((ids, ctx, slots, bt))
+    else:
+        r = ExpertRank(cfg, shape, arena, layout, rank - A, state_dict=sd, device=dev)
+    torch.cuda.synchronize()
+    dist.barrier()
+    r.iteration()
+    torch.cuda.synchronize()
+    dist.barrier()
+    status = gemm.check_status(dev)
+    if rank < A:
+        ref = FusedModelExecutor(cfg, CacheConfig(block_size=bs), device=dev, max_batch_size=B, max_prefill_tokens=B,
+                                 state_dict=sd, num_blocks=nb, enable_cuda_graph=False)
+        per = shard_rows(B, tp)
+        lo, hi = min(B, (rank % tp) * per), min(B, (rank % tp + 1) * per)
+        for m, (ids, ctx, slots, bt) in enumerate(inputs):
+            ref.kv_cache.copy_(kv)
+            ref.block_tables[:B, :4] = bt.to(dev)
+            _, lg = ref.decode(ids, ctx, slots, ctx + 1, torch.arange(B, dtype=torch.int32), want_logits=True)
+            got, want = r.mb[m]["logits"][:hi - lo].float(), lg[lo:hi].float()
+            if hi > lo:
+                err = max(err, float((got - want).abs().max() / want.abs().max()))
+                agree = min(agree, float((got.argmax(-1) == want.argmax(-1)).float().mean()))
+        torch.cuda.synchronize()
+    t = torch.tensor([err, -agree, float(status)], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return {"max_rel_err": round(float(t[0]), 5), "argmax_agree_min": round(-float(t[1]), 4), "kernel_status": int(t[2]),
+            "model": "tiny 2-layer MoE, same GPU layout, vs the colocated executor"}
 
 
 class DisaggDecodeBench:

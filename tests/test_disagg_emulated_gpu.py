@@ -13,6 +13,16 @@ from disagmoe_b200.parallel.peer import PeerArena
 pytestmark = pytest.mark.gpu
 
 
+def assert_close(got, ref, what):
+    """Logits of two bf16 pipelines that differ in summation order: every element within 2^-5 |ref| + 2^-5 rms(ref)
+    (each is ~2^-8 relative per rounding; a handful of roundings per layer accumulate over the layers)."""
+    got, ref = got.float(), ref.float()
+    bound = ref.abs() * 2 ** -5 + ref.pow(2).mean().sqrt() * 2 ** -5
+    bad = int(((got - ref).abs() > bound).sum())
+    assert bad == 0, f"{what}: {bad} of {ref.numel()} elements off, max err {(got - ref).abs().max().item():.4g}, " \
+                     f"rms {ref.pow(2).mean().sqrt().item():.4g}"
+
+
 def _model(variant, num_layers):
     """'mixtral': routed experts only. 'shared_dense': first layer with a dense FFN, a sigmoid-gated shared expert next to
     the routed ones and a Zipf(1.2) popularity skew on the router (the Qwen-MoE / DeepSeek-V2-Lite layer types)."""
@@ -81,18 +91,17 @@ def test_emulated_disagg_matches_colocated(A, X, n_mb, variant):
                 ref.kv_cache.copy_(attn[a].kv_cache_before)
             ref.block_tables[:B, :4] = bt.cuda()
             _, lg = ref.decode(ids, ctx, slots, ctx + 1, torch.arange(B, dtype=torch.int32), want_logits=True)
-            got = attn[a].mb[m]["logits"]
-            err = (got - lg).abs().max().item() / lg.abs().max().item()
-            assert err < 0.03, f"rank {a} mb {m} step {step}: rel err {err}"
+            assert_close(attn[a].mb[m]["logits"], lg, f"rank {a} mb {m} step {step}")
 
 
 @pytest.mark.parametrize("A,X,tp,n_mb,variant", [(2, 1, 2, 1, "mixtral"), (4, 2, 2, 2, "mixtral"),
-                                                 (2, 3, 2, 2, "shared_dense")])
+                                                 (2, 3, 2, 2, "shared_dense"), (4, 1, 4, 1, "mixtral")])
 def test_emulated_tensor_parallel_attention(A, X, tp, n_mb, variant):
-    """Attention TP: head-sharded QKV / attention / o_proj per rank, o_proj partials reduced inside the router kernel
-    from the peers' buffers, every rank dispatches its token slice, experts fan the combine out to the whole group."""
+    """Attention TP: all-gather of the normalised rows into the QKV GEMM, head-sharded QKV / attention / o_proj,
+    reduce-scatter in the o_proj epilogue, row-sharded router / dispatch / LM head, id exchange at the end. B = 6 rows
+    over tp = 4 gives shards of 2, 2, 2 and 0 rows: an empty shard still has to take part in every hand-shake."""
     cfg, sd, skew = _model(variant, 3 if variant == "shared_dense" else 2)
-    B = 4
+    B = 6 if tp == 4 else 4
     shape = DisaggShape(A, X, n_mb, B, cfg.top_k, cfg.hidden_size, cfg.num_experts, tp)
     layout = build_layout(shape)
     arenas = PeerArena.emulated(A + X, layout.size)
@@ -124,8 +133,11 @@ def test_emulated_tensor_parallel_attention(A, X, tp, n_mb, variant):
     for a in attn:
         for m in range(n_mb):
             a.embed(m)
+    # one stream, several ranks: every phase is launched for all ranks before the phase that waits for it
     for l in range(cfg.num_layers):
         for m in range(n_mb):
+            for a in attn:
+                a.layer_pre(l, m)
             for a in attn:
                 a.layer_attn(l, m)
             for a in attn:
@@ -135,16 +147,25 @@ def test_emulated_tensor_parallel_attention(A, X, tp, n_mb, variant):
     for a in attn:
         for m in range(n_mb):
             a.head(m)
+    for a in attn:
+        for m in range(n_mb):
+            a.head_wait(m)
     torch.cuda.synchronize()
     assert gemm.check_status() == 0
+    per = (B + tp - 1) // tp
     for (grp, m), (ids, ctx, slots, bt) in inputs.items():
         ref.kv_cache.copy_(kv)
         ref.block_tables[:B, :4] = bt.cuda()
-        _, lg = ref.decode(ids, ctx, slots, ctx + 1, torch.arange(B, dtype=torch.int32), want_logits=True)
+        nxt, lg = ref.decode(ids, ctx, slots, ctx + 1, torch.arange(B, dtype=torch.int32), want_logits=True)
         for r in range(tp):
-            got = attn[grp * tp + r].mb[m]["logits"]
-            err = (got - lg).abs().max().item() / lg.abs().max().item()
-            assert err < 0.03, f"group {grp} tp rank {r} mb {m}: rel err {err}"
+            a = attn[grp * tp + r]
+            lo, hi = min(B, r * per), min(B, (r + 1) * per)          # the rows this rank owns
+            got = a.mb[m]["logits"][:hi - lo]
+            assert_close(got, lg[lo:hi], f"group {grp} tp rank {r} mb {m}")
+            # every member holds the sampled ids of the whole group after the id exchange
+            own = a.mb[m]["next_local"][:hi - lo]
+            assert torch.equal(a.mb[m]["next_ids"][lo:hi], own)
+            assert torch.equal(a.mb[m]["next_ids"], attn[grp * tp].mb[m]["next_ids"])
 
 
 def test_emulated_mixed_prompt_and_decode_rows():
@@ -204,5 +225,4 @@ def test_emulated_mixed_prompt_and_decode_rows():
            3: attn.mb[1]["logits"][0], 4: attn.mb[1]["logits"][1], 5: attn.mb[1]["logits"][2]}
     want = {"prompt": lg_p[11], **{r: lg_d[i] for i, r in enumerate(rs)}}
     for k in got:
-        err = (got[k] - want[k]).abs().max().item() / want[k].abs().max().item()
-        assert err < 0.03, f"{k}: rel err {err}"
+        assert_close(got[k], want[k], str(k))
