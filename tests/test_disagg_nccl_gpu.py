@@ -65,3 +65,62 @@ def test_two_gpu_fused_serving_matches_colocated():
     assert info["kernel_status"] == 0 and info["requests_finished"] == 24
     assert check["check_first_tokens_agree"] >= 0.9, check
     assert check["check_tokens_agree"] >= 0.7, check
+
+
+def _torchrun(n, script, *args, port=29661, timeout=600):
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(n), "--master-addr",
+           "127.0.0.1", "--master-port", str(port), os.path.join(root, script), *args]
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+    import json
+    return [json.loads(l) for l in out.stdout.splitlines() if l.startswith("{")]
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_two_gpu_consumer_blocks_on_flag_until_the_producer_releases_it():
+    """The consumer's wait is launched before the producer's kernel exists: unlike the single-GPU emulation, this
+    exercises the release / acquire pairing and the system-scope fences of the peer-store path for real."""
+    lines = _torchrun(2, "tests/workers/flag_block_worker.py", port=29662, timeout=300)
+    consumer = next(l for l in lines if l["rank"] == 1)
+    assert consumer["ok"], consumer
+
+
+def _gpu_counts():
+    n = torch.cuda.device_count() if torch.cuda.is_available() else 0
+    return [c for c in (2, 4, 8) if c <= n] or [0]
+
+
+@pytest.mark.parametrize("n", _gpu_counts())
+def test_fused_pipeline_logits_match_colocated_on_the_real_gpus(n):
+    """bench.py's own correctness line on every GPU count this box offers: the tiny model runs through the fused
+    pipeline with the layout of the benchmark at that count (2: 1 attention + 1 expert GPU; 4: TP 2 + 2; 8: TP 4 + 4 --
+    all-gather into QKV, reduce-scatter out of o_proj, row-sharded router / dispatch / LM head) and every attention rank
+    compares its logits with the colocated executor. The two-layer truncated model then runs two timed steps."""
+    if n == 0:
+        pytest.skip("needs 2 GPUs")
+    lines = _torchrun(n, "bench.py", "--gpus", str(n), "--layers", "2", "--steps", "2", "--warmup", "3", "--batch", "32",
+                      "--ctx-min", "40", "--ctx-max", "200", port=29663 + n)
+    res = next(l for l in lines if "selfcheck" in l)
+    assert res["kernel_status"] == 0 and res["selfcheck"]["kernel_status"] == 0, res
+    assert res["selfcheck"]["max_rel_err"] < 0.04 and res["selfcheck"]["argmax_agree_min"] >= 0.75, res["selfcheck"]
+    if n >= 4:
+        assert "tp" in res["config"]["parallelism"]
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 4, reason="needs 4 GPUs")
+def test_four_gpu_tp_fused_serving_matches_colocated():
+    """Continuous batching with a tensor-parallel attention group (2 attention GPUs TP 2 + 2 expert GPUs): chunked
+    prefill, odd row counts per iteration (uneven and empty row shards), id exchange inside the group."""
+    lines = _torchrun(4, "benchmark/serve_fused.py", "--model", "tiny", "--n-attn", "2", "--attn-tp", "2", "-r", "200", "-n",
+                      "24", "--min-input-len", "8", "-i", "40", "--min-output-len", "4", "-o", "12", "--max-seqs-per-mb",
+                      "8", "--max-tokens-per-mb", "96", "--max-prefill-tokens-per-mb", "24", "--num-blocks", "512",
+                      "--time-limit", "120", "--check", port=29671)
+    info = next(l for l in lines if "iterations" in l)
+    check = next(l for l in lines if "check_tokens_agree" in l)
+    assert info["kernel_status"] == 0 and info["requests_finished"] == 24
+    assert check["check_first_tokens_agree"] >= 0.9, check
+    assert check["check_tokens_agree"] >= 0.7, check
