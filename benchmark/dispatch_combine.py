@@ -208,6 +208,7 @@ def main():
                           parts_bases=arena.ptr_table(list(range(A)), layout.offset("parts0")),
                           signal_ptrs=arena.ptr_table(list(range(A)), layout.offset("comb_flag0")))]
             er.bn = gemm.pick_bn(gemm._group_hint(A * T * k, E), gemm.EPI_SWIGLU)
+            er.bn2 = gemm.pick_bn(gemm._group_hint(A * T * k, E), gemm.EPI_COMBINE)
             fused = er
         nccl = NcclPath(cfg, A, X, rank, T, x, gate_w, norm_w, experts_mod)
 

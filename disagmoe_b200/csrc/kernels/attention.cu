@@ -264,6 +264,211 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
   out[static_cast<long long>(t) * ld_out + head * HD + d] = __float2bfloat16(L > 0.f ? O / L : 0.f);
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Tiled causal attention for prompt tokens (prefill, whole prompts or chunks of them).
+//
+// The per-token kernel above streams a prompt row's whole prefix for every row: O(n^2) K/V bytes per prompt with no
+// reuse. Here a CTA owns a tile of 64 query rows = (64 / GQ consecutive prompt tokens) x (the GQ query heads of one kv
+// head) and streams the sequence's K/V pages ONCE for the tile, 64 keys at a time, through a double-buffered
+// cp.async ring shared by its four warps; each warp holds 16 query rows as mma.sync A fragments, computes S = Q K^T
+// for the 64 keys, applies the causal mask (key position <= query position; the chunk's own K/V are already in the
+// cache), runs the online softmax on the accumulator fragments and reuses P in registers as the A operand of O += P V.
+// A chunk that continues a prompt attends to the cached prefix and to itself, so chunked prefill needs nothing else.
+//
+// tiles: one int4 per CTA column = {first row of the tile in q / out, tokens in the tile (<= 64 / GQ), block-table
+// row of the sequence, position of the tile's first token}.
+constexpr int kPreKeys = 64;       // keys per pipeline stage
+constexpr int kPreRows = 64;       // query rows per CTA (4 warps x 16)
+
+template <int HD, int GQ>
+__global__ void __launch_bounds__(128)
+prefill_attn_kernel(const __nv_bfloat16* __restrict__ q, long long ld_q, const __nv_bfloat16* __restrict__ kcache,
+                    const __nv_bfloat16* __restrict__ vcache, const int* __restrict__ block_tables, int max_blocks,
+                    const int4* __restrict__ tiles, int block_size, int n_kv, float scale_log2,
+                    __nv_bfloat16* __restrict__ out, long long ld_out) {
+  constexpr int ROWB = HD * 2;
+  constexpr int NCH = HD / 8;                       // 16-byte chunks per K / V row
+  constexpr int TILEB = kPreKeys * ROWB;
+  constexpr int STAGEB = 2 * TILEB;                 // K tile then V tile
+  constexpr int CPT = kPreKeys * NCH / 128;         // 16-byte copies per thread per tile
+  constexpr int KS = HD / 16;                       // k-steps of Q K^T
+  constexpr int NT = HD / 8;                        // n-tiles of the output
+  extern __shared__ __align__(128) uint8_t s_pre[];
+
+  const int4 tile = tiles[blockIdx.x];
+  const int row0 = tile.x, ntok = tile.y, pos0 = tile.w;
+  const int hkv = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, tq = lane & 3;
+  const int* bt = block_tables + static_cast<long long>(tile.z) * max_blocks;
+  const int kmax = pos0 + ntok;                     // keys [0, kmax) exist for the last token of the tile
+  const int nkb = (kmax + kPreKeys - 1) / kPreKeys;
+  const long long tok_stride = static_cast<long long>(n_kv) * HD;
+  const uint32_t sbase = smem_u32(s_pre);
+
+  auto issue = [&](int kb) {
+    if (kb < nkb) {
+      const uint32_t dst0 = sbase + (kb & 1) * STAGEB;
+#pragma unroll
+      for (int i = 0; i < CPT; ++i) {
+        const int id = threadIdx.x + i * 128;
+        const int r = id / NCH, c = id % NCH;
+        const int key = kb * kPreKeys + r;
+        const bool valid = key < kmax;
+        long long off = 0;
+        if (valid) {
+          const long long blk = bt[key / block_size];
+          off = (blk * block_size + key % block_size) * tok_stride + hkv * HD + c * 8;
+        }
+        const uint32_t d = dst0 + r * ROWB + ((c ^ (r & 7)) << 4);
+        cp_async16(d, kcache + off, valid);
+        cp_async16(d + TILEB, vcache + off, valid);
+      }
+    }
+    cp_async_commit();
+  };
+  issue(0);
+
+  // Q fragments: this warp's rows R0 = warp * 16 + g and R0 + 8; row R = (token R / GQ, head R % GQ)
+  const int R0 = warp * 16 + g, R1 = R0 + 8;
+  const int t0 = R0 / GQ, t1 = R1 / GQ;
+  const bool v0 = t0 < ntok, v1 = t1 < ntok;
+  const int qpos0 = pos0 + t0, qpos1 = pos0 + t1;
+  uint32_t qa[KS][4];
+  {
+    const __nv_bfloat16* q0 = q + static_cast<long long>(row0 + t0) * ld_q + (hkv * GQ + R0 % GQ) * HD;
+    const __nv_bfloat16* q1 = q + static_cast<long long>(row0 + t1) * ld_q + (hkv * GQ + R1 % GQ) * HD;
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+      qa[ks][0] = v0 ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + 2 * tq) : 0u;
+      qa[ks][1] = v1 ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + 2 * tq) : 0u;
+      qa[ks][2] = v0 ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + 8 + 2 * tq) : 0u;
+      qa[ks][3] = v1 ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + 8 + 2 * tq) : 0u;
+    }
+  }
+  float o[NT][4];
+#pragma unroll
+  for (int i = 0; i < NT; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+  const int lm_mi = lane >> 3, lm_r = lane & 7;
+  // the warp's last query position: key blocks entirely behind it are skipped by this warp (causal)
+  const int wlast = pos0 + min(ntok - 1, (warp * 16 + 15) / GQ);
+
+  for (int kb = 0; kb < nkb; ++kb) {
+    issue(kb + 1);
+    cp_async_wait<1>();
+    __syncthreads();
+    const uint32_t kbuf = sbase + (kb & 1) * STAGEB;
+    const uint32_t vbuf = kbuf + TILEB;
+    const int key0 = kb * kPreKeys;
+    if (key0 <= wlast && warp * 16 / GQ < ntok) {
+      float s[8][4];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
+#pragma unroll
+      for (int kg = 0; kg < 4; ++kg) {
+        const int r = kg * 16 + (lm_mi >> 1) * 8 + lm_r;       // key row this lane addresses
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+          const int c = 2 * ks + (lm_mi & 1);
+          uint32_t b0, b1, b2, b3;
+          ldmatrix_x4(kbuf + r * ROWB + ((c ^ (r & 7)) << 4), b0, b1, b2, b3);
+          mma_bf16_16816(s[2 * kg], qa[ks], b0, b1);
+          mma_bf16_16816(s[2 * kg + 1], qa[ks], b2, b3);
+        }
+      }
+      // mask + online softmax. s[nt][0..1]: row R0, keys key0 + nt * 8 + 2 tq + {0, 1}; s[nt][2..3]: row R1
+      float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+        const int k0 = key0 + nt * 8 + 2 * tq;
+        s[nt][0] = (v0 && k0 <= qpos0) ? s[nt][0] * scale_log2 : -INFINITY;
+        s[nt][1] = (v0 && k0 + 1 <= qpos0) ? s[nt][1] * scale_log2 : -INFINITY;
+        s[nt][2] = (v1 && k0 <= qpos1) ? s[nt][2] * scale_log2 : -INFINITY;
+        s[nt][3] = (v1 && k0 + 1 <= qpos1) ? s[nt][3] * scale_log2 : -INFINITY;
+        mx0 = fmaxf(mx0, fmaxf(s[nt][0], s[nt][1]));
+        mx1 = fmaxf(mx1, fmaxf(s[nt][2], s[nt][3]));
+      }
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+      const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+      // a row with nothing visible yet keeps -inf: subtract 0 instead so that exp2 gives 0, not NaN
+      const float sub0 = mn0 == -INFINITY ? 0.f : mn0, sub1 = mn1 == -INFINITY ? 0.f : mn1;
+      const float corr0 = exp2f(m0 - sub0), corr1 = exp2f(m1 - sub1);
+      float ls0 = 0.f, ls1 = 0.f;
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+        s[nt][0] = exp2f(s[nt][0] - sub0); s[nt][1] = exp2f(s[nt][1] - sub0);
+        s[nt][2] = exp2f(s[nt][2] - sub1); s[nt][3] = exp2f(s[nt][3] - sub1);
+        ls0 += s[nt][0] + s[nt][1];
+        ls1 += s[nt][2] + s[nt][3];
+      }
+      ls0 += __shfl_xor_sync(0xffffffffu, ls0, 1);
+      ls0 += __shfl_xor_sync(0xffffffffu, ls0, 2);
+      ls1 += __shfl_xor_sync(0xffffffffu, ls1, 1);
+      ls1 += __shfl_xor_sync(0xffffffffu, ls1, 2);
+      l0 = l0 * corr0 + ls0;
+      l1 = l1 * corr1 + ls1;
+      m0 = mn0;
+      m1 = mn1;
+#pragma unroll
+      for (int i = 0; i < NT; ++i) { o[i][0] *= corr0; o[i][1] *= corr0; o[i][2] *= corr1; o[i][3] *= corr1; }
+      // O += P V, 16 keys per k-step: P re-used in place as the A operand
+#pragma unroll
+      for (int kg = 0; kg < 4; ++kg) {
+        const uint32_t pa[4] = {pack_bf16(s[2 * kg][0], s[2 * kg][1]), pack_bf16(s[2 * kg][2], s[2 * kg][3]),
+                                pack_bf16(s[2 * kg + 1][0], s[2 * kg + 1][1]), pack_bf16(s[2 * kg + 1][2], s[2 * kg + 1][3])};
+        const int r = kg * 16 + (lm_mi & 1) * 8 + lm_r;
+#pragma unroll
+        for (int dp = 0; dp < NT / 2; ++dp) {
+          const int c = 2 * dp + (lm_mi >> 1);
+          uint32_t b0, b1, b2, b3;
+          ldmatrix_x4_trans(vbuf + r * ROWB + ((c ^ (r & 7)) << 4), b0, b1, b2, b3);
+          mma_bf16_16816(o[2 * dp], pa, b0, b1);
+          mma_bf16_16816(o[2 * dp + 1], pa, b2, b3);
+        }
+      }
+    }
+    __syncthreads();   // every warp is done with this stage before it is refilled
+  }
+  cp_async_wait<0>();
+
+  const float inv0 = l0 > 0.f ? 1.f / l0 : 0.f, inv1 = l1 > 0.f ? 1.f / l1 : 0.f;
+  if (v0) {
+    __nv_bfloat16* op = out + static_cast<long long>(row0 + t0) * ld_out + (hkv * GQ + R0 % GQ) * HD;
+#pragma unroll
+    for (int i = 0; i < NT; ++i)
+      *reinterpret_cast<uint32_t*>(op + i * 8 + 2 * tq) = pack_bf16(o[i][0] * inv0, o[i][1] * inv0);
+  }
+  if (v1) {
+    __nv_bfloat16* op = out + static_cast<long long>(row0 + t1) * ld_out + (hkv * GQ + R1 % GQ) * HD;
+#pragma unroll
+    for (int i = 0; i < NT; ++i)
+      *reinterpret_cast<uint32_t*>(op + i * 8 + 2 * tq) = pack_bf16(o[i][2] * inv1, o[i][3] * inv1);
+  }
+}
+
+template <int HD, int GQ>
+static int launch_prefill(const void* q, long long ld_q, const void* kc, const void* vc, const int* bt, int max_blocks,
+                          const void* tiles, int n_tiles, int block_size, int n_kv, float scale, void* out,
+                          long long ld_out, cudaStream_t stream) {
+  const size_t smem = 2 * 2 * static_cast<size_t>(kPreKeys) * HD * 2;
+  static PerDeviceOnce configured;
+  const int crc = configured.run([] {
+    return static_cast<int>(cudaFuncSetAttribute(prefill_attn_kernel<HD, GQ>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 96 * 1024));
+  });
+  if (crc != 0) return crc;
+  dim3 grid(n_tiles, n_kv);
+  prefill_attn_kernel<HD, GQ><<<grid, 128, smem, stream>>>(
+      static_cast<const __nv_bfloat16*>(q), ld_q, static_cast<const __nv_bfloat16*>(kc),
+      static_cast<const __nv_bfloat16*>(vc), bt, max_blocks, static_cast<const int4*>(tiles), block_size, n_kv,
+      scale * 1.4426950408889634f, static_cast<__nv_bfloat16*>(out), ld_out);
+  return static_cast<int>(cudaGetLastError());
+}
+
 template <int HD, int GQ>
 static int launch_attn(const void* q, long long ld_q, const void* kc, const void* vc, const int* bt, int max_blocks,
                        const int* bt_row, const int* ctx_len, int block_size, int T, int n_kv, float scale, int splits,
@@ -332,5 +537,42 @@ extern "C" int dmoe_paged_attention(const void* q, long long ld_q, const void* k
     }
   }
 #undef DMOE_ATTN
+  return -11;
+}
+
+// Tokens per tile of dmoe_prefill_attention for a query group of n_q / n_kv heads.
+extern "C" int dmoe_prefill_tile_tokens(int n_q, int n_kv) {
+  if (n_kv < 1 || n_q % n_kv != 0) return 0;
+  const int gq = n_q / n_kv;
+  return (gq == 1 || gq == 2 || gq == 4 || gq == 8) ? kPreRows / gq : 0;
+}
+
+extern "C" int dmoe_prefill_attention(const void* q, long long ld_q, const void* kcache, const void* vcache,
+                                      const int* block_tables, int max_blocks, const void* tiles, int n_tiles,
+                                      int block_size, int n_q, int n_kv, int hd, float scale, void* out, long long ld_out,
+                                      void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (n_tiles == 0) return 0;
+  if (n_kv < 1 || n_q % n_kv != 0 || n_kv > 65535 || n_tiles < 0 || block_size < 1 || tiles == nullptr) return -10;
+  const int gq = n_q / n_kv;
+#define DMOE_PRE(HD_, GQ_)                                                                                     \
+  return launch_prefill<HD_, GQ_>(q, ld_q, kcache, vcache, block_tables, max_blocks, tiles, n_tiles, block_size, \
+                                  n_kv, scale, out, ld_out, stream)
+  if (hd == 128) {
+    switch (gq) {
+      case 1: DMOE_PRE(128, 1);
+      case 2: DMOE_PRE(128, 2);
+      case 4: DMOE_PRE(128, 4);
+      case 8: DMOE_PRE(128, 8);
+    }
+  } else if (hd == 64) {
+    switch (gq) {
+      case 1: DMOE_PRE(64, 1);
+      case 2: DMOE_PRE(64, 2);
+      case 4: DMOE_PRE(64, 4);
+      case 8: DMOE_PRE(64, 8);
+    }
+  }
+#undef DMOE_PRE
   return -11;
 }

@@ -58,6 +58,12 @@ typedef struct DmoeGemm {
   void* kcache;
   void* vcache;
   int n_q, n_kv, hd, rope_max_pos;
+  // --- work distribution ---
+  // streamk != 0 (with splitk <= 1, ws and counters given): the K-block iterations of all tiles are dealt out in one
+  // equal contiguous share per CTA instead of whole tiles, so no SM idles in a last partial wave; tiles that straddle
+  // a share boundary are reduced through ws (2 slots of 128 x bn fp32 per accumulator and CTA). n_counters: ints
+  // available at `counters` (0 = 4096); one per tile is needed.
+  int streamk, n_counters;
 } DmoeGemm;
 
 int dmoe_gemm(const DmoeGemm* desc, void* stream);
@@ -86,6 +92,14 @@ int dmoe_paged_attention(const void* q, long long ld_q, const void* kcache, cons
                          const int* block_tables, int max_blocks, const int* bt_row, const int* ctx_len, int block_size,
                          int T, int n_q, int n_kv, int hd, float scale, int splits, void* out, long long ld_out,
                          float* workspace, void* stream);
+
+// Tiled causal attention for prompt tokens: CTA column i handles tiles[i] = int4 {first row in q / out, tokens
+// (<= dmoe_prefill_tile_tokens), block-table row, position of the first token}; the tokens of a tile are consecutive
+// rows at consecutive positions of one sequence, whose K / V (own tokens included) are already in the paged cache.
+int dmoe_prefill_tile_tokens(int n_q, int n_kv);
+int dmoe_prefill_attention(const void* q, long long ld_q, const void* kcache, const void* vcache,
+                           const int* block_tables, int max_blocks, const void* tiles, int n_tiles, int block_size,
+                           int n_q, int n_kv, int hd, float scale, void* out, long long ld_out, void* stream);
 
 // ---- routing (moe.cu) -------------------------------------------------------------------------------
 // (RMSNorm ->) gate -> softmax -> top-k (-> renormalise); counts[e] += tokens routed to e (may be NULL).

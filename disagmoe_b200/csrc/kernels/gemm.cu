@@ -26,6 +26,7 @@
 
 #include "dmoe_kernels.h"
 #include "sm100.cuh"
+#include "work_walker.cuh"
 
 namespace dmoe {
 
@@ -52,6 +53,7 @@ struct GemmArgs {
   const int4* recs;        // combine: per input row {dst_rank, dst_row, weight (fp32 bits), unused}
   void* const* bases;      // combine: destination base pointer per rank
   int splitk;
+  int streamk;   // 1: stream-K work distribution (see work_walker.cuh); splitk is then 1
   float* ws;
   int* counters;
   int* status;
@@ -112,56 +114,6 @@ struct Cfg {
   static_assert(kStages >= 3, "pipeline too shallow");
 };
 
-// Walks the persistent tile list. A group (expert) owns S segments of token rows, one per source; its token
-// tiles enumerate the segments one after the other, so all sources' tokens of an expert meet the same weight tile
-// back to back. Tiles of group g: for m in [0, MT) for n in [0, ntn_g) for ks in [0, splitk).
-struct TileWalker {
-  const int* seg_start;  // shared memory, [S * G] absolute first row of segment (s, g)
-  const int* seg_cnt;    // shared memory, [S * G]
-  int G, S, MT, splitk, BN;
-  int g, base;           // tiles of group g start at linear id `base`
-  int ntn;
-  __device__ void init(const int* s_start, const int* s_cnt, int G_, int S_, int MT_, int splitk_, int BN_) {
-    seg_start = s_start; seg_cnt = s_cnt; G = G_; S = S_; MT = MT_; splitk = splitk_; BN = BN_;
-    g = -1; base = 0; ntn = 0;
-    advance_group();
-  }
-  __device__ void advance_group() {
-    ++g;
-    ntn = 0;
-    if (g < G)
-      for (int s = 0; s < S; ++s) ntn += (seg_cnt[s * G + g] + BN - 1) / BN;
-  }
-  // Positions on linear tile id `tile` (monotonically increasing across calls). False when past the end.
-  // row0 / ntok: first token row and number of valid tokens of the tile.
-  __device__ bool seek(int tile, int& m, int& n, int& ks, int& row0, int& ntok) {
-    while (g < G) {
-      const int ntiles = MT * ntn * splitk;
-      if (tile < base + ntiles) {
-        int r = tile - base;
-        ks = r % splitk; r /= splitk;
-        n = r % ntn;
-        m = r / ntn;
-        int nl = n;
-        for (int s = 0; s < S; ++s) {
-          const int c = seg_cnt[s * G + g];
-          const int t = (c + BN - 1) / BN;
-          if (nl < t) {
-            row0 = seg_start[s * G + g] + nl * BN;
-            ntok = min(BN, c - nl * BN);
-            return true;
-          }
-          nl -= t;
-        }
-        return false;  // unreachable
-      }
-      base += ntiles;
-      advance_group();
-    }
-    return false;
-  }
-};
-
 __device__ __forceinline__ int ld_acquire_sys(const int* p) {
   int v;
   asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -194,7 +146,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
   const int lane = threadIdx.x & 31;
   const int MT = (a.F + kBM - 1) / kBM;
   const int kblocks = (a.K + kBK - 1) / kBK;
-  const int kb_per = (kblocks + a.splitk - 1) / a.splitk;
   // the producer may legitimately sit in a peer-flag wait (all-gather prologue): the warps behind it must outlast it
   const long long bar_budget = DMOE_WAIT_CYCLES + (a.shard_rows > 0 ? a.flag_cycles : 0);
 
@@ -269,8 +220,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      TileWalker tw;
-      tw.init(s_start, s_cnt, a.G, S, MT, a.splitk, BN);
+      WorkWalker tw;
+      tw.init(s_start, s_cnt, a.G, S, MT, BN, kblocks, a.splitk, a.streamk, blockIdx.x, gridDim.x);
       if (a.n_wait > 0) asm volatile("fence.proxy.async;" ::: "memory");  // peers' generic stores -> TMA reads
       const uint64_t pol_w = l2_policy_evict_first();
       const uint64_t pol_x = l2_policy_evict_last();
@@ -279,12 +230,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
       bool ok = true;
       unsigned long long shard_ready = 0;     // bit s: shard s of X has landed (all-gather prologue)
       const int shard_want = (a.shard_rows > 0) ? *a.wait_epoch + 1 : 0;
-      for (int tile = blockIdx.x; ok; tile += gridDim.x) {
-        int m, n, ks, xrow, ntok_;
-        if (!tw.seek(tile, m, n, ks, xrow, ntok_)) break;
-        const int wrow = tw.g * a.w_rows + m * kBM;
-        const int kb0 = ks * kb_per;
-        const int kb1 = min(kblocks, kb0 + kb_per);
+      WorkUnit u;
+      while (ok && tw.next(u)) {
+        const int xrow = u.row0, ntok_ = u.ntok;
+        const int wrow = u.g * a.w_rows + u.m * kBM;
+        const int kb0 = u.kb0, kb1 = u.kb1;
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_word)) { ok = false; break; }
           const uint32_t fb = smem_u32(&full_bar[stage]);
@@ -325,23 +275,24 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      TileWalker tw;
-      tw.init(s_start, s_cnt, a.G, S, MT, a.splitk, BN);
-      constexpr uint32_t idesc = umma_idesc_bf16(kBM, BN);
+      WorkWalker tw;
+      tw.init(s_start, s_cnt, a.G, S, MT, BN, kblocks, a.splitk, a.streamk, blockIdx.x, gridDim.x);
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok; tile += gridDim.x, ++it) {
-        int m, n, ks, row0_, ntok_;
-        if (!tw.seek(tile, m, n, ks, row0_, ntok_)) break;
+      WorkUnit u;
+      for (; ok && tw.next(u); ++it) {
         const int buf = it & 1;
         const uint32_t bphase = (it >> 1) & 1;
         if (!mbar_wait(smem_u32(&tempty_bar[buf]), bphase ^ 1, abort_word, bar_budget)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d0 = tmem_base + buf * C::kAccCols;
-        const int kb0 = ks * kb_per;
-        const int kb1 = min(kblocks, kb0 + kb_per);
+        // a ragged token tile only pays for the MMA columns it has (N is a run-time field of the instruction)
+        int n_eff = (u.ntok + 15) & ~15;
+        n_eff = n_eff < 16 ? 16 : (n_eff > BN ? BN : n_eff);
+        const uint32_t idesc = umma_idesc_bf16(kBM, n_eff);
+        const int kb0 = u.kb0, kb1 = u.kb1;
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(smem_u32(&full_bar[stage]), phase, abort_word, bar_budget)) { ok = false; break; }
           tc_fence_after();
@@ -369,13 +320,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
     const int q = warp & 3;                 // TMEM lane quarter this warp may read
     const int row = q * 32 + lane;          // accumulator lane = feature within the tile
     const int et = threadIdx.x - 64;        // 0..127
-    TileWalker tw;
-    tw.init(s_start, s_cnt, a.G, S, MT, a.splitk, BN);
+    WorkWalker tw;
+    tw.init(s_start, s_cnt, a.G, S, MT, BN, kblocks, a.splitk, a.streamk, blockIdx.x, gridDim.x);
+    constexpr size_t kSlotF4 = static_cast<size_t>(C::kNumA) * (BN / 4) * kBM;   // float4 per workspace slot
     int it = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; ok; tile += gridDim.x, ++it) {
-      int m, n, ks, tok_base, ntok;
-      if (!tw.seek(tile, m, n, ks, tok_base, ntok)) break;
+    WorkUnit u;
+    for (; ok && tw.next(u); ++it) {
+      const int m = u.m, tok_base = u.row0, ntok = u.ntok;
       const int buf = it & 1;
       const uint32_t bphase = (it >> 1) & 1;
       if (!mbar_wait(smem_u32(&tfull_bar[buf]), bphase, abort_word, bar_budget)) { ok = false; break; }
@@ -383,23 +335,28 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
       const uint32_t t0 = tmem_base + buf * C::kAccCols + (static_cast<uint32_t>(q * 32) << 16);
       const int f = m * kBM + row;
       const bool f_ok = f < a.F;
+      const int nchunk = (ntok + 31) / 32;        // 32-token chunks that hold valid tokens
 
-      bool reduce_here = true;       // split-K: only the last arriver runs the real epilogue
-      const int tile_mn = tile / a.splitk;
-      if (a.splitk > 1) {
-        // park this split's partial tile: ws[tile_mn][ks][c4][row][4]
-        float4* wsp = reinterpret_cast<float4*>(a.ws) + (static_cast<size_t>(tile_mn) * a.splitk + ks) * (BN / 4) * kBM;
+      // A tile computed by several units (split-K, or a stream-K share boundary inside the tile): every unit parks
+      // its fp32 partial accumulator(s) in its workspace slot; the last one to arrive adds them all up and runs the
+      // epilogue. Slot layout: [accumulator (gate, up)][chunk of 4 tokens][feature row] float4.
+      const bool shared_tile = u.ncontrib > 1;
+      if (shared_tile) {
+        float4* wsp = reinterpret_cast<float4*>(a.ws) + static_cast<size_t>(u.slot) * kSlotF4;
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t v[32];
-          tmem_ld32(t0 + c * 32, v);
-          tmem_ld_wait();
+        for (int c = 0; c < nchunk; ++c) {
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            float4 o;
-            o.x = __uint_as_float(v[4 * j]); o.y = __uint_as_float(v[4 * j + 1]);
-            o.z = __uint_as_float(v[4 * j + 2]); o.w = __uint_as_float(v[4 * j + 3]);
-            wsp[(c * 8 + j) * kBM + row] = o;
+          for (int h = 0; h < C::kNumA; ++h) {
+            uint32_t v[32];
+            tmem_ld32(t0 + h * BN + c * 32, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              float4 o;
+              o.x = __uint_as_float(v[4 * j]); o.y = __uint_as_float(v[4 * j + 1]);
+              o.z = __uint_as_float(v[4 * j + 2]); o.w = __uint_as_float(v[4 * j + 3]);
+              wsp[(static_cast<size_t>(h) * (BN / 4) + c * 8 + j) * kBM + row] = o;
+            }
           }
         }
         tc_fence_before();
@@ -407,20 +364,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
         __threadfence();
         named_bar_sync(1, kEpiThreads);
         if (et == 0) {
-          const int old = atomicAdd(&a.counters[tile_mn], 1);
-          const int last = (old == a.splitk - 1);
-          if (last) a.counters[tile_mn] = 0;  // self-resetting for the next launch
+          const int old = atomicAdd(&a.counters[u.tile], 1);
+          const int last = (old == u.ncontrib - 1);
+          if (last) a.counters[u.tile] = 0;  // self-resetting for the next launch
           *last_flag = last;
         }
         named_bar_sync(1, kEpiThreads);
-        reduce_here = (*last_flag != 0);
+        const bool reduce_here = (*last_flag != 0);
         named_bar_sync(1, kEpiThreads);      // everyone has read last_flag before the next tile rewrites it
-        if (reduce_here) __threadfence();
+        if (!reduce_here) continue;
+        __threadfence();
       }
-      if (a.splitk > 1 && !reduce_here) continue;
 
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = 0; c < nchunk; ++c) {             // chunks past the last valid token are never read
         float acc[32];
         const int jmax = min(32, ntok - c * 32);
         // Residual rows of this chunk are requested first, so that they travel together with the partial tiles /
@@ -436,38 +393,47 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
             r[j] = (j < jmax) ? __bfloat162float(a.R[t * a.ldr + f]) : 0.f;
           }
         }
-        if (a.splitk > 1) {
+        if (shared_tile) {
+          float up[(EPI == EPI_SWIGLU) ? 32 : 1];
 #pragma unroll
           for (int j = 0; j < 32; ++j) acc[j] = 0.f;
-          // two splits' worth of loads (16 x 16 bytes per thread) are in flight before the first add: the chain of
-          // L2 round trips of the last arriver is half as long as with one split at a time
-          for (int s = 0; s < a.splitk; s += 2) {
-            const float4* w0 = reinterpret_cast<const float4*>(a.ws) +
-                               (static_cast<size_t>(tile_mn) * a.splitk + s) * (BN / 4) * kBM;
-            const bool two = s + 1 < a.splitk;
-            const float4* w1 = two ? w0 + (BN / 4) * kBM : w0;
-            float4 o0[8], o1[8];
+          if (EPI == EPI_SWIGLU) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) up[j] = 0.f;
+          }
+          for (int s = 0; s < u.ncontrib; ++s) {
+            const float4* w0 = reinterpret_cast<const float4*>(a.ws) + static_cast<size_t>(tw.contrib_slot(u, s)) * kSlotF4;
+            float4 o0[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) o0[j] = __ldcg(&w0[(c * 8 + j) * kBM + row]);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) o1[j] = two ? __ldcg(&w1[(c * 8 + j) * kBM + row]) : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
             for (int j = 0; j < 8; ++j) {
-              acc[4 * j] += o0[j].x + o1[j].x; acc[4 * j + 1] += o0[j].y + o1[j].y;
-              acc[4 * j + 2] += o0[j].z + o1[j].z; acc[4 * j + 3] += o0[j].w + o1[j].w;
+              acc[4 * j] += o0[j].x; acc[4 * j + 1] += o0[j].y; acc[4 * j + 2] += o0[j].z; acc[4 * j + 3] += o0[j].w;
             }
+            if (EPI == EPI_SWIGLU) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) o0[j] = __ldcg(&w0[(static_cast<size_t>(BN / 4) + c * 8 + j) * kBM + row]);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                up[4 * j] += o0[j].x; up[4 * j + 1] += o0[j].y; up[4 * j + 2] += o0[j].z; up[4 * j + 3] += o0[j].w;
+              }
+            }
+          }
+          if (EPI == EPI_SWIGLU) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) acc[j] = (acc[j] / (1.f + __expf(-acc[j]))) * up[j];
           }
         } else {
           uint32_t v[32];
           tmem_ld32(t0 + c * 32, v);
           if (EPI == EPI_SWIGLU) {
-            uint32_t u[32];
-            tmem_ld32(t0 + BN + c * 32, u);
+            uint32_t uu[32];
+            tmem_ld32(t0 + BN + c * 32, uu);
             tmem_ld_wait();
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               const float g = __uint_as_float(v[j]);
-              const float up = __uint_as_float(u[j]);
+              const float up = __uint_as_float(uu[j]);
               acc[j] = (g / (1.f + __expf(-g))) * up;
             }
           } else {
@@ -475,7 +441,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
 #pragma unroll
             for (int j = 0; j < 32; ++j) acc[j] = __uint_as_float(v[j]);
           }
-          if (c == BN / 32 - 1) {
+          if (c == nchunk - 1) {
             // all of this thread's TMEM reads are done: hand the accumulator buffer back to the MMA warp
             tc_fence_before();
             mbar_arrive(smem_u32(&tempty_bar[buf]));
@@ -740,6 +706,9 @@ extern "C" int dmoe_gemm(const DmoeGemm* d, void* stream_) {
   }
   if (splitk > 1 && (epi == EPI_SWIGLU || d->offs != nullptr || d->S > 0 || d->group_regions || d->ws == nullptr || d->counters == nullptr)) return -12;
   if (splitk > 1 && dmoe_gemm_workspace_bytes(d->T, d->F, bn, splitk) > d->ws_bytes) return -13;
+  // stream-K: one contiguous share of the K-block iterations per CTA; needs two partial-tile slots per CTA and one
+  // counter per tile. Where the scratch is too small the launch quietly keeps whole tiles (a performance matter only).
+  int streamk = (d->streamk != 0 && splitk == 1 && d->ws != nullptr && d->counters != nullptr) ? 1 : 0;
   if (epi == EPI_COMBINE && (d->recs == nullptr || d->bases == nullptr)) return -14;
 
   GemmArgs a;
@@ -750,7 +719,7 @@ extern "C" int dmoe_gemm(const DmoeGemm* d, void* stream_) {
   a.R = static_cast<const __nv_bfloat16*>(d->R); a.ldr = d->ldr;
   a.recs = static_cast<const int4*>(d->recs);
   a.bases = static_cast<void* const*>(d->bases);
-  a.splitk = splitk; a.ws = static_cast<float*>(d->ws); a.counters = d->counters;
+  a.splitk = splitk; a.streamk = 0; a.ws = static_cast<float*>(d->ws); a.counters = d->counters;
   a.status = d->status;
   a.seg_cnt = d->seg_cnt; a.S = d->S; a.seg_cap = d->seg_cap;
   a.wait_flags = d->wait_flags; a.n_wait = d->n_wait; a.wait_epoch = d->wait_epoch;
@@ -800,6 +769,13 @@ extern "C" int dmoe_gemm(const DmoeGemm* d, void* stream_) {
   long long max_tiles = mt * ((d->T + bn - 1) / bn + ((d->offs || d->S > 0 || d->group_regions) ? d->G * (d->S > 0 ? d->S : 1) : 0)) * splitk;
   if (max_tiles > (1 << 30)) max_tiles = 1 << 30;
   const int mtiles = static_cast<int>(max_tiles);
+  if (streamk) {
+    const long long grid = mtiles < num_sms() ? mtiles : num_sms();
+    const long long slot_bytes = static_cast<long long>(epi == EPI_SWIGLU ? 2 : 1) * kBM * bn * 4;
+    const long long n_counters = d->n_counters > 0 ? d->n_counters : 4096;
+    if (grid * 2 * slot_bytes > d->ws_bytes || max_tiles / splitk > n_counters) streamk = 0;
+  }
+  a.streamk = streamk;
 
 #define DMOE_LAUNCH(BN_, EPI_) return launch<BN_, EPI_>(tmW, tmX, a, mtiles, stream)
   if (epi == EPI_PLAIN) {

@@ -1,14 +1,68 @@
 #include "muhelper.h"
 
+#include <dlfcn.h>
+
+#include <algorithm>
+
 namespace dmoe {
 
 // ------------------------------------------------------------------------------------------------ batches
+namespace {
+// dmoe_gather_ptrs of the package's kernel library (lib/libdmoe_kernels.so next to this module): dst[i] = the bf16 row
+// at device address ptrs[i]. Resolved once; nullptr when the library is not there (CPU-only installs).
+typedef int (*gather_ptrs_fn)(const void*, void*, long long, int, int, void*);
+
+gather_ptrs_fn kernel_gather() {
+  static gather_ptrs_fn fn = [] {
+    Dl_info info;
+    if (dladdr(reinterpret_cast<void*>(&set_helper_error), &info) == 0 || info.dli_fname == nullptr)
+      return static_cast<gather_ptrs_fn>(nullptr);
+    std::string dir(info.dli_fname);
+    const auto slash = dir.rfind('/');
+    dir = slash == std::string::npos ? std::string(".") : dir.substr(0, slash);
+    for (const char* rel : {"/lib/libdmoe_kernels.so", "/../../lib/libdmoe_kernels.so"}) {
+      if (void* h = dlopen((dir + rel).c_str(), RTLD_NOW | RTLD_LOCAL))
+        if (void* f = dlsym(h, "dmoe_gather_ptrs")) return reinterpret_cast<gather_ptrs_fn>(f);
+    }
+    return static_cast<gather_ptrs_fn>(nullptr);
+  }();
+  return fn;
+}
+}  // namespace
+
 static torch::Tensor gather_rows(const std::vector<TensorBatch>& batches, const std::vector<int>& order_src_of_dst) {
   // order_src_of_dst[r] = index (in the concatenation of all batches) of the row that lands at r
   std::vector<torch::Tensor> parts;
   for (auto& b : batches)
     if (b.data.defined() && b.data.size(0) > 0) parts.push_back(b.data);
   if (parts.empty()) return torch::Tensor();
+  const auto& first = parts[0];
+  bool device_rows = first.is_cuda() && first.scalar_type() == torch::kBFloat16 && first.dim() == 2 &&
+                     first.size(1) % 8 == 0 && kernel_gather() != nullptr;
+  for (auto& p : parts)
+    device_rows = device_rows && p.is_cuda() && p.scalar_type() == torch::kBFloat16 && p.dim() == 2 &&
+                  p.size(1) == first.size(1) && p.stride(1) == 1 && p.get_device() == first.get_device();
+  if (device_rows) {
+    // Row gather by the package's own kernel from a table of row addresses: no concatenated copy of all batches and
+    // no host synchronisation (the reference builds the same table but waits for the stream, csrc/cuda_ops/permute.cu:
+    // 144-152). The table goes up through pinned memory on the engine thread's (default) stream, where the kernel runs.
+    const int64_t n = static_cast<int64_t>(order_src_of_dst.size());
+    const int64_t H = first.size(1);
+    std::vector<int64_t> start(parts.size() + 1, 0);
+    for (size_t i = 0; i < parts.size(); ++i) start[i + 1] = start[i] + parts[i].size(0);
+    auto table = torch::empty({n}, torch::TensorOptions().dtype(torch::kInt64).pinned_memory(true));
+    int64_t* tp = table.data_ptr<int64_t>();
+    for (int64_t r = 0; r < n; ++r) {
+      const int64_t src = order_src_of_dst[r];
+      const size_t b = std::upper_bound(start.begin(), start.end(), src) - start.begin() - 1;
+      tp[r] = reinterpret_cast<int64_t>(parts[b].data_ptr()) + (src - start[b]) * parts[b].stride(0) * 2;
+    }
+    auto table_dev = table.to(first.device(), /*non_blocking=*/true);
+    auto out = torch::empty({n, H}, first.options());
+    const int rc = kernel_gather()(table_dev.data_ptr(), out.data_ptr(), H, static_cast<int>(n), static_cast<int>(H), nullptr);
+    DMOE_CHECK(rc == 0, "dmoe_gather_ptrs failed with code " + std::to_string(rc));
+    return out;
+  }
   auto all = parts.size() == 1 ? parts[0] : torch::cat(parts, 0);
   auto idx = torch::tensor(std::vector<int64_t>(order_src_of_dst.begin(), order_src_of_dst.end()),
                            torch::TensorOptions().dtype(torch::kInt64))

@@ -103,8 +103,9 @@ class CUDAGraphAttnExecutor:
         self.model_config, self.cache_config, self.attn_executor = model_config, cache_config, attn_executor
         self.max_batch_size = model_config.max_batch_size_attn
         self.graph_batch_sizes = graph_batch_sizes(self.max_batch_size, model_config.graph_stride, model_config.ep_size)
-        self.graphs: Dict[Tuple[int, int], torch.cuda.CUDAGraph] = {}
-        self.outputs: Dict[Tuple[int, int], Tuple[Tensor, Tensor, Tensor]] = {}
+        self.graphs: Dict[Tuple[int, int, int], torch.cuda.CUDAGraph] = {}      # (layer, bucket, partial rows)
+        self.outputs: Dict[Tuple[int, int, int], Tuple[Tensor, Tensor, Tensor]] = {}
+        self.static_parts: Optional[Tensor] = None
 
     def create_cuda_graph_buffers(self) -> None:
         cfg, dev, B = self.model_config, self.attn_executor.device, self.max_batch_size
@@ -119,41 +120,63 @@ class CUDAGraphAttnExecutor:
         return AttnMeta(self.static_positions[:b], self.static_slots[:b], self.static_block_table, None,
                         self.static_ctx[:b], num_decode_tokens=b, max_ctx=self.model_config.max_seq_len)
 
-    def capture(self) -> None:
+    def _capture_one(self, l: int, b: int, P: int) -> None:
+        """Warm-up and capture of layer l at batch bucket b with P partial rows per token added to the residual."""
         ex = self.attn_executor
+        if P > 0 and (self.static_parts is None or self.static_parts.shape[1] < P):
+            self.static_parts = torch.zeros(self.max_batch_size, P, self.model_config.hidden_size,
+                                            dtype=self.attn_executor.dtype, device=self.attn_executor.device)
+        parts = self.static_parts[:b, :P] if P > 0 else None
+        meta = self._meta(b)
         side = torch.cuda.Stream(ex.device)
-        for l in ex.layer_ids:
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            ex.execute(l, meta.positions, self.static_input[:b], meta, parts)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            out = ex.execute(l, meta.positions, self.static_input[:b], meta, parts)
+        self.graphs[(l, b, P)] = g
+        self.outputs[(l, b, P)] = out
+
+    def capture(self) -> None:
+        """Captures every (layer, bucket) graph up front for batches that carry no partial rows; graphs for batches
+        with partial rows (top-k expert outputs + carried residual) are captured the first time they are needed."""
+        for l in self.attn_executor.layer_ids:
             for b in self.graph_batch_sizes:
-                meta = self._meta(b)
-                side.wait_stream(torch.cuda.current_stream())
-                with torch.cuda.stream(side):
-                    ex.execute(l, meta.positions, self.static_input[:b], meta)
-                torch.cuda.current_stream().wait_stream(side)
-                torch.cuda.synchronize()
-                g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g):
-                    out = ex.execute(l, meta.positions, self.static_input[:b], meta)
-                self.graphs[(l, b)] = g
-                self.outputs[(l, b)] = out
+                self._capture_one(l, b, 0)
         torch.cuda.synchronize()
 
-    def run(self, layer_id: int, positions: Tensor, hidden_states: Tensor, meta: AttnMeta) -> Tuple[Tensor, Tensor, Tensor, Tensor]:
+    def fits(self, n: int) -> bool:
+        return 0 < n <= self.graph_batch_sizes[-1]
+
+    def run(self, layer_id: int, positions: Tensor, hidden_states: Tensor, meta: AttnMeta,
+            parts: Optional[Tensor] = None) -> Tuple[Tensor, Tensor, Tensor, Tensor]:
         """Copies the inputs into the static buffers, replays the bucket's graph; returns (expert input, weights, ids,
-        residual) views of the first ``n`` rows."""
+        residual) views of the first ``n`` rows (None where the layer has no router). The views alias static buffers
+        that the next replay of the same graph overwrites."""
         n = hidden_states.shape[0]
         _, b = get_graph_batch_size(n, self.graph_batch_sizes)
+        P = 0 if parts is None else parts.shape[1]
+        # capture warm-ups run the layer for real: slots = -1 and ctx = 0 keep them away from the KV cache
+        self.static_slots[:b].fill_(-1)
+        self.static_ctx[:b].fill_(0)
+        if (layer_id, b, P) not in self.graphs:
+            self._capture_one(layer_id, b, P)
         self.static_input[:n].copy_(hidden_states)
+        if P > 0:
+            self.static_parts[:n, :P].copy_(parts)
         self.static_positions[:n].copy_(positions)
         self.static_slots[:n].copy_(meta.slots)
-        self.static_slots[n:b].fill_(-1)
         self.static_ctx[:n].copy_(meta.ctx_len)
-        self.static_ctx[n:b].fill_(0)
         rows = meta.bt_row.long() if meta.bt_row is not None else torch.arange(n, device=hidden_states.device)
         w = meta.block_tables.shape[1]
         self.static_block_table[:n, :w].copy_(meta.block_tables.index_select(0, rows))
-        self.graphs[(layer_id, b)].replay()
-        y, tw, ti = self.outputs[(layer_id, b)]
-        return y[:n], tw[:n], ti[:n], self.static_input[:n]
+        self.graphs[(layer_id, b, P)].replay()
+        y, tw, ti = self.outputs[(layer_id, b, P)]
+        cut = lambda t: None if t is None else t[:n]
+        return cut(y), cut(tw), cut(ti), self.static_input[:n]
 
 
 class ExpertsExecutor(Executor):

@@ -48,6 +48,10 @@ class StepBuffers:
         self.parts_base = torch.tensor([self.parts.data_ptr()], dtype=torch.int64, device=device)
         self.next_ids = z(cap, dt=torch.int32)
         self.logits = z(cap, cfg.vocab_size, dt=torch.float32)
+        # prompt segments of the current step for the tiled causal attention kernel (filled by prefill())
+        self.prefill_tiles = z(cap, 4, dt=torch.int32)
+        self.ctx_len_decode = z(cap, dt=torch.int32)
+        self.n_prefill_tiles = 0
 
 
 class FusedModelExecutor:
@@ -111,7 +115,8 @@ class FusedModelExecutor:
     def _forward(self, buf: StepBuffers, T: int, max_ctx: int, want_logits: bool):
         cfg = self.cfg
         meta = AttnMeta(buf.positions[:T], buf.slots[:T], self.block_tables, buf.bt_row[:T], buf.ctx_len[:T],
-                        max_ctx=max_ctx)
+                        max_ctx=max_ctx, prefill_tiles=buf.prefill_tiles, n_prefill_tiles=buf.n_prefill_tiles,
+                        ctx_len_decode=buf.ctx_len_decode[:T])
         resid = buf.resid[:T]
         F.embed(buf.ids[:T], self.embed_w, out=resid)
         parts = None
@@ -152,8 +157,22 @@ class FusedModelExecutor:
         """Eager pass over prompt tokens (any number of sequences packed together). Host tensors in, device out."""
         T = ids.shape[0]
         assert T <= self.prefill_buf.cap, f"{T} prefill tokens exceed the buffer ({self.prefill_buf.cap})"
-        self._fill(self.prefill_buf, T, ids, positions, slots, ctx_len, bt_row)
-        return self._forward(self.prefill_buf, T, int(ctx_len.max()), want_logits)
+        buf = self.prefill_buf
+        self._fill(buf, T, ids, positions, slots, ctx_len, bt_row)
+        buf.n_prefill_tiles = 0
+        if self.device.type == "cuda":
+            a0 = self.attn[self.layer_ids[0]]
+            tiles, covered = F.build_prefill_tiles(bt_row, positions, F.prefill_tile_tokens(a0.num_heads, a0.num_kv_heads))
+            if len(tiles):
+                buf.n_prefill_tiles = len(tiles)
+                buf.prefill_tiles[:len(tiles)].copy_(tiles, non_blocking=True)
+                cd = torch.as_tensor(ctx_len).clone()
+                cd[covered] = 0
+                buf.ctx_len_decode[:T].copy_(cd, non_blocking=True)
+        try:
+            return self._forward(buf, T, int(ctx_len.max()), want_logits)
+        finally:
+            buf.n_prefill_tiles = 0      # the decode path (and its CUDA graphs) shares the buffers when they are one object
 
     def capture(self, sizes: Optional[List[int]] = None) -> None:
         """Warm-up (compiles nothing, but sizes scratch buffers and sets kernel attributes) and graph capture."""

@@ -586,6 +586,10 @@ class Controller:
     def worker_errors(self) -> Dict[int, Optional[str]]:
         return self._all("check_error")
 
+    def graph_attention_steps(self) -> Dict[int, int]:
+        """Per worker: attention steps that replayed a CUDA graph (0 unless ``enable_cuda_graph_attn`` is set)."""
+        return self._all("graph_attention_steps")
+
     def set_schedule_policy(self, policy: str) -> None:
         self._all("set_schedule_policy", policy)
 

@@ -65,6 +65,20 @@ class InitCoreArgs:
     tp_master_port: int = 0
 
 
+class _EngineLayers:
+    """The engine's attention layers and KV caches behind the executor interface that ``CUDAGraphAttnExecutor`` drives."""
+
+    def __init__(self, engine: "Engine", layer_ids):
+        self.engine, self.layer_ids = engine, list(layer_ids)
+        self.device, self.dtype = engine.device, engine.dtype
+
+    def execute(self, layer_id, positions, hidden_states, meta, parts=None):
+        e = self.engine
+        meta.positions = positions
+        out = e.attn_layers[layer_id].forward(hidden_states, parts, (e.kv_cache[layer_id][0], e.kv_cache[layer_id][1]), meta)
+        return out.expert_input, out.topk_weights, out.topk_ids
+
+
 class Engine:
     def __init__(self, device_id: int = 0, device: str = "cpu"):
         self.device_id = device_id
@@ -195,6 +209,14 @@ class Engine:
                              for l in attn_layers}
             self.block_mgr = C.BlockManager(cc.block_size, nb - cc.num_reserved_blocks, cc.num_reserved_blocks, 0)
             self.max_blocks = (cfg.max_seq_len + cc.block_size - 1) // cc.block_size
+            self.graph_attn = None
+            if cfg.enable_cuda_graph_attn and dev.type == "cuda" and getattr(self, "tp_size", 1) == 1 and attn_layers:
+                # decode-only attention batches replay one CUDA graph per (layer, batch-size bucket), captured on
+                # first use (reference: disagmoe/frontend/engine.py:325-383, disagmoe/executor/executor.py:118-347)
+                from ..executor.executor import CUDAGraphAttnExecutor
+                self.graph_attn = CUDAGraphAttnExecutor(cfg, cc, _EngineLayers(self, attn_layers))
+                self.graph_attn.create_cuda_graph_buffers()
+                self.graph_steps = 0
 
     # ---- loop -----------------------------------------------------------------------------------------------
     def start(self) -> None:
@@ -337,6 +359,9 @@ class Engine:
                         num_prefill_tokens=m.num_prefill_tokens, num_decode_tokens=m.num_decode_tokens,
                         max_ctx=max(pos) + 1)
 
+    def graph_attention_steps(self) -> int:
+        return int(getattr(self, "graph_steps", 0))
+
     def process_batch_attn(self, batch) -> None:
         cfg = self.model_config
         m = batch.metadata
@@ -361,7 +386,15 @@ class Engine:
             # the first partial row doubles as the residual buffer that the layer updates in place
             resid = parts[:, 0].contiguous()
             parts = parts[:, 1:] if parts.shape[1] > 1 else None
-        out = self.attn_layers[layer].forward(resid, parts, (self.kv_cache[layer][0], self.kv_cache[layer][1]), meta)
+        ga = getattr(self, "graph_attn", None)
+        if ga is not None and m.num_prefill_tokens == 0 and ga.fits(n) and self.attn_layers[layer].weighted_router is None:
+            from ..models.attention import AttnOutput
+            y, tw, ti, r = ga.run(layer, meta.positions, resid, meta, parts)
+            # the outputs alias the graph's static buffers: the dispatcher keeps rows beyond the next replay
+            out = AttnOutput(None if y is None else y.clone(), r.clone(), tw, ti)
+            self.graph_steps += 1
+        else:
+            out = self.attn_layers[layer].forward(resid, parts, (self.kv_cache[layer][0], self.kv_cache[layer][1]), meta)
         self.timer.stop("execute")
         self.timer.start("postprocess")
         keep = list(range(n))

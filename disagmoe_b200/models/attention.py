@@ -35,6 +35,11 @@ class AttnMeta:
     num_prefill_tokens: int = 0
     num_decode_tokens: int = 0
     max_ctx: int = 0
+    # prompt segments for the tiled causal kernel (CUDA only): device int32 [>= n_prefill_tiles, 4] from
+    # ops.functional.build_prefill_tiles, and ctx_len with the covered rows set to 0 for the per-token kernel
+    prefill_tiles: Optional[torch.Tensor] = None
+    n_prefill_tiles: int = 0
+    ctx_len_decode: Optional[torch.Tensor] = None
 
 
 @dataclass
@@ -165,8 +170,14 @@ class MoEAttention(torch.nn.Module):
         splits = 1
         if qkv.is_cuda:
             splits = F.pick_attn_splits(T, self.num_kv_heads, meta.max_ctx or cfg.max_seq_len, kc.shape[1])
-        attn = F.paged_attention(qkv[:, :self.q_size], kc, vc, meta.block_tables, meta.bt_row, meta.ctx_len,
+        tiled = qkv.is_cuda and meta.n_prefill_tiles > 0
+        attn = F.paged_attention(qkv[:, :self.q_size], kc, vc, meta.block_tables, meta.bt_row,
+                                 meta.ctx_len_decode if tiled else meta.ctx_len,
                                  self.num_heads, self.num_kv_heads, self.head_dim, splits=splits)
+        if tiled:
+            # prompt segments: one pass over the sequence's K / V per tile of 64 query rows instead of one per row
+            F.prefill_attention(qkv[:, :self.q_size], kc, vc, meta.block_tables, meta.prefill_tiles,
+                                meta.n_prefill_tiles, self.num_heads, self.num_kv_heads, self.head_dim, attn)
         if self.tp_size == 1:
             return gemm.linear(attn, self.o_w, residual=resid, out=resid)
         part = self._tp_reduce(gemm.linear(attn, self.o_w))

@@ -323,3 +323,55 @@ def ids_gather(src: torch.Tensor, n: int, dst_ptrs: torch.Tensor, n_dst: int, ds
 def wait_flags(flags: torch.Tensor, n: int, epoch: torch.Tensor, status: Optional[torch.Tensor]) -> None:
     """Stand-alone bounded wait: flags[i] >= epoch + 1 for i < n; advances the device-resident epoch."""
     _lib.check(_lib.lib().dmoe_wait_flags(_vp(flags), c_int(n), _vp(epoch), _vp(status), _st()), "dmoe_wait_flags")
+
+
+# ---- tiled causal attention for prompt tokens (csrc/kernels/attention.cu: prefill_attn_kernel) -----------------------
+def prefill_tile_tokens(n_q: int, n_kv: int) -> int:
+    """Prompt tokens per tile of :func:`prefill_attention` (64 query rows = tokens x query heads per kv head)."""
+    gq = n_q // n_kv
+    return 64 // gq if n_q % n_kv == 0 and gq in (1, 2, 4, 8) else 0
+
+
+def build_prefill_tiles(bt_row, positions, tile_tokens: int, min_len: int = 8):
+    """Finds the prompt segments of a flat token batch on the host and cuts them into attention tiles.
+
+    bt_row / positions: int sequences (lists, numpy arrays or CPU tensors) of the batch's rows. A segment is a run of
+    consecutive rows of one sequence (same block-table row) at consecutive positions; runs of at least ``min_len``
+    rows go to the tiled kernel. Returns (tiles int32 CPU tensor [n, 4] = (first row, tokens, block-table row, first
+    position), covered bool CPU tensor [T]): rows not covered stay with the per-token kernel."""
+    import numpy as np
+    rows = np.asarray(bt_row, dtype=np.int64)
+    pos = np.asarray(positions, dtype=np.int64)
+    T = len(rows)
+    covered = np.zeros(T, dtype=bool)
+    tiles = []
+    if T == 0 or tile_tokens <= 0:
+        return torch.zeros(0, 4, dtype=torch.int32), torch.from_numpy(covered)
+    brk = np.nonzero((rows[1:] != rows[:-1]) | (pos[1:] != pos[:-1] + 1))[0] + 1
+    starts = np.concatenate([[0], brk])
+    ends = np.concatenate([brk, [T]])
+    for a, b in zip(starts.tolist(), ends.tolist()):
+        if b - a < min_len:
+            continue
+        covered[a:b] = True
+        for t0 in range(a, b, tile_tokens):
+            tiles.append((t0, min(tile_tokens, b - t0), int(rows[a]), int(pos[t0])))
+    t = torch.tensor(tiles, dtype=torch.int32).reshape(-1, 4)
+    return t, torch.from_numpy(covered)
+
+
+def prefill_attention(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_tables: torch.Tensor,
+                      tiles: torch.Tensor, n_tiles: int, n_q: int, n_kv: int, hd: int, out: torch.Tensor,
+                      scale: Optional[float] = None) -> torch.Tensor:
+    """Causal attention of the prompt tokens named by ``tiles`` (device int32 [>= n_tiles, 4], see
+    :func:`build_prefill_tiles`) over the paged cache, which already holds their own K / V; writes their rows of
+    ``out``. Every tile streams its sequence's K / V once (the per-token kernel streams it once per row)."""
+    if n_tiles == 0:
+        return out
+    assert q.is_cuda and tiles.is_cuda and tiles.dtype == torch.int32 and tiles.is_contiguous()
+    scale = scale if scale is not None else 1.0 / math.sqrt(hd)
+    _lib.check(_lib.lib().dmoe_prefill_attention(
+        _vp(q), c_ll(q.stride(0)), _vp(kcache), _vp(vcache), _vp(block_tables), c_int(block_tables.stride(0)), _vp(tiles),
+        c_int(n_tiles), c_int(kcache.shape[1]), c_int(n_q), c_int(n_kv), c_int(hd), c_float(scale), _vp(out),
+        c_ll(out.stride(0)), _st()), "dmoe_prefill_attention")
+    return out

@@ -19,6 +19,7 @@ import torch
 from . import _lib
 
 EPI_PLAIN, EPI_SWIGLU, EPI_COMBINE = 0, 1, 2
+STREAM_K = True      # default work distribution of every GEMM launched without an explicit split (tests may turn it off)
 _num_sms_cache = {}
 
 
@@ -163,9 +164,11 @@ def rope_table(max_pos: int, hd: int, theta: float, device) -> torch.Tensor:
     return t
 
 
-def _launch(W, X, Y, R, offs, recs, bases, G, T, F, K, epi, bn, splitk, ldy, y_f32, comm: Optional[GemmComm] = None):
+def _launch(W, X, Y, R, offs, recs, bases, G, T, F, K, epi, bn, splitk, ldy, y_f32, comm: Optional[GemmComm] = None,
+            streamk: bool = False):
     s = scratch(X.device)
     d = _lib.DmoeGemm()
+    d.streamk, d.n_counters = int(streamk and splitk <= 1), s.counters.numel()
     if comm is not None:
         comm.fill(d)
     d.W, d.X, d.Y, d.R = W.data_ptr(), X.data_ptr(), _lib.ptr(Y), _lib.ptr(R)
@@ -212,13 +215,20 @@ def linear(x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor] = 
     assert scatter or (out.stride(1) == 1 and out.dtype in (torch.bfloat16, torch.float32))
     if T == 0:
         return out
+    # splitk = 0 (default): stream-K -- the K-block iterations of all tiles are dealt out evenly over the SMs, so
+    # neither the tile count nor the tile width has to match the SM count. An explicit splitk >= 1 selects plain
+    # split-K with that many equal K ranges per tile (1 = whole tiles).
+    streamk = splitk == 0 and STREAM_K
     if not bn:
         bn = pick_bn(T, EPI_PLAIN)
-        if bn == 256 and ((F + 127) // 128) * ((T + 255) // 256) < num_sms(x.device) // 2:
+        if not streamk and bn == 256 and ((F + 127) // 128) * ((T + 255) // 256) < num_sms(x.device) // 2:
             bn = 128     # too few 256-wide tiles to fill the GPU: halve the tile instead of splitting K further
-    splitk = splitk or pick_splitk(T, F, K, bn, num_sms(x.device))
+    if streamk:
+        splitk = 1
+    else:
+        splitk = splitk or pick_splitk(T, F, K, bn, num_sms(x.device))
     _launch(w, x, out, residual, None, None, None, 1, T, F, K, EPI_PLAIN, bn, splitk,
-            F if scatter else out.stride(0), (not scatter) and out.dtype == torch.float32, comm)
+            F if scatter else out.stride(0), (not scatter) and out.dtype == torch.float32, comm, streamk=streamk)
     return out
 
 
@@ -239,7 +249,7 @@ def _grouped_ref(x, w, offs, swiglu):
 
 
 def grouped_swiglu(x: torch.Tensor, w13: torch.Tensor, offs: Optional[torch.Tensor], out: Optional[torch.Tensor] = None,
-                   bn: int = 0, comm: Optional[GemmComm] = None) -> torch.Tensor:
+                   bn: int = 0, comm: Optional[GemmComm] = None, streamk: Optional[bool] = None) -> torch.Tensor:
     """act[T, I] = silu(x @ w13[g, :I].T) * (x @ w13[g, I:].T) for the rows of group g; w13 is [G, 2I, K]."""
     T, K = x.shape
     G, F2, _ = w13.shape
@@ -258,12 +268,13 @@ def grouped_swiglu(x: torch.Tensor, w13: torch.Tensor, offs: Optional[torch.Tens
     if T == 0:
         return out
     bn = bn or pick_bn(_group_hint(T, G), EPI_SWIGLU)
-    _launch(w13, x, out, None, offs, None, None, G, T, I, K, EPI_SWIGLU, bn, 1, out.stride(0), False, comm)
+    _launch(w13, x, out, None, offs, None, None, G, T, I, K, EPI_SWIGLU, bn, 1, out.stride(0), False, comm,
+            streamk=STREAM_K if streamk is None else streamk)
     return out
 
 
 def grouped_linear(x: torch.Tensor, w: torch.Tensor, offs: torch.Tensor, out: Optional[torch.Tensor] = None,
-                   bn: int = 0) -> torch.Tensor:
+                   bn: int = 0, streamk: Optional[bool] = None) -> torch.Tensor:
     """y[T, F] = x @ w[g].T for the rows of group g; w is [G, F, K]."""
     T, K = x.shape
     G, F, _ = w.shape
@@ -280,12 +291,14 @@ def grouped_linear(x: torch.Tensor, w: torch.Tensor, offs: torch.Tensor, out: Op
     if T == 0:
         return out
     bn = bn or pick_bn(_group_hint(T, G), EPI_PLAIN)
-    _launch(w, x, out, None, offs, None, None, G, T, F, K, EPI_PLAIN, bn, 1, out.stride(0), False)
+    _launch(w, x, out, None, offs, None, None, G, T, F, K, EPI_PLAIN, bn, 1, out.stride(0), False,
+            streamk=STREAM_K if streamk is None else streamk)
     return out
 
 
 def grouped_combine(x: torch.Tensor, w: torch.Tensor, offs: Optional[torch.Tensor], recs: torch.Tensor,
-                    bases: torch.Tensor, ld_out: int, bn: int = 0, outs=None, comm: Optional[GemmComm] = None) -> None:
+                    bases: torch.Tensor, ld_out: int, bn: int = 0, outs=None, comm: Optional[GemmComm] = None,
+                    streamk: Optional[bool] = None) -> None:
     """GEMM-2 with the combine epilogue: row t of group g becomes ``weight[t] * (x[t] @ w[g].T)`` written to row
     ``recs[t, 1]`` of the buffer ``bases[recs[t, 0]]`` (row stride ``ld_out`` elements).
 
@@ -307,7 +320,8 @@ def grouped_combine(x: torch.Tensor, w: torch.Tensor, offs: Optional[torch.Tenso
     if T == 0:
         return
     bn = bn or pick_bn(_group_hint(T, G), EPI_COMBINE)
-    _launch(w, x, None, None, offs, recs, bases, G, T, F, K, EPI_COMBINE, bn, 1, ld_out, False, comm)
+    _launch(w, x, None, None, offs, recs, bases, G, T, F, K, EPI_COMBINE, bn, 1, ld_out, False, comm,
+            streamk=STREAM_K if streamk is None else streamk)
 
 
 def swiglu_linear(x: torch.Tensor, w13: torch.Tensor, out: Optional[torch.Tensor] = None, bn: int = 0) -> torch.Tensor:
@@ -328,5 +342,5 @@ def swiglu_linear(x: torch.Tensor, w13: torch.Tensor, out: Optional[torch.Tensor
     if T == 0:
         return out
     bn = bn or pick_bn(T, EPI_SWIGLU)
-    _launch(w13, x, out, None, None, None, None, 1, T, I, K, EPI_SWIGLU, bn, 1, out.stride(0), False)
+    _launch(w13, x, out, None, None, None, None, 1, T, I, K, EPI_SWIGLU, bn, 1, out.stride(0), False, streamk=STREAM_K)
     return out

@@ -163,6 +163,7 @@ class AttentionRank:
                 qkv=torch.zeros(B, self.qkv_features, dtype=dt, device=dev),
                 attn=torch.zeros(B, a0.q_size, dtype=dt, device=dev),
                 disp_epoch=z(1), comb_epoch=z(1), ticket=z(1),
+                pre_tiles=z(B, 4), ctx_dec=z(B),
                 next_local=z(R), logits=torch.zeros(R, cfg.vocab_size, dtype=torch.float32, device=dev),
                 topk_ids=z(R, k), topk_w=torch.zeros(R, k, dtype=torch.float32, device=dev),
                 parts=arena.view(layout.offset(f"parts{m}"), (R, k, H), dt),
@@ -196,12 +197,32 @@ class AttentionRank:
             self.mb.append(d)
         self.status = gemm.scratch(dev).status
         self.active = [B] * S.n_mb      # rows of every micro-batch that the next launches process (<= B)
+        self.n_pre = [0] * S.n_mb       # prompt tiles of every micro-batch for the tiled causal attention kernel
 
     def set_active(self, m: int, T: int) -> None:
         """The next launches of micro-batch m process its first T rows (1 <= T <= batch): a serving step fills the
         buffers with however many decode and prompt tokens it scheduled."""
         assert 1 <= T <= self.shape.batch
         self.active[m] = T
+
+    def set_prefill_tiles(self, m: int, bt_row, positions, ctx_len) -> int:
+        """Eager (not graph-captured) iterations only: finds the prompt segments among the first ``active`` rows of
+        micro-batch m from the host copies of its block-table rows / positions / context lengths and routes them to
+        the tiled causal attention kernel; the other rows stay with the per-token kernel. Returns the tile count;
+        ``set_prefill_tiles(m, None, None, None)`` switches the tiled kernel off again."""
+        if bt_row is None:
+            self.n_pre[m] = 0
+            return 0
+        a0 = self.layers[0]
+        tiles, covered = F.build_prefill_tiles(bt_row, positions, F.prefill_tile_tokens(a0.num_heads, a0.num_kv_heads))
+        self.n_pre[m] = len(tiles)
+        if len(tiles):
+            d = self.mb[m]
+            d["pre_tiles"][:len(tiles)].copy_(tiles, non_blocking=True)
+            cd = torch.as_tensor(ctx_len).clone()
+            cd[covered] = 0
+            d["ctx_dec"][:len(cd)].copy_(cd, non_blocking=True)
+        return len(tiles)
 
     def rows(self, m: int):
         """(T, rows per TP rank, first own row, one past the last own row) of micro-batch m as currently active."""
@@ -264,9 +285,14 @@ class AttentionRank:
         else:
             comm = gemm.GemmComm(rope=rope)
         qkv = gemm.linear(d["hs"][:T], a.qkv_w, out=d["qkv"][:T], comm=comm)
-        attn = F.paged_attention(qkv[:, :a.q_size], kc, vc, meta.block_tables, meta.bt_row, meta.ctx_len,
+        n_pre = self.n_pre[m]
+        attn = F.paged_attention(qkv[:, :a.q_size], kc, vc, meta.block_tables, meta.bt_row,
+                                 d["ctx_dec"][:T] if n_pre else meta.ctx_len,
                                  a.num_heads, a.num_kv_heads, a.head_dim, out=d["attn"][:T],
                                  splits=F.pick_attn_splits(T, a.num_kv_heads, cfg.max_seq_len, self.block_size))
+        if n_pre:
+            F.prefill_attention(qkv[:, :a.q_size], kc, vc, meta.block_tables, d["pre_tiles"], n_pre, a.num_heads,
+                                a.num_kv_heads, a.head_dim, attn)
         if self.tp == 1:
             gemm.linear(attn, a.o_w, residual=d["resid"][:T], out=d["resid"][:T])
             return
@@ -375,7 +401,9 @@ class ExpertRank:
                 signal_ptrs=arena.ptr_table(attn_ranks, layout.offset(f"comb_flag{m}")),
             ))
         pairs = S.n_attn * S.rows_cap * S.top_k              # (token, k) pairs arriving per launch, all experts
-        self.bn = gemm.pick_bn(gemm._group_hint(pairs, S.num_experts), gemm.EPI_SWIGLU)
+        hint = gemm._group_hint(pairs, S.num_experts)
+        self.bn = gemm.pick_bn(hint, gemm.EPI_SWIGLU)          # GEMM-1 holds two accumulators per tile: tokens <= 128
+        self.bn2 = gemm.pick_bn(hint, gemm.EPI_COMBINE)        # GEMM-2: up to 256 tokens per weight tile
 
     def layer(self, l: int, m: int) -> None:
         d, S = self.mb[m], self.shape
@@ -389,7 +417,7 @@ class ExpertRank:
         sig = gemm.GemmComm(seg_cnt=d["cnt"], seg_cap=S.region_cap, group_regions=True, signal_ptrs=d["signal_ptrs"],
                             n_signal=S.n_attn, signal_slot=self.x, signal_epoch=d["signal_epoch"],
                             done_ticket=self.ticket, clear=d["cnt"])
-        gemm.grouped_combine(self.act, e.w2_weight, None, d["recs"], d["parts_bases"], S.hidden, bn=self.bn, comm=sig)
+        gemm.grouped_combine(self.act, e.w2_weight, None, d["recs"], d["parts_bases"], S.hidden, bn=self.bn2, comm=sig)
 
     def iteration(self) -> None:
         for l in range(self.cfg.num_layers):

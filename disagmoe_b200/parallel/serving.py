@@ -479,6 +479,14 @@ class FusedServingRank:
             self._fill_padding(m, T, size)
             self._upload(m, size)
             self.runner.set_active(m, size)
+            if not self.host_only:
+                # eager (prefill-heavy) iterations send their prompt segments through the tiled causal attention
+                # kernel; graph replays were captured without it
+                sl = slice(m * self.cap, m * self.cap + size)
+                if g is None:
+                    self.runner.set_prefill_tiles(m, self.h_row[sl], self.h_pos[sl], self.h_ctx[sl])
+                else:
+                    self.runner.set_prefill_tiles(m, None, None, None)
         if g is not None:
             self.graphs[g].replay()
             self._lib.add_launches(self.launches_per_graph)

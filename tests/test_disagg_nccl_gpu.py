@@ -14,10 +14,14 @@ from disagmoe_b200.utils.placement import ClusterConfig, get_model_placement
 pytestmark = pytest.mark.gpu
 
 
+@pytest.mark.parametrize("graph_attn", [False, True])
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_two_gpu_workers_over_nccl_channels():
+def test_two_gpu_workers_over_nccl_channels(graph_attn):
+    """graph_attn: decode-only attention batches replay CUDA graphs captured per (layer, batch bucket) on first use
+    (the reference's ``-ca`` mode); prompts still run eagerly."""
     from disagmoe_b200.frontend.controller import init_controller
-    cfg = tiny_config.clone(ep_size=1, dtype=torch.bfloat16)
+    cfg = tiny_config.clone(ep_size=1, dtype=torch.bfloat16, enable_cuda_graph_attn=graph_attn, max_batch_size_attn=16,
+                            graph_stride=8)
     sd = {k: v.to(torch.bfloat16) for k, v in init_state_dict(cfg, dtype=torch.float32).items()}
     path = os.path.join(tempfile.mkdtemp(), "tiny_bf16.pt")
     save_state_dict(sd, path)
@@ -39,6 +43,8 @@ def test_two_gpu_workers_over_nccl_channels():
             assert (got - ref).abs().max() / ref.abs().max() < 0.06
             assert len(r.tokens) == 4
         assert not [e for e in ctl.worker_errors().values() if e]
+        if graph_attn:
+            assert sum(ctl.graph_attention_steps().values()) > 0
     finally:
         ctl.stop_workers()
 

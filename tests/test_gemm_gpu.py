@@ -7,6 +7,16 @@ from disagmoe_b200.ops import gemm
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(params=["streamk", "whole_tiles"], autouse=True)
+def work_distribution(request):
+    """Every test of this file runs twice: with the stream-K distribution (the default: equal shares of K-block
+    iterations per SM, partial tiles reduced through the workspace) and with whole tiles per CTA."""
+    old = gemm.STREAM_K
+    gemm.STREAM_K = request.param == "streamk"
+    yield request.param
+    gemm.STREAM_K = old
+
+
 def _rand(*shape, scale=1.0):
     return (torch.randn(*shape, device="cuda", dtype=torch.float32) * scale).to(torch.bfloat16)
 
@@ -225,3 +235,48 @@ def test_oproj_reduce_scatter_epilogue_and_shard_gated_prologue():
     y2 = gemm.linear(x, w)            # the context is intact
     torch.cuda.synchronize()
     _close(y2, ref)
+
+
+@pytest.mark.parametrize("T,F,K", [(256, 6144, 4096), (64, 4096, 4096), (1024, 1536, 4096), (300, 384, 14336),
+                                   (17, 128, 64), (512, 32000, 4096)])
+def test_stream_k_linear_shapes(T, F, K, work_distribution):
+    """Decode-size and TP-size dense GEMMs of the model (QKV, o_proj, LM head) with automatic tile and distribution:
+    few tiles with long K loops (every tile shared by several CTAs) and many tiles (a boundary in every other tile)."""
+    torch.manual_seed(9)
+    x, w = _rand(T, K), _rand(F, K, scale=K ** -0.5)
+    r = _rand(T, F)
+    y = gemm.linear(x, w, residual=r)
+    torch.cuda.synchronize()
+    assert gemm.check_status() == 0
+    _close(y, x.float() @ w.float().T + r.float())
+    y2 = gemm.linear(x, w, residual=r)       # the tile counters must be back at zero
+    torch.cuda.synchronize()
+    assert torch.equal(y, y2)
+
+
+def test_stream_k_combine_matches_whole_tiles():
+    """GEMM-2 with the combine epilogue (scaled scatter through records) at a shape where most tiles are shared
+    between CTAs under stream-K: same result as with whole tiles."""
+    torch.manual_seed(10)
+    counts, F, K = [260, 250, 3, 0, 515], 512, 14336
+    G, T = len(counts), sum(counts)
+    x, w = _rand(T, K), _rand(G, F, K, scale=K ** -0.5)
+    offs = _offsets(counts)
+    perm = torch.randperm(T, device="cuda")
+    wts = torch.rand(T, device="cuda")
+    recs = torch.zeros(T, 4, dtype=torch.int32, device="cuda")
+    recs[:, 1] = perm.int()
+    recs[:, 2] = wts.view(torch.int32)
+    outs = []
+    for sk in (True, False):
+        out = torch.zeros(T, F, dtype=torch.bfloat16, device="cuda")
+        bases = torch.tensor([out.data_ptr()], dtype=torch.int64, device="cuda")
+        gemm.grouped_combine(x, w, offs, recs, bases, out.stride(0), bn=256, streamk=sk)
+        torch.cuda.synchronize()
+        assert gemm.check_status() == 0
+        outs.append(out)
+    ref = gemm._grouped_ref(x, w, offs, False) * wts[:, None]
+    exp = torch.zeros(T, F, device="cuda")
+    exp[perm] = ref
+    _close(outs[0], exp)
+    _close(outs[1], exp)

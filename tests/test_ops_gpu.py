@@ -308,3 +308,35 @@ def test_ids_gather():
         assert d[8:18].tolist() == list(range(100, 110)) and int(d.sum()) == sum(range(100, 110))
         assert f.tolist() == [0, 0, 7, 0]
     assert int(ep) == 7
+
+
+@pytest.mark.parametrize("n_q,n_kv,hd", [(32, 8, 128), (4, 4, 64), (16, 2, 128), (8, 4, 64), (2, 2, 128)])
+def test_prefill_attention_tiled_causal(n_q, n_kv, hd):
+    """The tiled causal kernel on a mixed batch: whole prompts of 1 ... 300 tokens, a chunk that continues a cached
+    prefix (chunked prefill), short runs and decode rows that stay with the per-token kernel. Reference: the fp32
+    restatement of paged attention with ctx_len = position + 1 for every row."""
+    torch.manual_seed(20)
+    bs, maxb = 16, 40
+    segs = [(0, 0, 300), (1, 0, 64), (2, 137, 70), (3, 500, 1), (4, 0, 5), (5, 90, 1), (6, 0, 17), (7, 31, 129)]   # (bt row, first pos, tokens)
+    rows, pos = [], []
+    for r, p0, n in segs:
+        rows += [r] * n
+        pos += list(range(p0, p0 + n))
+    T = len(rows)
+    nb = 8 * maxb
+    q = _bf(T, n_q * hd)
+    kc, vc = _bf(nb, bs, n_kv, hd), _bf(nb, bs, n_kv, hd)
+    bt = torch.randperm(nb, device=DEV)[:8 * maxb].view(8, maxb).int()
+    bt_row = torch.tensor(rows, dtype=torch.int32, device=DEV)
+    ctx = torch.tensor([p + 1 for p in pos], dtype=torch.int32, device=DEV)
+    tiles, covered = F.build_prefill_tiles(rows, pos, F.prefill_tile_tokens(n_q, n_kv))
+    assert int(covered.sum()) == 300 + 64 + 70 + 17 + 129 and not covered[434:435].any()      # runs of 1 and 5 rows stay
+    ctx_dec = ctx.clone()
+    ctx_dec[covered.to(DEV)] = 0
+    out = F.paged_attention(q, kc, vc, bt, bt_row, ctx_dec, n_q, n_kv, hd)
+    F.prefill_attention(q, kc, vc, bt, tiles.to(DEV), len(tiles), n_q, n_kv, hd, out)
+    ref = reference.paged_attention(q, kc, vc, bt, bt_row, ctx, n_q, n_kv, hd)
+    torch.cuda.synchronize()
+    _close(out, ref)
+    # and the per-token kernel agrees with both (it is what the tiled kernel replaces for these rows)
+    _close(F.paged_attention(q, kc, vc, bt, bt_row, ctx, n_q, n_kv, hd), ref)
