@@ -5,6 +5,7 @@
 #include <torch/extension.h>
 
 #include "engine.h"
+#include "fused_scheduler.h"
 
 namespace py = pybind11;
 using namespace dmoe;
@@ -305,6 +306,81 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         for (auto& u : b.drain_updates()) out.emplace_back(u.row, u.col, u.block);
         return out;
       });
+  // ---- serving scheduler of the fused data plane ------------------------------------------------------------------
+  py::class_<FusedSeq, fused_seq_t>(m, "FusedSeq")
+      .def(py::init([](int req_id, std::vector<int> prompt, int max_new_tokens, double t_arrival, int mb, int length,
+                       int last_token, std::vector<int> outputs, std::vector<double> t_tokens) {
+             auto s = std::make_shared<FusedSeq>();
+             s->req_id = req_id; s->prompt = std::move(prompt); s->max_new_tokens = max_new_tokens;
+             s->t_arrival = t_arrival; s->mb = mb; s->length = length; s->last_token = last_token;
+             s->outputs = std::move(outputs); s->t_tokens = std::move(t_tokens);
+             return s;
+           }),
+           py::arg("req_id"), py::arg("prompt"), py::arg("max_new_tokens"), py::arg("t_arrival") = 0.0, py::arg("mb") = -1,
+           py::arg("length") = 0, py::arg("last_token") = 0, py::arg("outputs") = std::vector<int>{},
+           py::arg("t_tokens") = std::vector<double>{})
+      .def_readwrite("req_id", &FusedSeq::req_id)
+      .def_readwrite("prompt", &FusedSeq::prompt)
+      .def_readwrite("max_new_tokens", &FusedSeq::max_new_tokens)
+      .def_readwrite("t_arrival", &FusedSeq::t_arrival)
+      .def_readwrite("mb", &FusedSeq::mb)
+      .def_readwrite("length", &FusedSeq::length)
+      .def_readwrite("last_token", &FusedSeq::last_token)
+      .def_readwrite("outputs", &FusedSeq::outputs)
+      .def_readwrite("t_tokens", &FusedSeq::t_tokens);
+  py::class_<FusedPlan>(m, "FusedPlan")
+      .def(py::init<>())
+      .def_readwrite("ids", &FusedPlan::ids)
+      .def_readwrite("pos", &FusedPlan::pos)
+      .def_readwrite("rows", &FusedPlan::rows)
+      .def_readwrite("slots", &FusedPlan::slots)
+      .def_readwrite("emit", &FusedPlan::emit)
+      .def("__len__", &FusedPlan::size)
+      .def("copy_to", [](const FusedPlan& p, torch::Tensor ids, torch::Tensor pos, torch::Tensor ctx, torch::Tensor rows,
+                         torch::Tensor slots, int64_t offset) {
+        const int64_t n = p.size();
+        for (auto* t : {&ids, &pos, &ctx, &rows})
+          DMOE_CHECK(t->scalar_type() == torch::kInt32 && t->is_contiguous() && !t->is_cuda() && t->numel() >= offset + n,
+                     "copy_to: int32 contiguous host tensors with room for the plan are needed");
+        DMOE_CHECK(slots.scalar_type() == torch::kInt64 && slots.is_contiguous() && !slots.is_cuda() &&
+                       slots.numel() >= offset + n, "copy_to: slots must be an int64 contiguous host tensor");
+        p.copy_to(ids.data_ptr<int32_t>() + offset, pos.data_ptr<int32_t>() + offset, ctx.data_ptr<int32_t>() + offset,
+                  rows.data_ptr<int32_t>() + offset, slots.data_ptr<int64_t>() + offset);
+      }, py::arg("ids"), py::arg("pos"), py::arg("ctx"), py::arg("rows"), py::arg("slots"), py::arg("offset") = 0);
+  py::class_<FusedScheduler, std::shared_ptr<FusedScheduler>>(m, "FusedScheduler")
+      .def(py::init<std::shared_ptr<BlockManager>, int, int, int, int, int, bool>(), py::arg("block_mgr"),
+           py::arg("block_size"), py::arg("n_mb"), py::arg("max_seqs_per_mb"), py::arg("max_tokens_per_mb"),
+           py::arg("max_prefill_tokens_per_mb") = 0, py::arg("ignore_eos") = true)
+      .def("add_request", &FusedScheduler::add_request, py::arg("req_id"), py::arg("prompt"), py::arg("max_new_tokens"),
+           py::arg("t_arrival"))
+      .def("num_unfinished", &FusedScheduler::num_unfinished)
+      .def("has_work", &FusedScheduler::has_work, py::arg("now"))
+      .def("build", &FusedScheduler::build, py::arg("now"), py::call_guard<py::gil_scoped_release>())
+      .def("commit", &FusedScheduler::commit, py::arg("plans"), py::arg("next_ids"), py::arg("now"))
+      .def("restore_running", &FusedScheduler::restore_running, py::arg("mb"), py::arg("seq"))
+      .def("restore_finished", &FusedScheduler::restore_finished, py::arg("seq"))
+      .def_property_readonly("waiting", [](const FusedScheduler& s) { return s.waiting(); })
+      .def_property_readonly("running", [](const FusedScheduler& s) {
+        // per micro-batch: request id -> sequence, in admission order
+        py::list out;
+        for (auto& r : s.running()) {
+          py::dict d;
+          for (auto& q : r) d[py::int_(q->req_id)] = q;
+          out.append(d);
+        }
+        return out;
+      })
+      .def_property_readonly("finished", [](const FusedScheduler& s) {
+        py::dict d;
+        for (auto& kv : s.finished()) d[py::int_(kv.first)] = kv.second;
+        return d;
+      })
+      .def_property_readonly("pool_blocks", &FusedScheduler::pool_blocks)
+      .def_property_readonly("max_tokens", &FusedScheduler::max_tokens)
+      .def_property_readonly("max_seqs", &FusedScheduler::max_seqs)
+      .def_property_readonly("max_prefill", &FusedScheduler::max_prefill)
+      .def_readonly_static("MIN_CHUNK", &FusedScheduler::MIN_CHUNK);
+
   m.def("prepare_batch_infos", [](const AttentionBatchMetadata& meta, const std::vector<int>& lens) {
     return torch::tensor(prepare_batch_infos(meta, lens), torch::TensorOptions().dtype(torch::kInt32));
   });

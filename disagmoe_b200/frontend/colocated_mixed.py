@@ -15,7 +15,7 @@ from typing import Dict, List, Optional, Tuple
 import torch
 
 from ..config import CacheConfig, ModelConfig
-from ..parallel.serving import FusedScheduler, ServeSeq
+from ..parallel.serving import FusedScheduler, PyFusedScheduler, ServeSeq, make_seq
 from .colocated import ColocatedEngine
 
 
@@ -107,16 +107,18 @@ class MixedBatchEngine(ColocatedEngine):
         st = torch.load(path, map_location="cpu", weights_only=True)   # plain containers + tensors only
         assert st["block_size"] == self.block_size and self.sched.num_unfinished() == 0
         for d in st["running"]:
-            s = ServeSeq(d["req_id"], d["prompt"], d["max_new_tokens"], d["t_arrival"], mb=0, length=d["length"],
-                         last_token=d["last_token"], outputs=list(d["outputs"]))
+            native = not isinstance(self.sched, PyFusedScheduler)
+            s = make_seq(d["req_id"], d["prompt"], d["max_new_tokens"], d["t_arrival"], native=native, mb=0,
+                         length=d["length"], last_token=d["last_token"], outputs=list(d["outputs"]))
             # the same reservation a fresh admission makes: room for the whole prompt, the rest grows step by step
             self.block_mgr.allocate(s.req_id, max(len(s.prompt), s.length) + 1)
             blocks = self.block_mgr.get_seq_block_list(s.req_id)
             n = min(d["pages"].shape[2], len(blocks))
             self.executor.kv_cache[:, :, torch.tensor(blocks[:n], device=self.device)] = d["pages"][:, :, :n].to(self.device)
-            self.sched.running[0][s.req_id] = s
+            self.sched.restore_running(0, s)
         for d in st["waiting"]:
             self.sched.add_request(d["req_id"], d["prompt"], d["max_new_tokens"], d["t_arrival"])
         for r, outs in st["finished"].items():
-            self.sched.finished[r] = ServeSeq(r, [], len(outs), 0.0, outputs=list(outs))
+            native = not isinstance(self.sched, PyFusedScheduler)
+            self.sched.restore_finished(make_seq(r, [], len(outs), 0.0, native=native, outputs=list(outs)))
         self._apply_block_table_patches()

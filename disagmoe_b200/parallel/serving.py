@@ -67,8 +67,10 @@ class MicroBatchPlan:
         return len(self.ids)
 
 
-class FusedScheduler:
-    """Admission + micro-batch construction of one attention group (pure host logic, no GPU).
+class PyFusedScheduler:
+    """Admission + micro-batch construction of one attention group (pure host logic, no GPU). This is the Python
+    statement of the policy; the serving path runs its C++ twin ``disagmoe_c.FusedScheduler``
+    (csrc/runtime/fused_scheduler.cpp) through :func:`FusedScheduler`, and a CPU test holds the two to identical plans.
 
     Every iteration a micro-batch holds one decode token per running sequence plus prompt tokens up to two budgets:
     ``max_tokens_per_mb`` rows in total and ``max_prefill_tokens_per_mb`` prompt rows. A prompt that does not fit is
@@ -179,6 +181,38 @@ class FusedScheduler:
                     self.running[m].pop(s.req_id, None)
                     self.finished[s.req_id] = s
         return out
+
+
+    def restore_running(self, mb: int, s: ServeSeq) -> None:
+        s.mb = mb
+        self.running[mb][s.req_id] = s
+
+    def restore_finished(self, s: ServeSeq) -> None:
+        self.finished[s.req_id] = s
+
+
+def FusedScheduler(block_mgr, block_size: int, n_mb: int, max_seqs_per_mb: int, max_tokens_per_mb: int,
+                   max_prefill_tokens_per_mb: Optional[int] = None, ignore_eos: bool = True, native: Optional[bool] = None):
+    """The serving scheduler of one attention group: the native implementation (C++, next to the block manager it
+    drives) unless ``native=False`` or DMOE_PY_SCHEDULER=1 asks for the Python one. Both expose ``add_request``,
+    ``has_work``, ``num_unfinished``, ``build``, ``commit``, ``restore_running`` / ``restore_finished`` and the
+    ``waiting`` / ``running`` / ``finished`` views."""
+    if native is None:
+        native = os.environ.get("DMOE_PY_SCHEDULER", "") != "1"
+    if native:
+        from .. import disagmoe_c as C
+        return C.FusedScheduler(block_mgr, block_size, n_mb, max_seqs_per_mb, max_tokens_per_mb,
+                                max_prefill_tokens_per_mb or 0, ignore_eos)
+    return PyFusedScheduler(block_mgr, block_size, n_mb, max_seqs_per_mb, max_tokens_per_mb, max_prefill_tokens_per_mb,
+                            ignore_eos)
+
+
+def make_seq(req_id: int, prompt, max_new_tokens: int, t_arrival: float = 0.0, native: bool = True, **kw):
+    """A sequence record for ``restore_running`` / ``restore_finished`` of the scheduler flavour in use."""
+    if native:
+        from .. import disagmoe_c as C
+        return C.FusedSeq(req_id, list(prompt), max_new_tokens, t_arrival, **kw)
+    return ServeSeq(req_id, list(prompt), max_new_tokens, t_arrival, **kw)
 
 
 # ------------------------------------------------------------------------------------------------ host-only stand-ins
@@ -399,7 +433,9 @@ class FusedServingRank:
         for m, p in enumerate(plans):
             T = len(p)
             o = m * self.cap
-            if T:
+            if T and hasattr(p, "copy_to"):
+                p.copy_to(self.h_ids, self.h_pos, self.h_ctx, self.h_row, self.h_slots, o)   # native plan: one pass in C++
+            elif T:
                 self.h_ids.numpy()[o:o + T] = p.ids
                 self.h_pos.numpy()[o:o + T] = p.pos
                 self.h_ctx.numpy()[o:o + T] = np.asarray(p.pos, dtype=np.int32) + 1

@@ -319,3 +319,39 @@ def test_serve_fused_script_host_only_dry_run(tmp_path):
     assert info["requests_finished"] == 30 and info["kernel_status"] == 0
     row = json.loads(out.read_text().strip().splitlines()[-1])
     assert row["token_throughput"] > 0 and trace.exists()
+
+
+def test_native_scheduler_builds_the_same_plans_as_the_python_statement():
+    """The C++ serving scheduler (csrc/runtime/fused_scheduler.cpp) against the Python statement of the same policy on
+    random request streams: identical plans (ids, positions, block-table rows, slots, emit lists) every iteration,
+    identical tokens committed, identical finish order."""
+    import random
+    from disagmoe_b200.parallel.serving import PyFusedScheduler
+    for seed in range(25):
+        rnd = random.Random(seed)
+        n_mb, max_seqs = rnd.randint(1, 3), rnd.randint(1, 6)
+        max_tokens, max_prefill = max(rnd.randint(24, 96), max_seqs + 16), rnd.randint(16, 64)
+        bms = [C.BlockManager(16, 96, 0, 64) for _ in range(2)]
+        a = C.FusedScheduler(bms[0], 16, n_mb, max_seqs, max_tokens, max_prefill, False)
+        b = PyFusedScheduler(bms[1], 16, n_mb, max_seqs, max_tokens, max_prefill, False)
+        reqs = [(i, [rnd.randrange(1000) for _ in range(rnd.randint(1, 120))], rnd.randint(1, 12), rnd.random() * 3)
+                for i in range(rnd.randint(1, 14))]
+        for r in sorted(reqs, key=lambda r: r[3]):
+            a.add_request(*r)
+            b.add_request(*r)
+        now = 0.0
+        while b.num_unfinished():
+            now += 0.25
+            assert a.has_work(now) == b.has_work(now) and a.num_unfinished() == b.num_unfinished()
+            pa, pb = a.build(now), b.build(now)
+            for x, y in zip(pa, pb):
+                assert list(x.ids) == y.ids and list(x.pos) == list(y.pos) and list(x.rows) == y.rows
+                assert list(x.slots) == list(y.slots)
+                assert [(r, q.req_id, g) for r, q, g in x.emit] == [(r, q.req_id, g) for r, q, g in y.emit]
+            toks = [[rnd.choice([2, 5, 9]) for _ in range(len(p))] for p in pb]      # 2 = EOS: early finishes too
+            assert a.commit(pa, toks, now) == b.commit(pb, toks, now)
+            assert [sorted(r) for r in a.running] == [sorted(r) for r in b.running]
+        assert a.num_unfinished() == 0 and set(a.finished) == set(b.finished)
+        for i in b.finished:
+            assert list(a.finished[i].outputs) == b.finished[i].outputs and a.finished[i].length == b.finished[i].length
+        assert bms[0].num_free_blocks() == bms[1].num_free_blocks() == 96
