@@ -136,9 +136,26 @@ def main():
     ap.add_argument("--route-skew", type=float, default=0.0,
                     help="Zipf exponent of a synthetic expert-popularity skew added to the router logits (0 = none)")
     ap.add_argument("--no-selfcheck", action="store_true", help="skip the tiny-model correctness run at N >= 2")
+    ap.add_argument("--serve", action="store_true",
+                    help="N >= 2: open-loop serving instead of the fixed decode batch: Poisson arrivals over a rate sweep "
+                         "(--rates, --duration seconds each), prompts U[128,1024], outputs U[64,512], real prefill, "
+                         "continuous batching; prints output tokens/s with p50 / p99 time per output token per rate")
+    ap.add_argument("--rates", default="2,8,16,32")
+    ap.add_argument("--duration", type=float, default=60.0)
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.serve:
+        from benchmark import serve_fused
+        A = args.n_attn or max(1, args.gpus // 2)
+        tp = args.attn_tp or A
+        argv = ["--model", args.model, "--n-attn", str(A), "--attn-tp", str(tp), "--rates", args.rates, "--duration",
+                str(args.duration), "--min-input-len", "128", "-i", "1024", "--min-output-len", "64", "-o", "512",
+                "--max-seqs-per-mb", "256", "--max-tokens-per-mb", "2048", "--max-prefill-tokens-per-mb", "1024",
+                "--num-blocks", "32768", "--time-limit", str(args.duration * 4 + 120)]
+        if args.layers:
+            argv += ["-L", str(args.layers)]
+        return serve_fused.main(argv)
 
     import torch
     import torch.distributed as dist

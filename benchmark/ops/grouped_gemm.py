@@ -1,7 +1,11 @@
 """Expert grouped GEMMs of one Mixtral layer (8 experts, hidden 4096, ffn 14336, bf16) over tokens per expert:
 GEMM-1 + SwiGLU and GEMM-2 of this package against ``torch._grouped_mm``.
 
-    python benchmark/ops/grouped_gemm.py [--tokens 8,32,64,128,512] [--iters 20]
+    python benchmark/ops/grouped_gemm.py [--tokens 8,32,64,128,512] [--iters 20] [--experts 8] [--ragged 0.06]
+
+``--experts 2`` is the shape of one expert GPU of the 8-GPU layout (2 local experts); ``--ragged f`` jitters the group
+sizes by +-f around the mean, as routing does. Every case runs with the stream-K work distribution and with whole
+tiles per CTA, and GEMM-2 additionally at both token-tile widths.
 
 CUDA-event timing, median of ``--iters``, a 256 MB buffer is written between iterations (L2 flush). Prints the time,
 the weight-streaming rate (GB/s of expert weights) and the FLOP rate of every case.
@@ -39,25 +43,39 @@ def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--tokens", default="8,32,64,128,512", help="tokens per expert")
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--experts", type=int, default=E, help="local experts (groups) of the launch")
+    ap.add_argument("--ragged", type=float, default=0.0, help="relative jitter of the group sizes around the mean")
     a = ap.parse_args(argv)
     dev = "cuda"
-    w13 = (torch.randn(E, 2 * I, H, device=dev) * 0.02).to(torch.bfloat16)        # runtime layout: K contiguous
-    w2 = (torch.randn(E, H, I, device=dev) * 0.02).to(torch.bfloat16)
+    G = a.experts
+    w13 = (torch.randn(G, 2 * I, H, device=dev) * 0.02).to(torch.bfloat16)        # runtime layout: K contiguous
+    w2 = (torch.randn(G, H, I, device=dev) * 0.02).to(torch.bfloat16)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    gen = torch.Generator().manual_seed(0)
     for t in (int(x) for x in a.tokens.split(",")):
-        T = t * E
+        sizes = [max(1, int(round(t * (1 + a.ragged * (2 * float(torch.rand(1, generator=gen)) - 1))))) for _ in range(G)]
+        T = sum(sizes)
         x = torch.randn(T, H, device=dev).to(torch.bfloat16)
-        offs = torch.arange(0, T + 1, t, dtype=torch.int32, device=dev)
+        offs = torch.tensor([0] + list(torch.tensor(sizes).cumsum(0)), dtype=torch.int32, device=dev)
         act = gemm.grouped_swiglu(x, w13, offs)
-        t1 = timed(lambda: gemm.grouped_swiglu(x, w13, offs), flush, a.iters)
-        t2 = timed(lambda: gemm.grouped_linear(act, w2, offs), flush, a.iters)
+        res = {}
+        for sk in (True, False):
+            res[("g1", sk)] = timed(lambda: gemm.grouped_swiglu(x, w13, offs, streamk=sk), flush, a.iters)
+            for bn in (128, 256):
+                res[("g2", sk, bn)] = timed(lambda: gemm.grouped_linear(act, w2, offs, bn=bn, streamk=sk), flush, a.iters)
         lib_offs = offs[1:].contiguous()
         t_lib = timed(lambda: torch._grouped_mm(x, w13.transpose(1, 2), offs=lib_offs), flush, a.iters)
+        t_lib2 = timed(lambda: torch._grouped_mm(act, w2.transpose(1, 2), offs=lib_offs), flush, a.iters)
         gb1, gb2 = w13.numel() * 2 / 1e9, w2.numel() * 2 / 1e9
         f1, f2 = 2.0 * T * 2 * I * H, 2.0 * T * H * I
-        print(f"{t} tokens/expert: GEMM-1+SwiGLU {t1:.1f} us ({gb1 / t1 * 1e6:.0f} GB/s, {f1 / t1 / 1e6:.0f} TFLOP/s); "
-              f"GEMM-2 {t2:.1f} us ({gb2 / t2 * 1e6:.0f} GB/s, {f2 / t2 / 1e6:.0f} TFLOP/s); "
-              f"torch._grouped_mm GEMM-1 {t_lib:.1f} us", flush=True)
+        t1 = res[("g1", True)]
+        t2 = min(res[("g2", True, 128)], res[("g2", True, 256)])
+        print(f"{G} experts x ~{t} tokens (sizes {sizes if G <= 8 else '...'}): "
+              f"GEMM-1+SwiGLU stream-K {t1:.1f} us ({gb1 / t1 * 1e6:.0f} GB/s, {f1 / t1 / 1e6:.0f} TFLOP/s), whole tiles "
+              f"{res[('g1', False)]:.1f} us; GEMM-2 stream-K bn128 {res[('g2', True, 128)]:.1f} / bn256 "
+              f"{res[('g2', True, 256)]:.1f} us (best {gb2 / t2 * 1e6:.0f} GB/s, {f2 / t2 / 1e6:.0f} TFLOP/s), whole tiles "
+              f"bn128 {res[('g2', False, 128)]:.1f} / bn256 {res[('g2', False, 256)]:.1f} us; torch._grouped_mm "
+              f"GEMM-1 {t_lib:.1f} us, GEMM-2 {t_lib2:.1f} us", flush=True)
     assert gemm.check_status() == 0
 
 

@@ -61,7 +61,50 @@ def write_trace(results, path: str) -> str:
     return path
 
 
-def main():
+def sweep(args, srv, cfg, groups, tp, rank, world, A):
+    """Poisson arrivals at each rate of ``--rates`` for ``--duration`` seconds on one engine (request ids are unique across
+    rates); per rate one JSON line: output tokens/s, time per output token p50 / p99 (inter-token latency), TTFT."""
+    from dataclasses import asdict
+    next_id = 0
+    for ri, rate in enumerate(float(r) for r in args.rates.split(",")):
+        n = max(4, int(round(rate * args.duration)))
+        gen = get_generator("poisson")(rate, 1.0, args.min_input_len, args.max_input_len, args.seed + ri,
+                                       args.min_output_len, args.max_output_len)
+        wl = gen.generate_num(n)
+        rng = np.random.default_rng(args.seed + 100 + ri)
+        reqs = []
+        for i in range(len(wl)):
+            at, n_in = wl[i]
+            reqs.append((next_id + i, rng.integers(0, cfg.vocab_size, int(n_in)).tolist(), int(wl.output_lens[i]), float(at)))
+        next_id += len(reqs)
+        ids = {r[0] for r in reqs}
+        owner = assign_requests(reqs, groups)
+        mine = [r for r in reqs if srv.is_leader and owner[r[0]] == rank // tp]
+        it0, g0 = srv.iterations, srv.graph_iterations
+        res = srv.serve(mine, time_limit=args.time_limit)
+        gathered = [None] * world if rank == 0 else None
+        dist.gather_object(res, gathered, dst=0, group=srv.ctl)
+        if rank == 0:
+            slo = [s for g in gathered for s in g["slo"] if s.req_id in ids]
+            arrivals = {k: v for g in gathered for k, v in g["arrivals"].items() if k in ids}
+            m = analyze_results(slo, arrivals, max(g["duration"] for g in gathered))
+            line = {"rate_req_s": rate, "requests": len(slo), "output_tokens_per_s": round(m.token_throughput, 1),
+                    "tpot_ms": {"p50": round(m.itl_latency_median_ms, 2), "p99": round(m.itl_latency_p99_ms, 2),
+                                "mean": round(m.itl_latency_mean_ms, 2)},
+                    "ttft_ms": {"mean": round(m.ttft_mean_ms, 1), "p99": round(m.ttft_p99_ms, 1)},
+                    "duration_s": round(m.e2e_duration, 2), "iterations": srv.iterations - it0,
+                    "graph_iterations": srv.graph_iterations - g0,
+                    "kernel_status": max(g["kernel_status"] for g in gathered),
+                    "layout": f"{groups} attention group(s) x tp{tp} + {world - A} expert GPUs",
+                    "workload": f"poisson, prompts U[{args.min_input_len},{args.max_input_len}], outputs "
+                                f"U[{args.min_output_len},{args.max_output_len}], {args.duration:.0f} s of arrivals"}
+            print(json.dumps(line), flush=True)
+            if args.file:
+                with open(args.file, "a") as f:
+                    f.write(json.dumps({**line, **asdict(m)}) + "\n")
+
+
+def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", default="mixtral")
     ap.add_argument("-L", "--num-layers", type=int, default=0)
@@ -87,7 +130,10 @@ def main():
                          "over gloo with a stand-in for the GPU side; --check then verifies the stand-in's tokens")
     ap.add_argument("-f", "--file", default="", help="append the metrics as one JSON line")
     ap.add_argument("--trace", default="", help="write a Chrome trace (json.gz) of every attention rank's iterations")
-    args = ap.parse_args()
+    ap.add_argument("--rates", default="", help="comma-separated request rates (req/s): runs the workload once per rate on "
+                    "the same engine, --duration seconds of arrivals each, and prints one JSON line per rate")
+    ap.add_argument("--duration", type=float, default=60.0, help="seconds of arrivals per rate of a --rates sweep")
+    args = ap.parse_args(argv)
 
     rank, world, lr = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     if os.environ.get("DMOE_SERVE_DEBUG"):
@@ -123,6 +169,10 @@ def main():
                            route_skew=args.route_skew,
                            max_prefill_tokens_per_mb=args.max_prefill_tokens_per_mb or None,
                            host_only_runner=host_only_runner(cfg.vocab_size) if args.host_only else None)
+    if args.rates:
+        sweep(args, srv, cfg, groups, tp, rank, world, A)
+        dist.destroy_process_group()
+        return 0
     owner = assign_requests(reqs, groups)
     mine = [r for r in reqs if srv.is_leader and owner[r[0]] == rank // tp]
     res = srv.serve(mine, time_limit=args.time_limit)
@@ -175,4 +225,4 @@ def main():
 
 
 if __name__ == "__main__":
-    main()
+    sys.exit(main() or 0)

@@ -337,6 +337,8 @@ def test_prefill_attention_tiled_causal(n_q, n_kv, hd):
     F.prefill_attention(q, kc, vc, bt, tiles.to(DEV), len(tiles), n_q, n_kv, hd, out)
     ref = reference.paged_attention(q, kc, vc, bt, bt_row, ctx, n_q, n_kv, hd)
     torch.cuda.synchronize()
-    _close(out, ref)
+    # probabilities are rounded to bf16 before P V and the output once more: a handful of elements in millions land two
+    # bf16 steps from the fp32 reference
+    _close(out, ref, tol=2 ** -6)
     # and the per-token kernel agrees with both (it is what the tiled kernel replaces for these rows)
-    _close(F.paged_attention(q, kc, vc, bt, bt_row, ctx, n_q, n_kv, hd), ref)
+    _close(F.paged_attention(q, kc, vc, bt, bt_row, ctx, n_q, n_kv, hd), ref, tol=2 ** -6)
