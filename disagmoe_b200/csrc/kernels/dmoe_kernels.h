@@ -64,6 +64,9 @@ typedef struct DmoeGemm {
   // a share boundary are reduced through ws (2 slots of 128 x bn fp32 per accumulator and CTA). n_counters: ints
   // available at `counters` (0 = 4096); one per tile is needed.
   int streamk, n_counters;
+  // pair != 0: clusters of two CTAs compute tiles of 256 weight rows x bn tokens with tcgen05.mma.cta_group::2 (each
+  // CTA stages its 128 weight rows and half of the token tile). bn = 128 or 256 (SwiGLU too), whole tiles only.
+  int pair;
 } DmoeGemm;
 
 int dmoe_gemm(const DmoeGemm* desc, void* stream);

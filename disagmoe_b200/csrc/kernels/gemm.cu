@@ -95,11 +95,16 @@ struct GemmArgs {
   long long flag_cycles;   // budget of the peer-flag waits
 };
 
-template <int BN, int EPI>
+// PAIR: the kernel runs as clusters of two CTAs on one tile of 256 weight rows (two m-tiles) x BN tokens with
+// tcgen05.mma.cta_group::2: each CTA stages its own 128 weight rows and HALF of the token tile, so the shared-memory
+// fill per output (the limiter at 128 and more tokens per expert) drops by a third to a half; each CTA keeps the
+// accumulator of its 128 rows in its own TMEM and runs its own epilogue.
+template <int BN, int EPI, bool PAIR = false>
 struct Cfg {
   static constexpr int kNumA = (EPI == EPI_SWIGLU) ? 2 : 1;
   static constexpr int kABytes = kBM * kBK * 2;
-  static constexpr int kBBytes = BN * kBK * 2;
+  static constexpr int kBRows = PAIR ? BN / 2 : BN;      // token rows this CTA stages
+  static constexpr int kBBytes = kBRows * kBK * 2;
   static constexpr int kStageBytes = kNumA * kABytes + kBBytes;
   // plain epilogue: one 32-token x 128-feature fp32 chunk is transposed through shared memory, so that Y (and the
   // residual) move as 16-byte row segments instead of one 2-byte element per thread
@@ -107,7 +112,9 @@ struct Cfg {
   static constexpr int kStagesRaw = (kSmemBudget - 1024 - kTailBytes - kEpiStageBytes) / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
   static constexpr int kAccCols = BN * kNumA;
-  static constexpr int kTmemCols = (2 * kAccCols) < 32 ? 32 : 2 * kAccCols;
+  // two accumulator buffers (the epilogue of a tile overlaps the next main loop) unless one already fills TMEM
+  static constexpr int kAccBufs = (2 * kAccCols <= 512) ? 2 : 1;
+  static constexpr int kTmemCols = (kAccBufs * kAccCols) < 32 ? 32 : kAccBufs * kAccCols;
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + kTailBytes + kEpiStageBytes;
   static_assert(kTmemCols <= 512, "accumulators do not fit TMEM");
   static_assert((kTmemCols & (kTmemCols - 1)) == 0, "TMEM columns must be a power of two");
@@ -123,10 +130,15 @@ __device__ __forceinline__ void st_release_sys(int* p, int v) {
   asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-template <int BN, int EPI>
+template <int BN, int EPI, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const GemmArgs a) {
-  using C = Cfg<BN, EPI>;
+  using C = Cfg<BN, EPI, PAIR>;
+  // pair mode: rank of this CTA in its pair (the even CTA issues the MMAs), work is dealt out per pair
+  const uint32_t prank = PAIR ? cluster_ctarank() : 0u;
+  const bool leader = prank == 0;
+  const int work_cta = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  const int work_grid = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* tail = smem + C::kStages * C::kStageBytes;
@@ -144,7 +156,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int MT = (a.F + kBM - 1) / kBM;
+  const int MT1 = (a.F + kBM - 1) / kBM;              // 128-row weight tiles
+  const int MT = PAIR ? (MT1 + 1) / 2 : MT1;          // work tiles along M (pairs of them in pair mode)
   const int kblocks = (a.K + kBK - 1) / kBK;
   // the producer may legitimately sit in a peer-flag wait (all-gather prologue): the warps behind it must outlast it
   const long long bar_budget = DMOE_WAIT_CYCLES + (a.shard_rows > 0 ? a.flag_cycles : 0);
@@ -158,7 +171,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&tfull_bar[b]), 1);
-      mbar_init(smem_u32(&tempty_bar[b]), kEpiThreads);
+      // pair mode: the epilogue threads of BOTH CTAs hand an accumulator buffer back to the even CTA's MMA thread
+      mbar_init(smem_u32(&tempty_bar[b]), PAIR ? 2 * kEpiThreads : kEpiThreads);
     }
     mbar_fence_init();
     tma_prefetch_desc(&tmW);
@@ -209,11 +223,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
     s_cnt[0] = a.T;
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_slot), C::kTmemCols);
-    tmem_relinquish();
+    if (PAIR) {
+      tmem_alloc_pair(smem_u32(tmem_slot), C::kTmemCols);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32(tmem_slot), C::kTmemCols);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();      // both CTAs' barriers are initialised before either is signalled from outside
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -221,7 +241,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       WorkWalker tw;
-      tw.init(s_start, s_cnt, a.G, S, MT, BN, kblocks, a.splitk, a.streamk, blockIdx.x, gridDim.x);
+      tw.init(s_start, s_cnt, a.G, S, MT, BN, kblocks, a.splitk, a.streamk, work_cta, work_grid);
       if (a.n_wait > 0) asm volatile("fence.proxy.async;" ::: "memory");  // peers' generic stores -> TMA reads
       const uint64_t pol_w = l2_policy_evict_first();
       const uint64_t pol_x = l2_policy_evict_last();
@@ -232,21 +252,31 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
       const int shard_want = (a.shard_rows > 0) ? *a.wait_epoch + 1 : 0;
       WorkUnit u;
       while (ok && tw.next(u)) {
-        const int xrow = u.row0, ntok_ = u.ntok;
-        const int wrow = u.g * a.w_rows + u.m * kBM;
+        const int ntok_ = u.ntok;
+        // pair mode: this CTA stages the token rows of its half of the MMA's N extent (the even CTA the first half)
+        int n_eff = (u.ntok + 31) & ~31;
+        n_eff = n_eff > BN ? BN : n_eff;
+        const int xrow = u.row0 + (PAIR ? static_cast<int>(prank) * (n_eff / 2) : 0);
+        const int wrow = u.g * a.w_rows + (PAIR ? 2 * u.m + static_cast<int>(prank) : u.m) * kBM;
         const int kb0 = u.kb0, kb1 = u.kb1;
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_word)) { ok = false; break; }
-          const uint32_t fb = smem_u32(&full_bar[stage]);
+          if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_word, bar_budget)) { ok = false; break; }
+          // pair mode: the bytes of both CTAs are counted on the even CTA's barrier, which its producer arms
+          const uint32_t fb = PAIR ? mapa_rank(smem_u32(&full_bar[stage]), 0) : smem_u32(&full_bar[stage]);
           uint8_t* st = smem + stage * C::kStageBytes;
-          mbar_expect_tx(fb, C::kStageBytes);
-          tma_load_2d(smem_u32(st), &tmW, kb * kBK, wrow, fb, pol_w);
-          if (EPI == EPI_SWIGLU) tma_load_2d(smem_u32(st + C::kABytes), &tmW, kb * kBK, wrow + a.F, fb, pol_w);
+          if (!PAIR) mbar_expect_tx(fb, C::kStageBytes);
+          else if (leader) mbar_expect_tx(smem_u32(&full_bar[stage]), 2 * C::kStageBytes);
+          auto load = [&](uint32_t dst, const CUtensorMap* m, int x, int y, uint64_t pol) {
+            if (PAIR) tma_load_2d_pair(dst, m, x, y, fb, pol);
+            else tma_load_2d(dst, m, x, y, fb, pol);
+          };
+          load(smem_u32(st), &tmW, kb * kBK, wrow, pol_w);
+          if (EPI == EPI_SWIGLU) load(smem_u32(st + C::kABytes), &tmW, kb * kBK, wrow + a.F, pol_w);
           if (a.shard_rows > 0 && kb == kb0) {
             // the weight tile is already on its way; the token tile may only be fetched once every peer whose rows
             // it covers has published them (the peers' stores are generic-proxy writes: fence before the TMA read)
-            const int s0 = xrow / a.shard_rows;
-            const int s1 = min((xrow + ntok_ - 1) / a.shard_rows, a.n_wait - 1);
+            const int s0 = u.row0 / a.shard_rows;
+            const int s1 = min((u.row0 + ntok_ - 1) / a.shard_rows, a.n_wait - 1);
             for (int sh = s0; sh <= s1 && ok; ++sh) {
               if ((shard_ready >> sh) & 1ull) continue;
               const long long t0 = clock64();
@@ -267,31 +297,34 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
             }
             if (!ok) break;
           }
-          tma_load_2d(smem_u32(st + C::kNumA * C::kABytes), &tmX, kb * kBK, xrow, fb, pol_x);
+          load(smem_u32(st + C::kNumA * C::kABytes), &tmX, kb * kBK, xrow, pol_x);
           if (++stage == C::kStages) { stage = 0; phase ^= 1; }
         }
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // ------------------------------------------------------------ MMA issuer (pair mode: the even CTA's only)
+    if (lane == 0 && leader) {
       WorkWalker tw;
-      tw.init(s_start, s_cnt, a.G, S, MT, BN, kblocks, a.splitk, a.streamk, blockIdx.x, gridDim.x);
+      tw.init(s_start, s_cnt, a.G, S, MT, BN, kblocks, a.splitk, a.streamk, work_cta, work_grid);
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
       WorkUnit u;
       for (; ok && tw.next(u); ++it) {
-        const int buf = it & 1;
-        const uint32_t bphase = (it >> 1) & 1;
-        if (!mbar_wait(smem_u32(&tempty_bar[buf]), bphase ^ 1, abort_word, bar_budget)) { ok = false; break; }
+        const int buf = it % C::kAccBufs;
+        const uint32_t bphase = (it / C::kAccBufs) & 1;
+        if (PAIR) {
+          if (!mbar_wait_cluster(smem_u32(&tempty_bar[buf]), bphase ^ 1, abort_word, bar_budget)) { ok = false; break; }
+        } else if (!mbar_wait(smem_u32(&tempty_bar[buf]), bphase ^ 1, abort_word, bar_budget)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d0 = tmem_base + buf * C::kAccCols;
         // a ragged token tile only pays for the MMA columns it has (N is a run-time field of the instruction)
-        int n_eff = (u.ntok + 15) & ~15;
-        n_eff = n_eff < 16 ? 16 : (n_eff > BN ? BN : n_eff);
-        const uint32_t idesc = umma_idesc_bf16(kBM, n_eff);
+        const int nq = PAIR ? 32 : 16;
+        int n_eff = (u.ntok + nq - 1) & ~(nq - 1);
+        n_eff = n_eff < nq ? nq : (n_eff > BN ? BN : n_eff);
+        const uint32_t idesc = umma_idesc_bf16(PAIR ? 2 * kBM : kBM, n_eff);
         const int kb0 = u.kb0, kb1 = u.kb1;
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(smem_u32(&full_bar[stage]), phase, abort_word, bar_budget)) { ok = false; break; }
@@ -303,16 +336,31 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
           for (int k = 0; k < kBK / kUmmaK; ++k) {
             const uint32_t acc = (kb > kb0 || k > 0) ? 1u : 0u;
             // advancing K by 16 bf16 = 32 bytes inside the 128-byte swizzle span: +2 in the (>>4) address field
-            umma_f16(d0, da + 2 * k, db + 2 * k, idesc, acc);
+            if (PAIR) umma_f16_pair(d0, da + 2 * k, db + 2 * k, idesc, acc);
+            else umma_f16(d0, da + 2 * k, db + 2 * k, idesc, acc);
             if (EPI == EPI_SWIGLU) {
               const uint64_t da2 = umma_desc_sw128(sa + C::kABytes);
-              umma_f16(d0 + BN, da2 + 2 * k, db + 2 * k, idesc, acc);
+              if (PAIR) umma_f16_pair(d0 + BN, da2 + 2 * k, db + 2 * k, idesc, acc);
+              else umma_f16(d0 + BN, da2 + 2 * k, db + 2 * k, idesc, acc);
             }
           }
-          umma_commit(smem_u32(&empty_bar[stage]));  // frees the smem stage when these MMAs retire
+          // frees the smem stage when these MMAs retire (pair mode: in both CTAs, one arrival each)
+          if (PAIR) {
+            umma_commit_pair(mapa_rank(smem_u32(&empty_bar[stage]), 0));
+            umma_commit_pair(mapa_rank(smem_u32(&empty_bar[stage]), 1));
+          } else {
+            umma_commit(smem_u32(&empty_bar[stage]));
+          }
           if (++stage == C::kStages) { stage = 0; phase ^= 1; }
         }
-        if (ok) umma_commit(smem_u32(&tfull_bar[buf]));
+        if (ok) {
+          if (PAIR) {
+            umma_commit_pair(mapa_rank(smem_u32(&tfull_bar[buf]), 0));
+            umma_commit_pair(mapa_rank(smem_u32(&tfull_bar[buf]), 1));
+          } else {
+            umma_commit(smem_u32(&tfull_bar[buf]));
+          }
+        }
       }
     }
   } else {
@@ -321,15 +369,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
     const int row = q * 32 + lane;          // accumulator lane = feature within the tile
     const int et = threadIdx.x - 64;        // 0..127
     WorkWalker tw;
-    tw.init(s_start, s_cnt, a.G, S, MT, BN, kblocks, a.splitk, a.streamk, blockIdx.x, gridDim.x);
+    tw.init(s_start, s_cnt, a.G, S, MT, BN, kblocks, a.splitk, a.streamk, work_cta, work_grid);
     constexpr size_t kSlotF4 = static_cast<size_t>(C::kNumA) * (BN / 4) * kBM;   // float4 per workspace slot
     int it = 0;
     bool ok = true;
     WorkUnit u;
     for (; ok && tw.next(u); ++it) {
-      const int m = u.m, tok_base = u.row0, ntok = u.ntok;
-      const int buf = it & 1;
-      const uint32_t bphase = (it >> 1) & 1;
+      const int m = PAIR ? 2 * u.m + static_cast<int>(prank) : u.m, tok_base = u.row0, ntok = u.ntok;
+      const int buf = it % C::kAccBufs;
+      const uint32_t bphase = (it / C::kAccBufs) & 1;
       if (!mbar_wait(smem_u32(&tfull_bar[buf]), bphase, abort_word, bar_budget)) { ok = false; break; }
       tc_fence_after();
       const uint32_t t0 = tmem_base + buf * C::kAccCols + (static_cast<uint32_t>(q * 32) << 16);
@@ -360,7 +408,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
           }
         }
         tc_fence_before();
-        mbar_arrive(smem_u32(&tempty_bar[buf]));
+        if (PAIR) mbar_arrive_cluster(mapa_rank(smem_u32(&tempty_bar[buf]), 0));
+        else mbar_arrive(smem_u32(&tempty_bar[buf]));
         __threadfence();
         named_bar_sync(1, kEpiThreads);
         if (et == 0) {
@@ -444,7 +493,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
           if (c == nchunk - 1) {
             // all of this thread's TMEM reads are done: hand the accumulator buffer back to the MMA warp
             tc_fence_before();
-            mbar_arrive(smem_u32(&tempty_bar[buf]));
+            if (PAIR) mbar_arrive_cluster(mapa_rank(smem_u32(&tempty_bar[buf]), 0));
+            else mbar_arrive(smem_u32(&tempty_bar[buf]));
           }
         }
         if (EPI == EPI_PLAIN && vec) {
@@ -611,9 +661,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
     for (int i = 0; i < 200; ++i) __nanosleep(1000);
     __syncthreads();
   }
+  if (PAIR) cluster_sync_all();      // neither CTA leaves (or frees TMEM) while the other may still signal or use it
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, C::kTmemCols);
+    if (PAIR) tmem_dealloc_pair(tmem_base, C::kTmemCols);
+    else tmem_dealloc(tmem_base, C::kTmemCols);
   }
 }
 
@@ -652,21 +704,41 @@ static int make_map_2d(CUtensorMap* map, const void* ptr, long long rows, long l
 
 static int num_sms() { return device_num_sms(); }
 
-template <int BN, int EPI>
+template <int BN, int EPI, bool PAIR = false>
 static int launch(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmArgs& a, int max_tiles,
                   cudaStream_t stream) {
-  using C = Cfg<BN, EPI>;
+  using C = Cfg<BN, EPI, PAIR>;
   static PerDeviceOnce configured;
   const int crc = configured.run([] {
-    return static_cast<int>(cudaFuncSetAttribute(gemm_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    return static_cast<int>(cudaFuncSetAttribute(gemm_kernel<BN, EPI, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                  C::kSmemBytes));
   });
   if (crc != 0) return crc;
-  int grid = num_sms();
-  if (max_tiles < grid) grid = max_tiles;
-  if (grid < 1) grid = 1;
-  gemm_kernel<BN, EPI><<<grid, kThreads, C::kSmemBytes, stream>>>(tmW, tmX, a);
-  return static_cast<int>(cudaGetLastError());
+  if (!PAIR) {
+    int grid = num_sms();
+    if (max_tiles < grid) grid = max_tiles;
+    if (grid < 1) grid = 1;
+    gemm_kernel<BN, EPI, false><<<grid, kThreads, C::kSmemBytes, stream>>>(tmW, tmX, a);
+    return static_cast<int>(cudaGetLastError());
+  }
+  // one cluster of two CTAs (two SMs of a TPC) per work tile
+  int pairs = num_sms() / 2;
+  if (max_tiles < pairs) pairs = max_tiles;
+  if (pairs < 1) pairs = 1;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(2 * pairs, 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = C::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return static_cast<int>(cudaLaunchKernelEx(&cfg, gemm_kernel<BN, EPI, true>, tmW, tmX, a));
 }
 
 }  // namespace dmoe
@@ -695,7 +767,9 @@ extern "C" int dmoe_gemm(const DmoeGemm* d, void* stream_) {
   int bn = d->bn;
   if (bn == 0) bn = dmoe_gemm_pick_bn((d->T + d->G - 1) / d->G, epi);
   if (bn != 32 && bn != 64 && bn != 128 && bn != 256) return -11;
-  if (epi == EPI_SWIGLU && bn > 128) return -11;
+  const bool pair = d->pair != 0;
+  if (epi == EPI_SWIGLU && bn > (pair ? 256 : 128)) return -11;
+  if (pair && (bn < 128 || d->splitk > 1)) return -11;
   int splitk = d->splitk < 1 ? 1 : d->splitk;
   const int kblocks = (d->K + kBK - 1) / kBK;
   if (splitk > kblocks) splitk = kblocks;
@@ -708,7 +782,7 @@ extern "C" int dmoe_gemm(const DmoeGemm* d, void* stream_) {
   if (splitk > 1 && dmoe_gemm_workspace_bytes(d->T, d->F, bn, splitk) > d->ws_bytes) return -13;
   // stream-K: one contiguous share of the K-block iterations per CTA; needs two partial-tile slots per CTA and one
   // counter per tile. Where the scratch is too small the launch quietly keeps whole tiles (a performance matter only).
-  int streamk = (d->streamk != 0 && splitk == 1 && d->ws != nullptr && d->counters != nullptr) ? 1 : 0;
+  int streamk = (d->streamk != 0 && !pair && splitk == 1 && d->ws != nullptr && d->counters != nullptr) ? 1 : 0;
   if (epi == EPI_COMBINE && (d->recs == nullptr || d->bases == nullptr)) return -14;
 
   GemmArgs a;
@@ -762,9 +836,10 @@ extern "C" int dmoe_gemm(const DmoeGemm* d, void* stream_) {
   CUtensorMap tmW, tmX;
   const long long ldx = d->ldx > 0 ? d->ldx : d->K;
   if (make_map_2d(&tmW, d->W, static_cast<long long>(d->G) * a.w_rows, d->K, d->K, kBM) != 0) return -20;
-  if (make_map_2d(&tmX, d->X, d->T, d->K, ldx, bn) != 0) return -21;
+  if (make_map_2d(&tmX, d->X, d->T, d->K, ldx, pair ? bn / 2 : bn) != 0) return -21;
 
-  const long long mt = (d->F + kBM - 1) / kBM;
+  long long mt = (d->F + kBM - 1) / kBM;
+  if (pair) mt = (mt + 1) / 2;
   // upper bound of the tile count (group sizes live on the device): every group may add one ragged tile
   long long max_tiles = mt * ((d->T + bn - 1) / bn + ((d->offs || d->S > 0 || d->group_regions) ? d->G * (d->S > 0 ? d->S : 1) : 0)) * splitk;
   if (max_tiles > (1 << 30)) max_tiles = 1 << 30;
@@ -778,6 +853,20 @@ extern "C" int dmoe_gemm(const DmoeGemm* d, void* stream_) {
   a.streamk = streamk;
 
 #define DMOE_LAUNCH(BN_, EPI_) return launch<BN_, EPI_>(tmW, tmX, a, mtiles, stream)
+#define DMOE_LAUNCH_PAIR(BN_, EPI_) return launch<BN_, EPI_, true>(tmW, tmX, a, mtiles, stream)
+  if (pair) {
+    if (epi == EPI_PLAIN) {
+      if (bn == 128) DMOE_LAUNCH_PAIR(128, EPI_PLAIN);
+      DMOE_LAUNCH_PAIR(256, EPI_PLAIN);
+    } else if (epi == EPI_SWIGLU) {
+      if (bn == 128) DMOE_LAUNCH_PAIR(128, EPI_SWIGLU);
+      DMOE_LAUNCH_PAIR(256, EPI_SWIGLU);
+    } else if (epi == EPI_COMBINE) {
+      if (bn == 128) DMOE_LAUNCH_PAIR(128, EPI_COMBINE);
+      DMOE_LAUNCH_PAIR(256, EPI_COMBINE);
+    }
+    return -15;
+  }
   if (epi == EPI_PLAIN) {
     switch (bn) {
       case 32: DMOE_LAUNCH(32, EPI_PLAIN);
@@ -800,6 +889,7 @@ extern "C" int dmoe_gemm(const DmoeGemm* d, void* stream_) {
     }
   }
 #undef DMOE_LAUNCH
+#undef DMOE_LAUNCH_PAIR
   return -15;
 }
 

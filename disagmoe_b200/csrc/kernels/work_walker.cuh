@@ -8,10 +8,13 @@
 // Two modes:
 //   split-K   every tile is cut into `splitk` equal K ranges (1 = whole tiles); unit i of the flat list (tile-major,
 //             split fastest) runs on CTA i mod grid.
-//   stream-K  the total work, counted in K blocks, is cut into one contiguous share per CTA (equal to within one K
-//             block), whatever the tile boundaries are: no CTA idles in a last partial wave. A tile that straddles
-//             a share boundary is computed by two (or more) CTAs; each parks its fp32 partial accumulator in a
-//             workspace slot and the last one to arrive adds them up and runs the epilogue.
+//   stream-K  full waves run as whole tiles (tile w * grid + c on CTA c in wave w: the CTAs of a wave work on
+//             neighbouring tiles at the same time, so a weight tile that two token tiles need is fetched from HBM
+//             once). The tiles of the last, partial wave are not left to a few CTAs: their work, counted in K blocks,
+//             is cut into one contiguous share per CTA (equal to within one K block). A tile that straddles a share
+//             boundary is computed by two or more CTAs; each parks its fp32 partial accumulator in a workspace slot
+//             and the last one to arrive adds them up and runs the epilogue. With fewer tiles than CTAs every tile is
+//             in that last wave.
 //
 // Plain C++ (also compiled for the host by the unit test of the partition arithmetic).
 #pragma once
@@ -40,8 +43,10 @@ struct WorkWalker {
   int G, S, MT, BN, kblocks, splitk, kb_per, streamk;
   int g, base, ntn;      // group cursor: tiles of group g start at id `base`
   long long lin, lin_step;              // split-K: next flat unit id of this CTA and the stride
-  long long it, it_end, total, it_begin;  // stream-K: this CTA's share [it_begin, it_end) of the K-block iterations
-  int active, cta;
+  // stream-K: `waves` full waves of whole tiles, then this CTA's share [it_begin, it_end) of the K-block iterations
+  // of the remaining tiles (ids from tile0 on); `total` counts the remainder's iterations
+  long long it, it_end, total, it_begin;
+  int active, cta, grid, waves, wave, tile0;
 
   DMOE_HD static int min_i(int a, int b) { return a < b ? a : b; }
 
@@ -57,12 +62,12 @@ struct WorkWalker {
   DMOE_HD int owner(long long i) const { return static_cast<int>(((i + 1) * active + total - 1) / total) - 1; }
 
   DMOE_HD void init(const int* s_start, const int* s_cnt, int G_, int S_, int MT_, int BN_, int kblocks_, int splitk_,
-                    int streamk_, int cta_, int grid) {
+                    int streamk_, int cta_, int grid_) {
     seg_start = s_start; seg_cnt = s_cnt; G = G_; S = S_; MT = MT_; BN = BN_; kblocks = kblocks_;
     splitk = splitk_ < 1 ? 1 : splitk_; streamk = streamk_; cta = cta_;
     kb_per = (kblocks + splitk - 1) / splitk;
-    lin = cta_; lin_step = grid;
-    it = it_end = it_begin = total = 0; active = 1;
+    lin = cta_; lin_step = grid_;
+    it = it_end = it_begin = total = 0; active = 1; grid = grid_; waves = wave = tile0 = 0;
     if (streamk) {
       long long tiles = 0;
       for (int gg = 0; gg < G; ++gg) {
@@ -70,12 +75,16 @@ struct WorkWalker {
         for (int s = 0; s < S; ++s) t += (seg_cnt[s * G + gg] + BN - 1) / BN;
         tiles += static_cast<long long>(MT) * t;
       }
-      total = tiles * kblocks;
-      // a share shorter than a few K blocks costs more in partial-tile traffic than it wins in balance
-      const int min_share = kblocks >= 8 ? 4 : kblocks;
+      waves = static_cast<int>(tiles / grid_);
+      tile0 = waves * grid_;
+      total = (tiles - tile0) * kblocks;
+      // a share shorter than a few K blocks (or a tile cut into more than 8 pieces) costs more in partial-tile
+      // traffic than it wins in balance
+      int min_share = kblocks >= 8 ? 4 : kblocks;
+      if (min_share < (kblocks + 7) / 8) min_share = (kblocks + 7) / 8;
       long long act = total / min_share;
       if (act < 1) act = 1;
-      active = act < grid ? static_cast<int>(act) : grid;
+      active = act < grid_ ? static_cast<int>(act) : grid_;
       if (total > 0 && cta_ < active) {
         it_begin = it = share_begin(cta_);
         it_end = share_begin(cta_ + 1);
@@ -125,10 +134,17 @@ struct WorkWalker {
       u.slot = tile * splitk + ks;
       return true;
     }
+    if (wave < waves) {
+      // full waves: whole tiles, neighbouring CTAs on neighbouring tiles
+      if (!locate(wave * grid + cta, u)) return false;
+      ++wave;
+      u.kb0 = 0; u.kb1 = kblocks; u.ncontrib = 1; u.c_first = cta; u.slot = 0;
+      return true;
+    }
     if (it >= it_end) return false;
-    const long long tile = it / kblocks;
-    if (!locate(static_cast<int>(tile), u)) return false;
-    const long long t0 = tile * kblocks, t1 = t0 + kblocks;
+    const long long rtile = it / kblocks;          // tile index inside the remainder
+    if (!locate(tile0 + static_cast<int>(rtile), u)) return false;
+    const long long t0 = rtile * kblocks, t1 = t0 + kblocks;
     const bool first_unit = (it == it_begin);
     u.kb0 = static_cast<int>(it - t0);
     const long long end = it_end < t1 ? it_end : t1;
@@ -144,7 +160,7 @@ struct WorkWalker {
   DMOE_HD long long contrib_slot(const WorkUnit& u, int j) const {
     if (!streamk) return static_cast<long long>(u.tile) * splitk + j;
     const long long c = u.c_first + j;
-    const long long first_tile = share_begin(c) / kblocks;   // the tile CTA c starts in: its slot 0
+    const long long first_tile = tile0 + share_begin(c) / kblocks;   // the tile CTA c's share starts in: its slot 0
     return c * 2 + (first_tile == u.tile ? 0 : 1);
   }
 };

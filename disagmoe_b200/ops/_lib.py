@@ -37,7 +37,7 @@ class DmoeGemm(ctypes.Structure):
         ("rope_table", ctypes.c_void_p), ("positions", ctypes.c_void_p), ("slots", ctypes.c_void_p),
         ("kcache", ctypes.c_void_p), ("vcache", ctypes.c_void_p),
         ("n_q", ctypes.c_int), ("n_kv", ctypes.c_int), ("hd", ctypes.c_int), ("rope_max_pos", ctypes.c_int),
-        ("streamk", ctypes.c_int), ("n_counters", ctypes.c_int),
+        ("streamk", ctypes.c_int), ("n_counters", ctypes.c_int), ("pair", ctypes.c_int),
     ]
 
 

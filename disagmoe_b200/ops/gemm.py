@@ -165,10 +165,11 @@ def rope_table(max_pos: int, hd: int, theta: float, device) -> torch.Tensor:
 
 
 def _launch(W, X, Y, R, offs, recs, bases, G, T, F, K, epi, bn, splitk, ldy, y_f32, comm: Optional[GemmComm] = None,
-            streamk: bool = False):
+            streamk: bool = False, pair: bool = False):
     s = scratch(X.device)
     d = _lib.DmoeGemm()
-    d.streamk, d.n_counters = int(streamk and splitk <= 1), s.counters.numel()
+    d.streamk, d.n_counters = int(streamk and splitk <= 1 and not pair), s.counters.numel()
+    d.pair = int(pair)
     if comm is not None:
         comm.fill(d)
     d.W, d.X, d.Y, d.R = W.data_ptr(), X.data_ptr(), _lib.ptr(Y), _lib.ptr(R)
@@ -193,8 +194,9 @@ def _check_x(x):
 
 def linear(x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor] = None,
            out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None, bn: int = 0,
-           splitk: int = 0, comm: Optional["GemmComm"] = None) -> torch.Tensor:
-    """y[T, F] = x[T, K] @ w[F, K].T (+ residual[T, F])."""
+           splitk: int = 0, comm: Optional["GemmComm"] = None, pair: bool = False) -> torch.Tensor:
+    """y[T, F] = x[T, K] @ w[F, K].T (+ residual[T, F]). ``pair``: CTA pairs (tcgen05 cta_group::2) on tiles of 256
+    weight rows x ``bn`` (128 / 256) tokens, whole tiles."""
     T, K = x.shape
     F = w.shape[0]
     if not x.is_cuda:
@@ -215,20 +217,25 @@ def linear(x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor] = 
     assert scatter or (out.stride(1) == 1 and out.dtype in (torch.bfloat16, torch.float32))
     if T == 0:
         return out
-    # splitk = 0 (default): stream-K -- the K-block iterations of all tiles are dealt out evenly over the SMs, so
-    # neither the tile count nor the tile width has to match the SM count. An explicit splitk >= 1 selects plain
-    # split-K with that many equal K ranges per tile (1 = whole tiles).
-    streamk = splitk == 0 and STREAM_K
+    # splitk = 0 (default): with at least one full wave of tiles, whole tiles per CTA plus a stream-K tail (the tiles of
+    # the last, partial wave are cut along K into equal shares for all SMs); with fewer tiles than SMs (decode sizes)
+    # plain split-K with a factor that fills the SMs. An explicit splitk >= 1 selects split-K with that factor.
+    sms = num_sms(x.device)
     if not bn:
         bn = pick_bn(T, EPI_PLAIN)
-        if not streamk and bn == 256 and ((F + 127) // 128) * ((T + 255) // 256) < num_sms(x.device) // 2:
+        if bn == 256 and ((F + 127) // 128) * ((T + 255) // 256) < sms // 2:
             bn = 128     # too few 256-wide tiles to fill the GPU: halve the tile instead of splitting K further
+    if pair:
+        bn = 256 if bn not in (128, 256) else bn
+        splitk = 1
+    streamk = splitk == 0 and STREAM_K and ((F + 127) // 128) * ((T + bn - 1) // bn) >= sms
     if streamk:
         splitk = 1
     else:
-        splitk = splitk or pick_splitk(T, F, K, bn, num_sms(x.device))
+        splitk = splitk or pick_splitk(T, F, K, bn, sms)
     _launch(w, x, out, residual, None, None, None, 1, T, F, K, EPI_PLAIN, bn, splitk,
-            F if scatter else out.stride(0), (not scatter) and out.dtype == torch.float32, comm, streamk=streamk)
+            F if scatter else out.stride(0), (not scatter) and out.dtype == torch.float32, comm, streamk=streamk,
+            pair=pair)
     return out
 
 
@@ -249,7 +256,8 @@ def _grouped_ref(x, w, offs, swiglu):
 
 
 def grouped_swiglu(x: torch.Tensor, w13: torch.Tensor, offs: Optional[torch.Tensor], out: Optional[torch.Tensor] = None,
-                   bn: int = 0, comm: Optional[GemmComm] = None, streamk: Optional[bool] = None) -> torch.Tensor:
+                   bn: int = 0, comm: Optional[GemmComm] = None, streamk: Optional[bool] = None,
+                   pair: bool = False) -> torch.Tensor:
     """act[T, I] = silu(x @ w13[g, :I].T) * (x @ w13[g, I:].T) for the rows of group g; w13 is [G, 2I, K]."""
     T, K = x.shape
     G, F2, _ = w13.shape
@@ -267,14 +275,16 @@ def grouped_swiglu(x: torch.Tensor, w13: torch.Tensor, offs: Optional[torch.Tens
         out = torch.empty(T, I, dtype=torch.bfloat16, device=x.device)
     if T == 0:
         return out
-    bn = bn or pick_bn(_group_hint(T, G), EPI_SWIGLU)
+    bn = bn or (pick_bn(_group_hint(T, G), EPI_COMBINE) if pair else pick_bn(_group_hint(T, G), EPI_SWIGLU))
+    if pair:
+        bn = max(bn, 128)
     _launch(w13, x, out, None, offs, None, None, G, T, I, K, EPI_SWIGLU, bn, 1, out.stride(0), False, comm,
-            streamk=STREAM_K if streamk is None else streamk)
+            streamk=STREAM_K if streamk is None else streamk, pair=pair)
     return out
 
 
 def grouped_linear(x: torch.Tensor, w: torch.Tensor, offs: torch.Tensor, out: Optional[torch.Tensor] = None,
-                   bn: int = 0, streamk: Optional[bool] = None) -> torch.Tensor:
+                   bn: int = 0, streamk: Optional[bool] = None, pair: bool = False) -> torch.Tensor:
     """y[T, F] = x @ w[g].T for the rows of group g; w is [G, F, K]."""
     T, K = x.shape
     G, F, _ = w.shape
@@ -291,14 +301,16 @@ def grouped_linear(x: torch.Tensor, w: torch.Tensor, offs: torch.Tensor, out: Op
     if T == 0:
         return out
     bn = bn or pick_bn(_group_hint(T, G), EPI_PLAIN)
+    if pair:
+        bn = max(bn, 128)
     _launch(w, x, out, None, offs, None, None, G, T, F, K, EPI_PLAIN, bn, 1, out.stride(0), False,
-            streamk=STREAM_K if streamk is None else streamk)
+            streamk=STREAM_K if streamk is None else streamk, pair=pair)
     return out
 
 
 def grouped_combine(x: torch.Tensor, w: torch.Tensor, offs: Optional[torch.Tensor], recs: torch.Tensor,
                     bases: torch.Tensor, ld_out: int, bn: int = 0, outs=None, comm: Optional[GemmComm] = None,
-                    streamk: Optional[bool] = None) -> None:
+                    streamk: Optional[bool] = None, pair: bool = False) -> None:
     """GEMM-2 with the combine epilogue: row t of group g becomes ``weight[t] * (x[t] @ w[g].T)`` written to row
     ``recs[t, 1]`` of the buffer ``bases[recs[t, 0]]`` (row stride ``ld_out`` elements).
 
@@ -320,8 +332,10 @@ def grouped_combine(x: torch.Tensor, w: torch.Tensor, offs: Optional[torch.Tenso
     if T == 0:
         return
     bn = bn or pick_bn(_group_hint(T, G), EPI_COMBINE)
+    if pair:
+        bn = max(bn, 128)
     _launch(w, x, None, None, offs, recs, bases, G, T, F, K, EPI_COMBINE, bn, 1, ld_out, False, comm,
-            streamk=STREAM_K if streamk is None else streamk)
+            streamk=STREAM_K if streamk is None else streamk, pair=pair)
 
 
 def swiglu_linear(x: torch.Tensor, w13: torch.Tensor, out: Optional[torch.Tensor] = None, bn: int = 0) -> torch.Tensor:

@@ -280,3 +280,48 @@ def test_stream_k_combine_matches_whole_tiles():
     exp[perm] = ref
     _close(outs[0], exp)
     _close(outs[1], exp)
+
+
+@pytest.mark.parametrize("T,F,K,bn", [(256, 512, 512, 256), (100, 256, 256, 128), (300, 384, 1024, 256), (37, 128, 64, 128),
+                                      (512, 6144, 4096, 256)])
+def test_cta_pair_linear(T, F, K, bn):
+    """Dense GEMM on CTA pairs (tcgen05.mma.cta_group::2: 256 weight rows per MMA, the token tile split between the two
+    CTAs' shared memories): full and ragged token tiles, an odd number of 128-row weight tiles (F = 384: the second CTA
+    of the last pair has no rows), residual add."""
+    torch.manual_seed(11)
+    x, w, r = _rand(T, K), _rand(F, K, scale=K ** -0.5), _rand(T, F)
+    y = gemm.linear(x, w, residual=r, bn=bn, pair=True)
+    torch.cuda.synchronize()
+    assert gemm.check_status() == 0
+    _close(y, x.float() @ w.float().T + r.float())
+
+
+@pytest.mark.parametrize("counts,I,K,bn", [([200, 0, 256, 31], 256, 512, 256), ([64] * 4, 384, 256, 128),
+                                            ([255, 260], 1408, 2048, 256)])
+def test_cta_pair_grouped_swiglu_and_combine(counts, I, K, bn):
+    """Expert GEMMs on CTA pairs: SwiGLU up-projection with gate and up accumulators for 256 tokens filling TMEM
+    (single-buffered), and the down-projection with the combine epilogue."""
+    torch.manual_seed(12)
+    G, T = len(counts), sum(counts)
+    x, w13 = _rand(T, K), _rand(G, 2 * I, K, scale=K ** -0.5)
+    offs = _offsets(counts)
+    act = gemm.grouped_swiglu(x, w13, offs, bn=bn, pair=True)
+    torch.cuda.synchronize()
+    assert gemm.check_status() == 0
+    ref_act = gemm._grouped_ref(x, w13, offs, True)
+    _close(act, ref_act)
+    F = 256
+    w2 = _rand(G, F, I, scale=I ** -0.5)
+    perm = torch.randperm(T, device="cuda")
+    wts = torch.rand(T, device="cuda")
+    recs = torch.zeros(T, 4, dtype=torch.int32, device="cuda")
+    recs[:, 1] = perm.int()
+    recs[:, 2] = wts.view(torch.int32)
+    out = torch.zeros(T, F, dtype=torch.bfloat16, device="cuda")
+    bases = torch.tensor([out.data_ptr()], dtype=torch.int64, device="cuda")
+    gemm.grouped_combine(act, w2, offs, recs, bases, out.stride(0), bn=bn, pair=True)
+    torch.cuda.synchronize()
+    assert gemm.check_status() == 0
+    exp = torch.zeros(T, F, device="cuda")
+    exp[perm] = gemm._grouped_ref(act, w2, offs, False) * wts[:, None]
+    _close(out, exp)
