@@ -63,6 +63,10 @@ def main(argv=None):
             res[("g1", sk)] = timed(lambda: gemm.grouped_swiglu(x, w13, offs, streamk=sk), flush, a.iters)
             for bn in (128, 256):
                 res[("g2", sk, bn)] = timed(lambda: gemm.grouped_linear(act, w2, offs, bn=bn, streamk=sk), flush, a.iters)
+        # CTA pairs (cta_group::2): 256 weight rows per MMA, the token tile split between the two CTAs' shared memories
+        for bn in (128, 256):
+            res[("g1p", bn)] = timed(lambda: gemm.grouped_swiglu(x, w13, offs, bn=bn, pair=True), flush, a.iters)
+            res[("g2p", bn)] = timed(lambda: gemm.grouped_linear(act, w2, offs, bn=bn, pair=True), flush, a.iters)
         lib_offs = offs[1:].contiguous()
         t_lib = timed(lambda: torch._grouped_mm(x, w13.transpose(1, 2), offs=lib_offs), flush, a.iters)
         t_lib2 = timed(lambda: torch._grouped_mm(act, w2.transpose(1, 2), offs=lib_offs), flush, a.iters)
@@ -74,7 +78,10 @@ def main(argv=None):
               f"GEMM-1+SwiGLU stream-K {t1:.1f} us ({gb1 / t1 * 1e6:.0f} GB/s, {f1 / t1 / 1e6:.0f} TFLOP/s), whole tiles "
               f"{res[('g1', False)]:.1f} us; GEMM-2 stream-K bn128 {res[('g2', True, 128)]:.1f} / bn256 "
               f"{res[('g2', True, 256)]:.1f} us (best {gb2 / t2 * 1e6:.0f} GB/s, {f2 / t2 / 1e6:.0f} TFLOP/s), whole tiles "
-              f"bn128 {res[('g2', False, 128)]:.1f} / bn256 {res[('g2', False, 256)]:.1f} us; torch._grouped_mm "
+              f"bn128 {res[('g2', False, 128)]:.1f} / bn256 {res[('g2', False, 256)]:.1f} us; CTA pairs GEMM-1 bn128 "
+              f"{res[('g1p', 128)]:.1f} / bn256 {res[('g1p', 256)]:.1f} us ({f1 / min(res[('g1p', 128)], res[('g1p', 256)]) / 1e6:.0f} "
+              f"TFLOP/s), GEMM-2 bn128 {res[('g2p', 128)]:.1f} / bn256 {res[('g2p', 256)]:.1f} us "
+              f"({f2 / min(res[('g2p', 128)], res[('g2p', 256)]) / 1e6:.0f} TFLOP/s); torch._grouped_mm "
               f"GEMM-1 {t_lib:.1f} us, GEMM-2 {t_lib2:.1f} us", flush=True)
     assert gemm.check_status() == 0
 
