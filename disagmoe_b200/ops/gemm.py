@@ -85,6 +85,18 @@ def pick_bn(tokens_per_group: int, epi: int) -> int:
     return bn
 
 
+def want_streamk(epi: int, F: int, G: int, T: int, bn: int, sms: int) -> bool:
+    """Work distribution of a grouped GEMM, from measurements on B200 (benchmark/ops/grouped_gemm.py): the stream-K
+    tail pays off when the expected tile count fills the last wave of CTAs badly (few experts with long K loops, the
+    down-projection at decode sizes); the SwiGLU up-projection, whose partial tiles carry two accumulators, is faster
+    with whole tiles. Group sizes are only known on the device: the estimate assumes even routing."""
+    if not STREAM_K or epi == EPI_SWIGLU:
+        return False
+    tiles = ((F + 127) // 128) * max(G, (T + bn - 1) // bn)
+    waves = (tiles + sms - 1) // sms
+    return tiles / (waves * sms) < 0.9
+
+
 def _group_hint(T: int, G: int) -> int:
     """Token-tile hint for a grouped GEMM whose group sizes are only known on the device: the mean group size plus
     head-room for routing imbalance, so that most groups fit one token tile (a second tile re-reads the weights)."""
@@ -278,8 +290,9 @@ def grouped_swiglu(x: torch.Tensor, w13: torch.Tensor, offs: Optional[torch.Tens
     bn = bn or (pick_bn(_group_hint(T, G), EPI_COMBINE) if pair else pick_bn(_group_hint(T, G), EPI_SWIGLU))
     if pair:
         bn = max(bn, 128)
+    sk = want_streamk(EPI_SWIGLU, I, G, T, bn, num_sms(x.device)) if streamk is None else streamk
     _launch(w13, x, out, None, offs, None, None, G, T, I, K, EPI_SWIGLU, bn, 1, out.stride(0), False, comm,
-            streamk=STREAM_K if streamk is None else streamk, pair=pair)
+            streamk=sk, pair=pair)
     return out
 
 
@@ -303,8 +316,8 @@ def grouped_linear(x: torch.Tensor, w: torch.Tensor, offs: torch.Tensor, out: Op
     bn = bn or pick_bn(_group_hint(T, G), EPI_PLAIN)
     if pair:
         bn = max(bn, 128)
-    _launch(w, x, out, None, offs, None, None, G, T, F, K, EPI_PLAIN, bn, 1, out.stride(0), False,
-            streamk=STREAM_K if streamk is None else streamk, pair=pair)
+    sk = want_streamk(EPI_PLAIN, F, G, T, bn, num_sms(x.device)) if streamk is None else streamk
+    _launch(w, x, out, None, offs, None, None, G, T, F, K, EPI_PLAIN, bn, 1, out.stride(0), False, streamk=sk, pair=pair)
     return out
 
 
@@ -334,8 +347,9 @@ def grouped_combine(x: torch.Tensor, w: torch.Tensor, offs: Optional[torch.Tenso
     bn = bn or pick_bn(_group_hint(T, G), EPI_COMBINE)
     if pair:
         bn = max(bn, 128)
-    _launch(w, x, None, None, offs, recs, bases, G, T, F, K, EPI_COMBINE, bn, 1, ld_out, False, comm,
-            streamk=STREAM_K if streamk is None else streamk, pair=pair)
+    sk = want_streamk(EPI_COMBINE, F, G, T, bn, num_sms(x.device)) if streamk is None else streamk
+    _launch(w, x, None, None, offs, recs, bases, G, T, F, K, EPI_COMBINE, bn, 1, ld_out, False, comm, streamk=sk,
+            pair=pair)
 
 
 def swiglu_linear(x: torch.Tensor, w13: torch.Tensor, out: Optional[torch.Tensor] = None, bn: int = 0) -> torch.Tensor:
@@ -356,5 +370,5 @@ def swiglu_linear(x: torch.Tensor, w13: torch.Tensor, out: Optional[torch.Tensor
     if T == 0:
         return out
     bn = bn or pick_bn(T, EPI_SWIGLU)
-    _launch(w13, x, out, None, None, None, None, 1, T, I, K, EPI_SWIGLU, bn, 1, out.stride(0), False, streamk=STREAM_K)
+    _launch(w13, x, out, None, None, None, None, 1, T, I, K, EPI_SWIGLU, bn, 1, out.stride(0), False)
     return out

@@ -70,7 +70,7 @@ def test_grouped_swiglu(counts, I, K, bn):
     G, T = len(counts), sum(counts)
     x, w13 = _rand(T, K), _rand(G, 2 * I, K, scale=K ** -0.5)
     offs = _offsets(counts)
-    y = gemm.grouped_swiglu(x, w13, offs, bn=bn)
+    y = gemm.grouped_swiglu(x, w13, offs, bn=bn, streamk=gemm.STREAM_K)
     torch.cuda.synchronize()
     assert gemm.check_status() == 0
     _close(y, gemm._grouped_ref(x, w13, offs, True))
@@ -83,7 +83,7 @@ def test_grouped_linear(counts, F, K, bn):
     G, T = len(counts), sum(counts)
     x, w = _rand(T, K), _rand(G, F, K, scale=K ** -0.5)
     offs = _offsets(counts)
-    y = gemm.grouped_linear(x, w, offs, bn=bn)
+    y = gemm.grouped_linear(x, w, offs, bn=bn, streamk=gemm.STREAM_K)
     torch.cuda.synchronize()
     _close(y, gemm._grouped_ref(x, w, offs, False))
 
@@ -120,13 +120,13 @@ def test_grouped_real_expert_shapes_bn256_and_empty_groups():
     x = _rand(T, H)
     w13 = _rand(G, 2 * I, H, scale=H ** -0.5)
     offs = _offsets(counts)
-    act = gemm.grouped_swiglu(x, w13, offs, bn=128)
+    act = gemm.grouped_swiglu(x, w13, offs, bn=128, streamk=gemm.STREAM_K)
     torch.cuda.synchronize()
     assert gemm.check_status() == 0
     _close(act, gemm._grouped_ref(x, w13, offs, True))
     del w13
     w2 = _rand(G, H, I, scale=I ** -0.5)
-    y = gemm.grouped_linear(act, w2, offs, bn=256)
+    y = gemm.grouped_linear(act, w2, offs, bn=256, streamk=gemm.STREAM_K)
     torch.cuda.synchronize()
     assert gemm.check_status() == 0
     _close(y, gemm._grouped_ref(act, w2, offs, False))
