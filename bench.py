@@ -193,6 +193,13 @@ def main():
             tp -= 1
         if not args.no_selfcheck:
             selfcheck = selfcheck_against_colocated(world, rank, local_rank, A, tp, args.micro_batches)
+            if tp > 1 and (selfcheck["kernel_status"] != 0 or selfcheck["max_rel_err"] > 0.1):
+                # the tensor-parallel layout did not reproduce the colocated logits on this box: measure the
+                # data-parallel layout instead and say so, rather than time a wrong computation
+                bad = selfcheck
+                tp = 1
+                selfcheck = selfcheck_against_colocated(world, rank, local_rank, A, tp, args.micro_batches)
+                selfcheck["fell_back_from_tp"] = bad
         runner = DisaggDecodeBench(cfg, world, rank, local_rank, B, args.ctx_min, args.ctx_max, K + W, g, tp=tp,
                                    n_attn=A, route_skew=args.route_skew, n_mb=args.micro_batches)
         parallelism = runner.parallelism

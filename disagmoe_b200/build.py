@@ -73,7 +73,9 @@ def build_kernels(force=False, verbose=False):
         for out in ex.map(lambda j: _run(j[0], j[1]), jobs):
             if verbose:
                 print(out)
-    _run([nvcc, "-shared", "-o", KERNEL_LIB] + objs + ["-lcudart"])
+    # link next to the product and rename: a reader (or a snapshot of the tree) never sees a half-written library
+    _run([nvcc, "-shared", "-o", KERNEL_LIB + ".tmp"] + objs + ["-lcudart"])
+    os.replace(KERNEL_LIB + ".tmp", KERNEL_LIB)
     return KERNEL_LIB
 
 
@@ -131,8 +133,9 @@ def build_runtime(force=False, verbose=False, sanitize=None):
             if verbose:
                 print(res)
     torch_lib = os.path.join(os.path.dirname(torch.__file__), "lib")
-    _run(["g++", "-shared", "-o", out] + san_flags + objs + ["-L" + torch_lib, "-Wl,-rpath," + torch_lib, "-ltorch", "-ltorch_cpu",
-                                                  "-lc10", "-ltorch_python", "-lpthread", "-ldl"])
+    _run(["g++", "-shared", "-o", out + ".tmp"] + san_flags + objs + ["-L" + torch_lib, "-Wl,-rpath," + torch_lib, "-ltorch",
+                                                           "-ltorch_cpu", "-lc10", "-ltorch_python", "-lpthread", "-ldl"])
+    os.replace(out + ".tmp", out)
     return out
 
 

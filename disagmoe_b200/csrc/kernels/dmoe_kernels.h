@@ -88,6 +88,8 @@ int dmoe_argmax(const void* logits, int is_f32, long long ld, int T, int V, int*
 int dmoe_permute_rows(const void* src, long long ld_src, void* dst, long long ld_dst, const int* map, int n, int H,
                       int repeat, int gather, void* stream);
 int dmoe_gather_ptrs(const void* ptrs, void* dst, long long ld_dst, int n, int H, void* stream);
+// Debug kernel of the launch / overlap tests: out[i] = in[i] + 1 (fp32).
+int dmoe_add_one(const float* in, float* out, long long n, void* stream);
 
 // ---- attention (attention.cu) -----------------------------------------------------------------------
 long long dmoe_paged_attention_workspace_floats(int T, int n_q, int hd, int splits);

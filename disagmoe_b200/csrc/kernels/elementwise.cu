@@ -234,9 +234,22 @@ __global__ void gather_ptrs_kernel(const __nv_bfloat16* const* __restrict__ ptrs
   }
 }
 
+// Debug kernel of the launch / overlap tests: out[i] = in[i] + 1 (reference: csrc/cuda_ops/test.cu:6-13, one thread per
+// block there; 256 here).
+__global__ void add_one_kernel(const float* __restrict__ in, float* __restrict__ out, long long n) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = in[i] + 1.f;
+}
+
 }  // namespace dmoe
 
 using namespace dmoe;
+
+extern "C" int dmoe_add_one(const float* in, float* out, long long n, void* stream) {
+  if (n <= 0) return 0;
+  add_one_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(in, out, n);
+  return static_cast<int>(cudaGetLastError());
+}
 
 extern "C" int dmoe_add_rmsnorm(const void* resid_in, const void* add, int n_add, long long add_row_stride,
                                 long long add_part_stride, const void* w, float eps, void* resid_out, void* y, int T,

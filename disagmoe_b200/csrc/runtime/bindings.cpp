@@ -1,5 +1,7 @@
 // pybind11 module `disagmoe_c`: the native host runtime exposed to Python.
 // Reference surface covered: csrc/bindings.cpp:24-221 (class and function names kept where the concept exists here).
+#include <chrono>
+
 #include <pybind11/functional.h>
 #include <pybind11/stl.h>
 #include <torch/extension.h>
@@ -126,6 +128,120 @@ bool test_nccl_p2p(int dev_a, int dev_b, int n, int hidden) {
   ts.join();
   tr.join();
   return torch::equal(src.cpu(), dst.cpu());
+}
+
+// N ranks of one NCCL group channel in one process (one thread per device): barrier, tensor broadcast from rank 0,
+// object broadcast, in-place all-reduce. True when every rank saw the expected values.
+bool test_nccl_group(std::vector<int> devices) {
+  const int world = static_cast<int>(devices.size());
+  const std::string uid = get_nccl_unique_id();
+  auto& api = GpuApi::get();
+  std::vector<int> ok(world, 0);
+  std::vector<std::thread> ts;
+  for (int r = 0; r < world; ++r) {
+    ts.emplace_back([&, r] {
+      const int dev = devices[r];
+      api.cudaSetDevice(dev);
+      auto ch = create_nccl_group_channel(r, world, uid);
+      ch->instantiate();
+      ch->barrier();
+      const auto opts = torch::TensorOptions().dtype(torch::kBFloat16).device(torch::kCUDA, dev);
+      Metadata m;
+      m.shape = {8, 64};
+      auto want = torch::arange(8 * 64, torch::TensorOptions().dtype(torch::kFloat32)).reshape({8, 64}).to(torch::kBFloat16);
+      torch::Tensor t = r == 0 ? want.to(opts.device()) : torch::zeros({8, 64}, opts);
+      if (r == 0) ch->send(t, m); else ch->recv(t, m);
+      ch->sync();
+      bool good = torch::equal(t.cpu(), want);
+      std::string obj = r == 0 ? std::string("schedule: layer 3, sequences 5 9 11") : std::string();
+      ch->bcast_obj(obj);
+      good = good && obj == "schedule: layer 3, sequences 5 9 11";
+      auto x = torch::full({4, 32}, static_cast<float>(r + 1), opts);
+      ch->all_reduce(x);
+      ch->sync();
+      good = good && torch::allclose(x.cpu().to(torch::kFloat32), torch::full({4, 32}, world * (world + 1) / 2.0f));
+      ch->barrier();
+      ok[r] = good ? 1 : 0;
+    });
+  }
+  for (auto& t : ts) t.join();
+  for (int v : ok)
+    if (!v) return false;
+  return true;
+}
+
+typedef int (*add_one_fn)(const float*, float*, long long, void*);
+
+// Many small launches of the debug kernel on two streams at once, each stream a dependent chain x -> x + 1 -> ...;
+// true when both chains end at `launches` (launch ordering inside a stream, independence between streams).
+bool test_multi_launch(int device, int launches, int n) {
+  auto fn = reinterpret_cast<add_one_fn>(kernel_library_symbol("dmoe_add_one"));
+  DMOE_CHECK(fn != nullptr, "the kernel library (lib/libdmoe_kernels.so) is not built");
+  auto& api = GpuApi::get();
+  api.cudaSetDevice(device);
+  const auto opts = torch::TensorOptions().dtype(torch::kFloat32).device(torch::kCUDA, device);
+  void* streams[2] = {nullptr, nullptr};
+  torch::Tensor buf[2][2];
+  for (int s = 0; s < 2; ++s) {
+    DMOE_CHECK(api.cudaStreamCreateWithFlags(&streams[s], 1) == 0, "cudaStreamCreateWithFlags failed");
+    buf[s][0] = torch::zeros({n}, opts);
+    buf[s][1] = torch::zeros({n}, opts);
+  }
+  api.cudaStreamSynchronize(nullptr);   // the zero fills ran on the default stream
+  bool ok = true;
+  for (int i = 0; i < launches; ++i)
+    for (int s = 0; s < 2; ++s)
+      ok = ok && fn(buf[s][i & 1].data_ptr<float>(), buf[s][(i + 1) & 1].data_ptr<float>(), n, streams[s]) == 0;
+  for (int s = 0; s < 2; ++s) {
+    api.cudaStreamSynchronize(streams[s]);
+    ok = ok && torch::allclose(buf[s][launches & 1].cpu(), torch::full({n}, static_cast<float>(launches)));
+    api.cudaStreamDestroy(streams[s]);
+  }
+  return ok;
+}
+
+// Does a collective on the group channel's stream overlap with kernels on a compute stream? Two ranks (one thread per
+// device) time, on the host, a run of broadcasts alone, a run of debug-kernel launches alone, and both together.
+// Returns rank 0's {broadcast ms, kernels ms, both ms}; overlap shows as both < broadcast + kernels.
+std::vector<double> test_op_overlap(int dev_a, int dev_b, int mbytes, int launches) {
+  auto fn = reinterpret_cast<add_one_fn>(kernel_library_symbol("dmoe_add_one"));
+  DMOE_CHECK(fn != nullptr, "the kernel library (lib/libdmoe_kernels.so) is not built");
+  const std::string uid = get_nccl_unique_id();
+  auto& api = GpuApi::get();
+  std::vector<double> out(3, 0.0);
+  const int devs[2] = {dev_a, dev_b};
+  auto worker = [&](int r) {
+    const int dev = devs[r];
+    api.cudaSetDevice(dev);
+    auto ch = create_nccl_group_channel(r, 2, uid);
+    ch->instantiate();
+    const int64_t n = static_cast<int64_t>(mbytes) << 18;   // fp32 elements
+    const auto opts = torch::TensorOptions().dtype(torch::kFloat32).device(torch::kCUDA, dev);
+    auto payload = torch::ones({n}, opts), a = torch::zeros({n}, opts), b = torch::zeros({n}, opts);
+    void* compute = nullptr;
+    DMOE_CHECK(api.cudaStreamCreateWithFlags(&compute, 1) == 0, "cudaStreamCreateWithFlags failed");
+    api.cudaStreamSynchronize(nullptr);
+    auto bcasts = [&] { for (int i = 0; i < 4; ++i) ch->broadcast(payload.data_ptr(), payload.data_ptr(), n, 7 /*float*/, 0); };
+    auto kernels = [&] { for (int i = 0; i < launches; ++i) fn(a.data_ptr<float>(), b.data_ptr<float>(), n, compute); };
+    auto wait_all = [&] { ch->sync(); api.cudaStreamSynchronize(compute); };
+    auto timed = [&](bool do_b, bool do_k) {
+      ch->barrier();
+      const auto t0 = std::chrono::steady_clock::now();
+      if (do_b) bcasts();
+      if (do_k) kernels();
+      wait_all();
+      return std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+    };
+    timed(true, true);   // warm-up
+    const double tb = timed(true, false), tk = timed(false, true), tboth = timed(true, true);
+    ch->barrier();
+    api.cudaStreamDestroy(compute);
+    if (r == 0) { out[0] = tb; out[1] = tk; out[2] = tboth; }
+  };
+  std::thread t0(worker, 0), t1(worker, 1);
+  t0.join();
+  t1.join();
+  return out;
 }
 
 }  // namespace
@@ -601,4 +717,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("test_parallel_attn_scheduler", &test_parallel_attn_scheduler, py::call_guard<py::gil_scoped_release>());
   m.def("test_recorder_threads", &test_recorder_threads, py::call_guard<py::gil_scoped_release>());
   m.def("test_nccl_p2p", &test_nccl_p2p, py::call_guard<py::gil_scoped_release>());
+  m.def("test_nccl_group", &test_nccl_group, py::arg("devices"), py::call_guard<py::gil_scoped_release>());
+  m.def("test_multi_launch", &test_multi_launch, py::arg("device") = 0, py::arg("launches") = 200, py::arg("n") = 4096,
+        py::call_guard<py::gil_scoped_release>());
+  m.def("test_op_overlap", &test_op_overlap, py::arg("dev_a") = 0, py::arg("dev_b") = 1, py::arg("mbytes") = 64,
+        py::arg("launches") = 200, py::call_guard<py::gil_scoped_release>());
 }

@@ -11,21 +11,27 @@ namespace {
 // dmoe_gather_ptrs of the package's kernel library (lib/libdmoe_kernels.so next to this module): dst[i] = the bf16 row
 // at device address ptrs[i]. Resolved once; nullptr when the library is not there (CPU-only installs).
 typedef int (*gather_ptrs_fn)(const void*, void*, long long, int, int, void*);
+}  // namespace
 
-gather_ptrs_fn kernel_gather() {
-  static gather_ptrs_fn fn = [] {
+// A symbol of the package's kernel library (lib/libdmoe_kernels.so next to this module), or nullptr.
+void* kernel_library_symbol(const char* name) {
+  static void* handle = [] {
     Dl_info info;
     if (dladdr(reinterpret_cast<void*>(&set_helper_error), &info) == 0 || info.dli_fname == nullptr)
-      return static_cast<gather_ptrs_fn>(nullptr);
+      return static_cast<void*>(nullptr);
     std::string dir(info.dli_fname);
     const auto slash = dir.rfind('/');
     dir = slash == std::string::npos ? std::string(".") : dir.substr(0, slash);
-    for (const char* rel : {"/lib/libdmoe_kernels.so", "/../../lib/libdmoe_kernels.so"}) {
-      if (void* h = dlopen((dir + rel).c_str(), RTLD_NOW | RTLD_LOCAL))
-        if (void* f = dlsym(h, "dmoe_gather_ptrs")) return reinterpret_cast<gather_ptrs_fn>(f);
-    }
-    return static_cast<gather_ptrs_fn>(nullptr);
+    for (const char* rel : {"/lib/libdmoe_kernels.so", "/../../lib/libdmoe_kernels.so"})
+      if (void* h = dlopen((dir + rel).c_str(), RTLD_NOW | RTLD_LOCAL)) return h;
+    return static_cast<void*>(nullptr);
   }();
+  return handle != nullptr ? dlsym(handle, name) : nullptr;
+}
+
+namespace {
+gather_ptrs_fn kernel_gather() {
+  static gather_ptrs_fn fn = reinterpret_cast<gather_ptrs_fn>(kernel_library_symbol("dmoe_gather_ptrs"));
   return fn;
 }
 }  // namespace

@@ -53,6 +53,8 @@ struct AttentionBatch {
 
 // First exception that ended a helper thread of this process (empty while all of them run).
 void set_helper_error(const std::string& what);
+// A symbol of the package's kernel library (lib/libdmoe_kernels.so next to this module), or nullptr (CPU-only installs).
+void* kernel_library_symbol(const char* name);
 std::string helper_error();
 
 class MuHelper {

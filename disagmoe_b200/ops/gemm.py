@@ -94,7 +94,7 @@ def want_streamk(epi: int, F: int, G: int, T: int, bn: int, sms: int) -> bool:
         return False
     tiles = ((F + 127) // 128) * max(G, (T + bn - 1) // bn)
     waves = (tiles + sms - 1) // sms
-    return tiles / (waves * sms) < 0.9
+    return tiles / (waves * sms) < 0.85
 
 
 def _group_hint(T: int, G: int) -> int:

@@ -342,3 +342,18 @@ def test_prefill_attention_tiled_causal(n_q, n_kv, hd):
     _close(out, ref, tol=2 ** -6)
     # and the per-token kernel agrees with both (it is what the tiled kernel replaces for these rows)
     _close(F.paged_attention(q, kc, vc, bt, bt_row, ctx, n_q, n_kv, hd), ref, tol=2 ** -6)
+
+
+def test_debug_add_one_kernel_and_multi_launch():
+    """The debug kernel of the launch / overlap experiments, and the native module's test that chains hundreds of its
+    launches on two streams at once (counterpart of the reference's test_multi_launch)."""
+    import ctypes
+    from disagmoe_b200 import disagmoe_c as C
+    from disagmoe_b200.ops import _lib
+    x = torch.randn(1000, device=DEV)
+    y = torch.empty_like(x)
+    rc = _lib.lib().dmoe_add_one(ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(y.data_ptr()), ctypes.c_longlong(1000),
+                                 ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    assert rc == 0 and torch.equal(y, x + 1)
+    assert C.test_multi_launch(0, 300, 4096)

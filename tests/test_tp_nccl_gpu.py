@@ -136,3 +136,17 @@ def test_in_module_nccl_p2p_two_devices():
     from disagmoe_b200 import disagmoe_c as C
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     assert C.test_nccl_p2p(0, 1, 64, 256)
+
+
+@needs_two
+def test_in_module_nccl_group_and_overlap():
+    """The native module's own tests of the N-rank group channel (barrier, tensor and object broadcast, all-reduce; one
+    thread per device in this process) and of collective / compute overlap (broadcasts on the channel's stream while the
+    debug kernel runs on a compute stream): counterparts of the reference's test_nccl_group and test_op_overlap."""
+    from disagmoe_b200 import disagmoe_c as C
+    n = min(4, torch.cuda.device_count())
+    assert C.test_nccl_group(list(range(n)))
+    tb, tk, tboth = C.test_op_overlap(0, 1, 64, 400)
+    assert tb > 0 and tk > 0 and tboth > 0
+    # overlap: running both takes clearly less than running one after the other (generous margin: shared machine)
+    assert tboth < 0.95 * (tb + tk) or tboth < 1.5 * max(tb, tk), (tb, tk, tboth)
