@@ -46,20 +46,25 @@ def main():
     ap.add_argument("--n-expert", type=int, default=4)
     ap.add_argument("--ctx", type=int, default=864)
     ap.add_argument("--side", default="both")
+    ap.add_argument("--tp", type=int, default=1, help="attention tensor-parallel degree: the measured rank is member 0 of a "
+                    "TP group that serves tp x batch rows (its peers' flags are pre-satisfied)")
     a = ap.parse_args()
     cfg = get_preset(a.model).clone(num_layers=a.layers)
-    S = DisaggShape(a.n_attn, a.n_expert, 2, a.batch, cfg.top_k, cfg.hidden_size, cfg.num_experts)
+    S = DisaggShape(a.n_attn, a.n_expert, 2, a.batch * a.tp, cfg.top_k, cfg.hidden_size, cfg.num_experts, a.tp)
     layout = build_layout(S)
     big = 2 ** 30
     if a.side in ("both", "attn"):
         arenas = PeerArena.emulated(a.n_attn + a.n_expert, layout.size)
-        B = a.batch
+        B = a.batch * a.tp
         blocks = 2 * B * ((a.ctx + 32) // 16 + 1) + 8
         r = AttentionRank(cfg, S, arenas[0], layout, 0, blocks)
         r.kv_cache.normal_(0, 0.5)
         per = (a.ctx + 32) // 16 + 1
         for m, d in enumerate(r.mb):
             d["comb_flag"].fill_(big)
+            for k in ("hsflag", "oflag", "nidflag"):
+                if k in d:
+                    d[k].fill_(big)
             d["ids"].random_(0, cfg.vocab_size)
             d["positions"].fill_(a.ctx); d["ctx_len"].fill_(a.ctx + 1)
             rows = torch.arange(B, dtype=torch.int32, device="cuda") + m * B
@@ -67,15 +72,30 @@ def main():
             bt = (rows.long()[:, None] * per + torch.arange(per, device="cuda")[None]).int()
             r.block_tables[m * B:(m + 1) * B, :per] = bt
             d["slots"].copy_(bt[:, a.ctx // 16].long() * 16 + a.ctx % 16)
-        ms = timed(r.iteration)
-        print(f"attention side: {ms:.2f} ms per iteration ({ms / a.layers / 2 * 1e3:.0f} us per layer and micro-batch), "
+        cursors = [arenas[a.n_attn + x].view(layout.offset(f"recv_cnt{m}"), (S.experts_per_rank,), torch.int32)
+                   for x in range(a.n_expert) for m in range(2)]
+
+        def attn_it():
+            for m in range(2):
+                r.embed(m)
+            for l in range(cfg.num_layers):
+                for c in cursors:      # no expert rank runs here to clear the row cursors it would have consumed
+                    c.zero_()
+                for m in range(2):
+                    r.layer(l, m)
+            for m in range(2):
+                r.head(m)
+            for m in range(2):
+                r.head_wait(m)
+        ms = timed(attn_it)
+        print(f"attention side (tp {a.tp}, {B} rows per micro-batch): {ms:.2f} ms per iteration ({ms / a.layers / 2 * 1e3:.0f} us per layer and micro-batch), "
               f"status {gemm.check_status()}")
         del r, arenas
         torch.cuda.empty_cache()
     if a.side in ("both", "expert"):
         arenas = PeerArena.emulated(a.n_attn + a.n_expert, layout.size)
         x = ExpertRank(cfg, S, arenas[a.n_attn], layout, 0)
-        pairs = a.n_attn * a.batch * cfg.top_k // cfg.num_experts      # rows per expert per launch
+        pairs = a.n_attn * a.batch * cfg.top_k // cfg.num_experts      # rows per expert per launch (any TP degree)
         for d in x.mb:
             d["flag"].fill_(big)
             d["cnt"].fill_(pairs)
