@@ -136,6 +136,10 @@ def main():
     ap.add_argument("--route-skew", type=float, default=0.0,
                     help="Zipf exponent of a synthetic expert-popularity skew added to the router logits (0 = none)")
     ap.add_argument("--no-selfcheck", action="store_true", help="skip the tiny-model correctness run at N >= 2")
+    ap.add_argument("--timeline", type=int, default=0,
+                    help="N >= 2: after the timed region, run this many eager coupled iterations with a timing event after "
+                         "every launch and print one JSON line per rank role with the device time per kernel (waits on "
+                         "peers' flags included)")
     ap.add_argument("--serve", action="store_true",
                     help="N >= 2: open-loop serving instead of the fixed decode batch: Poisson arrivals over a rate sweep "
                          "(--rates, --duration seconds each), prompts U[128,1024], outputs U[64,512], real prefill, "
@@ -172,7 +176,7 @@ def main():
     cfg = get_preset(args.model)
     if args.layers:
         cfg = cfg.clone(num_layers=args.layers)
-    cfg.max_seq_len = max(4096, (args.ctx_max + K + W + 2 + 15) // 16 * 16)
+    cfg.max_seq_len = max(4096, (args.ctx_max + K + W + args.timeline + 2 + 15) // 16 * 16)
     g = torch.Generator().manual_seed(1234 + rank)
     B = args.batch
     selfcheck = None
@@ -200,7 +204,7 @@ def main():
                 tp = 1
                 selfcheck = selfcheck_against_colocated(world, rank, local_rank, A, tp, args.micro_batches)
                 selfcheck["fell_back_from_tp"] = bad
-        runner = DisaggDecodeBench(cfg, world, rank, local_rank, B, args.ctx_min, args.ctx_max, K + W, g, tp=tp,
+        runner = DisaggDecodeBench(cfg, world, rank, local_rank, B, args.ctx_min, args.ctx_max, K + W + args.timeline, g, tp=tp,
                                    n_attn=A, route_skew=args.route_skew, n_mb=args.micro_batches)
         parallelism = runner.parallelism
     else:
@@ -312,6 +316,18 @@ def main():
         if kstatus != 0:
             out["invalid"] = "a device-side wait timed out (kernel status %d): results are not valid" % kstatus
         print(json.dumps(out))
+    if ours and world > 1 and args.timeline > 0:
+        tl = runner.timeline(args.timeline)
+        rows = [None] * world if rank == 0 else None
+        dist.gather_object({k: (n, round(ms, 3)) for k, (n, ms) in tl.items()}, rows, dst=0)
+        if rank == 0:
+            A = runner.shape.n_attn
+            for name, r in (("attention rank 0", rows[0]), (f"expert rank 0 (global rank {A})", rows[A])):
+                tot = sum(ms for _, ms in r.values())
+                print(json.dumps({"timeline": name, "iterations": args.timeline, "total_ms": round(tot, 2),
+                                  "ms_per_iteration": round(tot / args.timeline, 2),
+                                  "kernels": {k: {"launches": n, "ms": ms, "share": round(ms / tot, 3)}
+                                              for k, (n, ms) in sorted(r.items(), key=lambda kv: -kv[1][1])}}))
     if world > 1:
         dist.destroy_process_group()
     return 0

@@ -95,11 +95,42 @@ def stream_ptr() -> int:
 LAUNCHES = 0   # entry-point calls that launched kernels of this library (a graph replay adds its captured count)
 
 
+TIMELINE = None   # a list while a timeline is being taken: (label, CUDA event recorded right after the launch)
+TAG = ""          # set by callers to tell launches of one entry point apart (QKV / o_proj / LM head GEMM ...)
+
+
+def start_timeline() -> None:
+    """From now on every launch made through :func:`check` is followed by a timing event on the current stream (eager
+    launches only: do not capture a graph while a timeline is on)."""
+    global TIMELINE
+    TIMELINE = []
+    ev = torch.cuda.Event(enable_timing=True)
+    ev.record()
+    TIMELINE.append(("start", ev))
+
+
+def stop_timeline():
+    """Ends the timeline and returns {label: (launches, total ms)}: the device time between the end of the previous
+    launch and the end of this one, i.e. the kernel's run time including any wait on peers' flags inside it."""
+    global TIMELINE
+    tl, TIMELINE = TIMELINE, None
+    torch.cuda.synchronize()
+    out = {}
+    for (_, a), (name, b) in zip(tl[:-1], tl[1:]):
+        n, ms = out.get(name, (0, 0.0))
+        out[name] = (n + 1, ms + a.elapsed_time(b))
+    return out
+
+
 def check(code: int, what: str):
     global LAUNCHES
     if code != 0:
         raise KernelError(f"{what} failed with code {code}")
     LAUNCHES += 1
+    if TIMELINE is not None:
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        TIMELINE.append(((TAG + ":" if TAG else "") + what, ev))
 
 
 def add_launches(n: int):

@@ -284,7 +284,9 @@ class AttentionRank:
                                  done_ticket=d["gemm_ticket"], rope=rope)
         else:
             comm = gemm.GemmComm(rope=rope)
+        _lib.TAG = "qkv"
         qkv = gemm.linear(d["hs"][:T], a.qkv_w, out=d["qkv"][:T], comm=comm)
+        _lib.TAG = ""
         n_pre = self.n_pre[m]
         attn = F.paged_attention(qkv[:, :a.q_size], kc, vc, meta.block_tables, meta.bt_row,
                                  d["ctx_dec"][:T] if n_pre else meta.ctx_len,
@@ -293,13 +295,16 @@ class AttentionRank:
         if n_pre:
             F.prefill_attention(qkv[:, :a.q_size], kc, vc, meta.block_tables, d["pre_tiles"], n_pre, a.num_heads,
                                 a.num_kv_heads, a.head_dim, attn)
+        _lib.TAG = "o_proj"
         if self.tp == 1:
             gemm.linear(attn, a.o_w, residual=d["resid"][:T], out=d["resid"][:T])
+            _lib.TAG = ""
             return
         sig = gemm.GemmComm(rs_bases=d["opart_ptrs"], rs_rows=per, rs_slot=self.tp_rank, rs_cap=S.rows_cap,
                             signal_ptrs=d["oflag_ptrs"], n_signal=self.tp, signal_slot=self.tp_rank,
                             signal_epoch=d["o_sig_epoch"], done_ticket=d["gemm_ticket"])
         gemm.linear(attn, a.o_w, comm=sig)
+        _lib.TAG = ""
 
     def layer_route_dispatch(self, l: int, m: int) -> None:
         """[wait for the TP members' o_proj] reduce + residual, post-attention RMSNorm, router, dispatch of this
@@ -340,7 +345,9 @@ class AttentionRank:
                       wait_flags=d["comb_flag"] if wait else None, n_wait=S.n_expert if wait else 0,
                       wait_epoch=d["comb_epoch"] if wait else None, ticket=d["ticket"], status=self.status)
         if Tm > 0:
+            _lib.TAG = "lm_head"
             logits = gemm.linear(d["hfin"][:Tm], self.lm_head_w, out=d["logits"][:Tm], out_dtype=torch.float32)
+            _lib.TAG = ""
             F.argmax(logits, out=d["next_local"][:Tm])
         if self.tp > 1:
             F.ids_gather(d["next_local"], Tm, d["nid_ptrs"], self.tp, lo, d["nidflag_ptrs"], self.tp_rank,
@@ -412,12 +419,15 @@ class ExpertRank:
             return
         gate = gemm.GemmComm(seg_cnt=d["cnt"], seg_cap=S.region_cap, group_regions=True, wait_flags=d["flag"],
                              n_wait=S.n_attn, wait_epoch=d["wait_epoch"], done_ticket=self.ticket)
+        _lib.TAG = "expert_gemm1"
         gemm.grouped_swiglu(d["rows"], e.w13_weight, None, out=self.act, bn=self.bn, comm=gate)
+        _lib.TAG = "expert_gemm2"
         # the last CTA clears the row cursors before it signals: the senders reserve again only after that signal
         sig = gemm.GemmComm(seg_cnt=d["cnt"], seg_cap=S.region_cap, group_regions=True, signal_ptrs=d["signal_ptrs"],
                             n_signal=S.n_attn, signal_slot=self.x, signal_epoch=d["signal_epoch"],
                             done_ticket=self.ticket, clear=d["cnt"])
         gemm.grouped_combine(self.act, e.w2_weight, None, d["recs"], d["parts_bases"], S.hidden, bn=self.bn2, comm=sig)
+        _lib.TAG = ""
 
     def iteration(self) -> None:
         for l in range(self.cfg.num_layers):
@@ -620,6 +630,21 @@ class DisaggDecodeBench:
             torch.cuda.current_stream().synchronize()
         if ev:
             self.event_pairs.append(ev)
+
+    def timeline(self, iterations: int = 2) -> Dict[str, tuple]:
+        """Per-kernel device time of ``iterations`` EAGER (not graph-replayed) coupled iterations of this rank, every
+        rank of the job taking part: {label: (launches, total ms)}. A kernel's time includes the wait on its peers'
+        flags inside it, so the labels show where this rank's pipeline stalls."""
+        import torch.distributed as dist
+        torch.cuda.synchronize()
+        dist.barrier()
+        _lib.start_timeline()
+        for _ in range(iterations):
+            if self.is_attn:
+                self._stage_inputs(advance=True)
+                self.lens = [l + 1 for l in self.lens]
+            self.runner.iteration()
+        return _lib.stop_timeline()
 
     def tokens_per_step(self) -> int:
         # a sequence served by a TP group is counted once (by the group's first rank)
