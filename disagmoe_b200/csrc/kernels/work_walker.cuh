@@ -68,13 +68,26 @@ struct WorkWalker {
     kb_per = (kblocks + splitk - 1) / splitk;
     lin = cta_; lin_step = grid_;
     it = it_end = it_begin = total = 0; active = 1; grid = grid_; waves = wave = tile0 = 0;
-    if (streamk) {
-      long long tiles = 0;
-      for (int gg = 0; gg < G; ++gg) {
-        int t = 0;
-        for (int s = 0; s < S; ++s) t += (seg_cnt[s * G + gg] + BN - 1) / BN;
-        tiles += static_cast<long long>(MT) * t;
+    long long tiles = 0;
+    for (int gg = 0; gg < G; ++gg) {
+      int t = 0;
+      for (int s = 0; s < S; ++s) t += (seg_cnt[s * G + gg] + BN - 1) / BN;
+      tiles += static_cast<long long>(MT) * t;
+    }
+    if (!streamk) {
+      // Balanced waves: with u units and w = ceil(u / grid) waves, only ceil(u / w) CTAs take part, each with w (or
+      // w - 1) units, so that all of them finish together instead of a few CTAs running a last, nearly empty wave
+      // while the rest idle. A memory-bound launch loses nothing (fewer SMs still saturate HBM) and sheds the tail;
+      // a compute-bound one takes w unit times either way.
+      const long long units = tiles * splitk;
+      if (units > 0) {
+        const long long w = (units + grid_ - 1) / grid_;
+        const long long use = (units + w - 1) / w;
+        lin_step = use;
+        if (cta_ >= use) lin = units;      // idle CTA: its first unit is already past the end
       }
+    }
+    if (streamk) {
       waves = static_cast<int>(tiles / grid_);
       tile0 = waves * grid_;
       total = (tiles - tile0) * kblocks;
