@@ -90,8 +90,8 @@ def want_streamk(epi: int, F: int, G: int, T: int, bn: int, sms: int) -> bool:
     tail pays off when the expected tile count fills the last wave of CTAs badly (few experts with long K loops, the
     down-projection at decode sizes); the SwiGLU up-projection, whose partial tiles carry two accumulators, is faster
     with whole tiles. Group sizes are only known on the device: the estimate assumes even routing."""
-    if not STREAM_K or epi == EPI_SWIGLU:
-        return False
+    if not STREAM_K or epi == EPI_SWIGLU or T >= 192 * G:
+        return False      # (at ~256 tokens per expert and more, whole 256-token tiles measured faster)
     tiles = ((F + 127) // 128) * max(G, (T + bn - 1) // bn)
     waves = (tiles + sms - 1) // sms
     return tiles / (waves * sms) < 0.85
