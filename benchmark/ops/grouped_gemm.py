@@ -64,6 +64,7 @@ def main(argv=None):
             for bn in (128, 256):
                 res[("g2", sk, bn)] = timed(lambda: gemm.grouped_linear(act, w2, offs, bn=bn, streamk=sk), flush, a.iters)
         # CTA pairs (cta_group::2): 256 weight rows per MMA, the token tile split between the two CTAs' shared memories
+        res[("g1", False, 256)] = timed(lambda: gemm.grouped_swiglu(x, w13, offs, bn=256, streamk=False), flush, a.iters)
         for bn in (128, 256):
             res[("g1p", bn)] = timed(lambda: gemm.grouped_swiglu(x, w13, offs, bn=bn, pair=True), flush, a.iters)
             res[("g2p", bn)] = timed(lambda: gemm.grouped_linear(act, w2, offs, bn=bn, pair=True), flush, a.iters)
@@ -76,7 +77,7 @@ def main(argv=None):
         t2 = min(res[("g2", True, 128)], res[("g2", True, 256)])
         print(f"{G} experts x ~{t} tokens (sizes {sizes if G <= 8 else '...'}): "
               f"GEMM-1+SwiGLU stream-K {t1:.1f} us ({gb1 / t1 * 1e6:.0f} GB/s, {f1 / t1 / 1e6:.0f} TFLOP/s), whole tiles "
-              f"{res[('g1', False)]:.1f} us; GEMM-2 stream-K bn128 {res[('g2', True, 128)]:.1f} / bn256 "
+              f"{res[('g1', False)]:.1f} us (256-token tiles {res[('g1', False, 256)]:.1f}); GEMM-2 stream-K bn128 {res[('g2', True, 128)]:.1f} / bn256 "
               f"{res[('g2', True, 256)]:.1f} us (best {gb2 / t2 * 1e6:.0f} GB/s, {f2 / t2 / 1e6:.0f} TFLOP/s), whole tiles "
               f"bn128 {res[('g2', False, 128)]:.1f} / bn256 {res[('g2', False, 256)]:.1f} us; CTA pairs GEMM-1 bn128 "
               f"{res[('g1p', 128)]:.1f} / bn256 {res[('g1p', 256)]:.1f} us ({f1 / min(res[('g1p', 128)], res[('g1p', 256)]) / 1e6:.0f} "

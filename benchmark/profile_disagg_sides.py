@@ -23,10 +23,19 @@ from disagmoe_b200.parallel.disagg import AttentionRank, DisaggShape, ExpertRank
 from disagmoe_b200.parallel.peer import PeerArena
 
 
-def timed(fn, iters=5):
+def timed(fn, iters=5, graph=True):
+    """Median device time of fn(); with `graph` the launches are captured once and replayed, as the serving loop does
+    (eager launches through ctypes cost more host time than the small attention-side kernels run)."""
     for _ in range(2):
         fn()
     torch.cuda.synchronize()
+    if graph:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn()
+        fn = g.replay
+        fn()
+        torch.cuda.synchronize()
     ts = []
     for _ in range(iters):
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -46,6 +55,7 @@ def main():
     ap.add_argument("--n-expert", type=int, default=4)
     ap.add_argument("--ctx", type=int, default=864)
     ap.add_argument("--side", default="both")
+    ap.add_argument("--eager", action="store_true", help="time eager launches instead of a CUDA-graph replay")
     ap.add_argument("--tp", type=int, default=1, help="attention tensor-parallel degree: the measured rank is member 0 of a "
                     "TP group that serves tp x batch rows (its peers' flags are pre-satisfied)")
     a = ap.parse_args()
@@ -87,7 +97,7 @@ def main():
                 r.head(m)
             for m in range(2):
                 r.head_wait(m)
-        ms = timed(attn_it)
+        ms = timed(attn_it, graph=not a.eager)
         print(f"attention side (tp {a.tp}, {B} rows per micro-batch): {ms:.2f} ms per iteration ({ms / a.layers / 2 * 1e3:.0f} us per layer and micro-batch), "
               f"status {gemm.check_status()}")
         del r, arenas
@@ -107,7 +117,7 @@ def main():
                 for m in range(2):
                     x.layer(l, m)
                     x.mb[m]["cnt"].fill_(pairs)      # the combine cleared the cursors; refill for the next launch
-        ms = timed(it)
+        ms = timed(it, graph=not a.eager)
         print(f"expert side ({S.experts_per_rank} experts/GPU, {pairs} rows per expert, tile {x.bn}): {ms:.2f} ms per "
               f"iteration ({ms / a.layers / 2 * 1e3:.0f} us per layer and micro-batch), status {gemm.check_status()}")
 

@@ -768,7 +768,6 @@ extern "C" int dmoe_gemm(const DmoeGemm* d, void* stream_) {
   if (bn == 0) bn = dmoe_gemm_pick_bn((d->T + d->G - 1) / d->G, epi);
   if (bn != 32 && bn != 64 && bn != 128 && bn != 256) return -11;
   const bool pair = d->pair != 0;
-  if (epi == EPI_SWIGLU && bn > (pair ? 256 : 128)) return -11;
   if (pair && (bn < 128 || d->splitk > 1)) return -11;
   int splitk = d->splitk < 1 ? 1 : d->splitk;
   const int kblocks = (d->K + kBK - 1) / kBK;
@@ -878,7 +877,8 @@ extern "C" int dmoe_gemm(const DmoeGemm* d, void* stream_) {
     switch (bn) {
       case 32: DMOE_LAUNCH(32, EPI_SWIGLU);
       case 64: DMOE_LAUNCH(64, EPI_SWIGLU);
-      default: DMOE_LAUNCH(128, EPI_SWIGLU);
+      case 128: DMOE_LAUNCH(128, EPI_SWIGLU);
+      default: DMOE_LAUNCH(256, EPI_SWIGLU);   // gate + up accumulators fill TMEM: one buffer, epilogue not overlapped
     }
   } else if (epi == EPI_COMBINE) {
     switch (bn) {

@@ -77,6 +77,35 @@ def pick_splitk(T: int, F: int, K: int, bn: int, sms: int = 0) -> int:
     return max(1, min((sms * 128 // 148 + tiles // 2) // tiles, kblocks // 4, 16))
 
 
+def pick_dense(T: int, F: int, K: int, sms: int = 0):
+    """(token tile, split-K factor) of a dense GEMM below one wave of tiles, by a cost model fitted to the tile /
+    split sweep of benchmark/ops/dense_gemm.py on B200. At these sizes a CTA is bound by what its SM can pull from L2
+    (~100 GB/s: 16 KB of weights plus bn x 128 B of tokens per K block), so the model counts, per CTA, the bytes of
+    its K range times the number of waves, the parked and re-read partial tiles of a split (the last arriver reads
+    them chunk by chunk, latency-bound) and a fixed launch + pipeline-fill cost. It reproduces the order of the
+    measured configurations (QKV and o_proj of Mixtral at 64-512 tokens)."""
+    sms = sms or num_sms()
+    kblocks = (K + 63) // 64
+    mt = (F + 127) // 128
+    best = None
+    for bn in (32, 64, 128, 256):
+        if bn < 32 or (bn > 32 and bn // 2 >= T):
+            continue                      # a tile twice as wide as the batch only adds shared-memory traffic
+        nt = (T + bn - 1) // bn
+        for sk in (1, 2, 3, 4, 6, 8):
+            per = (kblocks + sk - 1) // sk
+            if sk > 1 and (per < 8 or (kblocks + per - 1) // per != sk):
+                continue
+            units = mt * nt * sk
+            waves = (units + sms - 1) // sms
+            cost = 6.0 + waves * per * (16384 + bn * 128) / 1e5 + (bn // 32) * 0.3
+            if sk > 1:
+                cost += 128 * bn * 4 / 1e5 + (bn // 32) * sk * 0.35
+            if best is None or cost < best[0] - 1e-9:
+                best = (cost, bn, sk)
+    return best[1], best[2]
+
+
 def pick_bn(tokens_per_group: int, epi: int) -> int:
     cap = 128 if epi == EPI_SWIGLU else 256
     bn = 32
@@ -90,8 +119,8 @@ def want_streamk(epi: int, F: int, G: int, T: int, bn: int, sms: int) -> bool:
     tail pays off when the expected tile count fills the last wave of CTAs badly (few experts with long K loops, the
     down-projection at decode sizes); the SwiGLU up-projection, whose partial tiles carry two accumulators, is faster
     with whole tiles. Group sizes are only known on the device: the estimate assumes even routing."""
-    if not STREAM_K or epi == EPI_SWIGLU or T >= 192 * G:
-        return False      # (at ~256 tokens per expert and more, whole 256-token tiles measured faster)
+    if not STREAM_K or epi == EPI_SWIGLU:
+        return False
     tiles = ((F + 127) // 128) * max(G, (T + bn - 1) // bn)
     waves = (tiles + sms - 1) // sms
     return tiles / (waves * sms) < 0.85
@@ -233,10 +262,11 @@ def linear(x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor] = 
     # the last, partial wave are cut along K into equal shares for all SMs); with fewer tiles than SMs (decode sizes)
     # plain split-K with a factor that fills the SMs. An explicit splitk >= 1 selects split-K with that factor.
     sms = num_sms(x.device)
+    auto_sk = 0
     if not bn:
         bn = pick_bn(T, EPI_PLAIN)
-        if bn == 256 and ((F + 127) // 128) * ((T + 255) // 256) < sms // 2:
-            bn = 128     # too few 256-wide tiles to fill the GPU: halve the tile instead of splitting K further
+        if ((F + 127) // 128) * ((T + bn - 1) // bn) < sms and not pair:
+            bn, auto_sk = pick_dense(T, F, K, sms)
     if pair:
         bn = 256 if bn not in (128, 256) else bn
         splitk = 1
@@ -244,7 +274,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor] = 
     if streamk:
         splitk = 1
     else:
-        splitk = splitk or pick_splitk(T, F, K, bn, sms)
+        splitk = splitk or auto_sk or pick_splitk(T, F, K, bn, sms)
     _launch(w, x, out, residual, None, None, None, 1, T, F, K, EPI_PLAIN, bn, splitk,
             F if scatter else out.stride(0), (not scatter) and out.dtype == torch.float32, comm, streamk=streamk,
             pair=pair)

@@ -12,3 +12,20 @@ def test_work_partition_covers_every_tile_exactly_once():
                     os.path.join(root, "tests", "native", "work_walker_check.cpp"), "-o", exe], check=True)
     out = subprocess.run([exe], capture_output=True, text=True, timeout=120)
     assert out.returncode == 0 and out.stdout.startswith("ok"), out.stdout + out.stderr
+
+
+def test_dense_tile_and_split_choice_is_launchable_and_follows_the_measured_order():
+    """The (token tile, split-K) picker of decode-size dense GEMMs: every choice is one the launcher accepts (no empty
+    split, at least 8 K blocks per split) and it prefers what the tile / split sweep on B200 measured as fastest."""
+    from disagmoe_b200.ops import gemm
+    for F, K in ((6144, 4096), (4096, 4096), (1536, 4096), (4096, 1024), (32000, 4096), (512, 128)):
+        for T in (1, 7, 16, 64, 100, 128, 256, 512, 1000):
+            bn, sk = gemm.pick_dense(T, F, K, 148)
+            kblocks = (K + 63) // 64
+            per = (kblocks + sk - 1) // sk
+            assert bn in (32, 64, 128, 256) and sk >= 1
+            assert sk == 1 or (per >= 8 and (kblocks + per - 1) // per == sk)
+    # measured: QKV (F 6144) at 256 tokens is fastest on 128-token tiles, o_proj (F 4096) at 256 tokens with a split
+    assert gemm.pick_dense(256, 6144, 4096, 148)[0] == 128
+    assert gemm.pick_dense(256, 4096, 4096, 148) == (128, 2)
+    assert gemm.pick_dense(64, 4096, 4096, 148)[1] >= 2
