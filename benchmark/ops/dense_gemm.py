@@ -5,7 +5,7 @@
 Every measurement is one CUDA graph of 24 launches over 24 distinct weight matrices (so weights always come from HBM,
 as in a decoder stack, and host launch overhead is excluded), timed with CUDA events around graph replays, best of 4.
 cuBLAS goes through ``torch.matmul`` / ``torch.addmm`` in the same harness. ``--sweep`` also tries every token tile
-(32..256) and split-K factor (1..16) and prints the four fastest.
+(32..256) and split-K factor (1..8) and prints the four fastest.
 """
 import argparse
 import os
@@ -28,7 +28,8 @@ def bench(fn, n=N_WEIGHTS, reps=4):
     with torch.cuda.graph(g):
         for i in range(n):
             fn(i)
-    g.replay()
+    for _ in range(12):      # clocks and caches settle before anything is timed
+        g.replay()
     torch.cuda.synchronize()
     best = float("inf")
     for _ in range(reps):
@@ -45,10 +46,14 @@ def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--tokens", default="64,128,256,512")
     ap.add_argument("--sweep", action="store_true")
+    ap.add_argument("--tp", type=int, default=1, help="shapes of one rank of a tensor-parallel attention group: QKV has "
+                    "6144 / tp output features, o_proj 4096 / tp input features and no residual (reduce-scatter epilogue)")
     ap.add_argument("--hbm-gbs", type=float, default=6549.0, help="copy bandwidth for the weight-streaming floor")
     a = ap.parse_args(argv)
     dev = "cuda"
-    for name, F, K, resid in (("qkv", 6144, 4096, False), ("o_proj+residual", 4096, 4096, True)):
+    shapes = (("qkv", 6144, 4096, False), ("o_proj+residual", 4096, 4096, True)) if a.tp == 1 else \
+        ((f"qkv/tp{a.tp}", 6144 // a.tp, 4096, False), (f"o_proj/tp{a.tp}", 4096, 4096 // a.tp, False))
+    for name, F, K, resid in shapes:
         ws = [torch.randn(F, K, device=dev, dtype=torch.bfloat16) * 0.02 for _ in range(N_WEIGHTS)]
         for T in (int(t) for t in a.tokens.split(",")):
             x = torch.randn(T, K, device=dev, dtype=torch.bfloat16)
@@ -70,7 +75,7 @@ def main(argv=None):
                 for bn in (32, 64, 128, 256):
                     if bn > max(32, T):
                         continue
-                    for sk in (1, 2, 4, 8, 16):
+                    for sk in (1, 2, 3, 4, 6, 8):
                         try:
                             res.append((bench(lambda i: gemm.linear(x, ws[i], residual=r, out=out, bn=bn, splitk=sk)), bn, sk))
                         except Exception:

@@ -45,6 +45,9 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--experts", type=int, default=E, help="local experts (groups) of the launch")
     ap.add_argument("--ragged", type=float, default=0.0, help="relative jitter of the group sizes around the mean")
+    ap.add_argument("--only", default="", help="run one variant only (for profilers): g1s / g1w / g1w256 / g1p128 / g1p256 "
+                    "(GEMM-1: stream-K, whole tiles, whole 256-token tiles, CTA pairs) or g2s128 / g2s256 / g2w128 / g2w256 "
+                    "/ g2p128 / g2p256 (GEMM-2)")
     a = ap.parse_args(argv)
     dev = "cuda"
     G = a.experts
@@ -58,6 +61,15 @@ def main(argv=None):
         x = torch.randn(T, H, device=dev).to(torch.bfloat16)
         offs = torch.tensor([0] + list(torch.tensor(sizes).cumsum(0)), dtype=torch.int32, device=dev)
         act = gemm.grouped_swiglu(x, w13, offs)
+        if a.only:
+            v = a.only
+            bn = int(v[3:]) if len(v) > 3 else 0
+            if v.startswith("g1"):
+                fn = lambda: gemm.grouped_swiglu(x, w13, offs, bn=bn, streamk=v[2] == "s", pair=v[2] == "p")
+            else:
+                fn = lambda: gemm.grouped_linear(act, w2, offs, bn=bn, streamk=v[2] == "s", pair=v[2] == "p")
+            print(f"{G} experts x ~{t} tokens, {v}: {timed(fn, flush, a.iters):.1f} us", flush=True)
+            continue
         res = {}
         for sk in (True, False):
             res[("g1", sk)] = timed(lambda: gemm.grouped_swiglu(x, w13, offs, streamk=sk), flush, a.iters)

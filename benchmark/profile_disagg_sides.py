@@ -18,7 +18,7 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 import torch
 
 from disagmoe_b200.config import get_preset
-from disagmoe_b200.ops import gemm
+from disagmoe_b200.ops import _lib, gemm
 from disagmoe_b200.parallel.disagg import AttentionRank, DisaggShape, ExpertRank, build_layout
 from disagmoe_b200.parallel.peer import PeerArena
 
@@ -46,6 +46,16 @@ def timed(fn, iters=5, graph=True):
     return ts[len(ts) // 2]
 
 
+def timeline(fn, per):
+    """Per-kernel device time (us per layer and micro-batch for the per-layer kernels) of one eager run of fn()."""
+    fn()
+    torch.cuda.synchronize()
+    _lib.start_timeline()
+    fn()
+    tl = _lib.stop_timeline()
+    return ", ".join(f"{k} {ms * 1e3 / n:.1f} us x {n}" for k, (n, ms) in sorted(tl.items(), key=lambda kv: -kv[1][1]))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", default="mixtral")
@@ -55,6 +65,8 @@ def main():
     ap.add_argument("--n-expert", type=int, default=4)
     ap.add_argument("--ctx", type=int, default=864)
     ap.add_argument("--side", default="both")
+    ap.add_argument("--timeline", action="store_true", help="also print the device time per kernel of one eager iteration "
+                    "(a timing event after every launch; the GPU stays backlogged, so gaps between kernels are small)")
     ap.add_argument("--eager", action="store_true", help="time eager launches instead of a CUDA-graph replay")
     ap.add_argument("--tp", type=int, default=1, help="attention tensor-parallel degree: the measured rank is member 0 of a "
                     "TP group that serves tp x batch rows (its peers' flags are pre-satisfied)")
@@ -100,6 +112,8 @@ def main():
         ms = timed(attn_it, graph=not a.eager)
         print(f"attention side (tp {a.tp}, {B} rows per micro-batch): {ms:.2f} ms per iteration ({ms / a.layers / 2 * 1e3:.0f} us per layer and micro-batch), "
               f"status {gemm.check_status()}")
+        if a.timeline:
+            print("  per kernel:", timeline(attn_it, a.layers * 2))
         del r, arenas
         torch.cuda.empty_cache()
     if a.side in ("both", "expert"):
@@ -120,6 +134,8 @@ def main():
         ms = timed(it, graph=not a.eager)
         print(f"expert side ({S.experts_per_rank} experts/GPU, {pairs} rows per expert, tile {x.bn}): {ms:.2f} ms per "
               f"iteration ({ms / a.layers / 2 * 1e3:.0f} us per layer and micro-batch), status {gemm.check_status()}")
+        if a.timeline:
+            print("  per kernel:", timeline(it, a.layers * 2))
 
 
 if __name__ == "__main__":

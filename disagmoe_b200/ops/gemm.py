@@ -97,6 +97,8 @@ def pick_dense(T: int, F: int, K: int, sms: int = 0):
             if sk > 1 and (per < 8 or (kblocks + per - 1) // per != sk):
                 continue
             units = mt * nt * sk
+            if sk > 1 and units > sms:
+                continue                  # a split that spills into a second wave measured far slower than whole tiles
             waves = (units + sms - 1) // sms
             cost = 6.0 + waves * per * (16384 + bn * 128) / 1e5 + (bn // 32) * 0.3
             if sk > 1:
