@@ -67,6 +67,8 @@ def main():
     ap.add_argument("--side", default="both")
     ap.add_argument("--timeline", action="store_true", help="also print the device time per kernel of one eager iteration "
                     "(a timing event after every launch; the GPU stays backlogged, so gaps between kernels are small)")
+    ap.add_argument("--parts", action="store_true", help="attention side: also time a graph of each stage alone (norm + "
+                    "all-gather push; QKV + attention + o_proj; reduce + router + dispatch) over all layers")
     ap.add_argument("--eager", action="store_true", help="time eager launches instead of a CUDA-graph replay")
     ap.add_argument("--tp", type=int, default=1, help="attention tensor-parallel degree: the measured rank is member 0 of a "
                     "TP group that serves tp x batch rows (its peers' flags are pre-satisfied)")
@@ -101,8 +103,7 @@ def main():
             for m in range(2):
                 r.embed(m)
             for l in range(cfg.num_layers):
-                for c in cursors:      # no expert rank runs here to clear the row cursors it would have consumed
-                    c.zero_()
+                torch._foreach_zero_(cursors)      # no expert rank runs here to clear the row cursors it consumed
                 for m in range(2):
                     r.layer(l, m)
             for m in range(2):
@@ -114,6 +115,17 @@ def main():
               f"status {gemm.check_status()}")
         if a.timeline:
             print("  per kernel:", timeline(attn_it, a.layers * 2))
+        if a.parts:
+            def stage(fn):
+                def run():
+                    for l in range(cfg.num_layers):
+                        if fn == r.layer_route_dispatch:
+                            torch._foreach_zero_(cursors)
+                        for m in range(2):
+                            fn(l, m)
+                return timed(run, graph=True) / a.layers / 2 * 1e3
+            print(f"  stages alone, us per layer and micro-batch (graph replay): norm_gather {stage(r.layer_pre):.1f}, "
+                  f"qkv + attention + o_proj {stage(r.layer_attn):.1f}, route_dispatch {stage(r.layer_route_dispatch):.1f}")
         del r, arenas
         torch.cuda.empty_cache()
     if a.side in ("both", "expert"):

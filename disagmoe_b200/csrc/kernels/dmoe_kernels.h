@@ -67,6 +67,9 @@ typedef struct DmoeGemm {
   // pair != 0: clusters of two CTAs compute tiles of 256 weight rows x bn tokens with tcgen05.mma.cta_group::2 (each
   // CTA stages its 128 weight rows and half of the token tile). bn = 128 or 256 (SwiGLU too), whole tiles only.
   int pair;
+  // combine epilogue: != 0 states that every destination base in `bases` is 16-byte aligned (with F and ldy multiples
+  // of 8 the rows then move as 16-byte segments); 0 keeps 2-byte stores
+  int combine_vec;
 } DmoeGemm;
 
 int dmoe_gemm(const DmoeGemm* desc, void* stream);

@@ -106,9 +106,9 @@ struct Cfg {
   static constexpr int kBRows = PAIR ? BN / 2 : BN;      // token rows this CTA stages
   static constexpr int kBBytes = kBRows * kBK * 2;
   static constexpr int kStageBytes = kNumA * kABytes + kBBytes;
-  // plain epilogue: one 32-token x 128-feature fp32 chunk is transposed through shared memory, so that Y (and the
-  // residual) move as 16-byte row segments instead of one 2-byte element per thread
-  static constexpr int kEpiStageBytes = (EPI == EPI_PLAIN) ? 32 * kBM * 4 : 0;
+  // plain and combine epilogues: one 32-token x 128-feature fp32 chunk is transposed through shared memory, so that
+  // Y (and the residual) move as 16-byte row segments instead of one 2-byte element per thread
+  static constexpr int kEpiStageBytes = (EPI == EPI_PLAIN || EPI == EPI_COMBINE) ? 32 * kBM * 4 : 0;
   static constexpr int kStagesRaw = (kSmemBudget - 1024 - kTailBytes - kEpiStageBytes) / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
   static constexpr int kAccCols = BN * kNumA;
@@ -593,6 +593,44 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
           named_bar_sync(1, kEpiThreads);            // the stage is free again for the next chunk / tile
           continue;
         }
+        if (EPI == EPI_COMBINE && a.epi_vec != 0) {
+          if (jmax <= 0) continue;                   // uniform over the CTA
+          // same transposition as the plain epilogue: thread (token lane, 8 features) scales its 8 values by the
+          // row's router weight and stores 16 bytes into the destination row named by the record
+#pragma unroll
+          for (int j = 0; j < 32; ++j) epi_stage[j * kBM + row] = acc[j];
+          named_bar_sync(1, kEpiThreads);
+          const int fg = et & 15, tk0 = et >> 4;
+          const int f0 = m * kBM + fg * 8;
+          if (f0 < a.F) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const int j = tk0 + q * 8;
+              if (j >= jmax) continue;
+              const int4 rec = __ldg(&a.recs[tok_base + c * 32 + j]);
+              if (rec.y < 0) continue;
+              const float w = __int_as_float(rec.z);
+              const float4 x0 = *reinterpret_cast<const float4*>(&epi_stage[j * kBM + fg * 8]);
+              const float4 x1 = *reinterpret_cast<const float4*>(&epi_stage[j * kBM + fg * 8 + 4]);
+              uint4 pk;
+              __nv_bfloat162* pp = reinterpret_cast<__nv_bfloat162*>(&pk);
+              pp[0] = __floats2bfloat162_rn(x0.x * w, x0.y * w);
+              pp[1] = __floats2bfloat162_rn(x0.z * w, x0.w * w);
+              pp[2] = __floats2bfloat162_rn(x1.x * w, x1.y * w);
+              pp[3] = __floats2bfloat162_rn(x1.z * w, x1.w * w);
+              const long long off = static_cast<long long>(rec.y) * a.ldy + f0;
+              if (a.fanout <= 1) {
+                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.bases[rec.x]) + off) = pk;
+              } else {
+                const int g0 = rec.x / a.fanout * a.fanout;
+                for (int i = 0; i < a.fanout; ++i)
+                  *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.bases[g0 + i]) + off) = pk;
+              }
+            }
+          }
+          named_bar_sync(1, kEpiThreads);            // the stage is free again for the next chunk / tile
+          continue;
+        }
         if (!f_ok) continue;
         if (EPI == EPI_COMBINE) {
 #pragma unroll
@@ -804,6 +842,8 @@ extern "C" int dmoe_gemm(const DmoeGemm* d, void* stream_) {
     const long long ymod = d->y_f32 ? 4 : 8;
     a.epi_vec = (epi == EPI_PLAIN && d->F % 8 == 0 && d->ldy % ymod == 0 && al16(d->Y) &&
                  (d->R == nullptr || (d->ldr % 8 == 0 && al16(d->R)))) ? 1 : 0;
+    // combine: the destination bases live in a device table; the caller states that all of them are 16-byte aligned
+    if (epi == EPI_COMBINE && d->combine_vec != 0 && d->F % 8 == 0 && d->ldy % 8 == 0) a.epi_vec = 1;
   }
   a.shard_rows = d->shard_rows;
   a.flag_cycles = g_dmoe_flag_wait_cycles;

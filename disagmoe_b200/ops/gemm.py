@@ -213,6 +213,7 @@ def _launch(W, X, Y, R, offs, recs, bases, G, T, F, K, epi, bn, splitk, ldy, y_f
     d = _lib.DmoeGemm()
     d.streamk, d.n_counters = int(streamk and splitk <= 1 and not pair), s.counters.numel()
     d.pair = int(pair)
+    d.combine_vec = int(epi == EPI_COMBINE and F % 8 == 0 and ldy % 8 == 0 and _bases_aligned(bases))
     if comm is not None:
         comm.fill(d)
     d.W, d.X, d.Y, d.R = W.data_ptr(), X.data_ptr(), _lib.ptr(Y), _lib.ptr(R)
@@ -351,6 +352,21 @@ def grouped_linear(x: torch.Tensor, w: torch.Tensor, offs: torch.Tensor, out: Op
     sk = want_streamk(EPI_PLAIN, F, G, T, bn, num_sms(x.device)) if streamk is None else streamk
     _launch(w, x, out, None, offs, None, None, G, T, F, K, EPI_PLAIN, bn, 1, out.stride(0), False, streamk=sk, pair=pair)
     return out
+
+
+_bases_checked = {}
+
+
+def _bases_aligned(bases: torch.Tensor) -> bool:
+    """Are all destination pointers of a combine table 16-byte aligned? Read back once per table (tables are built at
+    start-up and never change); a table first seen during a graph capture, where nothing can be read back, counts as
+    unaligned and keeps the 2-byte stores."""
+    key = (bases.data_ptr(), bases.numel())
+    if key not in _bases_checked:
+        if torch.cuda.is_current_stream_capturing():
+            return False
+        _bases_checked[key] = bool((bases % 16 == 0).all().item())
+    return _bases_checked[key]
 
 
 def grouped_combine(x: torch.Tensor, w: torch.Tensor, offs: Optional[torch.Tensor], recs: torch.Tensor,

@@ -411,6 +411,10 @@ class ExpertRank:
         hint = gemm._group_hint(pairs, S.num_experts)
         self.bn = gemm.pick_bn(hint, gemm.EPI_SWIGLU)          # GEMM-1 holds two accumulators per tile: tokens <= 128
         self.bn2 = gemm.pick_bn(hint, gemm.EPI_COMBINE)        # GEMM-2: up to 256 tokens per weight tile
+        # work distribution of GEMM-2 from the rows EXPECTED per launch (the receive regions are sized for the worst case)
+        n_local = min((expert_rank + 1) * epr, cfg.num_experts) - expert_rank * epr
+        self.sk2 = gemm.want_streamk(gemm.EPI_COMBINE, S.hidden, n_local, pairs * n_local // S.num_experts, self.bn2,
+                                     gemm.num_sms(dev))
 
     def layer(self, l: int, m: int) -> None:
         d, S = self.mb[m], self.shape
@@ -426,7 +430,8 @@ class ExpertRank:
         sig = gemm.GemmComm(seg_cnt=d["cnt"], seg_cap=S.region_cap, group_regions=True, signal_ptrs=d["signal_ptrs"],
                             n_signal=S.n_attn, signal_slot=self.x, signal_epoch=d["signal_epoch"],
                             done_ticket=self.ticket, clear=d["cnt"])
-        gemm.grouped_combine(self.act, e.w2_weight, None, d["recs"], d["parts_bases"], S.hidden, bn=self.bn2, comm=sig)
+        gemm.grouped_combine(self.act, e.w2_weight, None, d["recs"], d["parts_bases"], S.hidden, bn=self.bn2, comm=sig,
+                             streamk=self.sk2)
         _lib.TAG = ""
 
     def iteration(self) -> None:
