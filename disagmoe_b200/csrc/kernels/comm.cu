@@ -33,9 +33,6 @@ __device__ __forceinline__ int ld_acquire_sys_i32(const int* p) {
   asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ void st_release_sys_i32(int* p, int v) {
-  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
 
 struct DispatchRemoteArgs {
   const __nv_bfloat16* y;       // [T, H] normalised rows
@@ -103,7 +100,7 @@ __global__ void __launch_bounds__(256) dispatch_remote_kernel(const DispatchRemo
     if (old == static_cast<int>(gridDim.x) - 1) {
       __threadfence_system();
       const int epoch = *a.epoch + 1;
-      for (int d = 0; d < a.n_dst; ++d) st_release_sys_i32(a.flag_bases[d] + a.my_rank, epoch);
+      for (int d = 0; d < a.n_dst; ++d) st_relaxed_sys(a.flag_bases[d] + a.my_rank, epoch);
       *a.epoch = epoch;
       for (int e = 0; e < a.E; ++e) { counts[e] = 0; cursor[e] = 0; }
       *ticket = 0;

@@ -126,9 +126,6 @@ __device__ __forceinline__ int ld_acquire_sys(const int* p) {
   asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ void st_release_sys(int* p, int v) {
-  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
 
 template <int BN, int EPI, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -680,7 +677,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
         __threadfence_system();
         if (a.n_signal > 0) {
           const int epoch = *a.signal_epoch + 1;
-          for (int i = 0; i < a.n_signal; ++i) st_release_sys(a.signal_ptrs[i] + a.signal_slot, epoch);
+          for (int i = 0; i < a.n_signal; ++i) st_relaxed_sys(a.signal_ptrs[i] + a.signal_slot, epoch);   // fenced above
           *a.signal_epoch = epoch;
         }
         if (a.n_wait > 0) *a.wait_epoch = *a.wait_epoch + 1;

@@ -40,9 +40,6 @@ __device__ __forceinline__ int ld_acquire_sys_s(const int* p) {
   asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ void st_release_sys_s(int* p, int v) {
-  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
 __device__ __forceinline__ float warp_sum_s(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -80,7 +77,7 @@ __device__ __forceinline__ void cta_complete(int* ticket, int* const* signal_ptr
       __threadfence_system();
       if (n_signal > 0) {
         const int epoch = *signal_epoch + 1;
-        for (int i = 0; i < n_signal; ++i) st_release_sys_s(signal_ptrs[i] + signal_slot, epoch);
+        for (int i = 0; i < n_signal; ++i) st_relaxed_sys(signal_ptrs[i] + signal_slot, epoch);   // fenced above
         *signal_epoch = epoch;
       }
       if (n_wait > 0) *wait_epoch = *wait_epoch + 1;
@@ -166,6 +163,13 @@ __global__ void __launch_bounds__(kSendThreads) norm_gather_kernel(const NormGat
         for (int j = 0; j < 8; ++j) ss += x[i][j] * x[i][j];
       }
     }
+    // the norm weights do not depend on the row: request them before the block-wide reduction, not after it
+    bf16x8s wreg[kSendMaxVec];
+#pragma unroll
+    for (int i = 0; i < kSendMaxVec; ++i) {
+      const int v = threadIdx.x + i * kSendThreads;
+      if (v < nvec) wreg[i] = *reinterpret_cast<const bf16x8s*>(a.w + v * 8);
+    }
     ss = warp_sum_s(ss);
     __syncthreads();               // red[] of the previous row has been read by everyone
     if (lane == 0) red[warp] = ss;
@@ -177,7 +181,7 @@ __global__ void __launch_bounds__(kSendThreads) norm_gather_kernel(const NormGat
     for (int i = 0; i < kSendMaxVec; ++i) {
       const int v = threadIdx.x + i * kSendThreads;
       if (v < nvec) {
-        const bf16x8s wv = *reinterpret_cast<const bf16x8s*>(a.w + v * 8);
+        const bf16x8s wv = wreg[i];
         bf16x8s o;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -275,6 +279,12 @@ __global__ void __launch_bounds__(kSendThreads) route_dispatch_kernel(const Rout
         for (int j = 0; j < 8; ++j) ss += xr[i][j] * xr[i][j];
       }
     }
+    bf16x8s wreg[kSendMaxVec];       // norm weights: requested before the block-wide reduction
+#pragma unroll
+    for (int i = 0; i < kSendMaxVec; ++i) {
+      const int v = threadIdx.x + i * kSendThreads;
+      if (v < nvec) wreg[i] = *reinterpret_cast<const bf16x8s*>(a.norm_w + v * 8);
+    }
     ss = warp_sum_s(ss);
     __syncthreads();               // shared state of the previous row is no longer read
     if (lane == 0) red[warp] = ss;
@@ -287,7 +297,7 @@ __global__ void __launch_bounds__(kSendThreads) route_dispatch_kernel(const Rout
     for (int i = 0; i < kSendMaxVec; ++i) {
       const int v = threadIdx.x + i * kSendThreads;
       if (v < nvec) {
-        const bf16x8s wv = *reinterpret_cast<const bf16x8s*>(a.norm_w + v * 8);
+        const bf16x8s wv = wreg[i];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const float2 wf = __bfloat1622float2(wv.v[j]);
@@ -430,7 +440,8 @@ __global__ void ids_gather_kernel(const int* __restrict__ src, int n, int* const
   __syncthreads();
   if (threadIdx.x == 0 && signal_ptrs != nullptr) {
     const int epoch = *signal_epoch + 1;
-    for (int d = 0; d < n_dst; ++d) st_release_sys_s(signal_ptrs[d] + signal_slot, epoch);
+    __threadfence_system();      // release fence of the signalling thread, after the barrier that gathered the CTA's stores
+    for (int d = 0; d < n_dst; ++d) st_relaxed_sys(signal_ptrs[d] + signal_slot, epoch);
     *signal_epoch = epoch;
   }
 }

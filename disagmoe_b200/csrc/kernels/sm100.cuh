@@ -74,6 +74,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// Flag store of a release pattern: the caller has executed a system-scope fence (__threadfence_system) after the data
+// writes; the flags themselves then go out as relaxed system-scope stores, so that signalling n destinations costs one
+// fence and n independent stores instead of n fence + store pairs in a row (st.release implies a fence each time).
+__device__ __forceinline__ void st_relaxed_sys(int* p, int v) {
+  asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
 // ---------------------------------------------------------------- TMA
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
