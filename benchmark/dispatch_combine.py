@@ -209,6 +209,7 @@ def main():
                           signal_ptrs=arena.ptr_table(list(range(A)), layout.offset("comb_flag0")))]
             er.bn = gemm.pick_bn(gemm._group_hint(A * T * k, E), gemm.EPI_SWIGLU)
             er.bn2 = gemm.pick_bn(gemm._group_hint(A * T * k, E), gemm.EPI_COMBINE)
+            er.sk2 = gemm.want_streamk(gemm.EPI_COMBINE, H, EPR, A * T * k * EPR // E, er.bn2, gemm.num_sms(dev))
             fused = er
         nccl = NcclPath(cfg, A, X, rank, T, x, gate_w, norm_w, experts_mod)
 

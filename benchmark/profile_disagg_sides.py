@@ -124,8 +124,10 @@ def main():
                         for m in range(2):
                             fn(l, m)
                 return timed(run, graph=True) / a.layers / 2 * 1e3
+            one = lambda part: stage(lambda l, m: r.layer_attn(l, m, parts=(part,)))
             print(f"  stages alone, us per layer and micro-batch (graph replay): norm_gather {stage(r.layer_pre):.1f}, "
-                  f"qkv + attention + o_proj {stage(r.layer_attn):.1f}, route_dispatch {stage(r.layer_route_dispatch):.1f}")
+                  f"qkv {one('qkv'):.1f}, attention {one('attn'):.1f}, o_proj {one('o_proj'):.1f}, "
+                  f"route_dispatch {stage(r.layer_route_dispatch):.1f}")
         del r, arenas
         torch.cuda.empty_cache()
     if a.side in ("both", "expert"):

@@ -497,11 +497,27 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
         if (EPI == EPI_PLAIN && vec) {
           if (jmax <= 0) continue;                   // uniform over the CTA: no barrier is skipped by some threads only
           // transpose the chunk: thread = feature row writes its 32 token values; then thread (token, 8 features)
+          const int fg = et & 15, tk0 = et >> 4;
+          const int f0 = m * kBM + fg * 8;
+          // QKV epilogue: the positions and cache slots of this thread's four tokens are requested before the
+          // transposition, so that their latency overlaps it
+          int pos4[4] = {0, 0, 0, 0};
+          long long slot4[4] = {-1, -1, -1, -1};
+          if (a.rope_table != nullptr && f0 < a.F) {
+            const bool kv_tile = f0 / a.hd >= a.n_q;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const int j = tk0 + q * 8;
+              if (j < jmax) {
+                const long long t = tok_base + c * 32 + j;
+                pos4[q] = __ldg(a.positions + t);
+                if (kv_tile && a.slots != nullptr) slot4[q] = __ldg(a.slots + t);
+              }
+            }
+          }
 #pragma unroll
           for (int j = 0; j < 32; ++j) epi_stage[j * kBM + row] = acc[j];
           named_bar_sync(1, kEpiThreads);
-          const int fg = et & 15, tk0 = et >> 4;
-          const int f0 = m * kBM + fg * 8;
           if (f0 < a.F) {                            // F is a multiple of 8 on this path
             uint4 rr[4];
             if (a.R != nullptr) {
@@ -542,7 +558,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
                 const float4 p0 = *reinterpret_cast<const float4*>(&epi_stage[j * kBM + pf]);
                 const float4 p1 = *reinterpret_cast<const float4*>(&epi_stage[j * kBM + pf + 4]);
                 const float pr[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
-                int pos = a.positions[t];
+                int pos = pos4[q];
                 pos = pos < 0 ? 0 : (pos >= a.rope_max_pos ? a.rope_max_pos - 1 : pos);
                 const float4* cs = reinterpret_cast<const float4*>(a.rope_table + static_cast<long long>(pos) * half +
                                                                    (lower ? d0 : d0 - half));
@@ -569,7 +585,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
                   if (head < a.n_q) {
                     *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.Y) + t * a.ldy + f0) = pk;
                   } else {
-                    const long long slot = a.slots != nullptr ? a.slots[t] : -1;
+                    const long long slot = slot4[q];
                     if (slot >= 0) {
                       const int kvh = head - a.n_q;
                       __nv_bfloat16* cache = kvh < a.n_kv ? a.kcache : a.vcache;

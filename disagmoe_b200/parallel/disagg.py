@@ -269,10 +269,11 @@ class AttentionRank:
                       signal_slot=self.tp_rank, signal_epoch=d.get("hs_sig_epoch"), ticket=d["ticket"],
                       status=self.status)
 
-    def layer_attn(self, l: int, m: int) -> None:
+    def layer_attn(self, l: int, m: int, parts=("qkv", "attn", "o_proj")) -> None:
         """QKV (+ RoPE + KV append in the epilogue), paged attention, o_proj. With tensor parallelism the QKV GEMM
         consumes the all-gathered rows shard by shard and the o_proj epilogue scatters the partial sums to the rows'
-        owners; without it o_proj adds the residual in place."""
+        owners; without it o_proj adds the residual in place. ``parts`` lets a profiler run one of the three launches
+        alone (on whatever the buffers hold)."""
         d, S, cfg = self.mb[m], self.shape, self.cfg
         T, per, lo, hi = self.rows(m)
         a = self.layers[l]
@@ -284,17 +285,22 @@ class AttentionRank:
                                  done_ticket=d["gemm_ticket"], rope=rope)
         else:
             comm = gemm.GemmComm(rope=rope)
-        _lib.TAG = "qkv"
-        qkv = gemm.linear(d["hs"][:T], a.qkv_w, out=d["qkv"][:T], comm=comm)
-        _lib.TAG = ""
+        qkv, attn = d["qkv"][:T], d["attn"][:T]
+        if "qkv" in parts:
+            _lib.TAG = "qkv"
+            gemm.linear(d["hs"][:T], a.qkv_w, out=qkv, comm=comm)
+            _lib.TAG = ""
         n_pre = self.n_pre[m]
-        attn = F.paged_attention(qkv[:, :a.q_size], kc, vc, meta.block_tables, meta.bt_row,
-                                 d["ctx_dec"][:T] if n_pre else meta.ctx_len,
-                                 a.num_heads, a.num_kv_heads, a.head_dim, out=d["attn"][:T],
-                                 splits=F.pick_attn_splits(T, a.num_kv_heads, cfg.max_seq_len, self.block_size))
-        if n_pre:
-            F.prefill_attention(qkv[:, :a.q_size], kc, vc, meta.block_tables, d["pre_tiles"], n_pre, a.num_heads,
-                                a.num_kv_heads, a.head_dim, attn)
+        if "attn" in parts:
+            F.paged_attention(qkv[:, :a.q_size], kc, vc, meta.block_tables, meta.bt_row,
+                              d["ctx_dec"][:T] if n_pre else meta.ctx_len,
+                              a.num_heads, a.num_kv_heads, a.head_dim, out=attn,
+                              splits=F.pick_attn_splits(T, a.num_kv_heads, cfg.max_seq_len, self.block_size))
+            if n_pre:
+                F.prefill_attention(qkv[:, :a.q_size], kc, vc, meta.block_tables, d["pre_tiles"], n_pre, a.num_heads,
+                                    a.num_kv_heads, a.head_dim, attn)
+        if "o_proj" not in parts:
+            return
         _lib.TAG = "o_proj"
         if self.tp == 1:
             gemm.linear(attn, a.o_w, residual=d["resid"][:T], out=d["resid"][:T])
