@@ -42,6 +42,18 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool v
   const int sz = valid ? 16 : 0;
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(sz) : "memory");
 }
+// The decode kernel reads every K / V byte once per step: an evict-first L2 policy keeps that stream from pushing the
+// small hot tensors of the neighbouring kernels (residual rows, norm and gate weights, staged activations) out of L2.
+__device__ __forceinline__ uint64_t l2_stream_policy() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ void cp_async16_stream(uint32_t dst, const void* src, bool valid, uint64_t policy) {
+  const int sz = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2, %3;" ::"r"(dst), "l"(src), "r"(sz), "l"(policy)
+               : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {
@@ -111,6 +123,7 @@ paged_attn_kernel(const __nv_bfloat16* __restrict__ q, long long ld_q, const __n
   const int my_chunks = nchunk > warp ? (nchunk - warp + kAttnWarps - 1) / kAttnWarps : 0;
   const long long tok_stride = static_cast<long long>(n_kv) * HD;
   const uint32_t ring = smem_u32(s_dyn) + warp * WARPB;
+  const uint64_t stream_policy = l2_stream_policy();
 
   auto issue = [&](int j) {
     if (j < my_chunks) {
@@ -125,8 +138,8 @@ paged_attn_kernel(const __nv_bfloat16* __restrict__ q, long long ld_q, const __n
         const bool valid = tok0 + r < c1;
         const long long off = valid ? (slot0 + r) * tok_stride + hkv * HD + c * 8 : 0;
         const uint32_t d = dst0 + r * ROWB + ((c ^ (r & 7)) << 4);
-        cp_async16(d, kcache + off, valid);
-        cp_async16(d + TILEB, vcache + off, valid);
+        cp_async16_stream(d, kcache + off, valid, stream_policy);
+        cp_async16_stream(d + TILEB, vcache + off, valid, stream_policy);
       }
     }
     cp_async_commit();
