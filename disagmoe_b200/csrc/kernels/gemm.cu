@@ -106,9 +106,11 @@ struct Cfg {
   static constexpr int kBRows = PAIR ? BN / 2 : BN;      // token rows this CTA stages
   static constexpr int kBBytes = kBRows * kBK * 2;
   static constexpr int kStageBytes = kNumA * kABytes + kBBytes;
-  // plain and combine epilogues: one 32-token x 128-feature fp32 chunk is transposed through shared memory, so that
-  // Y (and the residual) move as 16-byte row segments instead of one 2-byte element per thread
-  static constexpr int kEpiStageBytes = (EPI == EPI_PLAIN || EPI == EPI_COMBINE) ? 32 * kBM * 4 : 0;
+  // plain and combine epilogues (and SwiGLU from 128-token tiles on, where the stage count does not pay for it): one
+  // 32-token x 128-feature fp32 chunk is transposed through shared memory, so that Y (and the residual) move as
+  // 16-byte row segments instead of one 2-byte element per thread
+  static constexpr int kEpiStageBytes =
+      (EPI == EPI_PLAIN || EPI == EPI_COMBINE || (EPI == EPI_SWIGLU && BN >= 128)) ? 32 * kBM * 4 : 0;
   static constexpr int kStagesRaw = (kSmemBudget - 1024 - kTailBytes - kEpiStageBytes) / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
   static constexpr int kAccCols = BN * kNumA;
@@ -430,7 +432,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
         // the TMEM read below instead of after them. Y may alias R (in-place update of the residual stream): all
         // loads of a chunk are issued before its first store, and chunks cover disjoint tokens.
         float r[32];
-        const bool vec = (EPI == EPI_PLAIN) && a.epi_vec != 0;
+        const bool vec = (EPI == EPI_PLAIN || (EPI == EPI_SWIGLU && C::kEpiStageBytes > 0)) && a.epi_vec != 0;
         const bool has_r = (EPI == EPI_PLAIN) && a.R != nullptr && f_ok && !vec;
         if (has_r) {
 #pragma unroll
@@ -494,7 +496,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
             else mbar_arrive(smem_u32(&tempty_bar[buf]));
           }
         }
-        if (EPI == EPI_PLAIN && vec) {
+        if ((EPI == EPI_PLAIN || EPI == EPI_SWIGLU) && vec) {
           if (jmax <= 0) continue;                   // uniform over the CTA: no barrier is skipped by some threads only
           // transpose the chunk: thread = feature row writes its 32 token values; then thread (token, 8 features)
           const int fg = et & 15, tk0 = et >> 4;
@@ -853,7 +855,7 @@ extern "C" int dmoe_gemm(const DmoeGemm* d, void* stream_) {
   {
     const auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
     const long long ymod = d->y_f32 ? 4 : 8;
-    a.epi_vec = (epi == EPI_PLAIN && d->F % 8 == 0 && d->ldy % ymod == 0 && al16(d->Y) &&
+    a.epi_vec = ((epi == EPI_PLAIN || epi == EPI_SWIGLU) && d->F % 8 == 0 && d->ldy % ymod == 0 && al16(d->Y) &&
                  (d->R == nullptr || (d->ldr % 8 == 0 && al16(d->R)))) ? 1 : 0;
     // combine: the destination bases live in a device table; the caller states that all of them are 16-byte aligned
     if (epi == EPI_COMBINE && d->combine_vec != 0 && d->F % 8 == 0 && d->ldy % 8 == 0) a.epi_vec = 1;
