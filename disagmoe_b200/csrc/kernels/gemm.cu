@@ -517,19 +517,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
               }
             }
           }
+          // the residual cells of this thread (the same cells it stores to when Y aliases R) are requested before the
+          // transposition as well
+          uint4 rr[4];
+          if (a.R != nullptr && f0 < a.F) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const int j = tk0 + q * 8;
+              const long long t = tok_base + c * 32 + j;
+              rr[q] = (j < jmax) ? *reinterpret_cast<const uint4*>(a.R + t * a.ldr + f0) : make_uint4(0, 0, 0, 0);
+            }
+          }
 #pragma unroll
           for (int j = 0; j < 32; ++j) epi_stage[j * kBM + row] = acc[j];
           named_bar_sync(1, kEpiThreads);
           if (f0 < a.F) {                            // F is a multiple of 8 on this path
-            uint4 rr[4];
-            if (a.R != nullptr) {
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                const int j = tk0 + q * 8;
-                const long long t = tok_base + c * 32 + j;
-                rr[q] = (j < jmax) ? *reinterpret_cast<const uint4*>(a.R + t * a.ldr + f0) : make_uint4(0, 0, 0, 0);
-              }
-            }
             // QKV epilogue geometry: a 128-feature tile holds whole heads (hd = 64 or 128), so the rotation partner
             // of a feature (d +- hd / 2) sits in the same shared-memory chunk
             const bool rope = a.rope_table != nullptr;
