@@ -96,6 +96,8 @@ class NcclPath:
         self.is_attn = rank < A
         self.epr = (cfg.num_experts + X - 1) // X          # contiguous blocks; the last expert GPU may hold fewer
         self.dev = torch.device("cuda", torch.cuda.current_device())
+        # the library GEMM wants row-major stacks; the fused path keeps its own copies tile-blocked
+        self.w13, self.w2 = experts.logical_weights() if experts is not None else (None, None)
 
     def run(self):
         cfg, A, X, k, H = self.cfg, self.A, self.X, self.cfg.top_k, self.cfg.hidden_size
@@ -132,10 +134,10 @@ class NcclPath:
             xs = got.index_select(0, perm)
             e = self.experts
             offs = cnt.sum(0).cumsum(0).int()[:e.num_experts]
-            up = torch._grouped_mm(xs, e.w13_weight.transpose(1, 2), offs=offs)
+            up = torch._grouped_mm(xs, self.w13.transpose(1, 2), offs=offs)
             I = up.shape[1] // 2
             act = torch.nn.functional.silu(up[:, :I]) * up[:, I:]
-            down = torch._grouped_mm(act, e.w2_weight.transpose(1, 2), offs=offs)
+            down = torch._grouped_mm(act, self.w2.transpose(1, 2), offs=offs)
             down = down * got_meta.index_select(0, perm)[:, 1:2].to(torch.bfloat16)
             back = torch.empty_like(down)
             back[perm] = down

@@ -76,6 +76,10 @@ def main(argv=None):
             for bn in (128, 256):
                 res[("g2", sk, bn)] = timed(lambda: gemm.grouped_linear(act, w2, offs, bn=bn, streamk=sk), flush, a.iters)
         # CTA pairs (cta_group::2): 256 weight rows per MMA, the token tile split between the two CTAs' shared memories
+        w13b, w2b = gemm.block_weight(w13), gemm.block_weight(w2)
+        res[("g1b",)] = timed(lambda: gemm.grouped_swiglu(x, w13b, offs, streamk=False, w_blocked=True), flush, a.iters)
+        res[("g2b",)] = timed(lambda: gemm.grouped_linear(act, w2b, offs, streamk=False, w_blocked=True), flush, a.iters)
+        del w13b, w2b
         res[("g1", False, 256)] = timed(lambda: gemm.grouped_swiglu(x, w13, offs, bn=256, streamk=False), flush, a.iters)
         for bn in (128, 256):
             res[("g1p", bn)] = timed(lambda: gemm.grouped_swiglu(x, w13, offs, bn=bn, pair=True), flush, a.iters)
@@ -95,7 +99,8 @@ def main(argv=None):
               f"{res[('g1p', 128)]:.1f} / bn256 {res[('g1p', 256)]:.1f} us ({f1 / min(res[('g1p', 128)], res[('g1p', 256)]) / 1e6:.0f} "
               f"TFLOP/s), GEMM-2 bn128 {res[('g2p', 128)]:.1f} / bn256 {res[('g2p', 256)]:.1f} us "
               f"({f2 / min(res[('g2p', 128)], res[('g2p', 256)]) / 1e6:.0f} TFLOP/s); torch._grouped_mm "
-              f"GEMM-1 {t_lib:.1f} us, GEMM-2 {t_lib2:.1f} us", flush=True)
+              f"GEMM-1 {t_lib:.1f} us, GEMM-2 {t_lib2:.1f} us; tile-blocked weights, whole tiles: GEMM-1 "
+              f"{res[('g1b',)]:.1f} us, GEMM-2 {res[('g2b',)]:.1f} us", flush=True)
     assert gemm.check_status() == 0
 
 

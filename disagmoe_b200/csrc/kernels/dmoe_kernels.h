@@ -70,6 +70,9 @@ typedef struct DmoeGemm {
   // combine epilogue: != 0 states that every destination base in `bases` is 16-byte aligned (with F and ldy multiples
   // of 8 the rows then move as 16-byte segments); 0 keeps 2-byte stores
   int combine_vec;
+  // != 0: W is stored tile by tile, [group][128-row tile][K / 64][128][64] (see ops/gemm.py: block_weight), so that
+  // every 16 KB box the kernel fetches is one contiguous run of HBM; needs F % 128 == 0 and K % 64 == 0
+  int w_blocked;
 } DmoeGemm;
 
 int dmoe_gemm(const DmoeGemm* desc, void* stream);

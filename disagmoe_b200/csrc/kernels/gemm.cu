@@ -93,6 +93,9 @@ struct GemmArgs {
   __nv_bfloat16* vcache;
   int n_q, n_kv, hd, rope_max_pos;
   long long flag_cycles;   // budget of the peer-flag waits
+  // w_blocked: the weights are stored tile by tile ([group][128-row tile][K block][128][64], every 16 KB TMA box one
+  // contiguous run of HBM) instead of row-major [group][row][K]
+  int w_blocked;
 };
 
 // PAIR: the kernel runs as clusters of two CTAs on one tile of 256 weight rows (two m-tiles) x BN tokens with
@@ -269,8 +272,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
             if (PAIR) tma_load_2d_pair(dst, m, x, y, fb, pol);
             else tma_load_2d(dst, m, x, y, fb, pol);
           };
-          load(smem_u32(st), &tmW, kb * kBK, wrow, pol_w);
-          if (EPI == EPI_SWIGLU) load(smem_u32(st + C::kABytes), &tmW, kb * kBK, wrow + a.F, pol_w);
+          if (a.w_blocked) {
+            // blocked weights: the map is a [tiles * K blocks * 128, 64] matrix, tile (t, kb) starts at row (t * kblocks + kb) * 128
+            const int wt = wrow / kBM;
+            load(smem_u32(st), &tmW, 0, (wt * kblocks + kb) * kBM, pol_w);
+            if (EPI == EPI_SWIGLU) load(smem_u32(st + C::kABytes), &tmW, 0, ((wt + a.F / kBM) * kblocks + kb) * kBM, pol_w);
+          } else {
+            load(smem_u32(st), &tmW, kb * kBK, wrow, pol_w);
+            if (EPI == EPI_SWIGLU) load(smem_u32(st + C::kABytes), &tmW, kb * kBK, wrow + a.F, pol_w);
+          }
           if (a.shard_rows > 0 && kb == kb0) {
             // the weight tile is already on its way; the token tile may only be fetched once every peer whose rows
             // it covers has published them (the peers' stores are generic-proxy writes: fence before the TMA read)
@@ -891,7 +901,15 @@ extern "C" int dmoe_gemm(const DmoeGemm* d, void* stream_) {
 
   CUtensorMap tmW, tmX;
   const long long ldx = d->ldx > 0 ? d->ldx : d->K;
-  if (make_map_2d(&tmW, d->W, static_cast<long long>(d->G) * a.w_rows, d->K, d->K, kBM) != 0) return -20;
+  a.w_blocked = d->w_blocked != 0;
+  if (a.w_blocked) {
+    // whole 128-row tiles and whole 64-element K blocks only; row coordinates must stay below 2^31
+    const long long rows = static_cast<long long>(d->G) * a.w_rows * (d->K / kBK);
+    if (d->K % kBK != 0 || d->F % kBM != 0 || rows >= (1ll << 31)) return -22;
+    if (make_map_2d(&tmW, d->W, rows, kBK, kBK, kBM) != 0) return -20;
+  } else if (make_map_2d(&tmW, d->W, static_cast<long long>(d->G) * a.w_rows, d->K, d->K, kBM) != 0) {
+    return -20;
+  }
   if (make_map_2d(&tmX, d->X, d->T, d->K, ldx, pair ? bn / 2 : bn) != 0) return -21;
 
   long long mt = (d->F + kBM - 1) / kBM;

@@ -208,9 +208,10 @@ def rope_table(max_pos: int, hd: int, theta: float, device) -> torch.Tensor:
 
 
 def _launch(W, X, Y, R, offs, recs, bases, G, T, F, K, epi, bn, splitk, ldy, y_f32, comm: Optional[GemmComm] = None,
-            streamk: bool = False, pair: bool = False):
+            streamk: bool = False, pair: bool = False, w_blocked: bool = False):
     s = scratch(X.device)
     d = _lib.DmoeGemm()
+    d.w_blocked = int(w_blocked)
     d.streamk, d.n_counters = int(streamk and splitk <= 1 and not pair), s.counters.numel()
     d.pair = int(pair)
     d.combine_vec = int(epi == EPI_COMBINE and F % 8 == 0 and ldy % 8 == 0 and _bases_aligned(bases))
@@ -302,7 +303,7 @@ def _grouped_ref(x, w, offs, swiglu):
 
 def grouped_swiglu(x: torch.Tensor, w13: torch.Tensor, offs: Optional[torch.Tensor], out: Optional[torch.Tensor] = None,
                    bn: int = 0, comm: Optional[GemmComm] = None, streamk: Optional[bool] = None,
-                   pair: bool = False) -> torch.Tensor:
+                   pair: bool = False, w_blocked: bool = False) -> torch.Tensor:
     """act[T, I] = silu(x @ w13[g, :I].T) * (x @ w13[g, I:].T) for the rows of group g; w13 is [G, 2I, K]."""
     T, K = x.shape
     G, F2, _ = w13.shape
@@ -325,12 +326,13 @@ def grouped_swiglu(x: torch.Tensor, w13: torch.Tensor, offs: Optional[torch.Tens
         bn = max(bn, 128)
     sk = want_streamk(EPI_SWIGLU, I, G, T, bn, num_sms(x.device)) if streamk is None else streamk
     _launch(w13, x, out, None, offs, None, None, G, T, I, K, EPI_SWIGLU, bn, 1, out.stride(0), False, comm,
-            streamk=sk, pair=pair)
+            streamk=sk, pair=pair, w_blocked=w_blocked)
     return out
 
 
 def grouped_linear(x: torch.Tensor, w: torch.Tensor, offs: torch.Tensor, out: Optional[torch.Tensor] = None,
-                   bn: int = 0, streamk: Optional[bool] = None, pair: bool = False) -> torch.Tensor:
+                   bn: int = 0, streamk: Optional[bool] = None, pair: bool = False,
+                   w_blocked: bool = False) -> torch.Tensor:
     """y[T, F] = x @ w[g].T for the rows of group g; w is [G, F, K]."""
     T, K = x.shape
     G, F, _ = w.shape
@@ -350,8 +352,29 @@ def grouped_linear(x: torch.Tensor, w: torch.Tensor, offs: torch.Tensor, out: Op
     if pair:
         bn = max(bn, 128)
     sk = want_streamk(EPI_PLAIN, F, G, T, bn, num_sms(x.device)) if streamk is None else streamk
-    _launch(w, x, out, None, offs, None, None, G, T, F, K, EPI_PLAIN, bn, 1, out.stride(0), False, streamk=sk, pair=pair)
+    _launch(w, x, out, None, offs, None, None, G, T, F, K, EPI_PLAIN, bn, 1, out.stride(0), False, streamk=sk, pair=pair,
+            w_blocked=w_blocked)
     return out
+
+
+def block_weight(w: torch.Tensor) -> torch.Tensor:
+    """Re-orders a K-contiguous weight stack [G, R, K] (or [R, K]) tile by tile: [G, R / 128, K / 64, 128, 64], returned
+    with the ORIGINAL shape (only the memory order changes), for launches with ``w_blocked=True``. Every 128-row x
+    64-column box the GEMM fetches is then 16 KB of consecutive addresses instead of 128 runs of 128 bytes one weight
+    row apart. R must be a multiple of 128 (for SwiGLU stacks: the gate and the up half each) and K of 64."""
+    shape = w.shape
+    w3 = w if w.dim() == 3 else w.unsqueeze(0)
+    G, R, K = w3.shape
+    assert R % 128 == 0 and K % 64 == 0, "blocked weights need whole 128 x 64 tiles"
+    return w3.view(G, R // 128, 128, K // 64, 64).permute(0, 1, 3, 2, 4).contiguous().view(shape)
+
+
+def unblock_weight(w: torch.Tensor) -> torch.Tensor:
+    """Inverse of :func:`block_weight`: a row-major copy of a tile-blocked stack."""
+    shape = w.shape
+    w3 = w if w.dim() == 3 else w.unsqueeze(0)
+    G, R, K = w3.shape
+    return w3.view(G, R // 128, K // 64, 128, 64).permute(0, 1, 3, 2, 4).contiguous().view(shape)
 
 
 _bases_checked = {}
@@ -371,7 +394,7 @@ def _bases_aligned(bases: torch.Tensor) -> bool:
 
 def grouped_combine(x: torch.Tensor, w: torch.Tensor, offs: Optional[torch.Tensor], recs: torch.Tensor,
                     bases: torch.Tensor, ld_out: int, bn: int = 0, outs=None, comm: Optional[GemmComm] = None,
-                    streamk: Optional[bool] = None, pair: bool = False) -> None:
+                    streamk: Optional[bool] = None, pair: bool = False, w_blocked: bool = False) -> None:
     """GEMM-2 with the combine epilogue: row t of group g becomes ``weight[t] * (x[t] @ w[g].T)`` written to row
     ``recs[t, 1]`` of the buffer ``bases[recs[t, 0]]`` (row stride ``ld_out`` elements).
 
@@ -397,7 +420,7 @@ def grouped_combine(x: torch.Tensor, w: torch.Tensor, offs: Optional[torch.Tenso
         bn = max(bn, 128)
     sk = want_streamk(EPI_COMBINE, F, G, T, bn, num_sms(x.device)) if streamk is None else streamk
     _launch(w, x, None, None, offs, recs, bases, G, T, F, K, EPI_COMBINE, bn, 1, ld_out, False, comm, streamk=sk,
-            pair=pair)
+            pair=pair, w_blocked=w_blocked)
 
 
 def swiglu_linear(x: torch.Tensor, w13: torch.Tensor, out: Optional[torch.Tensor] = None, bn: int = 0) -> torch.Tensor:

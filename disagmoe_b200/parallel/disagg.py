@@ -430,14 +430,14 @@ class ExpertRank:
         gate = gemm.GemmComm(seg_cnt=d["cnt"], seg_cap=S.region_cap, group_regions=True, wait_flags=d["flag"],
                              n_wait=S.n_attn, wait_epoch=d["wait_epoch"], done_ticket=self.ticket)
         _lib.TAG = "expert_gemm1"
-        gemm.grouped_swiglu(d["rows"], e.w13_weight, None, out=self.act, bn=self.bn, comm=gate)
+        gemm.grouped_swiglu(d["rows"], e.w13_weight, None, out=self.act, bn=self.bn, comm=gate, w_blocked=e.w_blocked)
         _lib.TAG = "expert_gemm2"
         # the last CTA clears the row cursors before it signals: the senders reserve again only after that signal
         sig = gemm.GemmComm(seg_cnt=d["cnt"], seg_cap=S.region_cap, group_regions=True, signal_ptrs=d["signal_ptrs"],
                             n_signal=S.n_attn, signal_slot=self.x, signal_epoch=d["signal_epoch"],
                             done_ticket=self.ticket, clear=d["cnt"])
         gemm.grouped_combine(self.act, e.w2_weight, None, d["recs"], d["parts_bases"], S.hidden, bn=self.bn2, comm=sig,
-                             streamk=self.sk2)
+                             streamk=self.sk2, w_blocked=e.w_blocked)
         _lib.TAG = ""
 
     def iteration(self) -> None:

@@ -325,3 +325,37 @@ def test_cta_pair_grouped_swiglu_and_combine(counts, I, K, bn):
     exp = torch.zeros(T, F, device="cuda")
     exp[perm] = gemm._grouped_ref(act, w2, offs, False) * wts[:, None]
     _close(out, exp)
+
+
+@pytest.mark.parametrize("counts,I,K,bn", [([64] * 8, 256, 512, 64), ([100, 7, 0, 0, 200, 1, 33, 64], 384, 256, 128),
+                                            ([31, 300], 1408, 2048, 0)])
+def test_blocked_weight_layout_swiglu_linear_and_combine(counts, I, K, bn):
+    """Weights stored tile by tile (every 128 x 64 box contiguous) give the same results as the row-major stack: the
+    SwiGLU up-projection (gate and up tiles of the fused stack), the grouped down-projection, and the combine epilogue."""
+    torch.manual_seed(9)
+    G, T = len(counts), sum(counts)
+    x, w13 = _rand(T, K), _rand(G, 2 * I, K, scale=K ** -0.5)
+    offs = _offsets(counts)
+    act = gemm.grouped_swiglu(x, gemm.block_weight(w13), offs, bn=bn, streamk=gemm.STREAM_K, w_blocked=True)
+    torch.cuda.synchronize()
+    assert gemm.check_status() == 0
+    _close(act, gemm._grouped_ref(x, w13, offs, True))
+    F2 = 256
+    w2 = _rand(G, F2, I, scale=I ** -0.5)
+    y = gemm.grouped_linear(act, gemm.block_weight(w2), offs, bn=bn, streamk=gemm.STREAM_K, w_blocked=True)
+    ref = gemm._grouped_ref(act, w2, offs, False)
+    _close(y, ref)
+    wts = torch.rand(T, device="cuda")
+    recs = torch.zeros(T, 4, dtype=torch.int32, device="cuda")
+    perm = torch.randperm(T, device="cuda")
+    recs[:, 1] = perm.int()
+    recs[:, 2] = wts.view(torch.int32)
+    out = torch.zeros(T, F2, dtype=torch.bfloat16, device="cuda")
+    bases = torch.tensor([out.data_ptr()], dtype=torch.int64, device="cuda")
+    gemm.grouped_combine(act, gemm.block_weight(w2), offs, recs, bases, out.stride(0), bn=bn, streamk=gemm.STREAM_K,
+                         w_blocked=True)
+    torch.cuda.synchronize()
+    assert gemm.check_status() == 0
+    exp = torch.zeros(T, F2, device="cuda")
+    exp[perm] = ref.float() * wts[:, None]
+    _close(out, exp)

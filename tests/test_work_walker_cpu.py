@@ -29,3 +29,19 @@ def test_dense_tile_and_split_choice_is_launchable_and_follows_the_measured_orde
     assert gemm.pick_dense(256, 6144, 4096, 148)[0] == 128
     assert gemm.pick_dense(256, 4096, 4096, 148) == (128, 2)
     assert gemm.pick_dense(64, 4096, 4096, 148)[1] >= 2
+
+
+def test_tile_blocked_weight_layout_round_trip_and_box_order():
+    """block_weight puts every 128-row x 64-column box of a K-contiguous stack into one contiguous run, boxes ordered
+    (group, row tile, K block) as the GEMM's blocked tensor map addresses them; unblock_weight inverts it."""
+    import torch
+    from disagmoe_b200.ops import gemm
+    w = torch.arange(2 * 256 * 192, dtype=torch.float32).view(2, 256, 192)
+    b = gemm.block_weight(w)
+    assert b.shape == w.shape and torch.equal(gemm.unblock_weight(b), w)
+    flat, KB = b.reshape(-1), 192 // 64
+    for g, m, kb in ((0, 0, 0), (0, 1, 2), (1, 0, 1), (1, 1, 2)):
+        box = flat[((g * 2 + m) * KB + kb) * 128 * 64:][:128 * 64].view(128, 64)
+        assert torch.equal(box, w[g, m * 128:(m + 1) * 128, kb * 64:(kb + 1) * 64])
+    w2 = torch.randn(128, 64)
+    assert torch.equal(gemm.block_weight(w2), w2)       # a single box is already in order
