@@ -197,7 +197,7 @@ def main():
             tp -= 1
         if not args.no_selfcheck:
             selfcheck = selfcheck_against_colocated(world, rank, local_rank, A, tp, args.micro_batches)
-            if tp > 1 and (selfcheck["kernel_status"] != 0 or selfcheck["max_rel_err"] > 0.1):
+            if tp > 1 and (selfcheck["kernel_status"] != 0 or selfcheck["rows_within_2pct"] < 0.9 * selfcheck["rows"]):
                 # the tensor-parallel layout did not reproduce the colocated logits on this box: measure the
                 # data-parallel layout instead and say so, rather than time a wrong computation
                 bad = selfcheck

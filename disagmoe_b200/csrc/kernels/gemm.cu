@@ -96,6 +96,11 @@ struct GemmArgs {
   // w_blocked: the weights are stored tile by tile ([group][128-row tile][K block][128][64], every 16 KB TMA box one
   // contiguous run of HBM) instead of row-major [group][row][K]
   int w_blocked;
+  // optional [16] nanosecond stamps written by CTA 0 (a profiling aid, null in normal launches): 0 entry, 1 set-up done,
+  // 2 first TMA issued, 3 first stage landed, 4 last MMA committed, 5 accumulator seen by the epilogue, 6 epilogue done,
+  // 7 tear-down reached; 8-12 inside the first epilogue chunk: TMEM read done, staged to shared memory, barrier passed,
+  // rows stored, second barrier passed
+  unsigned long long* trace;
 };
 
 // PAIR: the kernel runs as clusters of two CTAs on one tile of 256 weight rows (two m-tiles) x BN tokens with
@@ -125,6 +130,14 @@ struct Cfg {
   static_assert((kTmemCols & (kTmemCols - 1)) == 0, "TMEM columns must be a power of two");
   static_assert(kStages >= 3, "pipeline too shallow");
 };
+
+__device__ __forceinline__ void trace_stamp(const GemmArgs& a, int i) {
+  if (a.trace != nullptr && blockIdx.x == 0) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    a.trace[i] = t;
+  }
+}
 
 __device__ __forceinline__ int ld_acquire_sys(const int* p) {
   int v;
@@ -165,6 +178,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
   const long long bar_budget = DMOE_WAIT_CYCLES + (a.shard_rows > 0 ? a.flag_cycles : 0);
 
   if (threadIdx.x == 0) {
+    trace_stamp(a, 0);
     *abort_word = 0;
     *last_flag = 0;
     for (int s = 0; s < C::kStages; ++s) {
@@ -238,6 +252,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
   if (PAIR) cluster_sync_all();      // both CTAs' barriers are initialised before either is signalled from outside
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) trace_stamp(a, 1);
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -250,6 +265,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      bool traced = false;
       unsigned long long shard_ready = 0;     // bit s: shard s of X has landed (all-gather prologue)
       const int shard_want = (a.shard_rows > 0) ? *a.wait_epoch + 1 : 0;
       WorkUnit u;
@@ -307,6 +323,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
             if (!ok) break;
           }
           load(smem_u32(st + C::kNumA * C::kABytes), &tmX, kb * kBK, xrow, pol_x);
+          if (a.trace != nullptr && !traced) { trace_stamp(a, 2); traced = true; }
           if (++stage == C::kStages) { stage = 0; phase ^= 1; }
         }
       }
@@ -337,6 +354,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
         const int kb0 = u.kb0, kb1 = u.kb1;
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(smem_u32(&full_bar[stage]), phase, abort_word, bar_budget)) { ok = false; break; }
+          if (a.trace != nullptr && it == 0 && kb == kb0) trace_stamp(a, 3);
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + stage * C::kStageBytes);
           const uint64_t da = umma_desc_sw128(sa);
@@ -368,6 +386,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
             umma_commit_pair(mapa_rank(smem_u32(&tfull_bar[buf]), 1));
           } else {
             umma_commit(smem_u32(&tfull_bar[buf]));
+            trace_stamp(a, 4);
           }
         }
       }
@@ -388,6 +407,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
       const int buf = it % C::kAccBufs;
       const uint32_t bphase = (it / C::kAccBufs) & 1;
       if (!mbar_wait(smem_u32(&tfull_bar[buf]), bphase, abort_word, bar_budget)) { ok = false; break; }
+      if (et == 0) trace_stamp(a, 5);
       tc_fence_after();
       const uint32_t t0 = tmem_base + buf * C::kAccCols + (static_cast<uint32_t>(q * 32) << 16);
       const int f = m * kBM + row;
@@ -496,6 +516,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
             }
           } else {
             tmem_ld_wait();
+            if (et == 0 && c == 0) trace_stamp(a, 8);
 #pragma unroll
             for (int j = 0; j < 32; ++j) acc[j] = __uint_as_float(v[j]);
           }
@@ -540,7 +561,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
           }
 #pragma unroll
           for (int j = 0; j < 32; ++j) epi_stage[j * kBM + row] = acc[j];
+          if (et == 0 && c == 0) trace_stamp(a, 9);
           named_bar_sync(1, kEpiThreads);
+          if (et == 0 && c == 0) trace_stamp(a, 10);
           if (f0 < a.F) {                            // F is a multiple of 8 on this path
             // QKV epilogue geometry: a 128-feature tile holds whole heads (hd = 64 or 128), so the rotation partner
             // of a feature (d +- hd / 2) sits in the same shared-memory chunk
@@ -617,7 +640,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
               }
             }
           }
+          if (et == 0 && c == 0) trace_stamp(a, 11);
           named_bar_sync(1, kEpiThreads);            // the stage is free again for the next chunk / tile
+          if (et == 0 && c == 0) trace_stamp(a, 12);
           continue;
         }
         if (EPI == EPI_COMBINE && a.epi_vec != 0) {
@@ -693,6 +718,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
     }
   }
 
+  if (threadIdx.x == 64) trace_stamp(a, 6);
   // ---------------------------------------------------------------- completion: signal peers, advance epochs
   if (a.done_ticket != nullptr && warp >= 2) {
     // every epilogue thread makes its (possibly remote) stores visible system-wide, then the CTA takes a ticket.
@@ -720,6 +746,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
   // ---------------------------------------------------------------- tear-down
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) trace_stamp(a, 7);
   if (*abort_word) {
     if (threadIdx.x == 0 && a.status != nullptr) atomicCAS(a.status, kStatusOk, kStatusBarrierTimeout);
     // give copies that may still be in flight time to land before shared memory is released
@@ -901,6 +928,7 @@ extern "C" int dmoe_gemm(const DmoeGemm* d, void* stream_) {
 
   CUtensorMap tmW, tmX;
   const long long ldx = d->ldx > 0 ? d->ldx : d->K;
+  a.trace = static_cast<unsigned long long*>(d->trace);
   a.w_blocked = d->w_blocked != 0;
   if (a.w_blocked) {
     // whole 128-row tiles and whole 64-element K blocks only; row coordinates must stay below 2^31

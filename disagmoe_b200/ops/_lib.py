@@ -39,6 +39,7 @@ class DmoeGemm(ctypes.Structure):
         ("n_q", ctypes.c_int), ("n_kv", ctypes.c_int), ("hd", ctypes.c_int), ("rope_max_pos", ctypes.c_int),
         ("streamk", ctypes.c_int), ("n_counters", ctypes.c_int), ("pair", ctypes.c_int),
         ("combine_vec", ctypes.c_int), ("w_blocked", ctypes.c_int),
+        ("trace", ctypes.c_void_p),
     ]
 
 

