@@ -564,7 +564,30 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
           if (et == 0 && c == 0) trace_stamp(a, 9);
           named_bar_sync(1, kEpiThreads);
           if (et == 0 && c == 0) trace_stamp(a, 10);
-          if (f0 < a.F) {                            // F is a multiple of 8 on this path
+          const bool simple = a.rope_table == nullptr && a.R == nullptr && a.rs_bases == nullptr && !a.y_f32;
+          if (simple && f0 < a.F) {
+            // the common case (bf16 rows straight to Y: SwiGLU activations, plain linears) without any of the
+            // variants' branches inside the loop: four independent load -> pack -> store chains
+            __nv_bfloat16* ybase = reinterpret_cast<__nv_bfloat16*>(a.Y) + (tok_base + c * 32) * a.ldy + f0;
+            float4 x0[4], x1[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const int j = tk0 + q * 8;
+              x0[q] = *reinterpret_cast<const float4*>(&epi_stage[j * kBM + fg * 8]);
+              x1[q] = *reinterpret_cast<const float4*>(&epi_stage[j * kBM + fg * 8 + 4]);
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const int j = tk0 + q * 8;
+              uint4 pk;
+              __nv_bfloat162* pp = reinterpret_cast<__nv_bfloat162*>(&pk);
+              pp[0] = __floats2bfloat162_rn(x0[q].x, x0[q].y);
+              pp[1] = __floats2bfloat162_rn(x0[q].z, x0[q].w);
+              pp[2] = __floats2bfloat162_rn(x1[q].x, x1[q].y);
+              pp[3] = __floats2bfloat162_rn(x1[q].z, x1[q].w);
+              if (j < jmax) *reinterpret_cast<uint4*>(ybase + static_cast<long long>(j) * a.ldy) = pk;
+            }
+          } else if (f0 < a.F) {                     // F is a multiple of 8 on this path
             // QKV epilogue geometry: a 128-feature tile holds whole heads (hd = 64 or 128), so the rotation partner
             // of a feature (d +- hd / 2) sits in the same shared-memory chunk
             const bool rope = a.rope_table != nullptr;

@@ -34,7 +34,7 @@ struct WorkUnit {
   int kb0, kb1;    // K blocks [kb0, kb1) of the tile that this unit covers
   int ncontrib;    // units that together cover the tile (1: this unit is the whole tile)
   int c_first;     // stream-K: first CTA contributing to the tile
-  long long slot;  // workspace slot where this unit parks its partial accumulator (when ncontrib > 1)
+  int slot;        // workspace slot where this unit parks its partial accumulator (when ncontrib > 1)
 };
 
 struct WorkWalker {
@@ -42,10 +42,12 @@ struct WorkWalker {
   const int* seg_cnt;    // [S * G]
   int G, S, MT, BN, kblocks, splitk, kb_per, streamk;
   int g, base, ntn;      // group cursor: tiles of group g start at id `base`
-  long long lin, lin_step;              // split-K: next flat unit id of this CTA and the stride
+  // All counters are 32-bit on purpose (the launcher bounds tiles x splits by 2^30 and the stream-K remainder holds
+  // fewer tiles than the grid has CTAs): 64-bit divisions cost a microsecond of every launch's prologue.
+  int lin, lin_step;                    // split-K: next flat unit id of this CTA and the stride
   // stream-K: `waves` full waves of whole tiles, then this CTA's share [it_begin, it_end) of the K-block iterations
   // of the remaining tiles (ids from tile0 on); `total` counts the remainder's iterations
-  long long it, it_end, total, it_begin;
+  int it, it_end, total, it_begin;
   int active, cta, grid, waves, wave, tile0;
 
   DMOE_HD static int min_i(int a, int b) { return a < b ? a : b; }
@@ -57,9 +59,12 @@ struct WorkWalker {
       for (int s = 0; s < S; ++s) ntn += (seg_cnt[s * G + g] + BN - 1) / BN;
   }
 
-  DMOE_HD long long share_begin(long long c) const { return c * total / active; }
+  // (products of a CTA index and an iteration count: 64-bit multiply, 32-bit operands, one division each)
+  DMOE_HD int share_begin(int c) const { return static_cast<int>(static_cast<long long>(c) * total / active); }
   // CTA whose share holds iteration i: the largest c with share_begin(c) <= i
-  DMOE_HD int owner(long long i) const { return static_cast<int>(((i + 1) * active + total - 1) / total) - 1; }
+  DMOE_HD int owner(int i) const {
+    return static_cast<int>((static_cast<long long>(i + 1) * active + total - 1) / total) - 1;
+  }
 
   DMOE_HD void init(const int* s_start, const int* s_cnt, int G_, int S_, int MT_, int BN_, int kblocks_, int splitk_,
                     int streamk_, int cta_, int grid_) {
@@ -68,36 +73,36 @@ struct WorkWalker {
     kb_per = (kblocks + splitk - 1) / splitk;
     lin = cta_; lin_step = grid_;
     it = it_end = it_begin = total = 0; active = 1; grid = grid_; waves = wave = tile0 = 0;
-    long long tiles = 0;
+    int tiles = 0;
     for (int gg = 0; gg < G; ++gg) {
       int t = 0;
       for (int s = 0; s < S; ++s) t += (seg_cnt[s * G + gg] + BN - 1) / BN;
-      tiles += static_cast<long long>(MT) * t;
+      tiles += MT * t;
     }
     if (!streamk) {
       // Balanced waves: with u units and w = ceil(u / grid) waves, only ceil(u / w) CTAs take part, each with w (or
       // w - 1) units, so that all of them finish together instead of a few CTAs running a last, nearly empty wave
       // while the rest idle. A memory-bound launch loses nothing (fewer SMs still saturate HBM) and sheds the tail;
       // a compute-bound one takes w unit times either way.
-      const long long units = tiles * splitk;
+      const int units = tiles * splitk;
       if (units > 0) {
-        const long long w = (units + grid_ - 1) / grid_;
-        const long long use = (units + w - 1) / w;
+        const int w = (units + grid_ - 1) / grid_;
+        const int use = (units + w - 1) / w;
         lin_step = use;
         if (cta_ >= use) lin = units;      // idle CTA: its first unit is already past the end
       }
     }
     if (streamk) {
-      waves = static_cast<int>(tiles / grid_);
+      waves = tiles / grid_;
       tile0 = waves * grid_;
       total = (tiles - tile0) * kblocks;
       // a share shorter than a few K blocks (or a tile cut into more than 8 pieces) costs more in partial-tile
       // traffic than it wins in balance
       int min_share = kblocks >= 8 ? 4 : kblocks;
       if (min_share < (kblocks + 7) / 8) min_share = (kblocks + 7) / 8;
-      long long act = total / min_share;
+      int act = total / min_share;
       if (act < 1) act = 1;
-      active = act < grid_ ? static_cast<int>(act) : grid_;
+      active = act < grid_ ? act : grid_;
       if (total > 0 && cta_ < active) {
         it_begin = it = share_begin(cta_);
         it_end = share_begin(cta_ + 1);
@@ -136,9 +141,9 @@ struct WorkWalker {
   // The next unit of this CTA; false when it has none left.
   DMOE_HD bool next(WorkUnit& u) {
     if (!streamk) {
-      const long long tile = lin / splitk;
-      if (tile > 0x7fffffffll || !locate(static_cast<int>(tile), u)) return false;
-      const int ks = static_cast<int>(lin % splitk);
+      const int tile = lin / splitk;
+      if (lin < 0 || !locate(tile, u)) return false;
+      const int ks = lin - tile * splitk;
       lin += lin_step;
       u.kb0 = ks * kb_per;
       u.kb1 = min_i(kblocks, u.kb0 + kb_per);
@@ -155,25 +160,25 @@ struct WorkWalker {
       return true;
     }
     if (it >= it_end) return false;
-    const long long rtile = it / kblocks;          // tile index inside the remainder
-    if (!locate(tile0 + static_cast<int>(rtile), u)) return false;
-    const long long t0 = rtile * kblocks, t1 = t0 + kblocks;
+    const int rtile = it / kblocks;                // tile index inside the remainder
+    if (!locate(tile0 + rtile, u)) return false;
+    const int t0 = rtile * kblocks, t1 = t0 + kblocks;
     const bool first_unit = (it == it_begin);
-    u.kb0 = static_cast<int>(it - t0);
-    const long long end = it_end < t1 ? it_end : t1;
-    u.kb1 = static_cast<int>(end - t0);
+    u.kb0 = it - t0;
+    const int end = it_end < t1 ? it_end : t1;
+    u.kb1 = end - t0;
     it = end;
     u.c_first = owner(t0);
     u.ncontrib = owner(t1 - 1) - u.c_first + 1;
-    u.slot = static_cast<long long>(cta) * 2 + (first_unit ? 0 : 1);
+    u.slot = cta * 2 + (first_unit ? 0 : 1);
     return true;
   }
 
   // Workspace slot of contributor j (0 <= j < ncontrib) of unit u's tile.
-  DMOE_HD long long contrib_slot(const WorkUnit& u, int j) const {
-    if (!streamk) return static_cast<long long>(u.tile) * splitk + j;
-    const long long c = u.c_first + j;
-    const long long first_tile = tile0 + share_begin(c) / kblocks;   // the tile CTA c's share starts in: its slot 0
+  DMOE_HD int contrib_slot(const WorkUnit& u, int j) const {
+    if (!streamk) return u.tile * splitk + j;
+    const int c = u.c_first + j;
+    const int first_tile = tile0 + share_begin(c) / kblocks;   // the tile CTA c's share starts in: its slot 0
     return c * 2 + (first_tile == u.tile ? 0 : 1);
   }
 };
