@@ -259,9 +259,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
     if (lane == 0) {
       WorkWalker tw;
       tw.init(s_start, s_cnt, a.G, S, MT, BN, kblocks, a.splitk, a.streamk, work_cta, work_grid);
+      trace_stamp(a, 13);
       if (a.n_wait > 0) asm volatile("fence.proxy.async;" ::: "memory");  // peers' generic stores -> TMA reads
       const uint64_t pol_w = l2_policy_evict_first();
       const uint64_t pol_x = l2_policy_evict_last();
+      trace_stamp(a, 14);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -279,6 +281,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
         const int kb0 = u.kb0, kb1 = u.kb1;
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_word, bar_budget)) { ok = false; break; }
+          if (a.trace != nullptr && !traced) trace_stamp(a, 15);
           // pair mode: the bytes of both CTAs are counted on the even CTA's barrier, which its producer arms
           const uint32_t fb = PAIR ? mapa_rank(smem_u32(&full_bar[stage]), 0) : smem_u32(&full_bar[stage]);
           uint8_t* st = smem + stage * C::kStageBytes;
@@ -587,33 +590,85 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
               pp[3] = __floats2bfloat162_rn(x1[q].z, x1[q].w);
               if (j < jmax) *reinterpret_cast<uint4*>(ybase + static_cast<long long>(j) * a.ldy) = pk;
             }
-          } else if (f0 < a.F) {                     // F is a multiple of 8 on this path
-            // QKV epilogue geometry: a 128-feature tile holds whole heads (hd = 64 or 128), so the rotation partner
-            // of a feature (d +- hd / 2) sits in the same shared-memory chunk
-            const bool rope = a.rope_table != nullptr;
-            const int half = a.hd >> 1;
-            const int d0 = rope ? f0 % a.hd : 0;               // first of this thread's 8 features inside its head
-            const int head = rope ? f0 / a.hd : 0;
-            const bool rot = rope && head < a.n_q + a.n_kv;
-            const bool lower = d0 < half;
-            const int pf = fg * 8 + (lower ? half : -half);     // partner features inside the tile
+          } else if (f0 < a.F && a.rope_table == nullptr) {
+            // residual / fp32 output / reduce-scatter variants, each as four independent load -> combine -> store
+            // chains: the variant is chosen outside the loops, stores are predicated on the token being valid
+            float o[4][8];
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
               const int j = tk0 + q * 8;
-              if (j >= jmax) continue;
-              const long long t = tok_base + c * 32 + j;
               const float4 x0 = *reinterpret_cast<const float4*>(&epi_stage[j * kBM + fg * 8]);
               const float4 x1 = *reinterpret_cast<const float4*>(&epi_stage[j * kBM + fg * 8 + 4]);
-              float o[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
-              if (a.R != nullptr) {
+              o[q][0] = x0.x; o[q][1] = x0.y; o[q][2] = x0.z; o[q][3] = x0.w;
+              o[q][4] = x1.x; o[q][5] = x1.y; o[q][6] = x1.z; o[q][7] = x1.w;
+            }
+            if (a.R != nullptr) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
                 const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&rr[q]);
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                   const float2 rf = __bfloat1622float2(rp[i]);
-                  o[2 * i] += rf.x;
-                  o[2 * i + 1] += rf.y;
+                  o[q][2 * i] += rf.x;
+                  o[q][2 * i + 1] += rf.y;
                 }
               }
+            }
+            if (a.y_f32) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const int j = tk0 + q * 8;
+                float* yp = reinterpret_cast<float*>(a.Y) + (tok_base + c * 32 + j) * a.ldy + f0;
+                if (j < jmax) {
+                  *reinterpret_cast<float4*>(yp) = make_float4(o[q][0], o[q][1], o[q][2], o[q][3]);
+                  *reinterpret_cast<float4*>(yp + 4) = make_float4(o[q][4], o[q][5], o[q][6], o[q][7]);
+                }
+              }
+            } else {
+              __nv_bfloat16* dst[4];
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const int j = tk0 + q * 8;
+                const long long t = tok_base + c * 32 + j;
+                if (a.rs_bases != nullptr) {
+                  // reduce-scatter: the row goes to slot rs_slot of the partial buffer of the rank that owns it
+                  const int tt = j < jmax ? static_cast<int>(t) : tok_base;      // keep the table index in range
+                  const int owner = tt / a.rs_rows;
+                  const long long lrow = static_cast<long long>(a.rs_slot) * a.rs_cap + (tt - owner * a.rs_rows);
+                  dst[q] = static_cast<__nv_bfloat16*>(a.rs_bases[owner]) + lrow * a.ldy + f0;
+                } else {
+                  dst[q] = reinterpret_cast<__nv_bfloat16*>(a.Y) + t * a.ldy + f0;
+                }
+              }
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                uint4 pk;
+                __nv_bfloat162* pp = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) pp[i] = __floats2bfloat162_rn(o[q][2 * i], o[q][2 * i + 1]);
+                if (tk0 + q * 8 < jmax) *reinterpret_cast<uint4*>(dst[q]) = pk;
+              }
+            }
+          } else if (f0 < a.F) {
+            // QKV epilogue: neox RoPE on the q and k heads, q to Y, K / V into the paged cache. A 128-feature tile
+            // holds whole heads (hd = 64 or 128), so the rotation partner of a feature (d +- hd / 2) sits in the same
+            // shared-memory chunk. Everything that depends on the thread's features only is computed once.
+            const int half = a.hd >> 1;
+            const int d0 = f0 % a.hd;                          // first of this thread's 8 features inside its head
+            const int head = f0 / a.hd;
+            const bool rot = head < a.n_q + a.n_kv;
+            const bool lower = d0 < half;
+            const int pf = fg * 8 + (lower ? half : -half);     // partner features inside the tile
+            const int kvh = head - a.n_q;
+            __nv_bfloat16* const cache = kvh < a.n_kv ? a.kcache : a.vcache;
+            const int hh = kvh < a.n_kv ? kvh : kvh - a.n_kv;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const int j = tk0 + q * 8;
+              const long long t = tok_base + c * 32 + j;
+              const float4 x0 = *reinterpret_cast<const float4*>(&epi_stage[j * kBM + fg * 8]);
+              const float4 x1 = *reinterpret_cast<const float4*>(&epi_stage[j * kBM + fg * 8 + 4]);
+              float o[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
               if (rot) {
                 const float4 p0 = *reinterpret_cast<const float4*>(&epi_stage[j * kBM + pf]);
                 const float4 p1 = *reinterpret_cast<const float4*>(&epi_stage[j * kBM + pf + 4]);
@@ -632,34 +687,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
                   o[2 * i + 1] = lower ? a1 * v.z - b1 * v.w : a1 * v.z + b1 * v.w;
                 }
               }
-              if (a.y_f32) {
-                float* yp = reinterpret_cast<float*>(a.Y) + t * a.ldy + f0;
-                *reinterpret_cast<float4*>(yp) = make_float4(o[0], o[1], o[2], o[3]);
-                *reinterpret_cast<float4*>(yp + 4) = make_float4(o[4], o[5], o[6], o[7]);
-              } else {
-                uint4 pk;
-                __nv_bfloat162* pp = reinterpret_cast<__nv_bfloat162*>(&pk);
+              uint4 pk;
+              __nv_bfloat162* pp = reinterpret_cast<__nv_bfloat162*>(&pk);
 #pragma unroll
-                for (int i = 0; i < 4; ++i) pp[i] = __floats2bfloat162_rn(o[2 * i], o[2 * i + 1]);
-                if (rope) {
-                  if (head < a.n_q) {
-                    *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.Y) + t * a.ldy + f0) = pk;
-                  } else {
-                    const long long slot = slot4[q];
-                    if (slot >= 0) {
-                      const int kvh = head - a.n_q;
-                      __nv_bfloat16* cache = kvh < a.n_kv ? a.kcache : a.vcache;
-                      const int hh = kvh < a.n_kv ? kvh : kvh - a.n_kv;
-                      *reinterpret_cast<uint4*>(cache + (slot * a.n_kv + hh) * a.hd + d0) = pk;
-                    }
-                  }
-                } else if (a.rs_bases != nullptr) {
-                  const int owner = static_cast<int>(t) / a.rs_rows;
-                  const long long lrow = static_cast<long long>(a.rs_slot) * a.rs_cap + (static_cast<int>(t) - owner * a.rs_rows);
-                  *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(a.rs_bases[owner]) + lrow * a.ldy + f0) = pk;
-                } else {
-                  *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.Y) + t * a.ldy + f0) = pk;
-                }
+              for (int i = 0; i < 4; ++i) pp[i] = __floats2bfloat162_rn(o[2 * i], o[2 * i + 1]);
+              if (head < a.n_q) {
+                if (j < jmax) *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.Y) + t * a.ldy + f0) = pk;
+              } else {
+                const long long slot = slot4[q];
+                if (j < jmax && slot >= 0) *reinterpret_cast<uint4*>(cache + (slot * a.n_kv + hh) * a.hd + d0) = pk;
               }
             }
           }
@@ -671,35 +707,43 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
         if (EPI == EPI_COMBINE && a.epi_vec != 0) {
           if (jmax <= 0) continue;                   // uniform over the CTA
           // same transposition as the plain epilogue: thread (token lane, 8 features) scales its 8 values by the
-          // row's router weight and stores 16 bytes into the destination row named by the record
+          // row's router weight and stores 16 bytes into the destination row named by the record. The four records
+          // of the thread are requested before the transposition, so that their latency overlaps it.
+          const int fg = et & 15, tk0 = et >> 4;
+          const int f0 = m * kBM + fg * 8;
+          int4 rec4[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const int j = tk0 + q * 8;
+            rec4[q] = (j < jmax) ? __ldg(&a.recs[tok_base + c * 32 + j]) : make_int4(0, -1, 0, 0);
+          }
 #pragma unroll
           for (int j = 0; j < 32; ++j) epi_stage[j * kBM + row] = acc[j];
           named_bar_sync(1, kEpiThreads);
-          const int fg = et & 15, tk0 = et >> 4;
-          const int f0 = m * kBM + fg * 8;
           if (f0 < a.F) {
+            uint4 pk[4];
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
               const int j = tk0 + q * 8;
-              if (j >= jmax) continue;
-              const int4 rec = __ldg(&a.recs[tok_base + c * 32 + j]);
-              if (rec.y < 0) continue;
-              const float w = __int_as_float(rec.z);
+              const float w = __int_as_float(rec4[q].z);
               const float4 x0 = *reinterpret_cast<const float4*>(&epi_stage[j * kBM + fg * 8]);
               const float4 x1 = *reinterpret_cast<const float4*>(&epi_stage[j * kBM + fg * 8 + 4]);
-              uint4 pk;
-              __nv_bfloat162* pp = reinterpret_cast<__nv_bfloat162*>(&pk);
+              __nv_bfloat162* pp = reinterpret_cast<__nv_bfloat162*>(&pk[q]);
               pp[0] = __floats2bfloat162_rn(x0.x * w, x0.y * w);
               pp[1] = __floats2bfloat162_rn(x0.z * w, x0.w * w);
               pp[2] = __floats2bfloat162_rn(x1.x * w, x1.y * w);
               pp[3] = __floats2bfloat162_rn(x1.z * w, x1.w * w);
-              const long long off = static_cast<long long>(rec.y) * a.ldy + f0;
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              if (rec4[q].y < 0) continue;
+              const long long off = static_cast<long long>(rec4[q].y) * a.ldy + f0;
               if (a.fanout <= 1) {
-                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.bases[rec.x]) + off) = pk;
+                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.bases[rec4[q].x]) + off) = pk[q];
               } else {
-                const int g0 = rec.x / a.fanout * a.fanout;
+                const int g0 = rec4[q].x / a.fanout * a.fanout;
                 for (int i = 0; i < a.fanout; ++i)
-                  *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.bases[g0 + i]) + off) = pk;
+                  *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.bases[g0 + i]) + off) = pk[q];
               }
             }
           }
