@@ -73,9 +73,9 @@ typedef struct DmoeGemm {
   // != 0: W is stored tile by tile, [group][128-row tile][K / 64][128][64] (see ops/gemm.py: block_weight), so that
   // every 16 KB box the kernel fetches is one contiguous run of HBM; needs F % 128 == 0 and K % 64 == 0
   int w_blocked;
-  // profiling aid, normally null: 8 x uint64 of device memory that CTA 0 fills with %globaltimer stamps (entry, set-up
+  // profiling aid, normally null: 16 x uint64 of device memory that CTA 0 fills with %globaltimer stamps (entry, set-up
   // done, first TMA issued, first stage landed, last MMA committed, accumulator seen by the epilogue, epilogue done,
-  // tear-down reached)
+  // tear-down reached, then five points inside the first epilogue chunk and three inside the producer's start)
   void* trace;
 } DmoeGemm;
 

@@ -99,7 +99,7 @@ struct GemmArgs {
   // optional [16] nanosecond stamps written by CTA 0 (a profiling aid, null in normal launches): 0 entry, 1 set-up done,
   // 2 first TMA issued, 3 first stage landed, 4 last MMA committed, 5 accumulator seen by the epilogue, 6 epilogue done,
   // 7 tear-down reached; 8-12 inside the first epilogue chunk: TMEM read done, staged to shared memory, barrier passed,
-  // rows stored, second barrier passed
+  // rows stored, second barrier passed; 13-15 in the producer: work walker initialised, L2 policies made, first stage free
   unsigned long long* trace;
 };
 
@@ -511,6 +511,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
             uint32_t uu[32];
             tmem_ld32(t0 + BN + c * 32, uu);
             tmem_ld_wait();
+            if (et == 0 && c == 0) trace_stamp(a, 8);
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               const float g = __uint_as_float(v[j]);
