@@ -40,6 +40,15 @@ __device__ __forceinline__ int ld_acquire_sys_s(const int* p) {
   asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
+// Requests `bytes` at `p` into L2 (the whole CTA takes part, one 128-byte line per thread and round): used for what a
+// kernel will need AFTER its flag wait and does not depend on it (weights, this CTA's residual row), so that the HBM
+// latency of those reads overlaps the wait instead of following it.
+__device__ __forceinline__ void cta_prefetch_l2(const void* p, long long bytes) {
+  const char* c = static_cast<const char*>(p);
+  for (long long off = static_cast<long long>(threadIdx.x) * 128; off < bytes; off += static_cast<long long>(blockDim.x) * 128)
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(c + off));
+}
+
 __device__ __forceinline__ float warp_sum_s(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -115,6 +124,8 @@ struct NormGatherArgs {
 __global__ void __launch_bounds__(kSendThreads) norm_gather_kernel(const NormGatherArgs a) {
   __shared__ float red[32];
   const int want = a.n_wait > 0 ? *a.wait_epoch + 1 : 0;
+  cta_prefetch_l2(a.w, static_cast<long long>(a.H) * 2);
+  if (a.resid_in != nullptr && blockIdx.x < a.T) cta_prefetch_l2(a.resid_in + blockIdx.x * a.ld_in, static_cast<long long>(a.H) * 2);
   cta_wait_flags(a.wait_flags, a.n_wait, want, a.status, a.max_cycles);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = kSendThreads / 32;
   const int nvec = a.H / 8;
@@ -236,6 +247,9 @@ __global__ void __launch_bounds__(kSendThreads) route_dispatch_kernel(const Rout
   __shared__ float s_wt[kSendMaxTopK];
   __shared__ long long s_row[kSendMaxTopK];  // destination row (-1: dropped)
   const int want = a.n_wait > 0 ? *a.wait_epoch + 1 : 0;
+  if (a.gate_w != nullptr) cta_prefetch_l2(a.gate_w, static_cast<long long>(a.E) * a.H * 2);
+  cta_prefetch_l2(a.norm_w, static_cast<long long>(a.H) * 2);
+  if (blockIdx.x < a.T) cta_prefetch_l2(a.resid + blockIdx.x * a.ld_resid, static_cast<long long>(a.H) * 2);
   cta_wait_flags(a.wait_flags, a.n_wait, want, a.status, a.max_cycles);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = kSendThreads / 32;
   const int nvec = a.H / 8;
