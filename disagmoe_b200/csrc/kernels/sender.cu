@@ -124,7 +124,7 @@ struct NormGatherArgs {
 __global__ void __launch_bounds__(kSendThreads) norm_gather_kernel(const NormGatherArgs a) {
   __shared__ float red[32];
   const int want = a.n_wait > 0 ? *a.wait_epoch + 1 : 0;
-  cta_prefetch_l2(a.w, static_cast<long long>(a.H) * 2);
+  if (blockIdx.x == 0) cta_prefetch_l2(a.w, static_cast<long long>(a.H) * 2);
   if (a.resid_in != nullptr && blockIdx.x < a.T) cta_prefetch_l2(a.resid_in + blockIdx.x * a.ld_in, static_cast<long long>(a.H) * 2);
   cta_wait_flags(a.wait_flags, a.n_wait, want, a.status, a.max_cycles);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = kSendThreads / 32;
@@ -247,8 +247,13 @@ __global__ void __launch_bounds__(kSendThreads) route_dispatch_kernel(const Rout
   __shared__ float s_wt[kSendMaxTopK];
   __shared__ long long s_row[kSendMaxTopK];  // destination row (-1: dropped)
   const int want = a.n_wait > 0 ? *a.wait_epoch + 1 : 0;
-  if (a.gate_w != nullptr) cta_prefetch_l2(a.gate_w, static_cast<long long>(a.E) * a.H * 2);
-  cta_prefetch_l2(a.norm_w, static_cast<long long>(a.H) * 2);
+  if (a.gate_w != nullptr && blockIdx.x < 16) {
+    // the gate matrix is shared by all CTAs: the first 16 request one sixteenth each
+    const long long slice = (static_cast<long long>(a.E) * a.H * 2 + 15) / 16;
+    cta_prefetch_l2(reinterpret_cast<const char*>(a.gate_w) + blockIdx.x * slice,
+                    min(slice, static_cast<long long>(a.E) * a.H * 2 - blockIdx.x * slice));
+  }
+  if (blockIdx.x == 16 % gridDim.x) cta_prefetch_l2(a.norm_w, static_cast<long long>(a.H) * 2);
   if (blockIdx.x < a.T) cta_prefetch_l2(a.resid + blockIdx.x * a.ld_resid, static_cast<long long>(a.H) * 2);
   cta_wait_flags(a.wait_flags, a.n_wait, want, a.status, a.max_cycles);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = kSendThreads / 32;
