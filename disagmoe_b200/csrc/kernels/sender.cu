@@ -20,6 +20,8 @@
 // disagmoe/models/linear.py:1064-1089 / csrc/muhelper/comm.cpp:399-416, the broadcast of a TP group's inputs
 // disagmoe/frontend/engine.py:494-535, and the dispatch path disagmoe/frontend/engine.py:667-677 +
 // csrc/muhelper/muhelper.cpp:189-228.
+#include <stdlib.h>
+
 #include "dmoe_kernels.h"
 #include "sm100.cuh"
 
@@ -119,13 +121,14 @@ struct NormGatherArgs {
   int* ticket;
   int* status;
   long long max_cycles;
+  int prefetch;
 };
 
 __global__ void __launch_bounds__(kSendThreads) norm_gather_kernel(const NormGatherArgs a) {
   __shared__ float red[32];
   const int want = a.n_wait > 0 ? *a.wait_epoch + 1 : 0;
-  if (blockIdx.x == 0) cta_prefetch_l2(a.w, static_cast<long long>(a.H) * 2);
-  if (a.resid_in != nullptr && blockIdx.x < a.T) cta_prefetch_l2(a.resid_in + blockIdx.x * a.ld_in, static_cast<long long>(a.H) * 2);
+  if (a.prefetch && blockIdx.x == 0) cta_prefetch_l2(a.w, static_cast<long long>(a.H) * 2);
+  if (a.prefetch && a.resid_in != nullptr && blockIdx.x < a.T) cta_prefetch_l2(a.resid_in + blockIdx.x * a.ld_in, static_cast<long long>(a.H) * 2);
   cta_wait_flags(a.wait_flags, a.n_wait, want, a.status, a.max_cycles);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = kSendThreads / 32;
   const int nvec = a.H / 8;
@@ -237,6 +240,7 @@ struct RouteDispatchArgs {
   int* ticket;
   int* status;
   long long max_cycles;
+  int prefetch;
 };
 
 __global__ void __launch_bounds__(kSendThreads) route_dispatch_kernel(const RouteDispatchArgs a) {
@@ -247,14 +251,14 @@ __global__ void __launch_bounds__(kSendThreads) route_dispatch_kernel(const Rout
   __shared__ float s_wt[kSendMaxTopK];
   __shared__ long long s_row[kSendMaxTopK];  // destination row (-1: dropped)
   const int want = a.n_wait > 0 ? *a.wait_epoch + 1 : 0;
-  if (a.gate_w != nullptr && blockIdx.x < 16) {
+  if (a.prefetch && a.gate_w != nullptr && blockIdx.x < 16) {
     // the gate matrix is shared by all CTAs: the first 16 request one sixteenth each
     const long long slice = (static_cast<long long>(a.E) * a.H * 2 + 15) / 16;
     cta_prefetch_l2(reinterpret_cast<const char*>(a.gate_w) + blockIdx.x * slice,
                     min(slice, static_cast<long long>(a.E) * a.H * 2 - blockIdx.x * slice));
   }
-  if (blockIdx.x == 16 % gridDim.x) cta_prefetch_l2(a.norm_w, static_cast<long long>(a.H) * 2);
-  if (blockIdx.x < a.T) cta_prefetch_l2(a.resid + blockIdx.x * a.ld_resid, static_cast<long long>(a.H) * 2);
+  if (a.prefetch && blockIdx.x == 16 % gridDim.x) cta_prefetch_l2(a.norm_w, static_cast<long long>(a.H) * 2);
+  if (a.prefetch && blockIdx.x < a.T) cta_prefetch_l2(a.resid + blockIdx.x * a.ld_resid, static_cast<long long>(a.H) * 2);
   cta_wait_flags(a.wait_flags, a.n_wait, want, a.status, a.max_cycles);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = kSendThreads / 32;
   const int nvec = a.H / 8;
@@ -469,6 +473,15 @@ __global__ void ids_gather_kernel(const int* __restrict__ src, int n, int* const
 
 using namespace dmoe;
 
+// DMOE_SENDER_PREFETCH=0 turns the L2 prefetches of the sender kernels off (read once per process)
+static int sender_prefetch() {
+  static const int v = [] {
+    const char* e = getenv("DMOE_SENDER_PREFETCH");
+    return (e != nullptr && e[0] == '0') ? 0 : 1;
+  }();
+  return v;
+}
+
 extern "C" int dmoe_norm_gather(const DmoeNormGather* d, void* stream) {
   if (d->H % 8 != 0 || d->H > kSendThreads * kSendMaxVec * 8 || d->T < 0 || d->n_dst < 1 || d->n_dst > kSendMaxDst ||
       d->dst_ptrs == nullptr || d->w == nullptr || d->n_wait < 0 || d->n_wait > kSendThreads || d->n_signal < 0)
@@ -487,7 +500,7 @@ extern "C" int dmoe_norm_gather(const DmoeNormGather* d, void* stream) {
   a.T = d->T; a.H = d->H;
   a.wait_flags = d->wait_flags; a.n_wait = d->n_wait; a.wait_epoch = d->wait_epoch;
   a.signal_ptrs = reinterpret_cast<int* const*>(d->signal_ptrs); a.n_signal = d->n_signal; a.signal_slot = d->signal_slot;
-  a.signal_epoch = d->signal_epoch; a.ticket = d->ticket; a.status = d->status; a.max_cycles = g_dmoe_flag_wait_cycles;
+  a.signal_epoch = d->signal_epoch; a.ticket = d->ticket; a.status = d->status; a.max_cycles = g_dmoe_flag_wait_cycles; a.prefetch = sender_prefetch();
   // an empty shard still takes part in the hand-shake (it waits, signals and advances its epochs)
   const int grid = d->T > 0 ? d->T : 1;
   norm_gather_kernel<<<grid, kSendThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
@@ -524,7 +537,7 @@ extern "C" int dmoe_route_dispatch(const DmoeRouteDispatch* d, void* stream) {
   a.rec_bases = static_cast<void* const*>(d->rec_bases); a.cnt_bases = static_cast<int* const*>(d->cnt_bases);
   a.flag_bases = static_cast<int* const*>(d->flag_bases); a.disp_epoch = d->disp_epoch;
   a.wait_flags = d->wait_flags; a.n_wait = d->n_wait; a.wait_epoch = d->wait_epoch;
-  a.ticket = (send || d->n_wait > 0) ? d->ticket : nullptr; a.status = d->status; a.max_cycles = g_dmoe_flag_wait_cycles;
+  a.ticket = (send || d->n_wait > 0) ? d->ticket : nullptr; a.status = d->status; a.max_cycles = g_dmoe_flag_wait_cycles; a.prefetch = sender_prefetch();
   const int grid = d->T > 0 ? d->T : 1;   // an empty slice still publishes its flags
   route_dispatch_kernel<<<grid, kSendThreads, d->H * sizeof(float), static_cast<cudaStream_t>(stream)>>>(a);
   return static_cast<int>(cudaGetLastError());
