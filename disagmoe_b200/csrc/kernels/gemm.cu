@@ -791,8 +791,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
   if (a.done_ticket != nullptr && warp >= 2) {
     // every epilogue thread makes its (possibly remote) stores visible system-wide, then the CTA takes a ticket.
     // The last CTA of the grid publishes this call's epoch to every destination and advances the gate's epoch
-    // (by then every CTA has long read it).
-    __threadfence_system();
+    // (by then every CTA has long read it). A launch that signals nobody (it only advances its gate's epoch) has
+    // nothing to publish: its output is consumed in stream order.
+    if (a.n_signal > 0) __threadfence_system();
     named_bar_sync(1, kEpiThreads);
     if (threadIdx.x == 64) {
       const int old = atomicAdd(a.done_ticket, 1);
