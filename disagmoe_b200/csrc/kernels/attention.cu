@@ -107,6 +107,8 @@ paged_attn_kernel(const __nv_bfloat16* __restrict__ q, long long ld_q, const __n
   __shared__ float s_l[kAttnWarps][8];
   extern __shared__ __align__(128) uint8_t s_dyn[];  // per-warp rings; reused as [warps][GQ][HD] floats at the end
 
+  pdl_trigger();
+  pdl_wait();      // q, the new K / V rows and the sequence tables come from the kernels before this one
   const int t = blockIdx.x, hkv = blockIdx.y, split = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, tq = lane & 3;            // accumulator row / column-pair of this lane
@@ -496,11 +498,10 @@ static int launch_attn(const void* q, long long ld_q, const void* kc, const void
   });
   if (crc != 0) return crc;
   dim3 grid(T, n_kv, splits);
-  paged_attn_kernel<HD, GQ><<<grid, kAttnThreads, smem, stream>>>(
+  cudaError_t e = launch_kernel(paged_attn_kernel<HD, GQ>, grid, dim3(kAttnThreads), smem, stream,
       static_cast<const __nv_bfloat16*>(q), ld_q, static_cast<const __nv_bfloat16*>(kc),
       static_cast<const __nv_bfloat16*>(vc), bt, max_blocks, bt_row, ctx_len, block_size, n_kv,
       scale * 1.4426950408889634f, splits, static_cast<__nv_bfloat16*>(out), ld_out, part_o, part_lse);
-  cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return static_cast<int>(e);
   if (splits > 1) {
     dim3 g2(T, n_kv * GQ);

@@ -177,6 +177,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
   // the producer may legitimately sit in a peer-flag wait (all-gather prologue): the warps behind it must outlast it
   const long long bar_budget = DMOE_WAIT_CYCLES + (a.shard_rows > 0 ? a.flag_cycles : 0);
 
+  pdl_trigger();
   if (threadIdx.x == 0) {
     trace_stamp(a, 0);
     *abort_word = 0;
@@ -194,6 +195,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
     tma_prefetch_desc(&tmW);
     tma_prefetch_desc(&tmX);
   }
+  pdl_wait();      // nothing above reads global data; everything below may read what the previous kernel wrote
   if (a.n_wait > 0 && a.shard_rows == 0) {
     // arrival gate: the senders' rows, counts and records are complete once their flag carries this call's epoch
     if (threadIdx.x < a.n_wait) {
@@ -879,8 +881,8 @@ static int launch(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmArgs
     int grid = num_sms();
     if (max_tiles < grid) grid = max_tiles;
     if (grid < 1) grid = 1;
-    gemm_kernel<BN, EPI, false><<<grid, kThreads, C::kSmemBytes, stream>>>(tmW, tmX, a);
-    return static_cast<int>(cudaGetLastError());
+    return static_cast<int>(launch_kernel(gemm_kernel<BN, EPI, false>, dim3(grid), dim3(kThreads), C::kSmemBytes, stream,
+                                          tmW, tmX, a));
   }
   // one cluster of two CTAs (two SMs of a TPC) per work tile
   int pairs = num_sms() / 2;

@@ -126,8 +126,10 @@ struct NormGatherArgs {
 
 __global__ void __launch_bounds__(kSendThreads) norm_gather_kernel(const NormGatherArgs a) {
   __shared__ float red[32];
-  const int want = a.n_wait > 0 ? *a.wait_epoch + 1 : 0;
+  pdl_trigger();
   if (a.prefetch && blockIdx.x == 0) cta_prefetch_l2(a.w, static_cast<long long>(a.H) * 2);
+  pdl_wait();
+  const int want = a.n_wait > 0 ? *a.wait_epoch + 1 : 0;
   if (a.prefetch && a.resid_in != nullptr && blockIdx.x < a.T) cta_prefetch_l2(a.resid_in + blockIdx.x * a.ld_in, static_cast<long long>(a.H) * 2);
   cta_wait_flags(a.wait_flags, a.n_wait, want, a.status, a.max_cycles);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = kSendThreads / 32;
@@ -250,7 +252,7 @@ __global__ void __launch_bounds__(kSendThreads) route_dispatch_kernel(const Rout
   __shared__ int s_sel[kSendMaxTopK];        // chosen experts
   __shared__ float s_wt[kSendMaxTopK];
   __shared__ long long s_row[kSendMaxTopK];  // destination row (-1: dropped)
-  const int want = a.n_wait > 0 ? *a.wait_epoch + 1 : 0;
+  pdl_trigger();
   if (a.prefetch && a.gate_w != nullptr && blockIdx.x < 16) {
     // the gate matrix is shared by all CTAs: the first 16 request one sixteenth each
     const long long slice = (static_cast<long long>(a.E) * a.H * 2 + 15) / 16;
@@ -258,6 +260,8 @@ __global__ void __launch_bounds__(kSendThreads) route_dispatch_kernel(const Rout
                     min(slice, static_cast<long long>(a.E) * a.H * 2 - blockIdx.x * slice));
   }
   if (a.prefetch && blockIdx.x == 16 % gridDim.x) cta_prefetch_l2(a.norm_w, static_cast<long long>(a.H) * 2);
+  pdl_wait();
+  const int want = a.n_wait > 0 ? *a.wait_epoch + 1 : 0;
   if (a.prefetch && blockIdx.x < a.T) cta_prefetch_l2(a.resid + blockIdx.x * a.ld_resid, static_cast<long long>(a.H) * 2);
   cta_wait_flags(a.wait_flags, a.n_wait, want, a.status, a.max_cycles);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = kSendThreads / 32;
@@ -503,7 +507,8 @@ extern "C" int dmoe_norm_gather(const DmoeNormGather* d, void* stream) {
   a.signal_epoch = d->signal_epoch; a.ticket = d->ticket; a.status = d->status; a.max_cycles = g_dmoe_flag_wait_cycles; a.prefetch = sender_prefetch();
   // an empty shard still takes part in the hand-shake (it waits, signals and advances its epochs)
   const int grid = d->T > 0 ? d->T : 1;
-  norm_gather_kernel<<<grid, kSendThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  if (launch_kernel(norm_gather_kernel, dim3(grid), dim3(kSendThreads), 0, static_cast<cudaStream_t>(stream), a) != cudaSuccess)
+    return static_cast<int>(cudaGetLastError());
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -539,7 +544,9 @@ extern "C" int dmoe_route_dispatch(const DmoeRouteDispatch* d, void* stream) {
   a.wait_flags = d->wait_flags; a.n_wait = d->n_wait; a.wait_epoch = d->wait_epoch;
   a.ticket = (send || d->n_wait > 0) ? d->ticket : nullptr; a.status = d->status; a.max_cycles = g_dmoe_flag_wait_cycles; a.prefetch = sender_prefetch();
   const int grid = d->T > 0 ? d->T : 1;   // an empty slice still publishes its flags
-  route_dispatch_kernel<<<grid, kSendThreads, d->H * sizeof(float), static_cast<cudaStream_t>(stream)>>>(a);
+  if (launch_kernel(route_dispatch_kernel, dim3(grid), dim3(kSendThreads), d->H * sizeof(float),
+                    static_cast<cudaStream_t>(stream), a) != cudaSuccess)
+    return static_cast<int>(cudaGetLastError());
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -9,6 +9,10 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <utility>
 
 namespace dmoe {
 
@@ -296,6 +300,44 @@ struct PerDeviceOnce {
     return rc;
   }
 };
+
+// ---------------------------------------------------------------- programmatic dependent launch
+// With DMOE_PDL=1 the per-layer kernels are launched with the programmatic-stream-serialization attribute: a kernel
+// may become resident (and run the part of its prologue that touches no global data) while its predecessor in the
+// stream is still draining. Every such kernel calls pdl_trigger() first (its own successor may start early too) and
+// pdl_wait() before it reads anything a predecessor wrote; pdl_wait() returns once the predecessor grid has completed
+// and its writes are visible. Without the attribute both are no-ops.
+inline bool pdl_enabled() {
+  static const bool v = [] {
+    const char* e = getenv("DMOE_PDL");
+    return e != nullptr && e[0] == '1';
+  }();
+  return v;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 Args&&... args) {
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if (pdl_enabled()) {
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
+#if defined(__CUDACC__)
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#endif
 
 // Number of SMs of the current device (cached per device).
 inline int device_num_sms() {
