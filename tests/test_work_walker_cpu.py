@@ -45,3 +45,20 @@ def test_tile_blocked_weight_layout_round_trip_and_box_order():
         assert torch.equal(box, w[g, m * 128:(m + 1) * 128, kb * 64:(kb + 1) * 64])
     w2 = torch.randn(128, 64)
     assert torch.equal(gemm.block_weight(w2), w2)       # a single box is already in order
+
+
+def test_stream_k_policy_follows_the_measured_operating_points():
+    """want_streamk: never for the SwiGLU up-projection (two accumulators per partial tile); for the down-projection
+    only where the expected tiles fill the last wave badly (2 local experts at decode sizes), not at 8 experts x 64."""
+    from disagmoe_b200.ops import gemm
+    H, I, sms = 4096, 14336, 148
+    assert not gemm.want_streamk(gemm.EPI_SWIGLU, I, 2, 128, 128, sms)
+    assert gemm.want_streamk(gemm.EPI_COMBINE, H, 2, 128, 128, sms)        # 64 tiles on 148 SMs
+    assert gemm.want_streamk(gemm.EPI_COMBINE, H, 2, 512, 256, sms)
+    assert not gemm.want_streamk(gemm.EPI_COMBINE, H, 8, 512, 128, sms)    # 256 tiles: 0.86 of two waves
+    old = gemm.STREAM_K
+    try:
+        gemm.STREAM_K = False
+        assert not gemm.want_streamk(gemm.EPI_COMBINE, H, 2, 128, 128, sms)
+    finally:
+        gemm.STREAM_K = old
