@@ -165,6 +165,9 @@ typedef struct DmoeRouteDispatch {
   long long ld_resid, add_slot_stride, ld_add, ld_y, ld_dst;
   float eps;
   int n_add, T, H, E, K, renorm, experts_per_rank, n_dst, my_rank, region_cap, n_wait;
+  // rank written into the records as the owner the experts return the rows to, where that is not the sender itself
+  // (pipeline-parallel attention: the stage that owns the next layer); 0 with ret_rank_set == 0 means my_rank
+  int ret_rank, ret_rank_set;
 } DmoeRouteDispatch;
 int dmoe_route_dispatch(const DmoeRouteDispatch* desc, void* stream);
 // dst_ptrs[d][dst0 + i] = src[i] (i < n) for every d < n_dst, then signal_ptrs[d][signal_slot] = *signal_epoch + 1.

@@ -230,6 +230,7 @@ struct RouteDispatchArgs {
   float* topk_w;                   // optional [T, K]
   // dispatch
   int experts_per_rank, n_dst, my_rank, region_cap;
+  int ret_rank;                    // rank named in the records (the rows' owner for the experts' combine)
   void* const* x_bases;            // [n_dst] receive rows ([experts_per_rank * region_cap, H] bf16)
   long long ld_dst;
   void* const* rec_bases;          // [n_dst] records (int4 per row)
@@ -422,7 +423,7 @@ __global__ void __launch_bounds__(kSendThreads) route_dispatch_kernel(const Rout
             } else {
               row = static_cast<long long>(le) * a.region_cap + slot;
               int4 rec;
-              rec.x = a.my_rank;
+              rec.x = a.ret_rank;
               rec.y = static_cast<int>(p);     // row of the pair in this rank's [T, K, H] partial-output buffer
               rec.z = __float_as_int(w);
               rec.w = e;
@@ -538,6 +539,7 @@ extern "C" int dmoe_route_dispatch(const DmoeRouteDispatch* d, void* stream) {
   a.T = d->T; a.H = d->H; a.E = d->E; a.K = d->K; a.renorm = d->renorm;
   a.y = static_cast<__nv_bfloat16*>(d->y); a.ld_y = d->ld_y; a.topk_ids = d->topk_ids; a.topk_w = d->topk_w;
   a.experts_per_rank = d->experts_per_rank; a.n_dst = d->n_dst; a.my_rank = d->my_rank; a.region_cap = d->region_cap;
+  a.ret_rank = d->ret_rank_set ? d->ret_rank : d->my_rank;
   a.x_bases = send ? static_cast<void* const*>(d->x_bases) : nullptr; a.ld_dst = d->ld_dst;
   a.rec_bases = static_cast<void* const*>(d->rec_bases); a.cnt_bases = static_cast<int* const*>(d->cnt_bases);
   a.flag_bases = static_cast<int* const*>(d->flag_bases); a.disp_epoch = d->disp_epoch;

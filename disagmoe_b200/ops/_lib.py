@@ -61,7 +61,7 @@ class DmoeRouteDispatch(ctypes.Structure):
                [(n, _ll) for n in ("ld_resid", "add_slot_stride", "ld_add", "ld_y", "ld_dst")] + \
                [("eps", _f)] + \
                [(n, _i) for n in ("n_add", "T", "H", "E", "K", "renorm", "experts_per_rank", "n_dst", "my_rank",
-                                  "region_cap", "n_wait")]
+                                  "region_cap", "n_wait", "ret_rank", "ret_rank_set")]
 
 
 def lib_path() -> str:

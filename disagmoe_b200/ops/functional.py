@@ -291,6 +291,7 @@ def route_dispatch(resid: torch.Tensor, norm_w: torch.Tensor, eps: float, gate_w
                    topk_ids: Optional[torch.Tensor] = None, topk_w: Optional[torch.Tensor] = None,
                    logit_bias: Optional[torch.Tensor] = None, x_bases=None, rec_bases=None, cnt_bases=None,
                    flag_bases=None, ld_dst: int = 0, experts_per_rank: int = 1, n_dst: int = 0, my_rank: int = 0,
+                   ret_rank: Optional[int] = None,
                    region_cap: int = 0, disp_epoch=None, wait_flags=None, n_wait: int = 0, wait_epoch=None, ticket=None,
                    status=None) -> None:
     """One launch for the post-attention half of a layer on an attention GPU: [wait for the TP peers' o_proj flags]
@@ -306,6 +307,7 @@ def route_dispatch(resid: torch.Tensor, norm_w: torch.Tensor, eps: float, gate_w
     d.topk_ids, d.topk_w = _lib.ptr(topk_ids), _lib.ptr(topk_w)
     d.x_bases, d.rec_bases, d.cnt_bases, d.flag_bases = (_lib.ptr(t) for t in (x_bases, rec_bases, cnt_bases, flag_bases))
     d.ld_dst, d.experts_per_rank, d.n_dst, d.my_rank, d.region_cap = ld_dst, experts_per_rank, n_dst, my_rank, region_cap
+    d.ret_rank, d.ret_rank_set = (ret_rank, 1) if ret_rank is not None else (0, 0)
     d.disp_epoch, d.wait_flags, d.n_wait, d.wait_epoch = _lib.ptr(disp_epoch), _lib.ptr(wait_flags), n_wait, _lib.ptr(wait_epoch)
     d.ticket, d.status = _lib.ptr(ticket), _lib.ptr(status)
     _lib.check(_lib.lib().dmoe_route_dispatch(ctypes.byref(d), _st()), "dmoe_route_dispatch")

@@ -56,6 +56,27 @@ class DisaggShape:
     hidden: int
     num_experts: int
     tp: int = 1         # attention tensor-parallel degree: consecutive groups of `tp` attention ranks share sequences
+    # layer striping (the reference's step_attn placement, disagmoe/utils/placement.py:369-434): with stripes > 1 the
+    # n_attn = stripes attention GPUs form ONE pipeline over the layers instead of data-parallel replicas. Rank g owns
+    # a contiguous block of layers and the KV cache of those layers for every micro-batch of the job; the residual
+    # stream of a micro-batch is handed from rank g to rank g + 1 by peer stores, and the experts return the output of
+    # a stripe's last layer to the rank that owns the next layer.
+    stripes: int = 1
+    num_layers: int = 0   # needed with stripes > 1 only
+
+    def __post_init__(self):
+        if self.stripes > 1:
+            assert self.tp == 1 and self.stripes == self.n_attn and self.num_layers >= self.stripes, \
+                "layer striping: one pipeline over all attention GPUs, no TP inside a stage, at least one layer each"
+
+    def layers_per_stripe(self) -> int:
+        return (self.num_layers + self.stripes - 1) // self.stripes
+
+    def layer_owner(self, l: int) -> int:
+        """Attention rank that runs layer l (and the LM head for l == num_layers); -1 without striping."""
+        if self.stripes <= 1:
+            return -1
+        return min(l // self.layers_per_stripe(), self.stripes - 1)
 
     @property
     def experts_per_rank(self) -> int:
@@ -87,6 +108,11 @@ def build_layout(s: DisaggShape) -> ArenaLayout:
         L.add(f"disp_flag{m}", s.n_attn * 4)
         L.add(f"parts{m}", s.rows_cap * s.top_k * s.hidden * 2)
         L.add(f"comb_flag{m}", s.n_expert * 4)
+        if s.stripes > 1:
+            # pipeline hand-off: the residual rows of the micro-batch live in the arena so that the previous stage can
+            # store them here, and one flag says that they have arrived
+            L.add(f"ho_resid{m}", s.rows_cap * s.hidden * 2)
+            L.add(f"ho_flag{m}", 4)
         if s.tp > 1:
             # all-gather target: the normalised rows of the whole group, every rank pushes its shard to every member
             L.add(f"hs{m}", s.batch * s.hidden * 2)
@@ -131,8 +157,19 @@ class AttentionRank:
         self.tp = shape.tp
         self.tp_rank = attn_rank % shape.tp
         self.group0 = attn_rank // shape.tp * shape.tp      # first attention rank of this TP group
-        self.layers: List[MoEAttention] = []
+        # layer striping: this rank holds the weights and the KV cache of layers [l0, l1) only
+        self.stripes = shape.stripes
+        if self.stripes > 1:
+            per = shape.layers_per_stripe()
+            self.l0 = min(attn_rank * per, cfg.num_layers)
+            self.l1 = cfg.num_layers if attn_rank == self.stripes - 1 else min((attn_rank + 1) * per, cfg.num_layers)
+        else:
+            self.l0, self.l1 = 0, cfg.num_layers
+        self.layers: List[Optional[MoEAttention]] = []
         for l in range(cfg.num_layers):
+            if not self.l0 <= l < self.l1:
+                self.layers.append(None)
+                continue
             m = MoEAttention(cfg, l, tp_size=self.tp, tp_rank=self.tp_rank, device=dev, dtype=dt)
             m.load_weights(state_dict) if state_dict is not None else m.init_weights()
             self.layers.append(m)
@@ -143,10 +180,10 @@ class AttentionRank:
         self.lm_head_w = sd["lm_head.weight"].to(device=dev, dtype=dt).contiguous()
         S = shape
         B, R, k, H, E = S.batch, S.rows_cap, S.top_k, S.hidden, S.num_experts
-        a0 = self.layers[0]
+        a0 = self.layers[self.l0]
         self.block_size = block_size
         self.max_blocks = (cfg.max_seq_len + block_size - 1) // block_size
-        self.kv_cache = torch.zeros(cfg.num_layers, 2, num_blocks, block_size, a0.num_kv_heads, cfg.head_dim,
+        self.kv_cache = torch.zeros(self.l1 - self.l0, 2, num_blocks, block_size, a0.num_kv_heads, cfg.head_dim,
                                     dtype=dt, device=dev)
         self.block_tables = torch.zeros(S.n_mb * B, self.max_blocks, dtype=torch.int32, device=dev)
         self.rope = gemm.rope_table(cfg.max_seq_len, cfg.head_dim, cfg.rope_theta, dev)
@@ -173,6 +210,15 @@ class AttentionRank:
                 cnt_bases=arena.ptr_table(expert_ranks, layout.offset(f"recv_cnt{m}")),
                 flag_bases=arena.ptr_table(expert_ranks, layout.offset(f"disp_flag{m}")),
             )
+            if self.stripes > 1:
+                # the residual rows live in the arena: the previous stage stores them here and releases ho_flag
+                nxt = attn_rank + 1 if attn_rank + 1 < self.stripes else attn_rank
+                d.update(
+                    resid=arena.view(layout.offset(f"ho_resid{m}"), (R, H), dt),
+                    ho_flag=arena.view(layout.offset(f"ho_flag{m}"), (1,), torch.int32),
+                    ho_next_resid=arena.view(layout.offset(f"ho_resid{m}"), (R, H), dt, rank=nxt),
+                    ho_sig_ptrs=arena.ptr_table([nxt], layout.offset(f"ho_flag{m}")),
+                    ho_sig_epoch=z(1), ho_wait_epoch=z(1))
             if self.tp > 1:
                 d.update(
                     hs=arena.view(layout.offset(f"hs{m}"), (B, H), dt),
@@ -213,7 +259,7 @@ class AttentionRank:
         if bt_row is None:
             self.n_pre[m] = 0
             return 0
-        a0 = self.layers[0]
+        a0 = self.layers[self.l0]
         tiles, covered = F.build_prefill_tiles(bt_row, positions, F.prefill_tile_tokens(a0.num_heads, a0.num_kv_heads))
         self.n_pre[m] = len(tiles)
         if len(tiles):
@@ -238,11 +284,15 @@ class AttentionRank:
     def embed(self, m: int) -> None:
         d = self.mb[m]
         _, _, lo, hi = self.rows(m)
+        if self.stripes > 1 and self.a != 0:
+            return      # the first pipeline stage embeds; the others receive the residual rows by hand-off
         if hi > lo:
             F.embed(d["ids"][lo:hi], self.embed_w, out=d["resid"][:hi - lo])
 
     def layer(self, l: int, m: int) -> None:
         """Attention half of layer l for micro-batch m, ending with the peer-memory dispatch."""
+        if not self.l0 <= l < self.l1:
+            return      # another pipeline stage owns this layer
         self.layer_pre(l, m)
         self.layer_attn(l, m)
         self.layer_route_dispatch(l, m)
@@ -261,6 +311,9 @@ class AttentionRank:
         a = self.layers[l]
         wait = self._expert_parts(l)
         tp = self.tp
+        if self.stripes > 1 and l == self.l0 and self.a > 0:
+            # first layer of this stage: the previous stage's residual rows must have landed
+            F.wait_flags(d["ho_flag"], 1, d["ho_wait_epoch"], self.status)
         F.norm_gather(d["resid"][:Tm], d["parts"][:Tm] if wait else None, a.pre_ln, cfg.rms_norm_eps,
                       d["resid"][:Tm] if wait else None, d["hs_ptrs"], tp, lo, S.hidden, Tm, S.hidden,
                       wait_flags=d["comb_flag"] if wait else None, n_wait=S.n_expert if wait else 0,
@@ -277,7 +330,7 @@ class AttentionRank:
         d, S, cfg = self.mb[m], self.shape, self.cfg
         T, per, lo, hi = self.rows(m)
         a = self.layers[l]
-        kc, vc = self.kv_cache[l, 0], self.kv_cache[l, 1]
+        kc, vc = self.kv_cache[l - self.l0, 0], self.kv_cache[l - self.l0, 1]
         meta = self._meta(m)
         rope = gemm.RopeAppend(self.rope, meta.positions, meta.slots, kc, vc, a.num_heads, a.num_kv_heads, a.head_dim)
         if self.tp > 1:
@@ -329,20 +382,40 @@ class AttentionRank:
                       flag_bases=d["flag_bases"], ld_dst=S.hidden, experts_per_rank=S.experts_per_rank,
                       n_dst=S.n_expert, my_rank=self.a, region_cap=S.region_cap, disp_epoch=d["disp_epoch"],
                       logit_bias=a.route_bias, topk_ids=d["topk_ids"], topk_w=d["topk_w"])
+            if self.stripes > 1:
+                # the experts return this layer's output to the stage that owns the next layer (the LM head counts
+                # as layer num_layers and belongs to the last stage)
+                kw["ret_rank"] = S.layer_owner(l + 1)
         F.route_dispatch(d["resid"], a.post_ln, cfg.rms_norm_eps, None if a.is_dense else a.gate_w, S.top_k,
                          cfg.norm_topk_prob, Tm, y=d["y"], ticket=d["ticket"], status=self.status, **kw)
-        if Tm == 0:
-            return
-        if a.is_dense:
-            a.dense_ffn(d["resid"][:Tm], h=d["y"][:Tm])
-            return
-        # shared experts stay on the attention GPU and run while the expert GPUs work on the rows just sent
-        a.shared_experts(d["y"][:Tm], d["resid"][:Tm])
+        if Tm > 0:
+            if a.is_dense:
+                a.dense_ffn(d["resid"][:Tm], h=d["y"][:Tm])
+            else:
+                # shared experts stay on the attention GPU and run while the expert GPUs work on the rows just sent
+                a.shared_experts(d["y"][:Tm], d["resid"][:Tm])
+        if self.stripes > 1 and l == self.l1 - 1 and self.a + 1 < self.stripes:
+            self._hand_off(m)
+
+    def _hand_off(self, m: int) -> None:
+        """Last layer of this pipeline stage: the residual rows of micro-batch m go to the next stage's residual
+        buffer (peer stores) and its hand-off flag is released; the experts send this layer's output there too. One
+        launch of the norm + push kernel: the row copy is its residual output, the normalised rows land in a scratch
+        buffer nobody reads. Replaces the residual-stream send / recv between pipeline stages of the host-scheduled
+        path (the reference's layer striping: disagmoe/utils/placement.py:369-434)."""
+        d, S = self.mb[m], self.shape
+        T, per, lo, hi = self.rows(m)
+        Tm = hi - lo
+        F.norm_gather(d["resid"][:Tm], None, self.norm_w, self.cfg.rms_norm_eps, d["ho_next_resid"][:Tm], d["hfin_ptrs"], 1, 0,
+                      S.hidden, Tm, S.hidden, signal_ptrs=d["ho_sig_ptrs"], n_signal=1, signal_slot=0,
+                      signal_epoch=d["ho_sig_epoch"], ticket=d["ticket"], status=self.status)
 
     def head(self, m: int) -> None:
         """[wait for the last layer's combine] final norm, LM head and greedy sampling on this rank's rows; a TP group
         then exchanges the sampled ids so that every member holds all of them."""
         d, S, cfg = self.mb[m], self.shape, self.cfg
+        if self.stripes > 1 and self.a != self.stripes - 1:
+            return      # the last pipeline stage owns the LM head
         T, per, lo, hi = self.rows(m)
         Tm = hi - lo
         wait = self._expert_parts(cfg.num_layers)
@@ -409,7 +482,9 @@ class ExpertRank:
                 recs=arena.view(layout.offset(f"recv_recs{m}"), (rows, 4), torch.int32),
                 cnt=arena.view(layout.offset(f"recv_cnt{m}"), (epr,), torch.int32),
                 flag=arena.view(layout.offset(f"disp_flag{m}"), (S.n_attn,), torch.int32),
-                wait_epoch=z(1), signal_epoch=z(1),
+                # one epoch counter per attention rank: with layer striping a layer's rows come from (and go back to) one
+                # pipeline stage only, and every stage counts its own hand-shakes; without it slot 0 counts for all
+                wait_epoch=z(S.n_attn), signal_epoch=z(S.n_attn),
                 parts_bases=arena.ptr_table(attn_ranks, layout.offset(f"parts{m}")),
                 signal_ptrs=arena.ptr_table(attn_ranks, layout.offset(f"comb_flag{m}")),
             ))
@@ -427,14 +502,22 @@ class ExpertRank:
         e = self.layers[l]
         if e is None:
             return
-        gate = gemm.GemmComm(seg_cnt=d["cnt"], seg_cap=S.region_cap, group_regions=True, wait_flags=d["flag"],
-                             n_wait=S.n_attn, wait_epoch=d["wait_epoch"], done_ticket=self.ticket)
+        if S.stripes > 1:
+            # layer striping: only the stage that owns layer l dispatches it, only the owner of layer l + 1 is told
+            src, dst = S.layer_owner(l), S.layer_owner(l + 1)
+            flags, n_wait, wait_epoch = d["flag"][src:src + 1], 1, d["wait_epoch"][src:src + 1]
+            sig_ptrs, n_sig, sig_epoch = d["signal_ptrs"][dst:dst + 1], 1, d["signal_epoch"][dst:dst + 1]
+        else:
+            flags, n_wait, wait_epoch = d["flag"], S.n_attn, d["wait_epoch"][:1]
+            sig_ptrs, n_sig, sig_epoch = d["signal_ptrs"], S.n_attn, d["signal_epoch"][:1]
+        gate = gemm.GemmComm(seg_cnt=d["cnt"], seg_cap=S.region_cap, group_regions=True, wait_flags=flags,
+                             n_wait=n_wait, wait_epoch=wait_epoch, done_ticket=self.ticket)
         _lib.TAG = "expert_gemm1"
         gemm.grouped_swiglu(d["rows"], e.w13_weight, None, out=self.act, bn=self.bn, comm=gate, w_blocked=e.w_blocked)
         _lib.TAG = "expert_gemm2"
         # the last CTA clears the row cursors before it signals: the senders reserve again only after that signal
-        sig = gemm.GemmComm(seg_cnt=d["cnt"], seg_cap=S.region_cap, group_regions=True, signal_ptrs=d["signal_ptrs"],
-                            n_signal=S.n_attn, signal_slot=self.x, signal_epoch=d["signal_epoch"],
+        sig = gemm.GemmComm(seg_cnt=d["cnt"], seg_cap=S.region_cap, group_regions=True, signal_ptrs=sig_ptrs,
+                            n_signal=n_sig, signal_slot=self.x, signal_epoch=sig_epoch,
                             done_ticket=self.ticket, clear=d["cnt"])
         gemm.grouped_combine(self.act, e.w2_weight, None, d["recs"], d["parts_bases"], S.hidden, bn=self.bn2, comm=sig,
                              streamk=self.sk2, w_blocked=e.w_blocked)

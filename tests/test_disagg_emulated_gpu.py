@@ -226,3 +226,67 @@ def test_emulated_mixed_prompt_and_decode_rows():
     want = {"prompt": lg_p[11], **{r: lg_d[i] for i, r in enumerate(rs)}}
     for k in got:
         assert_close(got[k], want[k], str(k))
+
+
+@pytest.mark.parametrize("A,X,n_layers,variant", [(2, 2, 4, "mixtral"), (3, 1, 5, "mixtral"), (2, 3, 4, "shared_dense")])
+def test_emulated_layer_striping_pipeline(A, X, n_layers, variant):
+    """Layer striping on the fused path: the A attention ranks form one pipeline over the layers (rank g holds the
+    weights and the KV cache of its block of layers only); the residual rows of a micro-batch are handed from stage to
+    stage by peer stores, the experts return a stage's last layer to the next stage, the last stage runs the LM head.
+    Two iterations (every stage's epochs carry over), two micro-batches, against the colocated executor."""
+    cfg, sd, skew = _model(variant, n_layers)
+    n_mb, B = 2, 4
+    shape = DisaggShape(A, X, n_mb, B, cfg.top_k, cfg.hidden_size, cfg.num_experts, stripes=A, num_layers=n_layers)
+    layout = build_layout(shape)
+    arenas = PeerArena.emulated(A + X, layout.size)
+    attn = [AttentionRank(cfg, shape, arenas[a], layout, a, num_blocks=64, state_dict=sd) for a in range(A)]
+    exps = [ExpertRank(cfg, shape, arenas[A + x], layout, x, state_dict=sd) for x in range(X)]
+    ref = FusedModelExecutor(cfg, CacheConfig(block_size=16), device="cuda", max_batch_size=B, max_prefill_tokens=B,
+                             state_dict=sd, num_blocks=64, enable_cuda_graph=False)
+    for layer in [x for a in attn for x in a.layers if x is not None] + list(ref.attn.values()):
+        layer.set_route_skew(skew)
+    assert [a.l1 - a.l0 for a in attn] == [len([l for l in range(n_layers) if shape.layer_owner(l) == g]) for g in range(A)]
+    assert all(a.kv_cache.shape[0] == a.l1 - a.l0 for a in attn) and shape.layer_owner(n_layers) == A - 1
+    g = torch.Generator().manual_seed(5)
+    kv = torch.randn(ref.kv_cache.shape, generator=g).to(torch.bfloat16).cuda() * 0.5     # [L, 2, nb, bs, kvh, hd]
+    for a in attn:
+        a.kv_cache.copy_(kv[a.l0:a.l1])
+    ref_kv = kv.clone()
+    perm = torch.randperm(60, generator=g)
+    for step in range(2):
+        inputs = []
+        for m in range(n_mb):
+            ids = torch.randint(0, cfg.vocab_size, (B,), generator=g).int()
+            ctx = torch.randint(3, 40, (B,), generator=g).int() + step
+            bt = perm[m * B * 4:(m + 1) * B * 4].view(B, 4).int()
+            slots = torch.tensor([int(bt[i, int(ctx[i]) // 16]) * 16 + int(ctx[i]) % 16 for i in range(B)])
+            inputs.append((ids, ctx, slots, bt))
+            for a in attn:      # every stage needs the positions and the block tables, the first one the ids
+                a.block_tables[m * B:(m + 1) * B, :4] = bt.cuda()
+                d = a.mb[m]
+                d["ids"].copy_(ids); d["positions"].copy_(ctx); d["ctx_len"].copy_(ctx + 1)
+                d["bt_row"].copy_(torch.arange(B, dtype=torch.int32) + m * B); d["slots"].copy_(slots)
+        for a in attn:
+            for m in range(n_mb):
+                a.embed(m)
+        # one stream, several ranks: a layer runs on its owner, then on the expert ranks, before anything waits for it
+        for l in range(n_layers):
+            for m in range(n_mb):
+                attn[shape.layer_owner(l)].layer(l, m)
+                for e in exps:
+                    e.layer(l, m)
+        for a in attn:
+            for m in range(n_mb):
+                a.head(m)
+        torch.cuda.synchronize()
+        assert gemm.check_status() == 0
+        for m, (ids, ctx, slots, bt) in enumerate(inputs):
+            ref.kv_cache.copy_(ref_kv)
+            ref.block_tables[:B, :4] = bt.cuda()
+            _, lg = ref.decode(ids, ctx, slots, ctx + 1, torch.arange(B, dtype=torch.int32), want_logits=True)
+            # the step appended one K / V row per sequence: carry it into the next step's reference cache
+            assert_close(attn[-1].mb[m]["logits"], lg, f"step {step} mb {m}")
+            ref_kv.copy_(ref.kv_cache)
+        # the stages' caches hold the rows the reference appended, layer block by layer block
+        for a in attn:
+            assert_close(a.kv_cache, ref_kv[a.l0:a.l1], f"KV cache of stage {a.a} after step {step}")
