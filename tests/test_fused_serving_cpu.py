@@ -355,3 +355,20 @@ def test_native_scheduler_builds_the_same_plans_as_the_python_statement():
         for i in b.finished:
             assert list(a.finished[i].outputs) == b.finished[i].outputs and a.finished[i].length == b.finished[i].length
         assert bms[0].num_free_blocks() == bms[1].num_free_blocks() == 96
+
+
+def test_layer_striping_shape_assigns_contiguous_layer_blocks():
+    """DisaggShape(stripes=A): contiguous blocks of ceil(L / A) layers per pipeline stage, the LM head (layer L) on the
+    last stage, and an arena layout that adds one residual hand-off buffer and flag per micro-batch."""
+    import pytest
+    from disagmoe_b200.parallel.disagg import DisaggShape, build_layout
+    s = DisaggShape(3, 2, 2, 8, 2, 256, 8, stripes=3, num_layers=8)
+    assert [s.layer_owner(l) for l in range(9)] == [0, 0, 0, 1, 1, 1, 2, 2, 2]
+    assert DisaggShape(2, 2, 2, 8, 2, 256, 8).layer_owner(3) == -1
+    lay, plain = build_layout(s), build_layout(DisaggShape(3, 2, 2, 8, 2, 256, 8))
+    assert {"ho_resid0", "ho_flag0", "ho_resid1", "ho_flag1"} <= set(lay.entries) and "ho_resid0" not in plain.entries
+    assert lay.entries["ho_resid0"][1] == 8 * 256 * 2
+    with pytest.raises(AssertionError):
+        DisaggShape(4, 2, 2, 8, 2, 256, 8, tp=2, stripes=4, num_layers=8)      # no TP inside a stage
+    with pytest.raises(AssertionError):
+        DisaggShape(4, 2, 2, 8, 2, 256, 8, stripes=2, num_layers=8)            # one pipeline over all attention GPUs
