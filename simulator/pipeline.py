@@ -14,12 +14,16 @@ Flags cost ``hop_us`` each way. The model answers sizing questions (how many att
 micro-batches) before a run is spent on them; its inputs are the stand-alone side times that
 ``benchmark/profile_disagg_sides.py`` measures.
 
-Calibration against the measured Mixtral runs (256 sequences per micro-batch): with the stand-alone side times
-(attention 279 us; experts 250 us per launch at 2 experts per GPU, 309 us at 4) and an 8 us hop the model gives 18.4 ms
-at 4 + 4 GPUs and 20.3 ms at 2 + 2, where 22.1 ms and 26.8 ms were measured. Raising the hop to 50 us only reaches
-20.9 / 22.7 ms, so flag latency alone does not explain the gap: the coupled sides run slower than they do alone
-(dispatch and combine traffic landing while the GEMMs stream weights, the gate waiting for the slowest sender). The
-model is therefore a lower bound on the step time and a tool for relative comparisons between layouts.
+Calibration against the measured Mixtral runs (256 sequences per micro-batch). First build: stand-alone side times
+attention 279 us, experts 250 us per launch at 2 experts per GPU, 309 us at 4, 8 us hop: the model gives 18.4 ms at
+4 + 4 GPUs and 20.3 ms at 2 + 2, where 22.1 ms and 26.8 ms were measured. Current build: attention 248 us
+(data-parallel; 260 us for a TP4 rank), experts 239 us at 2 per GPU (120 us per expert), 281 us at 4 (70 us per expert):
+the model gives 16.8 ms and 18.4 ms, measured 19.9 ms (4 + 4, data-parallel attention; 20.9 ms with TP4) and 23.1 ms
+(2 + 2). Raising the hop to 50 us moves the model by ~2.5 ms at most, so flag latency alone does not explain the gap:
+the coupled sides run slower than they do alone (remote atomics and stores over NVLink inside the sender kernels,
+dispatch and combine traffic landing while the GEMMs stream weights, the gate waiting for the slowest sender), and
+every step pays a pipeline fill and drain. The model is therefore a lower bound on the step time and a tool for
+relative comparisons between layouts.
 """
 from __future__ import annotations
 
