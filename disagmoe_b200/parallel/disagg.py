@@ -146,7 +146,13 @@ class AttentionRank:
     per) of the group's micro-batch (per = ceil(T / tp)), runs both norms, the router, the dispatch, shared experts /
     dense FFN and the LM head on those rows only, and receives the experts' combine output for those rows only.
     Replaces, for TP groups, the reference's broadcast of inputs (disagmoe/frontend/engine.py:494-535) and its
-    all-reduce after o_proj (disagmoe/models/linear.py:1064-1089, csrc/muhelper/comm.cpp:399-416)."""
+    all-reduce after o_proj (disagmoe/models/linear.py:1064-1089, csrc/muhelper/comm.cpp:399-416).
+
+    With layer striping (``shape.stripes`` = number of attention ranks) the ranks are the stages of one pipeline over
+    the layers: a rank loads the weights and keeps the KV cache of its block of layers only, ``layer`` is a no-op for
+    the other layers, the first stage embeds and the last one runs the LM head. After its last layer a stage stores the
+    residual rows of the micro-batch into the next stage's residual buffer and releases its hand-off flag; the dispatch
+    records of that layer name the next stage as the owner the experts return to."""
 
     def __init__(self, cfg: ModelConfig, shape: DisaggShape, arena: PeerArena, layout: ArenaLayout, attn_rank: int,
                  num_blocks: int, block_size: int = 16, state_dict: Optional[W.StateDict] = None, device=None):
