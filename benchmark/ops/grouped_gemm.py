@@ -47,7 +47,7 @@ def main(argv=None):
     ap.add_argument("--ragged", type=float, default=0.0, help="relative jitter of the group sizes around the mean")
     ap.add_argument("--only", default="", help="run one variant only (for profilers): g1s / g1w / g1w256 / g1p128 / g1p256 "
                     "(GEMM-1: stream-K, whole tiles, whole 256-token tiles, CTA pairs) or g2s128 / g2s256 / g2w128 / g2w256 "
-                    "/ g2p128 / g2p256 (GEMM-2)")
+                    "/ g2p128 / g2p256 (GEMM-2); g1b / g2b: whole tiles over tile-blocked weights")
     a = ap.parse_args(argv)
     dev = "cuda"
     G = a.experts
@@ -64,10 +64,13 @@ def main(argv=None):
         if a.only:
             v = a.only
             bn = int(v[3:]) if len(v) > 3 else 0
+            blocked = v[2] == "b"       # g1b / g2b: whole tiles over tile-blocked weight stacks
             if v.startswith("g1"):
-                fn = lambda: gemm.grouped_swiglu(x, w13, offs, bn=bn, streamk=v[2] == "s", pair=v[2] == "p")
+                wa = gemm.block_weight(w13) if blocked else w13
+                fn = lambda: gemm.grouped_swiglu(x, wa, offs, bn=bn, streamk=v[2] == "s", pair=v[2] == "p", w_blocked=blocked)
             else:
-                fn = lambda: gemm.grouped_linear(act, w2, offs, bn=bn, streamk=v[2] == "s", pair=v[2] == "p")
+                wa = gemm.block_weight(w2) if blocked else w2
+                fn = lambda: gemm.grouped_linear(act, wa, offs, bn=bn, streamk=v[2] == "s", pair=v[2] == "p", w_blocked=blocked)
             print(f"{G} experts x ~{t} tokens, {v}: {timed(fn, flush, a.iters):.1f} us", flush=True)
             continue
         res = {}
