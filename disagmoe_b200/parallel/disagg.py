@@ -536,33 +536,35 @@ class ExpertRank:
 
 
 def selfcheck_against_colocated(world: int, rank: int, local_rank: int, n_attn: int, tp: int, n_mb: int = 2,
-                                batch: int = 8) -> Dict[str, float]:
+                                batch: int = 8, stripes: int = 1) -> Dict[str, float]:
     """Correctness line of a multi-GPU job: a tiny model (2 layers, hidden 256, 8 experts) runs one decode iteration
     through the fused pipeline on the job's real GPUs with the job's layout (attention groups, TP degree, expert
     GPUs), and every attention rank compares the logits of the rows it owns with the single-GPU colocated executor
     fed the same weights, KV history and inputs. Collective over the world; returns the worst relative error
-    (max |diff| / max |ref|) and the worst fraction of rows whose arg-max agrees, over all ranks."""
+    (max |diff| / max |ref|) and the worst fraction of rows whose arg-max agrees, over all ranks. With ``stripes`` =
+    n_attn the attention GPUs run as one pipeline over 2 x stripes layers and the last stage holds the logits."""
     import torch.distributed as dist
     from ..config import CacheConfig, tiny_config
     from ..executor.fused import FusedModelExecutor
     A, X = n_attn, world - n_attn
-    cfg = tiny_config.clone(dtype=torch.bfloat16, num_layers=2)
+    cfg = tiny_config.clone(dtype=torch.bfloat16, num_layers=2 if stripes <= 1 else 2 * stripes)
     dev = torch.device("cuda", local_rank)
     sd = {k: v.to(torch.bfloat16) for k, v in W.init_state_dict(cfg, dtype=torch.float32).items()}
     B = batch * tp
-    shape = DisaggShape(A, X, n_mb, B, cfg.top_k, cfg.hidden_size, cfg.num_experts, tp)
+    shape = DisaggShape(A, X, n_mb, B, cfg.top_k, cfg.hidden_size, cfg.num_experts, tp, stripes=stripes,
+                        num_layers=cfg.num_layers)
     layout = build_layout(shape)
     arena = PeerArena.create(layout.size, device=dev)
     nb, bs = 4 * n_mb * B + 1, 16
     err, agree, err_close, rows_close, rows_total = 0.0, 1.0, 0.0, 0, 0
     if rank < A:
-        grp = rank // tp
+        grp = rank // tp if stripes <= 1 else 0      # the stages of a pipeline serve the same requests
         g = torch.Generator().manual_seed(99 + grp)
         r = AttentionRank(cfg, shape, arena, layout, rank, nb, state_dict=sd, device=dev)
         kvh = cfg.num_kv_heads // tp if cfg.num_kv_heads >= tp else 1
         kv = torch.randn(cfg.num_layers, 2, nb, bs, cfg.num_kv_heads, cfg.head_dim, generator=g).to(torch.bfloat16) * 0.5
         k0 = (rank % tp) * kvh if cfg.num_kv_heads >= tp else (rank % tp) // (tp // cfg.num_kv_heads)
-        r.kv_cache.copy_(kv[..., k0:k0 + kvh, :])
+        r.kv_cache.copy_(kv[r.l0:r.l1, ..., k0:k0 + kvh, :])
         inputs = []
         for m in range(n_mb):
             ids = torch.randint(0, cfg.vocab_size, (B,), generator=g).int()
@@ -588,6 +590,8 @@ def selfcheck_against_colocated(world: int, rank: int, local_rank: int, n_attn: 
                                  state_dict=sd, num_blocks=nb, enable_cuda_graph=False)
         per = shard_rows(B, tp)
         lo, hi = min(B, (rank % tp) * per), min(B, (rank % tp + 1) * per)
+        if stripes > 1 and rank != A - 1:
+            inputs = []                             # only the last stage of a pipeline holds logits
         for m, (ids, ctx, slots, bt) in enumerate(inputs):
             ref.kv_cache.copy_(kv)
             ref.block_tables[:B, :4] = bt.to(dev)

@@ -133,3 +133,14 @@ def test_four_gpu_tp_fused_serving_matches_colocated():
     assert info["kernel_status"] == 0 and info["requests_finished"] == 24
     assert check["check_first_tokens_agree"] >= 0.9, check
     assert check["check_tokens_agree"] >= 0.7, check
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 4, reason="needs 4 GPUs")
+def test_four_gpu_layer_striping_pipeline_matches_colocated():
+    """Layer striping on real GPUs: 2 attention GPUs as the stages of one pipeline over 4 layers + 2 expert GPUs; the
+    residual rows cross NVLink between the stages, the experts return to the stage that owns the next layer, the last
+    stage's logits are compared with the colocated executor."""
+    lines = _torchrun(4, "tests/workers/striping_worker.py", "2", port=29672, timeout=300)
+    res = lines[-1]
+    assert res["kernel_status"] == 0 and res["rows"] == 16, res
+    assert res["rows_within_2pct"] >= 0.9 * res["rows"] and res["max_rel_err_of_those_rows"] < 0.02, res
