@@ -613,7 +613,7 @@ def selfcheck_against_colocated(world: int, rank: int, local_rank: int, n_attn: 
     dist.all_reduce(n)
     return {"max_rel_err": round(float(t[0]), 5), "argmax_agree_min": round(-float(t[1]), 4), "kernel_status": int(t[2]),
             "rows_within_2pct": int(n[0]), "rows": int(n[1]), "max_rel_err_of_those_rows": round(float(t[3]), 5),
-            "model": "tiny 2-layer MoE, same GPU layout, vs the colocated executor; a row outside 2 % is a router near-tie "
+            "model": f"tiny {cfg.num_layers}-layer MoE, same GPU layout, vs the colocated executor; a row outside 2 % is a router near-tie "
                      "that flips under the TP group's bf16 summation order (benchmark/emulated_selfcheck.py runs the same "
                      "layout sequentially on one GPU for comparison)"}
 
