@@ -372,3 +372,21 @@ def test_layer_striping_shape_assigns_contiguous_layer_blocks():
         DisaggShape(4, 2, 2, 8, 2, 256, 8, tp=2, stripes=4, num_layers=8)      # no TP inside a stage
     with pytest.raises(AssertionError):
         DisaggShape(4, 2, 2, 8, 2, 256, 8, stripes=2, num_layers=8)            # one pipeline over all attention GPUs
+
+
+def test_prefill_tile_builder_finds_prompt_runs_and_leaves_the_rest():
+    """build_prefill_tiles (host side of the tiled causal attention): runs of consecutive positions of one sequence
+    with at least min_len rows become tiles of at most tile_tokens rows; decode rows and short runs stay uncovered."""
+    import torch
+    from disagmoe_b200.ops.functional import build_prefill_tiles
+    #        decode rows   | prompt of seq 7: positions 10..29        | short run of seq 9 | prompt chunk of seq 3
+    rows = [0, 1, 2] + [7] * 20 + [9] * 3 + [3] * 9
+    pos = [55, 12, 80] + list(range(10, 30)) + [0, 1, 2] + list(range(100, 109))
+    tiles, covered = build_prefill_tiles(rows, pos, tile_tokens=16, min_len=8)
+    assert tiles.dtype == torch.int32 and tiles.tolist() == [[3, 16, 7, 10], [19, 4, 7, 26], [26, 9, 3, 100]]
+    assert covered.tolist() == [False] * 3 + [True] * 20 + [False] * 3 + [True] * 9
+    # a break in the positions splits a run even inside one sequence; nothing to do for an empty batch
+    tiles2, cov2 = build_prefill_tiles([4] * 16, list(range(8)) + list(range(20, 28)), tile_tokens=16)
+    assert tiles2.tolist() == [[0, 8, 4, 0], [8, 8, 4, 20]] and bool(cov2.all())
+    t0, c0 = build_prefill_tiles([], [], 16)
+    assert t0.shape == (0, 4) and c0.numel() == 0
